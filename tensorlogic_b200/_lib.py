@@ -1,0 +1,114 @@
+"""ctypes view of libtlcuda.so (the C ABI declared in include/tlcuda.h).
+
+The library is built in-tree by ``tensorlogic_b200.build``.  There is no
+fallback: if the shared object is missing, or no CUDA device is present, the
+calls fail loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtlcuda.so")
+
+OK = 0
+ERR_SHAPE_MISMATCH, ERR_INVALID_OPERATION, ERR_DEVICE, ERR_CUDA = -1, -2, -3, -4
+ERR_ALLOCATION, ERR_LOAD, ERR_BUFFER_EXHAUSTED, ERR_INDEX = -5, -6, -7, -8
+ERR_INVALID_DIMENSION, ERR_TIMEOUT, ERR_COMM = -9, -10, -11
+
+TYPE_F32, TYPE_F16, TYPE_Q4_0, TYPE_Q8_0 = 0, 1, 2, 8
+SPLIT_NONE, SPLIT_ROWS, SPLIT_COLS = 0, 1, 2
+
+_ERROR_NAMES = {
+    -1: "ShapeMismatch", -2: "InvalidOperation", -3: "DeviceConversionError", -4: "CudaError",
+    -5: "AllocationError", -6: "LoadError", -7: "BufferExhausted", -8: "IndexOutOfBounds",
+    -9: "InvalidDimension", -10: "Timeout", -11: "CommError",
+}
+
+
+class TensorError(RuntimeError):
+    """Mirror of TensorLogic's TensorError (src/error.rs:9-49): ``kind`` names the variant."""
+
+    def __init__(self, code: int, message: str):
+        self.code = code
+        self.kind = _ERROR_NAMES.get(code, f"Error{code}")
+        super().__init__(f"{self.kind}: {message}")
+
+
+class PoolStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("total_pooled", "size_classes", "total_memory", "reuse_count",
+                                          "allocation_count", "eviction_count", "live_bytes")]
+
+
+vp, i32, i64, u32, u64, sz, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_uint64, C.c_size_t, C.c_float
+P = C.POINTER
+
+# name -> (restype, argtypes).  Every function declared in include/tlcuda.h.
+PROTOTYPES = {
+    "tlc_last_error": (C.c_char_p, []),
+    "tlc_version": (C.c_char_p, []),
+    "tlc_init": (i32, [i32, P(vp)]),
+    "tlc_destroy": (i32, [vp]),
+    "tlc_device_name": (i32, [vp, C.c_char_p, sz]),
+    "tlc_mem_info": (i32, [vp, P(sz), P(sz)]),
+    "tlc_sm_count": (i32, [vp, P(i32)]),
+    "tlc_synchronize": (i32, [vp]),
+    "tlc_stream": (vp, [vp]),
+    "tlc_launch_count": (u64, [vp]),
+    "tlc_alloc": (i32, [vp, sz, P(vp)]),
+    "tlc_free": (i32, [vp]),
+    "tlc_buf_ptr": (vp, [vp]),
+    "tlc_buf_size": (sz, [vp]),
+    "tlc_pool_stats_get": (i32, [vp, P(PoolStats)]),
+    "tlc_pool_trim": (i32, [vp, sz]),
+    "tlc_upload": (i32, [vp, vp, vp, sz]),
+    "tlc_download": (i32, [vp, vp, vp, sz]),
+    "tlc_host_alloc": (i32, [sz, P(vp)]),
+    "tlc_host_free": (i32, [vp]),
+    "tlc_qtensor_create": (i32, [vp, i32, i64, i64, vp, sz, i32, i32, i32, P(vp)]),
+    "tlc_qtensor_create_synthetic": (i32, [vp, i32, i64, i64, u64, u64, i32, i32, i32, P(vp)]),
+    "tlc_synth_blocks_host": (i32, [i32, u64, u64, i64, i64, vp]),
+    "tlc_qtensor_destroy": (i32, [vp]),
+    "tlc_qtensor_info": (i32, [vp, P(i32), P(i64), P(i64), P(sz), P(vp)]),
+    "tlc_dequant": (i32, [vp, vp, vp]),
+    "tlc_linear": (i32, [vp, vp, vp, i32, i64, vp, vp]),
+    "tlc_linear_host": (i32, [vp, vp, vp, i32, i64, vp, vp]),
+    "tlc_rms_norm": (i32, [vp, vp, vp, vp, i32, i32, f32]),
+    "tlc_rope": (i32, [vp, vp, vp, i32, i32, i32, i32, u32, vp]),
+    "tlc_sigmoid": (i32, [vp, vp, vp, sz]),
+    "tlc_mul": (i32, [vp, vp, vp, vp, sz]),
+    "tlc_add": (i32, [vp, vp, vp, vp, sz]),
+    "tlc_swiglu": (i32, [vp, vp, vp, vp, sz]),
+    "tlc_softmax": (i32, [vp, vp, vp, i32, i32]),
+    "tlc_embedding": (i32, [vp, vp, i32, i32, P(i32), i32, vp]),
+    "tlc_norm_linear_multi": (i32, [vp, i32, P(vp), P(vp), P(i32), vp, i32, vp, f32, i32, u32, vp]),
+    "tlc_swiglu_gate_up": (i32, [vp, vp, vp, vp, i32, vp, f32, vp]),
+    "tlc_linear_residual": (i32, [vp, vp, vp, i32, vp, vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """dlopen libtlcuda.so and attach prototypes.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m tensorlogic_b200.build` "
+            "(needs nvcc); there is no fallback implementation")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        msg = load().tlc_last_error()
+        raise TensorError(rc, msg.decode("utf-8", "replace") if msg else "")

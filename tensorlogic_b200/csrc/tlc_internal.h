@@ -1,0 +1,130 @@
+// Internal declarations shared by the translation units of libtlcuda.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "tlcuda.h"
+
+// Device-side status word polled by tlc_synchronize: kernels with bounded
+// waits store a non-zero code here instead of spinning forever.
+struct tlc_dev_status {
+    int code;   // 0 = fine
+    int where;  // kernel-specific location id of the wait that gave up
+};
+
+struct tlc_pool {
+    // idle buffers by class size
+    std::map<size_t, std::vector<void *>> idle;
+    size_t max_per_class = 10;  // BufferPool::new, buffer_pool.rs:106
+    tlc_pool_stats stats{};
+};
+
+struct tlc_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaDeviceProp prop{};
+    int sm_count = 0;
+    tlc_pool pool;
+    uint64_t launches = 0;
+    tlc_dev_status *dev_status = nullptr;   // device memory
+    tlc_dev_status *host_status = nullptr;  // pinned mirror
+    // Reusable scratch for kernels that need global workspace (grows on demand).
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+};
+
+struct tlc_buf {
+    tlc_ctx *ctx;
+    void *ptr;
+    size_t class_bytes;
+    size_t requested;
+};
+
+struct tlc_qtensor {
+    tlc_ctx *ctx;
+    int32_t type;        // TLC_TYPE_*
+    int64_t n_rows;      // local rows (N of this rank)
+    int64_t n_cols;      // local cols (K of this rank)
+    int64_t full_rows;   // unsharded shape
+    int64_t full_cols;
+    size_t row_bytes;    // bytes of one local row (no padding)
+    size_t row_pitch;    // distance between rows in HBM: row_bytes rounded up to 16
+    size_t bytes;        // n_rows * row_pitch
+    void *data;          // device
+    int32_t tp_rank, tp_size, split;
+};
+
+// ---- error plumbing -------------------------------------------------------
+int32_t tlc_fail(int32_t code, const char *fmt, ...);
+void tlc_clear_error();
+
+#define TLC_CUDA(expr)                                                                     \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess)                                                             \
+            return tlc_fail(TLC_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                  \
+                            cudaGetErrorString(_e), __FILE__, __LINE__);                   \
+    } while (0)
+
+#define TLC_CHECK_LAUNCH(ctx)                                                              \
+    do {                                                                                   \
+        (ctx)->launches++;                                                                 \
+        cudaError_t _e = cudaGetLastError();                                               \
+        if (_e != cudaSuccess)                                                             \
+            return tlc_fail(TLC_ERR_CUDA, "kernel launch failed: %s (%s:%d)",              \
+                            cudaGetErrorString(_e), __FILE__, __LINE__);                   \
+    } while (0)
+
+#define TLC_REQUIRE(cond, code, ...)                                                       \
+    do {                                                                                   \
+        if (!(cond)) return tlc_fail((code), __VA_ARGS__);                                 \
+    } while (0)
+
+static inline size_t tlc_block_bytes(int32_t type) {
+    return type == TLC_TYPE_Q4_0 ? 18 : type == TLC_TYPE_Q8_0 ? 34 : 0;
+}
+
+// Makes the context's device current; every entry point calls it first.
+int32_t tlc_enter(tlc_ctx *ctx);
+// Ensures ctx->scratch holds at least `bytes`.
+int32_t tlc_scratch_reserve(tlc_ctx *ctx, size_t bytes);
+
+// ---- launchers implemented in the kernel translation units ----------------
+
+// One weight of a fused multi-GEMV launch.
+struct tlc_gemv_out {
+    const tlc_qtensor *w;
+    void *y;             // f16 [m, N]
+    int32_t rope_heads;  // >0: apply rope over [m, heads, N/heads]
+};
+
+enum tlc_gemv_epilogue {
+    TLC_EPI_STORE = 0,     // y = f16(acc) [+ bias]
+    TLC_EPI_RESIDUAL = 1,  // y = f16(acc) + residual
+    TLC_EPI_SWIGLU = 2,    // outs[0]=gate, outs[1]=up -> act = silu(g)*u into outs[0].y
+};
+
+struct tlc_gemv_args {
+    int32_t n_out = 0;
+    tlc_gemv_out outs[3]{};
+    const void *x = nullptr;  // f16 [m, K]
+    int32_t m = 0;
+    const void *norm_w = nullptr;  // f16 [K] or null
+    float eps = 0.f;
+    int32_t epilogue = TLC_EPI_STORE;
+    const void *bias = nullptr;      // f16 [N] (STORE, single output)
+    const void *residual = nullptr;  // f16 [m, N] (RESIDUAL)
+    int32_t pos_offset = 0;
+    uint32_t rope_base = 10000;
+    const int32_t *positions = nullptr;  // device int32 [m] or null
+};
+
+int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a);

@@ -1,0 +1,309 @@
+// Quantized weights kept in HBM in their native GGUF block layout, the
+// device-side dequantizer, and the counter-based synthetic weight generator.
+//
+// Replaces the load-time CPU dequantization of the TensorLogic loaders
+// (src/model/formats/gguf.rs:22-112, :377-450; mmap_gguf.rs:383-439).
+#include <cstring>
+
+#include "tlc_internal.h"
+#include "tlc_synth.cuh"
+
+// ---------------------------------------------------------------------------
+// Dequantization: one thread per block of 32.  Bit-exact with
+// GGUFLoader::dequantize_q4_0 (gguf.rs:68-112): value = f16_rne((nib-8)*f32(d));
+// low nibbles -> elements 0..15, high nibbles -> 16..31.  And with
+// dequantize_q8_0 (gguf.rs:22-53): f16_rne(float(q)*float(d)).
+// ---------------------------------------------------------------------------
+__global__ void dequant_q4_0_kernel(const uint8_t *__restrict__ data, size_t row_pitch,
+                                    int blocks_per_row, int64_t n_rows, __half *__restrict__ out) {
+    int64_t gb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t total = n_rows * blocks_per_row;
+    if (gb >= total) return;
+    int64_t row = gb / blocks_per_row;
+    int bc = (int)(gb % blocks_per_row);
+    const uint8_t *blk = data + row * row_pitch + (size_t)bc * 18;
+    uint16_t dbits = (uint16_t)(blk[0] | (blk[1] << 8));
+    float d = __half2float(__ushort_as_half(dbits));
+    __half *o = out + (row * blocks_per_row + bc) * 32;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        uint8_t b = blk[2 + j];
+        o[j] = __float2half_rn(__fmul_rn((float)((int)(b & 0x0F) - 8), d));
+        o[j + 16] = __float2half_rn(__fmul_rn((float)((int)(b >> 4) - 8), d));
+    }
+}
+
+__global__ void dequant_q8_0_kernel(const uint8_t *__restrict__ data, size_t row_pitch,
+                                    int blocks_per_row, int64_t n_rows, __half *__restrict__ out) {
+    int64_t gb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t total = n_rows * blocks_per_row;
+    if (gb >= total) return;
+    int64_t row = gb / blocks_per_row;
+    int bc = (int)(gb % blocks_per_row);
+    const uint8_t *blk = data + row * row_pitch + (size_t)bc * 34;
+    uint16_t dbits = (uint16_t)(blk[0] | (blk[1] << 8));
+    float d = __half2float(__ushort_as_half(dbits));
+    __half *o = out + (row * blocks_per_row + bc) * 32;
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        int8_t q = (int8_t)blk[2 + j];
+        o[j] = __float2half_rn(__fmul_rn((float)q, d));
+    }
+}
+
+__global__ void copy_rows_f16_kernel(const uint8_t *__restrict__ data, size_t row_pitch, int64_t n_cols,
+                                     int64_t n_rows, __half *__restrict__ out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows * n_cols) return;
+    int64_t r = i / n_cols, c = i % n_cols;
+    out[i] = reinterpret_cast<const __half *>(data + r * row_pitch)[c];
+}
+
+// ---------------------------------------------------------------------------
+// Synthetic blocks generated in place (one thread per block).  The byte
+// stream is defined by tlc_synth.cuh and restated in numpy by the Python
+// package so that host- and device-generated weights are identical.
+// ---------------------------------------------------------------------------
+__global__ void synth_blocks_kernel(uint8_t *__restrict__ data, size_t row_pitch, int type,
+                                    int blocks_per_row, int64_t n_rows, int64_t row0, int64_t bc0,
+                                    int64_t full_blocks_per_row, uint64_t key) {
+    int64_t lb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (lb >= n_rows * blocks_per_row) return;
+    int64_t row = lb / blocks_per_row;
+    int bc = (int)(lb % blocks_per_row);
+    uint64_t gb = (uint64_t)((row0 + row) * full_blocks_per_row + bc0 + bc);
+    if (type == TLC_TYPE_Q4_0) {
+        uint8_t tmp[18];
+        tlc_synth_q4_0_block(key, gb, tmp);
+        uint8_t *dst = data + row * row_pitch + (size_t)bc * 18;
+        for (int i = 0; i < 18; i++) dst[i] = tmp[i];
+    } else {
+        uint8_t tmp[34];
+        tlc_synth_q8_0_block(key, gb, tmp);
+        uint8_t *dst = data + row * row_pitch + (size_t)bc * 34;
+        for (int i = 0; i < 34; i++) dst[i] = tmp[i];
+    }
+}
+
+// ---------------------------------------------------------------------------
+
+static int32_t shard_shape(int32_t type, int64_t n_rows, int64_t n_cols, int32_t tp_rank, int32_t tp_size,
+                           int32_t split, int64_t *rows, int64_t *cols, int64_t *row0, int64_t *col0) {
+    TLC_REQUIRE(type == TLC_TYPE_F16 || type == TLC_TYPE_F32 || type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0,
+                TLC_ERR_LOAD, "unsupported GGUF tensor type %d (supported: F32, F16, Q4_0, Q8_0)", type);
+    TLC_REQUIRE(n_rows > 0 && n_cols > 0, TLC_ERR_INVALID_DIMENSION, "tensor shape [%lld, %lld] is empty",
+                (long long)n_rows, (long long)n_cols);
+    bool quant = type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0;
+    TLC_REQUIRE(!quant || n_cols % 32 == 0, TLC_ERR_LOAD,
+                "quantized tensor needs columns in multiples of 32 (got %lld)", (long long)n_cols);
+    TLC_REQUIRE(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, TLC_ERR_INVALID_OPERATION,
+                "bad tensor-parallel rank %d of %d", tp_rank, tp_size);
+    *rows = n_rows;
+    *cols = n_cols;
+    *row0 = 0;
+    *col0 = 0;
+    if (tp_size > 1 && split == TLC_SPLIT_ROWS) {
+        TLC_REQUIRE(n_rows % tp_size == 0, TLC_ERR_SHAPE_MISMATCH,
+                    "rows %lld do not divide over %d ranks", (long long)n_rows, tp_size);
+        *rows = n_rows / tp_size;
+        *row0 = *rows * tp_rank;
+    } else if (tp_size > 1 && split == TLC_SPLIT_COLS) {
+        int64_t unit = quant ? 32 : 1;
+        TLC_REQUIRE((n_cols / unit) % tp_size == 0, TLC_ERR_SHAPE_MISMATCH,
+                    "columns %lld do not divide over %d ranks in units of %lld", (long long)n_cols, tp_size,
+                    (long long)unit);
+        *cols = n_cols / tp_size;
+        *col0 = *cols * tp_rank;
+    } else {
+        TLC_REQUIRE(tp_size == 1 || split == TLC_SPLIT_NONE, TLC_ERR_INVALID_OPERATION, "bad split mode %d",
+                    split);
+    }
+    return TLC_OK;
+}
+
+static size_t bytes_per_row(int32_t type, int64_t cols) {
+    if (type == TLC_TYPE_Q4_0) return (size_t)(cols / 32) * 18;
+    if (type == TLC_TYPE_Q8_0) return (size_t)(cols / 32) * 34;
+    return (size_t)cols * 2;  // F16 (F32 is converted on the host first)
+}
+
+static int32_t alloc_qtensor(tlc_ctx *ctx, int32_t type, int64_t rows, int64_t cols, int64_t full_rows,
+                             int64_t full_cols, int32_t tp_rank, int32_t tp_size, int32_t split,
+                             tlc_qtensor **out) {
+    tlc_qtensor *qt = new tlc_qtensor();
+    qt->ctx = ctx;
+    qt->type = type == TLC_TYPE_F32 ? TLC_TYPE_F16 : type;
+    qt->n_rows = rows;
+    qt->n_cols = cols;
+    qt->full_rows = full_rows;
+    qt->full_cols = full_cols;
+    qt->row_bytes = bytes_per_row(qt->type, cols);
+    // Rows start on 16-byte boundaries so that the GEMV can move them with
+    // 16-byte bulk copies; for column counts in multiples of 256 this pitch
+    // equals the GGUF row size and the tensor is a verbatim copy.
+    qt->row_pitch = (qt->row_bytes + 15) & ~(size_t)15;
+    qt->bytes = qt->row_pitch * (size_t)rows;
+    qt->tp_rank = tp_rank;
+    qt->tp_size = tp_size;
+    qt->split = split;
+    cudaError_t e = cudaMalloc(&qt->data, qt->bytes + 16);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        size_t want = qt->bytes;
+        delete qt;
+        return tlc_fail(TLC_ERR_ALLOCATION, "weight allocation of %zu bytes failed: %s", want,
+                        cudaGetErrorString(e));
+    }
+    *out = qt;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows, int64_t n_cols,
+                                      const void *blocks, size_t bytes, int32_t tp_rank, int32_t tp_size,
+                                      int32_t split, tlc_qtensor **out) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(out && blocks, TLC_ERR_INVALID_OPERATION, "tlc_qtensor_create: null pointer");
+    *out = nullptr;
+    int64_t rows, cols, row0, col0;
+    if (int32_t rc = shard_shape(type, n_rows, n_cols, tp_rank, tp_size, split, &rows, &cols, &row0, &col0))
+        return rc;
+    size_t src_row_bytes = type == TLC_TYPE_F32 ? (size_t)n_cols * 4 : bytes_per_row(type, n_cols);
+    TLC_REQUIRE(bytes >= src_row_bytes * (size_t)n_rows, TLC_ERR_LOAD,
+                "tensor data too short: %zu bytes for shape [%lld, %lld] (need %zu)", bytes, (long long)n_rows,
+                (long long)n_cols, src_row_bytes * (size_t)n_rows);
+    tlc_qtensor *qt = nullptr;
+    if (int32_t rc = alloc_qtensor(ctx, type, rows, cols, n_rows, n_cols, tp_rank, tp_size, split, &qt)) return rc;
+
+    const uint8_t *src = static_cast<const uint8_t *>(blocks);
+    std::vector<__half> conv;
+    size_t src_pitch = src_row_bytes;
+    size_t col_off;
+    if (type == TLC_TYPE_F32) {
+        // f32 -> f16 with round-to-nearest-even (half::f16::from_f32, gguf.rs:384-395).
+        conv.resize((size_t)rows * cols);
+        const float *f = reinterpret_cast<const float *>(src);
+        for (int64_t r = 0; r < rows; r++)
+            for (int64_t c = 0; c < cols; c++)
+                conv[(size_t)r * cols + c] = __float2half_rn(f[(size_t)(row0 + r) * n_cols + col0 + c]);
+        src = reinterpret_cast<const uint8_t *>(conv.data());
+        src_pitch = (size_t)cols * 2;
+        row0 = 0;
+        col_off = 0;
+    } else if (type == TLC_TYPE_F16) {
+        col_off = (size_t)col0 * 2;
+    } else {
+        col_off = (size_t)(col0 / 32) * tlc_block_bytes(type);
+    }
+    cudaError_t e = cudaMemsetAsync(qt->data, 0, qt->bytes + 16, ctx->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpy2DAsync(qt->data, qt->row_pitch, src + (size_t)row0 * src_pitch + col_off, src_pitch,
+                              qt->row_bytes, (size_t)rows, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // `blocks`/`conv` may go away
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(qt->data);
+        delete qt;
+        return tlc_fail(TLC_ERR_CUDA, "weight upload failed: %s", cudaGetErrorString(e));
+    }
+    *out = qt;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_qtensor_create_synthetic(tlc_ctx *ctx, int32_t type, int64_t n_rows, int64_t n_cols,
+                                                uint64_t seed, uint64_t tensor_id, int32_t tp_rank,
+                                                int32_t tp_size, int32_t split, tlc_qtensor **out) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(out, TLC_ERR_INVALID_OPERATION, "tlc_qtensor_create_synthetic: null pointer");
+    *out = nullptr;
+    TLC_REQUIRE(type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0, TLC_ERR_INVALID_OPERATION,
+                "synthetic weights exist for Q4_0 and Q8_0 only (got type %d)", type);
+    int64_t rows, cols, row0, col0;
+    if (int32_t rc = shard_shape(type, n_rows, n_cols, tp_rank, tp_size, split, &rows, &cols, &row0, &col0))
+        return rc;
+    tlc_qtensor *qt = nullptr;
+    if (int32_t rc = alloc_qtensor(ctx, type, rows, cols, n_rows, n_cols, tp_rank, tp_size, split, &qt)) return rc;
+    cudaError_t e = cudaMemsetAsync(qt->data, 0, qt->bytes + 16, ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(qt->data);
+        delete qt;
+        return tlc_fail(TLC_ERR_CUDA, "memset failed: %s", cudaGetErrorString(e));
+    }
+    int bpr = (int)(cols / 32);
+    int64_t total = rows * bpr;
+    int threads = 256;
+    int64_t grid = (total + threads - 1) / threads;
+    synth_blocks_kernel<<<(unsigned)grid, threads, 0, ctx->stream>>>(
+        static_cast<uint8_t *>(qt->data), qt->row_pitch, type, bpr, rows, row0, col0 / 32, n_cols / 32,
+        tlc_synth_key(seed, tensor_id));
+    ctx->launches++;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        cudaFree(qt->data);
+        delete qt;
+        return tlc_fail(TLC_ERR_CUDA, "generator launch failed: %s", cudaGetErrorString(e));
+    }
+    *out = qt;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_synth_blocks_host(int32_t type, uint64_t seed, uint64_t tensor_id, int64_t first_block,
+                                         int64_t n_blocks, void *out_host) {
+    TLC_REQUIRE(type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0, TLC_ERR_INVALID_OPERATION,
+                "synthetic weights exist for Q4_0 and Q8_0 only (got type %d)", type);
+    TLC_REQUIRE(out_host && first_block >= 0 && n_blocks >= 0, TLC_ERR_INVALID_OPERATION,
+                "tlc_synth_blocks_host: bad arguments");
+    const uint64_t key = tlc_synth_key(seed, tensor_id);
+    uint8_t *o = static_cast<uint8_t *>(out_host);
+    const size_t bb = tlc_block_bytes(type);
+    for (int64_t i = 0; i < n_blocks; i++) {
+        if (type == TLC_TYPE_Q4_0)
+            tlc_synth_q4_0_block(key, (uint64_t)(first_block + i), o + (size_t)i * bb);
+        else
+            tlc_synth_q8_0_block(key, (uint64_t)(first_block + i), o + (size_t)i * bb);
+    }
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_qtensor_destroy(tlc_qtensor *qt) {
+    if (!qt) return TLC_OK;
+    cudaSetDevice(qt->ctx->device);
+    cudaFree(qt->data);  // waits for queued work that still reads it
+    delete qt;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_qtensor_info(tlc_qtensor *qt, int32_t *type, int64_t *n_rows, int64_t *n_cols,
+                                    size_t *row_pitch, const void **dev_ptr) {
+    TLC_REQUIRE(qt != nullptr, TLC_ERR_INVALID_OPERATION, "tlc_qtensor_info: null tensor");
+    if (type) *type = qt->type;
+    if (n_rows) *n_rows = qt->n_rows;
+    if (n_cols) *n_cols = qt->n_cols;
+    if (row_pitch) *row_pitch = qt->row_pitch;
+    if (dev_ptr) *dev_ptr = qt->data;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_dequant(tlc_ctx *ctx, tlc_qtensor *qt, void *out_f16_dev) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(qt && out_f16_dev, TLC_ERR_INVALID_OPERATION, "tlc_dequant: null pointer");
+    TLC_REQUIRE(qt->ctx->device == ctx->device, TLC_ERR_DEVICE, "tlc_dequant: tensor lives on device %d, context on %d",
+                qt->ctx->device, ctx->device);
+    const int threads = 256;
+    const uint8_t *data = static_cast<const uint8_t *>(qt->data);
+    __half *out = static_cast<__half *>(out_f16_dev);
+    if (qt->type == TLC_TYPE_F16) {
+        int64_t total = qt->n_rows * qt->n_cols;
+        copy_rows_f16_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, ctx->stream>>>(
+            data, qt->row_pitch, qt->n_cols, qt->n_rows, out);
+    } else {
+        int bpr = (int)(qt->n_cols / 32);
+        int64_t total = qt->n_rows * bpr;
+        unsigned grid = (unsigned)((total + threads - 1) / threads);
+        if (qt->type == TLC_TYPE_Q4_0)
+            dequant_q4_0_kernel<<<grid, threads, 0, ctx->stream>>>(data, qt->row_pitch, bpr, qt->n_rows, out);
+        else
+            dequant_q8_0_kernel<<<grid, threads, 0, ctx->stream>>>(data, qt->row_pitch, bpr, qt->n_rows, out);
+    }
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}

@@ -1,0 +1,61 @@
+// Counter-based generator of the synthetic benchmark weights.  Usable from
+// host and device code; tensorlogic_b200/synth.py restates it in numpy and the
+// tests check that the two produce the same bytes.
+//
+//   key        = mix64(mix64(seed) ^ tensor_id)
+//   r(i)       = mix64(key + i)
+//   Q4_0 block b: d = f16_rne(float(2000 + r(3b) % 18001) * 1e-6f)   (U[0.002, 0.02])
+//                 qs[0..7] = bytes of r(3b+1), qs[8..15] = bytes of r(3b+2)  (little endian)
+//   Q8_0 block b: d as above from r(9b); q[4j..4j+3] = ((u16 * 255) >> 16) - 127 over
+//                 the four 16-bit fields of r(9b+1+j), j = 0..7      (U{-127..127})
+// where b counts blocks of the FULL (unsharded) tensor in row-major order.
+#pragma once
+#include <cuda_fp16.h>
+#include <cstdint>
+
+__host__ __device__ inline uint64_t tlc_mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__host__ __device__ inline uint64_t tlc_synth_key(uint64_t seed, uint64_t tensor_id) {
+    return tlc_mix64(tlc_mix64(seed) ^ tensor_id);
+}
+
+__host__ __device__ inline uint16_t tlc_synth_scale_bits(uint64_t r) {
+    float v = (float)(uint32_t)(2000u + (uint32_t)(r % 18001ull));
+#ifdef __CUDA_ARCH__
+    float d = __fmul_rn(v, 1e-6f);
+#else
+    volatile float dv = v * 1e-6f;
+    float d = dv;
+#endif
+    __half h = __float2half_rn(d);
+    return __half_as_ushort(h);
+}
+
+__host__ __device__ inline void tlc_synth_q4_0_block(uint64_t key, uint64_t b, uint8_t *out18) {
+    uint16_t d = tlc_synth_scale_bits(tlc_mix64(key + 3 * b));
+    out18[0] = (uint8_t)(d & 0xFF);
+    out18[1] = (uint8_t)(d >> 8);
+    uint64_t r1 = tlc_mix64(key + 3 * b + 1), r2 = tlc_mix64(key + 3 * b + 2);
+    for (int i = 0; i < 8; i++) {
+        out18[2 + i] = (uint8_t)(r1 >> (8 * i));
+        out18[10 + i] = (uint8_t)(r2 >> (8 * i));
+    }
+}
+
+__host__ __device__ inline void tlc_synth_q8_0_block(uint64_t key, uint64_t b, uint8_t *out34) {
+    uint16_t d = tlc_synth_scale_bits(tlc_mix64(key + 9 * b));
+    out34[0] = (uint8_t)(d & 0xFF);
+    out34[1] = (uint8_t)(d >> 8);
+    for (int j = 0; j < 8; j++) {
+        uint64_t r = tlc_mix64(key + 9 * b + 1 + j);
+        for (int i = 0; i < 4; i++) {
+            uint32_t u = (uint32_t)((r >> (16 * i)) & 0xFFFF);
+            out34[2 + 4 * j + i] = (uint8_t)(int8_t)((int)((u * 255u) >> 16) - 127);
+        }
+    }
+}

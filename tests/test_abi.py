@@ -1,0 +1,89 @@
+"""CPU-side checks of the C-ABI boundary: the library loads, exports every
+symbol include/tlcuda.h declares, refuses to run without a CUDA device, and its
+host-side generator matches the numpy restatement."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "tlcuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"TLC_API\s+[\w\s\*]+?\b(tlc_\w+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound(lib):
+    from tensorlogic_b200 import _lib
+    names = _declared_symbols()
+    assert len(names) >= 35
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in tlcuda.h but not exported"
+        assert n in _lib.PROTOTYPES, f"{n} has no ctypes prototype"
+    assert set(_lib.PROTOTYPES) <= set(names), set(_lib.PROTOTYPES) - set(names)
+
+
+def test_no_oracle_in_product():
+    """The shipped package must not reach into oracle/ (it is test infrastructure)."""
+    pkg = os.path.join(ROOT, "tensorlogic_b200")
+    for dirpath, _, files in os.walk(pkg):
+        if os.path.basename(dirpath) == "build":
+            continue
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "tl_ref" not in src and "libtlref" not in src, f
+
+
+def test_init_fails_loudly_without_gpu(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    h = C.c_void_p()
+    rc = lib.tlc_init(0, C.byref(h))
+    from tensorlogic_b200 import _lib
+    assert rc == _lib.ERR_DEVICE and not h.value
+    assert b"no CPU path" in lib.tlc_last_error()
+    from tensorlogic_b200.api import Device, TensorError
+    with pytest.raises(TensorError):
+        Device(0)
+
+
+def test_version_string(lib):
+    assert b"sm_100a" in lib.tlc_version()
+
+
+@pytest.mark.parametrize("qtype,bb", [(2, 18), (8, 34)])
+def test_host_generator_matches_numpy(lib, qtype, bb):
+    from tensorlogic_b200 import synth
+    seed, tid = 7, synth.tensor_id("blk.3.ffn_gate.weight")
+    n_rows, n_cols = 6, 256
+    want = synth.blocks(qtype, seed, tid, n_rows, n_cols)
+    got = np.empty((n_rows * (n_cols // 32), bb), np.uint8)
+    assert lib.tlc_synth_blocks_host(qtype, seed, tid, 0, got.shape[0], got.ctypes.data) == 0
+    assert np.array_equal(got.reshape(want.shape), want)
+    # a shard generated on its own equals the slice of the whole
+    part = synth.blocks(qtype, seed, tid, n_rows, n_cols, row0=2, rows=3)
+    assert np.array_equal(part, want[2:5])
+    got2 = np.empty((3 * 8, bb), np.uint8)
+    assert lib.tlc_synth_blocks_host(qtype, seed, tid, 2 * 8, 24, got2.ctypes.data) == 0
+    assert np.array_equal(got2.reshape(part.shape), part)
+
+
+def test_synthetic_distributions():
+    from tensorlogic_b200 import synth
+    b = synth.q4_0_blocks(0, 1, 64, 2048)
+    d = b[..., :2].copy().view(np.float16).astype(np.float32)
+    assert 0.0019 < d.min() and d.max() < 0.0201 and abs(d.mean() - 0.011) < 3e-4
+    nib = np.concatenate([(b[..., 2:] & 15).ravel(), (b[..., 2:] >> 4).ravel()])
+    assert abs(nib.mean() - 7.5) < 0.02 and set(np.unique(nib)) == set(range(16))
+    q = synth.q8_0_blocks(0, 2, 64, 2048)[..., 2:].view(np.int8)
+    assert q.min() == -127 and q.max() == 127 and abs(q.astype(np.float64).mean()) < 0.6
+    x = synth.activations(0, "x", (1, 65536)).astype(np.float64)
+    assert abs(x.mean()) < 0.02 and abs(x.std() - 1.0) < 0.02
+    ids = synth.token_ids(0, "ids", 4096, 32000)
+    assert ids.min() >= 0 and ids.max() < 32000 and len(np.unique(ids)) > 3800
