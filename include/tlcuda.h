@@ -236,6 +236,126 @@ TLC_API int32_t tlc_swiglu_gate_up(tlc_ctx *ctx, tlc_qtensor *w_gate, tlc_qtenso
 TLC_API int32_t tlc_linear_residual(tlc_ctx *ctx, tlc_qtensor *w, const void *x_dev, int32_t m,
                                     const void *residual_dev, void *y_dev);
 
+/* ---- KV cache and attention ----------------------------------------------- */
+
+typedef struct tlc_kvcache tlc_kvcache;
+
+/* KVCache::new_f16(n_layers) (src/model/llama.rs:51-76) with the storage
+ * pre-allocated the way src/ops/cache_ops.rs:28-60 does it: per layer
+ * K and V [max_batch, max_seq, n_kv_heads, head_dim] f16, zero-filled. */
+TLC_API int32_t tlc_kvcache_create(tlc_ctx *ctx, int32_t n_layers, int32_t max_batch,
+                                   int32_t max_seq, int32_t n_kv_heads, int32_t head_dim,
+                                   tlc_kvcache **out);
+TLC_API int32_t tlc_kvcache_destroy(tlc_kvcache *cache);
+TLC_API int32_t tlc_kvcache_layer_ptrs(tlc_kvcache *cache, int32_t layer, void **k_dev,
+                                       void **v_dev);
+/* cache.append(layer, K, V) (src/model/llama.rs:78-99; kernel cache_append_f16,
+ * shaders/unified.metal:4189-4197) without the O(T) concat: rows of k/v
+ * [m, n_kv_heads*head_dim] are written in place.  positions_dev == NULL: the m
+ * rows are consecutive tokens of sequence 0 starting at pos_offset (prefill);
+ * otherwise row r is the new token of sequence r at positions_dev[r] (decode). */
+TLC_API int32_t tlc_kvcache_append(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer,
+                                   const void *k_dev, const void *v_dev, int32_t m,
+                                   int32_t pos_offset, const int32_t *positions_dev);
+/* Grouped-query causal attention over the cache; replaces the script-level
+ * chain reshape/broadcast_to/einsum/scale/causal_mask/apply_attention_mask/
+ * softmax/einsum (debug/chat_demo_with_kvcache.tl:44-88, :247-282; kernels at
+ * shaders/unified.metal:2524-2683, :4474-4488, :2057-2200).
+ * q, out: [batch * n_queries, n_heads, head_dim] f16.  Query i of a sequence
+ * sits at position q_pos0 + i and sees keys 0 .. q_pos0 + i; the cache must
+ * already hold the keys of these positions.  With positions_dev (int32[batch],
+ * n_queries must be 1) each sequence's query sits at positions_dev[b] and
+ * max_keys bounds positions_dev[b] + 1.  KV head of query head h is
+ * h / (n_heads / n_kv_heads). */
+TLC_API int32_t tlc_attention(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer, const void *q_dev,
+                              void *out_dev, int32_t batch, int32_t n_queries, int32_t n_heads,
+                              int32_t q_pos0, const int32_t *positions_dev, int32_t max_keys,
+                              float scale);
+
+/* ---- GGUF models ----------------------------------------------------------- */
+
+/* load_model(path) (src/interpreter/builtin_model.rs:106-131 -> Model::load,
+ * src/model/mod.rs:165-184 -> GGUFLoader::load, src/model/formats/gguf.rs:256;
+ * header walk of src/model/formats/mmap_gguf.rs:187-275): reads a GGUF v2/v3
+ * file and uploads every tensor; Q4_0/Q8_0 tensors keep their blocks, F32 is
+ * rounded to f16.  Rank >= 2 dims are reversed to [out, in] (gguf.rs:288-291).
+ * With tp_size > 1 the LLaMA projections are sharded by name (q/k/v/gate/up/
+ * output: rows; attn_output/ffn_down: columns). */
+TLC_API int32_t tlc_model_load_gguf(tlc_ctx *ctx, const char *path, int32_t tp_rank,
+                                    int32_t tp_size, tlc_model **out);
+/* MmapGGUFLoader::new (src/model/formats/mmap_gguf.rs:120, header walk
+ * :187-275): parses header, metadata and tensor table only -- no device needed.
+ * Per tensor: reversed [rows, cols], GGUF type id, absolute file offset and
+ * byte size (n/32*18 for Q4_0, n/32*34 for Q8_0, mmap_gguf.rs:361-379). */
+typedef struct tlc_gguf tlc_gguf;
+TLC_API int32_t tlc_gguf_open(const char *path, tlc_gguf **out);
+TLC_API int32_t tlc_gguf_close(tlc_gguf *g);
+TLC_API int32_t tlc_gguf_tensor_count(tlc_gguf *g);
+TLC_API int32_t tlc_gguf_tensor_info(tlc_gguf *g, int32_t index, const char **name, int32_t *type,
+                                     int64_t *rows, int64_t *cols, uint64_t *file_offset,
+                                     uint64_t *nbytes);
+TLC_API int32_t tlc_gguf_meta_num(tlc_gguf *g, const char *key, double *out);
+TLC_API const char *tlc_gguf_meta_str(tlc_gguf *g, const char *key);
+TLC_API uint64_t tlc_gguf_data_start(tlc_gguf *g);
+/* Model::new / insert for weights that do not come from a file (synthetic). */
+TLC_API int32_t tlc_model_create(tlc_ctx *ctx, tlc_model **out);
+TLC_API int32_t tlc_model_add(tlc_model *m, const char *name, tlc_qtensor *qt); /* takes ownership */
+TLC_API int32_t tlc_model_destroy(tlc_model *m);
+/* get_tensor(model, name) (src/interpreter/builtin_model.rs:203-246); the
+ * handle stays owned by the model.  TLC_ERR_LOAD when the name is unknown. */
+TLC_API int32_t tlc_model_get(tlc_model *m, const char *name, tlc_qtensor **out);
+TLC_API int32_t tlc_model_tensor_count(tlc_model *m);
+TLC_API const char *tlc_model_tensor_name(tlc_model *m, int32_t index);
+/* GGUF metadata (numeric and bool keys as double; "<key>.length" for arrays). */
+TLC_API int32_t tlc_model_meta_num(tlc_model *m, const char *key, double *out);
+TLC_API const char *tlc_model_meta_str(tlc_model *m, const char *key);
+
+/* ---- LLaMA forward pass ----------------------------------------------------- */
+
+/* LlamaConfig (src/model/llama.rs:14-42; defaults there are TinyLlama's). */
+typedef struct tlc_llama_config {
+    int32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn_dim, vocab;
+    float rms_eps;
+    uint32_t rope_base;
+    int32_t max_seq;         /* KV cache positions per sequence                */
+    int32_t max_batch;       /* sequences decoded together (<= 64)              */
+    int32_t max_prefill;     /* longest prompt chunk one prefill call may take  */
+    int32_t tp_rank, tp_size;
+    int32_t logits_all_rows; /* keep logits of every prompt row (parity checks) */
+    int32_t no_graph;        /* launch kernels one by one, no CUDA graph replay */
+} tlc_llama_config;
+
+/* The forward pass the TL scripts spell out builtin by builtin
+ * (debug/chat_demo_with_kvcache.tl:136-181 prefill, :213-296 decode;
+ * LlamaModel::forward itself is a stub, src/model/llama.rs:257-266), bound to
+ * the GGUF tensor names token_embd / blk.N.* / output_norm / output. */
+TLC_API int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_llama_config *cfg,
+                                 tlc_llama **out);
+TLC_API int32_t tlc_llama_destroy(tlc_llama *l);
+/* Prompt tokens ids_host[0..n) of sequence 0 at positions pos0.. : fills the
+ * cache, returns the greedy next token (last-index-wins ties,
+ * src/interpreter/builtin_sampling.rs:176-181) and optionally the f16 logits
+ * of the last row (or of all n rows when all_rows != 0). */
+TLC_API int32_t tlc_llama_prefill(tlc_llama *l, const int32_t *ids_host, int32_t n, int32_t pos0,
+                                  void *logits_host, int32_t all_rows, int32_t *next_id_host);
+/* Sets the pending token and position of `batch` sequences (batched decode). */
+TLC_API int32_t tlc_llama_set_state(tlc_llama *l, int32_t batch, const int32_t *ids_host,
+                                    const int32_t *positions_host);
+/* One greedy decode step through host buffers: ids_host (NULL = continue with
+ * the tokens sampled by the previous step) is uploaded, the step runs, the
+ * sampled tokens (and the f16 logits [batch, vocab] if logits_host != NULL)
+ * are downloaded. */
+TLC_API int32_t tlc_llama_decode_host(tlc_llama *l, int32_t batch, const int32_t *ids_host,
+                                      int32_t *next_ids_host, void *logits_host);
+/* Enqueues `steps` greedy decode steps back to back on the device; nothing is
+ * read back (use tlc_llama_read_state). */
+TLC_API int32_t tlc_llama_decode_enqueue(tlc_llama *l, int32_t batch, int32_t steps);
+TLC_API int32_t tlc_llama_read_state(tlc_llama *l, int32_t batch, int32_t *next_ids_host,
+                                     int32_t *positions_host);
+/* Kernels one decode step launches (for launch accounting). */
+TLC_API int32_t tlc_llama_launches_per_step(tlc_llama *l);
+TLC_API tlc_kvcache *tlc_llama_cache(tlc_llama *l);
+
 #ifdef __cplusplus
 }
 #endif

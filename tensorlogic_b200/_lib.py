@@ -41,6 +41,15 @@ class PoolStats(C.Structure):
                                           "allocation_count", "eviction_count", "live_bytes")]
 
 
+class LlamaConfig(C.Structure):
+    """tlc_llama_config of include/tlcuda.h."""
+    _fields_ = [("n_layers", C.c_int32), ("d_model", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("ffn_dim", C.c_int32), ("vocab", C.c_int32), ("rms_eps", C.c_float),
+                ("rope_base", C.c_uint32), ("max_seq", C.c_int32), ("max_batch", C.c_int32),
+                ("max_prefill", C.c_int32), ("tp_rank", C.c_int32), ("tp_size", C.c_int32),
+                ("logits_all_rows", C.c_int32), ("no_graph", C.c_int32)]
+
+
 vp, i32, i64, u32, u64, sz, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint32, C.c_uint64, C.c_size_t, C.c_float
 P = C.POINTER
 
@@ -85,6 +94,36 @@ PROTOTYPES = {
     "tlc_norm_linear_multi": (i32, [vp, i32, P(vp), P(vp), P(i32), vp, i32, vp, f32, i32, u32, vp]),
     "tlc_swiglu_gate_up": (i32, [vp, vp, vp, vp, i32, vp, f32, vp]),
     "tlc_linear_residual": (i32, [vp, vp, vp, i32, vp, vp]),
+    "tlc_kvcache_create": (i32, [vp, i32, i32, i32, i32, i32, P(vp)]),
+    "tlc_kvcache_destroy": (i32, [vp]),
+    "tlc_kvcache_layer_ptrs": (i32, [vp, i32, P(vp), P(vp)]),
+    "tlc_kvcache_append": (i32, [vp, vp, i32, vp, vp, i32, i32, vp]),
+    "tlc_attention": (i32, [vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, f32]),
+    "tlc_model_load_gguf": (i32, [vp, C.c_char_p, i32, i32, P(vp)]),
+    "tlc_gguf_open": (i32, [C.c_char_p, P(vp)]),
+    "tlc_gguf_close": (i32, [vp]),
+    "tlc_gguf_tensor_count": (i32, [vp]),
+    "tlc_gguf_tensor_info": (i32, [vp, i32, P(C.c_char_p), P(i32), P(i64), P(i64), P(u64), P(u64)]),
+    "tlc_gguf_meta_num": (i32, [vp, C.c_char_p, P(C.c_double)]),
+    "tlc_gguf_meta_str": (C.c_char_p, [vp, C.c_char_p]),
+    "tlc_gguf_data_start": (u64, [vp]),
+    "tlc_model_create": (i32, [vp, P(vp)]),
+    "tlc_model_add": (i32, [vp, C.c_char_p, vp]),
+    "tlc_model_destroy": (i32, [vp]),
+    "tlc_model_get": (i32, [vp, C.c_char_p, P(vp)]),
+    "tlc_model_tensor_count": (i32, [vp]),
+    "tlc_model_tensor_name": (C.c_char_p, [vp, i32]),
+    "tlc_model_meta_num": (i32, [vp, C.c_char_p, P(C.c_double)]),
+    "tlc_model_meta_str": (C.c_char_p, [vp, C.c_char_p]),
+    "tlc_llama_create": (i32, [vp, vp, P(LlamaConfig), P(vp)]),
+    "tlc_llama_destroy": (i32, [vp]),
+    "tlc_llama_prefill": (i32, [vp, P(i32), i32, i32, vp, i32, P(i32)]),
+    "tlc_llama_set_state": (i32, [vp, i32, P(i32), P(i32)]),
+    "tlc_llama_decode_host": (i32, [vp, i32, P(i32), P(i32), vp]),
+    "tlc_llama_decode_enqueue": (i32, [vp, i32, i32]),
+    "tlc_llama_read_state": (i32, [vp, i32, P(i32), P(i32)]),
+    "tlc_llama_launches_per_step": (i32, [vp]),
+    "tlc_llama_cache": (vp, [vp]),
 }
 
 _lib = None

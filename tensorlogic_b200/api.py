@@ -326,6 +326,78 @@ def swiglu_gate_up(x: Tensor, w_gate: QTensor, w_up: QTensor, norm_weight: Optio
     return act
 
 
+class KVCache:
+    """KVCache::new_f16 (src/model/llama.rs:51-116) over pre-allocated device storage.
+
+    ``append`` writes rows in place instead of concatenating the whole cache;
+    ``attention`` is the fused replacement of the script-level GQA chain.
+    """
+
+    def __init__(self, dev: Device, n_layers: int, n_kv_heads: int, head_dim: int, max_seq: int = 2048,
+                 max_batch: int = 1):
+        self.dev = dev
+        self.n_layers, self.n_kv_heads, self.head_dim = n_layers, n_kv_heads, head_dim
+        self.max_seq, self.max_batch = max_seq, max_batch
+        h = C.c_void_p()
+        check(dev.lib.tlc_kvcache_create(dev.handle, n_layers, max_batch, max_seq, n_kv_heads, head_dim, C.byref(h)))
+        self.handle = h
+        self.lengths = [0] * n_layers  # sequence-0 token counts, like KVCache::seq_len upstream
+
+    def __del__(self):
+        try:
+            if self.handle and self.dev.handle:
+                self.dev.lib.tlc_kvcache_destroy(self.handle)
+            self.handle = None
+        except Exception:
+            pass
+
+    def append(self, layer: int, k: Tensor, v: Tensor, positions: Optional[np.ndarray] = None) -> None:
+        """cache.append(layer, K, V): K/V are [m, n_kv_heads, head_dim] (or [m, n_kv_heads*head_dim])."""
+        row = self.n_kv_heads * self.head_dim
+        if k.size % row or k.size != v.size:
+            raise TensorError(_lib.ERR_SHAPE_MISMATCH, f"KV rows must have {row} elements")
+        m = k.size // row
+        pos_t = _upload_i32(self.dev, np.ascontiguousarray(positions, dtype=np.int32)) if positions is not None else None
+        check(self.dev.lib.tlc_kvcache_append(self.dev.handle, self.handle, layer, k.ptr, v.ptr, m,
+                                              self.lengths[layer] if positions is None else 0,
+                                              pos_t.ptr if pos_t is not None else None))
+        if positions is None:
+            self.lengths[layer] += m
+
+    def layer_arrays(self, layer: int, batch_index: int = 0, length: Optional[int] = None):
+        """get_k / get_v (src/model/llama.rs:101-116): host copies [len, n_kv_heads, head_dim]."""
+        kp, vp_ = C.c_void_p(), C.c_void_p()
+        check(self.dev.lib.tlc_kvcache_layer_ptrs(self.handle, layer, C.byref(kp), C.byref(vp_)))
+        n = self.lengths[layer] if length is None else length
+        row = self.n_kv_heads * self.head_dim
+        out = []
+        for p in (kp.value, vp_.value):
+            a = np.empty((n, self.n_kv_heads, self.head_dim), np.float16)
+            if n:
+                check(self.dev.lib.tlc_download(self.dev.handle, a.ctypes.data,
+                                                p + batch_index * self.max_seq * row * 2, a.nbytes))
+            out.append(a)
+        return out
+
+    def attention(self, layer: int, q: Tensor, n_heads: int, q_pos0: int = 0, batch: int = 1,
+                  positions: Optional[np.ndarray] = None, scale: Optional[float] = None) -> Tensor:
+        """softmax(q.K^T * scale + causal mask).V for q [batch*n_queries, n_heads, head_dim]."""
+        D = self.head_dim
+        if q.size % (n_heads * D * batch):
+            raise TensorError(_lib.ERR_SHAPE_MISMATCH, f"attention: q has {q.size} elements")
+        nq = q.size // (n_heads * D * batch)
+        out = self.dev.empty(q.shape)
+        scale = float(1.0 / np.sqrt(D)) if scale is None else scale
+        pos_t, max_keys = None, q_pos0 + nq
+        if positions is not None:
+            pos = np.ascontiguousarray(positions, dtype=np.int32)
+            pos_t = _upload_i32(self.dev, pos)
+            max_keys = int(pos.max()) + 1
+        check(self.dev.lib.tlc_attention(self.dev.handle, self.handle, layer, q.ptr, out.ptr, batch, nq, n_heads,
+                                         q_pos0, pos_t.ptr if pos_t is not None else None, max_keys, scale))
+        return out
+
+
 def linear_residual(x: Tensor, weight: QTensor, residual: Tensor) -> Tensor:
     m, _ = _rows_cols(x)
     y = x.dev.empty((m, weight.shape[0]))

@@ -1,0 +1,519 @@
+// Pre-allocated f16 KV cache and fused grouped-query attention over it.
+//
+// Takes the place of the builtin chain the TL scripts run per layer
+// (debug/chat_demo_with_kvcache.tl:44-88 prefill, :247-282 decode):
+//   cache.append (a concat of the whole cache, src/model/llama.rs:85-99)
+//   reshape -> broadcast_to -> reshape            (GQA expansion, 8x copies)
+//   einsum("ihd,jhd->ihj") -> * 0.125 -> causal_mask -> apply_attention_mask
+//   softmax -> einsum("ihj,jhd->ihd")
+// (kernels einsum_ihd_jhd_ihj_f16, apply_attention_mask_f16, softmax_f16,
+// einsum_ihj_jhd_ihd_f16 of shaders/unified.metal:2524-2683, :4474-4488,
+// :2057-2200) by one kernel that never materialises the [I, H, J] scores.
+//
+// One CTA owns a tile of 16 (query, head) rows that share a KV head -- the G
+// query heads of the group times 16/G query positions -- and a range of keys.
+// K/V tiles of 64 keys are staged in shared memory with 16-byte cp.async
+// (zero-filled past the end), each of the 4 warps takes 16 keys of a tile:
+// S = Q.K^T with m16n8k16 (f32 accumulate), the two f16 roundings the reference
+// applies to the scores (einsum output, then the f16 multiply by the scale),
+// online softmax in f32, P rounded to f16 as the reference stores it, and
+// O += P.V with f32 accumulation.  The 4 warps' partial (max, sum, O) are merged
+// through shared memory.  For decode the key range of a sequence is split over
+// several CTAs; each writes its partial to global scratch and the last one to
+// finish (atomic ticket) merges them, so no second launch is needed.
+#include <cuda_fp16.h>
+
+#include "tlc_internal.h"
+
+struct tlc_kvcache {
+    tlc_ctx *ctx;
+    int n_layers, max_batch, max_seq, n_kv_heads, head_dim;
+    __half *k;  // [layer][batch][max_seq][n_kv_heads][head_dim]
+    __half *v;
+    size_t layer_stride;  // elements
+};
+
+namespace {
+
+constexpr int kTileKeys = 64;
+constexpr int kAttnThreads = 128;
+
+struct AttnParams {
+    const __half *q;   // [B*I, H, D]
+    const __half *kc;  // this layer's K cache [B][Tmax][Hkv][D]
+    const __half *vc;
+    __half *out;       // [B*I, H, D]
+    int I, H, Hkv, G, Tmax;
+    int q_pos0;            // position of query 0 (prefill); ignored when positions != null
+    const int *positions;  // device int32[B]: position of each sequence's single query (decode)
+    float scale;
+    int nsplit;
+    int keys_per_split;  // multiple of kTileKeys
+    int q_tiles;
+    float *part_ml;  // [rows][nsplit][2]
+    float *part_o;   // [rows][nsplit][D]
+    int *counters;   // [B][q_tiles][Hkv], zero between launches
+};
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int sz = valid ? 16 : 0;  // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void *p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void *p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParams p) {
+    constexpr int PITCH = D + 8;             // halves; +16 B keeps ldmatrix rows on distinct banks
+    constexpr int TILE = kTileKeys * PITCH;  // halves per K (or V) tile
+    constexpr int KSTEPS = D / 16;
+    constexpr int NDT = D / 8;               // n8 tiles of the output
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __half *ks = reinterpret_cast<__half *>(smem_raw);  // [2][TILE]
+    __half *vs = ks + 2 * TILE;                         // [2][TILE]
+    __shared__ float sm_m[4][16], sm_l[4][16];
+    __shared__ int sm_last;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int b = blockIdx.z, hk = blockIdx.y;
+    const int qt = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
+    const int G = p.G, RQ = 16 / G;
+
+    const int pos0 = p.positions ? p.positions[b] : p.q_pos0;  // position of this sequence's query 0
+    const int T = pos0 + p.I;                                    // keys in the cache (incl. the new ones)
+    // Rows of the tile: r -> (query qt*RQ + r/G, head hk*G + r%G).
+    const int qi_lo = qt * RQ + g / G, qi_hi = qt * RQ + (g + 8) / G;
+    const int head_lo = hk * G + g % G, head_hi = hk * G + (g + 8) % G;
+    const bool valid_lo = qi_lo < p.I, valid_hi = qi_hi < p.I;
+    const int rpos_lo = pos0 + qi_lo, rpos_hi = pos0 + qi_hi;  // last visible key of the row
+
+    // Keys this CTA covers: its split, cut at the last key any row of the tile may see.
+    const int last_q = min(p.I, (qt + 1) * RQ) - 1;
+    const int visible_end = min(T, pos0 + last_q + 1);
+    const int k_begin = split * p.keys_per_split;
+    const int k_end = min(visible_end, k_begin + p.keys_per_split);
+    const int ntiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
+
+    // Q fragments (A operand), straight from global memory.
+    uint32_t qa[KSTEPS][4];
+    {
+        const __half *q_lo = p.q + ((size_t)(b * p.I + (valid_lo ? qi_lo : 0)) * p.H + head_lo) * D;
+        const __half *q_hi = p.q + ((size_t)(b * p.I + (valid_hi ? qi_hi : 0)) * p.H + head_hi) * D;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; kk++) {
+            qa[kk][0] = valid_lo ? *reinterpret_cast<const uint32_t *>(q_lo + 16 * kk + 2 * t) : 0u;
+            qa[kk][1] = valid_hi ? *reinterpret_cast<const uint32_t *>(q_hi + 16 * kk + 2 * t) : 0u;
+            qa[kk][2] = valid_lo ? *reinterpret_cast<const uint32_t *>(q_lo + 16 * kk + 8 + 2 * t) : 0u;
+            qa[kk][3] = valid_hi ? *reinterpret_cast<const uint32_t *>(q_hi + 16 * kk + 8 + 2 * t) : 0u;
+        }
+    }
+
+    const __half *kbase = p.kc + ((size_t)b * p.Tmax * p.Hkv + hk) * D;
+    const __half *vbase = p.vc + ((size_t)b * p.Tmax * p.Hkv + hk) * D;
+    const size_t key_stride = (size_t)p.Hkv * D;
+
+    auto load_tile = [&](int tile, int stage) {
+        const int j0 = k_begin + tile * kTileKeys;
+        constexpr int CHUNKS = kTileKeys * (D / 8);
+#pragma unroll
+        for (int c = tid; c < CHUNKS; c += kAttnThreads) {
+            const int key = c / (D / 8), part = c % (D / 8);
+            const bool ok = j0 + key < k_end;
+            const size_t off = (size_t)(ok ? j0 + key : 0) * key_stride + part * 8;
+            cp_async16(ks + stage * TILE + key * PITCH + part * 8, kbase + off, ok);
+            cp_async16(vs + stage * TILE + key * PITCH + part * 8, vbase + off, ok);
+        }
+        cp_async_commit();
+    };
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[NDT][4];
+#pragma unroll
+    for (int i = 0; i < NDT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const __half scale_h = __float2half_rn(p.scale);
+
+    if (ntiles > 0) load_tile(0, 0);
+    for (int tile = 0; tile < ntiles; tile++) {
+        const int stage = tile & 1;
+        if (tile + 1 < ntiles) {
+            load_tile(tile + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+
+        const int j0 = k_begin + tile * kTileKeys;
+        const int kw0 = warp * 16;  // this warp's 16 keys of the tile
+        if (j0 + kw0 < k_end) {
+            const __half *kt = ks + stage * TILE;
+            const __half *vt = vs + stage * TILE;
+            float s[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; kk++) {
+                uint32_t r[4];
+                const int mi = lane >> 3;
+                ldsm_x4(r, kt + (kw0 + (mi >> 1) * 8 + (lane & 7)) * PITCH + 16 * kk + (mi & 1) * 8);
+                mma16816(s[0], qa[kk], r[0], r[1]);
+                mma16816(s[1], qa[kk], r[2], r[3]);
+            }
+            // Scores: f16 rounding of the einsum output, f16 multiply by the scale
+            // (scripts multiply the f16 score tensor by 0.125), then the causal mask.
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int key = j0 + kw0 + nt * 8 + 2 * t + (e & 1);
+                    const int rpos = e < 2 ? rpos_lo : rpos_hi;
+                    float v = __half2float(__hmul(__float2half_rn(s[nt][e]), scale_h));
+                    if (key >= k_end || key > rpos) v = -INFINITY;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float corr[2], msafe[2];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_run[h], mx[h]);
+                msafe[h] = m_new == -INFINITY ? 0.f : m_new;
+                corr[h] = expf(m_run[h] - msafe[h]);  // exp(-inf) = 0 on the first tile
+                m_run[h] = m_new;
+            }
+            float psum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float pv = expf(s[nt][e] - msafe[e >> 1]);
+                    s[nt][e] = pv;
+                    psum[e >> 1] += pv;
+                }
+            l_run[0] = l_run[0] * corr[0] + psum[0];
+            l_run[1] = l_run[1] * corr[1] + psum[1];
+#pragma unroll
+            for (int i = 0; i < NDT; i++) {
+                o[i][0] *= corr[0];
+                o[i][1] *= corr[0];
+                o[i][2] *= corr[1];
+                o[i][3] *= corr[1];
+            }
+            uint32_t pa[4];
+            pa[0] = pack_half2(s[0][0], s[0][1]);
+            pa[1] = pack_half2(s[0][2], s[0][3]);
+            pa[2] = pack_half2(s[1][0], s[1][1]);
+            pa[3] = pack_half2(s[1][2], s[1][3]);
+#pragma unroll
+            for (int jd = 0; jd < KSTEPS; jd++) {
+                uint32_t r[4];
+                const int mi = lane >> 3;
+                ldsm_x4_trans(r, vt + (kw0 + (mi & 1) * 8 + (lane & 7)) * PITCH + 16 * jd + (mi >> 1) * 8);
+                mma16816(o[2 * jd], pa, r[0], r[1]);
+                mma16816(o[2 * jd + 1], pa, r[2], r[3]);
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- merge the 4 warps (each saw a different quarter of every tile) ----
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    float *so = reinterpret_cast<float *>(smem_raw);  // [4][16][D], reuses the K/V tiles
+    if (t == 0) {
+        sm_m[warp][g] = m_run[0];
+        sm_m[warp][g + 8] = m_run[1];
+        sm_l[warp][g] = l_run[0];
+        sm_l[warp][g + 8] = l_run[1];
+    }
+#pragma unroll
+    for (int i = 0; i < NDT; i++) {
+        float *base = so + (size_t)warp * 16 * D;
+        *reinterpret_cast<float2 *>(base + g * D + 8 * i + 2 * t) = make_float2(o[i][0], o[i][1]);
+        *reinterpret_cast<float2 *>(base + (g + 8) * D + 8 * i + 2 * t) = make_float2(o[i][2], o[i][3]);
+    }
+    __syncthreads();
+
+    // thread -> (row, D/8 consecutive dims)
+    constexpr int DPT = D / 8;
+    const int row = tid >> 3, d0 = (tid & 7) * DPT;
+    const int qi = qt * RQ + row / G, head = hk * G + row % G;
+    const bool row_valid = qi < p.I;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; w++) M = fmaxf(M, sm_m[w][row]);
+    float L = 0.f, acc[DPT];
+#pragma unroll
+    for (int j = 0; j < DPT; j++) acc[j] = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        const float wgt = sm_m[w][row] == -INFINITY ? 0.f : expf(sm_m[w][row] - M);
+        L += sm_l[w][row] * wgt;
+#pragma unroll
+        for (int j = 0; j < DPT; j++) acc[j] += so[((size_t)w * 16 + row) * D + d0 + j] * wgt;
+    }
+    const size_t out_row = (size_t)(b * p.I + (row_valid ? qi : 0)) * p.H + head;
+
+    if (p.nsplit == 1) {
+        if (row_valid) {
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+            for (int j = 0; j < DPT; j++) p.out[out_row * D + d0 + j] = __float2half_rn(acc[j] * inv);
+        }
+        return;
+    }
+
+    // ---- split keys: publish the partial, last CTA of the tile merges ----
+    if (row_valid) {
+        const size_t pi = out_row * p.nsplit + split;
+        if ((tid & 7) == 0) {
+            p.part_ml[pi * 2] = M;
+            p.part_ml[pi * 2 + 1] = L;
+        }
+#pragma unroll
+        for (int j = 0; j < DPT; j++) p.part_o[pi * D + d0 + j] = acc[j];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int *ctr = p.counters + ((size_t)b * p.q_tiles + qt) * p.Hkv + hk;
+        const int ticket = atomicAdd(ctr, 1);
+        sm_last = ticket == p.nsplit - 1;
+        if (sm_last) *ctr = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!sm_last) return;
+    __threadfence();
+    if (row_valid) {
+        float Mg = -INFINITY;
+        for (int sp = 0; sp < p.nsplit; sp++) Mg = fmaxf(Mg, __ldcg(&p.part_ml[(out_row * p.nsplit + sp) * 2]));
+        float Lg = 0.f;
+#pragma unroll
+        for (int j = 0; j < DPT; j++) acc[j] = 0.f;
+        for (int sp = 0; sp < p.nsplit; sp++) {
+            const size_t pi = out_row * p.nsplit + sp;
+            const float ms = __ldcg(&p.part_ml[pi * 2]);
+            const float wgt = ms == -INFINITY ? 0.f : expf(ms - Mg);
+            Lg += __ldcg(&p.part_ml[pi * 2 + 1]) * wgt;
+#pragma unroll
+            for (int j = 0; j < DPT; j++) acc[j] += __ldcg(&p.part_o[pi * D + d0 + j]) * wgt;
+        }
+        const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;
+#pragma unroll
+        for (int j = 0; j < DPT; j++) p.out[out_row * D + d0 + j] = __float2half_rn(acc[j] * inv);
+    }
+}
+
+// cache.append for the unfused surface: rows of K/V [m, Hkv*D] go to position
+// pos(row) of sequence seq(row).
+__global__ void kv_append_kernel(const __half *__restrict__ k, const __half *__restrict__ v,
+                                 __half *__restrict__ kc, __half *__restrict__ vc, int m, int row_elems,
+                                 int tmax, int pos_offset, const int *__restrict__ positions, int batched) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)m * row_elems) return;
+    const int r = (int)(i / row_elems), c = (int)(i % row_elems);
+    const int pos = positions ? positions[r] : pos_offset + (batched ? 0 : r);
+    const size_t seq = batched ? r : 0;
+    const size_t dst = (seq * tmax + pos) * row_elems + c;
+    kc[dst] = k[i];
+    vc[dst] = v[i];
+}
+
+}  // namespace
+
+// Host-side launcher shared by the ABI entry point and the decode runner.
+//   batch sequences, I queries each (I == 1 when positions_dev is given).
+//   nsplit_hint <= 0: choose from the key count; with positions_dev the key
+//   count is only known on the device, so max_keys bounds it.
+int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const void *q_dev, void *out_dev,
+                             int batch, int I, int n_heads, int q_pos0, const int *positions_dev, int max_keys,
+                             float scale) {
+    TLC_REQUIRE(cache && q_dev && out_dev, TLC_ERR_INVALID_OPERATION, "attention: null pointer");
+    TLC_REQUIRE(layer >= 0 && layer < cache->n_layers, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d",
+                layer, cache->n_layers);
+    TLC_REQUIRE(batch >= 1 && batch <= cache->max_batch, TLC_ERR_SHAPE_MISMATCH,
+                "attention: batch %d exceeds the cache's %d sequences", batch, cache->max_batch);
+    const int D = cache->head_dim, Hkv = cache->n_kv_heads;
+    TLC_REQUIRE(n_heads % Hkv == 0, TLC_ERR_SHAPE_MISMATCH, "attention: %d query heads over %d KV heads", n_heads,
+                Hkv);
+    const int G = n_heads / Hkv;
+    TLC_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8 || G == 16, TLC_ERR_INVALID_OPERATION,
+                "attention: group size %d unsupported (1, 2, 4, 8, 16)", G);
+    TLC_REQUIRE(D == 64 || D == 128, TLC_ERR_INVALID_OPERATION, "attention: head_dim %d unsupported (64, 128)", D);
+    TLC_REQUIRE(I >= 1 && (positions_dev == nullptr || I == 1), TLC_ERR_INVALID_OPERATION,
+                "attention: per-sequence positions need one query per sequence");
+    const int T = positions_dev ? max_keys : q_pos0 + I;
+    TLC_REQUIRE(T >= 1 && T <= cache->max_seq, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d", T,
+                cache->max_seq);
+
+    AttnParams p{};
+    p.q = static_cast<const __half *>(q_dev);
+    p.kc = cache->k + (size_t)layer * cache->layer_stride;
+    p.vc = cache->v + (size_t)layer * cache->layer_stride;
+    p.out = static_cast<__half *>(out_dev);
+    p.I = I;
+    p.H = n_heads;
+    p.Hkv = Hkv;
+    p.G = G;
+    p.Tmax = cache->max_seq;
+    p.q_pos0 = q_pos0;
+    p.positions = positions_dev;
+    p.scale = scale;
+    const int RQ = 16 / G;
+    p.q_tiles = (I + RQ - 1) / RQ;
+    // Decode: split the keys so that about two CTAs per SM are busy.
+    int nsplit = 1;
+    if (I == 1) {
+        const int tiles = (T + kTileKeys - 1) / kTileKeys;
+        const int want = (2 * ctx->sm_count + batch * Hkv - 1) / (batch * Hkv);
+        nsplit = tiles < want ? tiles : want;
+        if (nsplit < 1) nsplit = 1;
+        if (nsplit > 64) nsplit = 64;
+    }
+    p.nsplit = nsplit;
+    const int tiles_total = (T + kTileKeys - 1) / kTileKeys;
+    p.keys_per_split = ((tiles_total + nsplit - 1) / nsplit) * kTileKeys;
+    if (nsplit > 1) {
+        const size_t rows = (size_t)batch * I * n_heads;
+        const size_t ml = rows * nsplit * 2 * sizeof(float), po = rows * nsplit * D * sizeof(float);
+        // Ticket counters (one per tile, zero between launches: the merging
+        // CTA resets its own) live in a small zero-initialised context buffer.
+        TLC_REQUIRE((size_t)batch * p.q_tiles * Hkv <= ctx->n_tickets, TLC_ERR_INVALID_OPERATION,
+                    "attention: %d x %d tiles exceed the ticket area", batch, Hkv);
+        if (int32_t rc = tlc_scratch_reserve(ctx, ml + po)) return rc;
+        p.part_ml = static_cast<float *>(ctx->scratch);
+        p.part_o = reinterpret_cast<float *>(static_cast<uint8_t *>(ctx->scratch) + ml);
+        p.counters = ctx->tickets;
+    }
+    dim3 grid(p.q_tiles * nsplit, Hkv, batch);
+    const size_t smem = (size_t)4 * kTileKeys * (D + 8) * sizeof(__half);
+    const size_t smem_o = (size_t)4 * 16 * D * sizeof(float);
+    const size_t smem_bytes = smem > smem_o ? smem : smem_o;
+    if (D == 64) {
+        attention_kernel<64><<<grid, kAttnThreads, smem_bytes, ctx->stream>>>(p);
+    } else {
+        static bool configured[64] = {};
+        if (!configured[ctx->device & 63]) {
+            TLC_CUDA(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem_bytes));
+            configured[ctx->device & 63] = true;
+        }
+        attention_kernel<128><<<grid, kAttnThreads, smem_bytes, ctx->stream>>>(p);
+    }
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_kvcache_create(tlc_ctx *ctx, int32_t n_layers, int32_t max_batch, int32_t max_seq,
+                                      int32_t n_kv_heads, int32_t head_dim, tlc_kvcache **out) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(out, TLC_ERR_INVALID_OPERATION, "kvcache_create: null out pointer");
+    *out = nullptr;
+    TLC_REQUIRE(n_layers > 0 && max_batch > 0 && max_seq > 0 && n_kv_heads > 0 && head_dim > 0 && head_dim % 8 == 0,
+                TLC_ERR_INVALID_DIMENSION, "kvcache_create: bad shape");
+    tlc_kvcache *c = new tlc_kvcache();
+    c->ctx = ctx;
+    c->n_layers = n_layers;
+    c->max_batch = max_batch;
+    c->max_seq = max_seq;
+    c->n_kv_heads = n_kv_heads;
+    c->head_dim = head_dim;
+    c->layer_stride = (size_t)max_batch * max_seq * n_kv_heads * head_dim;
+    const size_t bytes = c->layer_stride * n_layers * sizeof(__half);
+    cudaError_t e = cudaMalloc(&c->k, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&c->v, bytes);
+    if (e == cudaSuccess) e = cudaMemsetAsync(c->k, 0, bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(c->v, 0, bytes, ctx->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        if (c->k) cudaFree(c->k);
+        if (c->v) cudaFree(c->v);
+        delete c;
+        return tlc_fail(TLC_ERR_ALLOCATION, "KV cache allocation of 2 x %zu bytes failed: %s", bytes,
+                        cudaGetErrorString(e));
+    }
+    *out = c;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_kvcache_destroy(tlc_kvcache *cache) {
+    if (!cache) return TLC_OK;
+    cudaSetDevice(cache->ctx->device);
+    cudaFree(cache->k);
+    cudaFree(cache->v);
+    delete cache;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_kvcache_layer_ptrs(tlc_kvcache *cache, int32_t layer, void **k_dev, void **v_dev) {
+    TLC_REQUIRE(cache && layer >= 0 && layer < cache->n_layers, TLC_ERR_INDEX, "kvcache: bad layer %d", layer);
+    if (k_dev) *k_dev = cache->k + (size_t)layer * cache->layer_stride;
+    if (v_dev) *v_dev = cache->v + (size_t)layer * cache->layer_stride;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_kvcache_append(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer, const void *k_dev,
+                                      const void *v_dev, int32_t m, int32_t pos_offset,
+                                      const int32_t *positions_dev) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(cache && k_dev && v_dev, TLC_ERR_INVALID_OPERATION, "kvcache_append: null pointer");
+    TLC_REQUIRE(layer >= 0 && layer < cache->n_layers, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d",
+                layer, cache->n_layers);
+    const bool batched = positions_dev != nullptr;
+    if (batched)
+        TLC_REQUIRE(m <= cache->max_batch, TLC_ERR_SHAPE_MISMATCH, "kvcache_append: %d rows for %d sequences", m,
+                    cache->max_batch);
+    else
+        TLC_REQUIRE(pos_offset >= 0 && pos_offset + m <= cache->max_seq, TLC_ERR_INDEX,
+                    "Index out of bounds: index %d, size %d", pos_offset + m, cache->max_seq);
+    if (m <= 0) return TLC_OK;
+    const int row_elems = cache->n_kv_heads * cache->head_dim;
+    const size_t total = (size_t)m * row_elems;
+    kv_append_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
+        static_cast<const __half *>(k_dev), static_cast<const __half *>(v_dev),
+        cache->k + (size_t)layer * cache->layer_stride, cache->v + (size_t)layer * cache->layer_stride, m, row_elems,
+        cache->max_seq, pos_offset, positions_dev, batched ? 1 : 0);
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_attention(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer, const void *q_dev,
+                                 void *out_dev, int32_t batch, int32_t n_queries, int32_t n_heads,
+                                 int32_t q_pos0, const int32_t *positions_dev, int32_t max_keys, float scale) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    return tlc_launch_attention(ctx, cache, layer, q_dev, out_dev, batch, n_queries, n_heads, q_pos0,
+                                positions_dev, max_keys, scale);
+}

@@ -59,14 +59,18 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaMalloc(&ctx->dev_status, sizeof(tlc_dev_status)) != cudaSuccess ||
         cudaMemset(ctx->dev_status, 0, sizeof(tlc_dev_status)) != cudaSuccess ||
+        cudaMalloc(&ctx->tickets, 16384 * sizeof(int)) != cudaSuccess ||
+        cudaMemset(ctx->tickets, 0, 16384 * sizeof(int)) != cudaSuccess ||
         cudaMallocHost(&ctx->host_status, sizeof(tlc_dev_status)) != cudaSuccess) {
         const char *msg = cudaGetErrorString(cudaGetLastError());
         if (ctx->stream) cudaStreamDestroy(ctx->stream);
         if (ctx->dev_status) cudaFree(ctx->dev_status);
+        if (ctx->tickets) cudaFree(ctx->tickets);
         delete ctx;
         return tlc_fail(TLC_ERR_CUDA, "context set-up failed: %s", msg);
     }
     memset(ctx->host_status, 0, sizeof(tlc_dev_status));
+    ctx->n_tickets = 16384;
     *out = ctx;
     return TLC_OK;
 }
@@ -79,6 +83,7 @@ extern "C" int32_t tlc_destroy(tlc_ctx *ctx) {
         for (void *p : kv.second) cudaFree(p);
     if (ctx->scratch) cudaFree(ctx->scratch);
     cudaFree(ctx->dev_status);
+    cudaFree(ctx->tickets);
     cudaFreeHost(ctx->host_status);
     cudaStreamDestroy(ctx->stream);
     delete ctx;

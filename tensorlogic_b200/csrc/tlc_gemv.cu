@@ -34,7 +34,8 @@
 namespace {
 
 constexpr int kRows = 16;           // rows of W per slab (the M of m16n8k16)
-constexpr int kConsumerWarps = 4;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kWaitLimit = 1u << 22;
@@ -68,6 +69,8 @@ struct GemvTensor {
     __half *y;
     int rope_heads;
     int head_dim;
+    long long row_stride;  // elements between the outputs of consecutive activation rows
+    long long pos_stride;  // elements per position (0 unless the destination is a KV cache)
 };
 
 struct GemvParams {
@@ -142,7 +145,9 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         "l"(src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
-__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void consumer_bar() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
 
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
                                          const float (&c)[4]) {
@@ -235,18 +240,8 @@ __device__ __forceinline__ void load_pair(const uint32_t *seg, int p, int t, uin
     }
 }
 
-__device__ __forceinline__ float normed(const __half *x, const __half *norm_w, float inv, int k, bool do_norm) {
-    float v = __half2float(x[k]);
-    if (do_norm) {
-        // f16((x * inv) * w): two separately rounded f32 multiplies, then RNE
-        // (Tensor::rms_norm_cpu, src/ops/normalization.rs:236-240).
-        v = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v, inv), __half2float(norm_w[k]))));
-    }
-    return v;
-}
-
 template <int QT, int NT>
-__global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams p) {
     using T = QTraits<QT>;
     constexpr int MP = 8 * NT;  // padded activation rows
     constexpr int PITCH = stage_pitch(T::KCB * T::BB);
@@ -319,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
     }
 
     // -------------------------------- consumers --------------------------------
-    const int ctid = tid;  // 0..127
+    const int ctid = tid;  // 0..kConsumerThreads-1
     const bool do_norm = p.norm_w != nullptr;
 
     // (a) RMS statistics: warp w owns activation rows w, w+4, ...
@@ -340,7 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
             }
         }
     }
-    for (int i = ctid; i < p.nblk_pad * MP; i += 128) xs8[i] = 0.f;
+    for (int i = ctid; i < p.nblk_pad * MP; i += kConsumerThreads) xs8[i] = 0.f;
     consumer_bar();
 
     // (b) activations into fragment order + per-block sums.  Item = (block b,
@@ -348,9 +343,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
     // lanes, so a 2-step shuffle gives the block sum.
     {
         const int items = p.nblk_pad * p.m * 4;
-        const int rounds = (items + 127) / 128;
+        const int rounds = (items + kConsumerThreads - 1) / kConsumerThreads;
         for (int r = 0; r < rounds; r++) {
-            const int idx = ctid + r * 128;
+            const int idx = ctid + r * kConsumerThreads;
             const bool live = idx < items;
             const int t = idx & 3;
             const int bm = idx >> 2;
@@ -360,17 +355,42 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
 #pragma unroll
             for (int j = 0; j < 8; j++) v[j] = 0.f;
             if (live && b < p.nblk) {
-                const __half *xr = p.x + (size_t)m * p.k;
+                // Fragment order of the 8 activations this lane supplies for block b:
+                //   Q4_0: {4t, 4t+2, 16+4t, 18+4t | 4t+1, 4t+3, 17+4t, 19+4t}
+                //   Q8_0: {8t .. 8t+7}
+                const __half *xr = p.x + (size_t)m * p.k + b * 32;
                 const float inv = do_norm ? inv_rms[m] : 1.f;
-                const int k0 = b * 32;
+                __half raw[8], nw[8];
                 if (QT == TLC_TYPE_Q4_0) {
-                    const int idxs[8] = {4 * t, 4 * t + 2, 16 + 4 * t, 18 + 4 * t,
-                                         4 * t + 1, 4 * t + 3, 17 + 4 * t, 19 + 4 * t};
+                    *reinterpret_cast<uint2 *>(&raw[0]) = *reinterpret_cast<const uint2 *>(xr + 4 * t);
+                    *reinterpret_cast<uint2 *>(&raw[4]) = *reinterpret_cast<const uint2 *>(xr + 16 + 4 * t);
+                    if (do_norm) {
+                        const __half *wr = p.norm_w + b * 32;
+                        *reinterpret_cast<uint2 *>(&nw[0]) = *reinterpret_cast<const uint2 *>(wr + 4 * t);
+                        *reinterpret_cast<uint2 *>(&nw[4]) = *reinterpret_cast<const uint2 *>(wr + 16 + 4 * t);
+                    }
+                } else {
+                    *reinterpret_cast<uint4 *>(&raw[0]) = *reinterpret_cast<const uint4 *>(xr + 8 * t);
+                    if (do_norm)
+                        *reinterpret_cast<uint4 *>(&nw[0]) =
+                            *reinterpret_cast<const uint4 *>(p.norm_w + b * 32 + 8 * t);
+                }
+                float f[8];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) v[j] = normed(xr, p.norm_w, inv, k0 + idxs[j], do_norm);
+                for (int j = 0; j < 8; j++) {
+                    f[j] = __half2float(raw[j]);
+                    // f16((x * inv) * w): two separately rounded f32 multiplies, then RNE
+                    // (Tensor::rms_norm_cpu, src/ops/normalization.rs:236-240).
+                    if (do_norm)
+                        f[j] = __half2float(
+                            __float2half_rn(__fmul_rn(__fmul_rn(f[j], inv), __half2float(nw[j]))));
+                }
+                if (QT == TLC_TYPE_Q4_0) {
+                    v[0] = f[0]; v[1] = f[2]; v[2] = f[4]; v[3] = f[6];
+                    v[4] = f[1]; v[5] = f[3]; v[6] = f[5]; v[7] = f[7];
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) v[j] = normed(xr, p.norm_w, inv, k0 + 8 * t + j, do_norm);
+                    for (int j = 0; j < 8; j++) v[j] = f[j];
                 }
             }
             float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
@@ -397,9 +417,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
     const int g = lane >> 2, t = lane & 3;
     uint32_t it = 0;
     int slab_count = 0;
-    __half hold[NT];  // gate value kept between the two slabs of a gate/up unit
-#pragma unroll
-    for (int i = 0; i < NT; i++) hold[i] = __float2half(0.f);
+    __half hold[1] = {__float2half(0.f)};  // gate value kept between the two slabs of a gate/up unit
 
     for (int unit = blockIdx.x; unit < p.total_units; unit += gridDim.x) {
         for (int sub = 0; sub < p.subs; sub++, slab_count++) {
@@ -473,9 +491,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
                 mine[(g + 8) * MP + nt * 8 + 2 * t + 1] = acc[nt * 4 + 3];
             }
             consumer_bar();
-#pragma unroll
-            for (int oi = 0; oi < NT; oi++) {
-                const int o = ctid + oi * 128;
+            if (ctid < kRows * MP) {
+                const int oi = 0;
+                const int o = ctid;
                 const int col = o >> 4, row = o & 15;
                 const int n = sl * kRows + row;
                 auto total = [&](int r_) {
@@ -486,7 +504,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
                 };
                 if (col < p.m && n < gt.n) {
                     __half h = __float2half_rn(total(row));
-                    const size_t oidx = (size_t)col * gt.n + n;
+                    const size_t oidx = (size_t)col * gt.n + n;  // dense [m, N] index (residual, act)
+                    const int pos = p.positions ? p.positions[col] : p.pos_offset + col;
+                    // Where this output goes: dense rows by default; a KV-cache destination
+                    // addresses rows by (sequence, position) instead.
+                    const size_t yidx = (size_t)((long long)col * gt.row_stride + (long long)pos * gt.pos_stride) + n;
                     if (gt.rope_heads > 0) {
                         // Interleaved RoPE on the f16-rounded projection
                         // (rope_f16, shaders/unified.metal:2355-2417).
@@ -495,16 +517,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
                         const int pair = dim >> 1;
                         const float x0 = __half2float((dim & 1) ? hp : h);
                         const float x1 = __half2float((dim & 1) ? h : hp);
-                        const int pos = p.positions ? p.positions[col] : p.pos_offset + col;
                         const float exponent = (float)(2 * pair) / (float)gt.head_dim;
                         const float freq = 1.0f / powf(p.rope_base, exponent);
                         const float theta = (float)(unsigned)pos * freq;
                         const float cs = cosf(theta), sn = sinf(theta);
                         const float r = (dim & 1) ? __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs))
                                                   : __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
-                        gt.y[oidx] = __float2half_rn(r);
+                        gt.y[yidx] = __float2half_rn(r);
                     } else if (p.epilogue == TLC_EPI_RESIDUAL) {
-                        gt.y[oidx] = __hadd(h, p.residual[oidx]);
+                        gt.y[yidx] = __hadd(h, p.residual[oidx]);
                     } else if (p.epilogue == TLC_EPI_SWIGLU) {
                         if (sub == 0) {
                             hold[oi] = h;
@@ -518,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvParams 
                         }
                     } else {
                         if (p.bias) h = __hadd(h, p.bias[n]);
-                        gt.y[oidx] = h;
+                        gt.y[yidx] = h;
                     }
                 }
             }
@@ -586,10 +607,17 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p, size_t smem_fixed) {
     const size_t budget = (size_t)ctx->prop.sharedMemPerBlockOptin;
     TLC_REQUIRE(smem_fixed + 2 * STAGE_BYTES <= budget, TLC_ERR_INVALID_OPERATION,
                 "gemv: activations of %d x %d do not fit in shared memory", p.m, p.k);
-    int grid = p.total_units < ctx->sm_count ? p.total_units : ctx->sm_count;
+    // Two CTAs per SM (16 consumer warps hide the shared-memory and MMA latency
+    // of the unpack loop) whenever the activations leave room for at least
+    // three ring stages in half of the SM's shared memory.
+    const size_t half = (size_t)ctx->prop.sharedMemPerMultiprocessor / 2 - 1024;
+    const bool two = smem_fixed + 3 * STAGE_BYTES <= half;
+    const size_t cap = two ? half : budget;
+    const int max_ctas = two ? 2 * ctx->sm_count : ctx->sm_count;
+    int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
     // No more stages than this CTA will ever fill.
     long per_cta = ((long)(p.total_units + grid - 1) / grid) * p.subs * p.nchunks;
-    int stages = (int)((budget - smem_fixed) / STAGE_BYTES);
+    int stages = (int)((cap - smem_fixed) / STAGE_BYTES);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages > per_cta) stages = per_cta < 2 ? 2 : (int)per_cta;
     p.nstages = stages;
@@ -682,7 +710,10 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
             p.t[i].pitch = w->row_pitch;
             p.t[i].n = (int)w->n_rows;
             // Outputs are [m, N] row-major: a pass over rows m0.. writes at y + m0*N.
-            p.t[i].y = static_cast<__half *>(a.outs[i].y) + (size_t)m0 * w->n_rows;
+            const long long rs = a.outs[i].row_stride >= 0 ? a.outs[i].row_stride : (long long)w->n_rows;
+            p.t[i].row_stride = rs;
+            p.t[i].pos_stride = a.outs[i].pos_stride;
+            p.t[i].y = static_cast<__half *>(a.outs[i].y) + (size_t)m0 * rs;
             p.t[i].rope_heads = a.outs[i].rope_heads;
             p.t[i].head_dim = a.outs[i].rope_heads > 0 ? (int)(w->n_rows / a.outs[i].rope_heads) : 0;
             p.slabs[i] = (int)((w->n_rows + kRows - 1) / kRows);

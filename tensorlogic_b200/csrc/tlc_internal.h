@@ -39,6 +39,10 @@ struct tlc_ctx {
     // Reusable scratch for kernels that need global workspace (grows on demand).
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
+    // Zero-initialised ticket counters for kernels whose last CTA merges
+    // partial results; every user leaves them at zero again.
+    int *tickets = nullptr;
+    size_t n_tickets = 0;
 };
 
 struct tlc_buf {
@@ -104,6 +108,11 @@ struct tlc_gemv_out {
     const tlc_qtensor *w;
     void *y;             // f16 [m, N]
     int32_t rope_heads;  // >0: apply rope over [m, heads, N/heads]
+    // Output addressing: element (row r, output n) lands at
+    //   y[r * row_stride + pos(r) * pos_stride + n],
+    // pos(r) = positions[r] or pos_offset + r.  Defaults give dense [m, N].
+    int64_t row_stride = -1;  // < 0: N
+    int64_t pos_stride = 0;
 };
 
 enum tlc_gemv_epilogue {
@@ -128,3 +137,8 @@ struct tlc_gemv_args {
 };
 
 int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a);
+
+struct tlc_kvcache;
+int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const void *q_dev, void *out_dev,
+                             int batch, int n_queries, int n_heads, int q_pos0, const int *positions_dev,
+                             int max_keys, float scale);

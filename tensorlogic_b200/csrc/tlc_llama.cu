@@ -1,0 +1,461 @@
+// LLaMA-architecture forward pass over quantized-resident weights.
+//
+// The reference has no compiled model: LlamaModel::forward is a stub
+// (src/model/llama.rs:257-266) and the forward pass is a TL script that calls
+// builtins one by one (debug/chat_demo_with_kvcache.tl:136-181 prefill,
+// :213-296 decode), about 28 dispatches per layer plus a host read-back of all
+// logits per token (src/interpreter/builtin_sampling.rs:131-140).  This runner
+// executes the same sequence of operations with 5 launches per layer:
+//
+//   [rms_norm + q/k/v linears + rope(q), rope(k) + cache append]   1 launch
+//   [grouped-query attention over the cache]                        1 launch
+//   [o projection + residual add]                                   1 launch
+//   [rms_norm + gate/up linears + silu*mul]                         1 launch
+//   [down projection + residual add]                                1 launch
+//
+// then [rms_norm + lm_head] and an on-device greedy sample.  Token ids,
+// positions and the sampled token live in device memory, so a decode step has
+// no host-dependent kernel argument and is replayed as a CUDA graph.
+// RoPE takes the true position of every token (the reference's decode branch
+// calls rope() with its default offset 0, chat_demo_with_kvcache.tl:236,:244).
+#include <cmath>
+#include <cstring>
+#include <memory>
+
+#include "tlc_internal.h"
+
+struct tlc_kvcache;
+extern "C" int32_t tlc_kvcache_create(tlc_ctx *, int32_t, int32_t, int32_t, int32_t, int32_t, tlc_kvcache **);
+extern "C" int32_t tlc_kvcache_destroy(tlc_kvcache *);
+extern "C" int32_t tlc_kvcache_layer_ptrs(tlc_kvcache *, int32_t, void **, void **);
+struct tlc_model;
+extern "C" int32_t tlc_model_get(tlc_model *, const char *, tlc_qtensor **);
+
+struct LayerWeights {
+    tlc_qtensor *attn_norm, *wq, *wk, *wv, *wo, *ffn_norm, *w_gate, *w_up, *w_down;
+};
+
+struct tlc_llama {
+    tlc_ctx *ctx;
+    tlc_llama_config cfg;
+    std::vector<LayerWeights> layers;
+    tlc_qtensor *tok_embd, *out_norm, *out_w;
+    tlc_kvcache *cache;
+    int max_rows;  // rows of the activation buffers
+    __half *x, *x1, *q, *attn, *act, *logits;
+    int32_t *ids, *positions, *next_ids;
+    int32_t *host_ids;  // pinned staging
+    int32_t *host_next;
+    cudaGraphExec_t graph[65];  // decode graph per batch size
+    int launches_per_step = 0;
+    int heads_local, kv_heads_local, ffn_local, vocab_local;
+};
+
+namespace {
+
+__global__ void embed_kernel(const uint8_t *__restrict__ table, size_t pitch, int vocab, int d,
+                             const int *__restrict__ ids, int m, __half *__restrict__ y) {
+    const int vec = d >> 3;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)m * vec) return;
+    const int r = (int)(i / vec), c = (int)(i % vec);
+    int id = ids[r];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; never read outside
+    reinterpret_cast<uint4 *>(y + (size_t)r * d)[c] = reinterpret_cast<const uint4 *>(table + (size_t)id * pitch)[c];
+}
+
+// Greedy sample + step bookkeeping, one CTA per sequence.  Ties go to the LAST
+// maximal index, like Iterator::max_by in temperature_sample's greedy arm
+// (src/interpreter/builtin_sampling.rs:176-181).  Also feeds the sampled token
+// back as the next input and advances the sequence position.
+__global__ void argmax_advance_kernel(const __half *__restrict__ logits, int vocab, int *__restrict__ next_ids,
+                                      int *__restrict__ ids, int *__restrict__ positions, int advance) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int b = blockIdx.x;
+    const __half *row = logits + (size_t)b * vocab;
+    float best = -INFINITY;
+    int bi = -1;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = __half2float(row[i]);
+        if (bi < 0 || !(v < best)) {  // v >= best (or unordered): later index wins
+            best = v;
+            bi = i;
+        }
+    }
+    auto better = [](float v, int i, float bv, int bidx) {
+        if (bidx < 0) return true;
+        if (i < 0) return false;
+        if (v > bv) return true;
+        if (v < bv) return false;
+        return i > bidx;
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, best, bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = best;
+        si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nw = blockDim.x >> 5;
+        best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < nw ? si[threadIdx.x] : -1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, best, bi)) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (threadIdx.x == 0) {
+            next_ids[b] = bi;
+            if (advance) {
+                ids[b] = bi;
+                positions[b] += 1;
+            }
+        }
+    }
+}
+
+int32_t get(tlc_model *m, const std::string &name, tlc_qtensor **out) { return tlc_model_get(m, name.c_str(), out); }
+
+}  // namespace
+
+extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_llama_config *cfg, tlc_llama **out) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(model && cfg && out, TLC_ERR_INVALID_OPERATION, "llama_create: null pointer");
+    *out = nullptr;
+    const tlc_llama_config &c = *cfg;
+    TLC_REQUIRE(c.n_layers > 0 && c.d_model > 0 && c.n_heads > 0 && c.n_kv_heads > 0 && c.head_dim > 0 &&
+                    c.ffn_dim > 0 && c.vocab > 0 && c.max_seq > 0 && c.max_batch > 0 && c.max_batch <= 64,
+                TLC_ERR_INVALID_DIMENSION, "llama_create: bad configuration");
+    const int tp = c.tp_size < 1 ? 1 : c.tp_size;
+    TLC_REQUIRE(c.n_heads % c.n_kv_heads == 0 && c.n_heads % tp == 0 && c.n_kv_heads % tp == 0 && c.ffn_dim % tp == 0,
+                TLC_ERR_SHAPE_MISMATCH, "heads %d / kv heads %d / ffn %d do not divide over %d ranks", c.n_heads,
+                c.n_kv_heads, c.ffn_dim, tp);
+    std::unique_ptr<tlc_llama> L(new tlc_llama());
+    memset(L->graph, 0, sizeof(L->graph));
+    L->ctx = ctx;
+    L->cfg = c;
+    L->cfg.tp_size = tp;
+    L->heads_local = c.n_heads / tp;
+    L->kv_heads_local = c.n_kv_heads / tp;
+    L->ffn_local = c.ffn_dim / tp;
+    L->layers.resize(c.n_layers);
+    auto expect = [&](tlc_qtensor *t, int64_t rows, int64_t cols, const std::string &name) -> int32_t {
+        TLC_REQUIRE(t->n_rows == rows && t->n_cols == cols, TLC_ERR_SHAPE_MISMATCH,
+                    "tensor '%s' is [%lld, %lld], expected [%lld, %lld]", name.c_str(), (long long)t->n_rows,
+                    (long long)t->n_cols, (long long)rows, (long long)cols);
+        return TLC_OK;
+    };
+    const int64_t d = c.d_model, qd = (int64_t)L->heads_local * c.head_dim, kvd = (int64_t)L->kv_heads_local * c.head_dim;
+    for (int l = 0; l < c.n_layers; l++) {
+        const std::string p = "blk." + std::to_string(l) + ".";
+        LayerWeights &w = L->layers[l];
+        struct { tlc_qtensor **t; const char *n; int64_t r, cc; } want[] = {
+            {&w.attn_norm, "attn_norm.weight", 1, d},   {&w.wq, "attn_q.weight", qd, d},
+            {&w.wk, "attn_k.weight", kvd, d},           {&w.wv, "attn_v.weight", kvd, d},
+            {&w.wo, "attn_output.weight", d, qd},       {&w.ffn_norm, "ffn_norm.weight", 1, d},
+            {&w.w_gate, "ffn_gate.weight", L->ffn_local, d}, {&w.w_up, "ffn_up.weight", L->ffn_local, d},
+            {&w.w_down, "ffn_down.weight", d, L->ffn_local}};
+        for (auto &e : want) {
+            if (int32_t rc = get(model, p + e.n, e.t)) return rc;
+            if (int32_t rc = expect(*e.t, e.r, e.cc, p + e.n)) return rc;
+        }
+        TLC_REQUIRE(w.attn_norm->type == TLC_TYPE_F16 && w.ffn_norm->type == TLC_TYPE_F16, TLC_ERR_LOAD,
+                    "norm weights of layer %d must be f16/f32", l);
+    }
+    if (int32_t rc = get(model, "token_embd.weight", &L->tok_embd)) return rc;
+    if (int32_t rc = get(model, "output_norm.weight", &L->out_norm)) return rc;
+    if (int32_t rc = get(model, "output.weight", &L->out_w)) return rc;
+    TLC_REQUIRE(L->tok_embd->type == TLC_TYPE_F16 && L->tok_embd->n_cols == d && d % 8 == 0, TLC_ERR_LOAD,
+                "token_embd.weight must be f16 [vocab, %lld]", (long long)d);
+    TLC_REQUIRE(c.vocab % tp == 0, TLC_ERR_SHAPE_MISMATCH, "vocab %d does not divide over %d ranks", c.vocab, tp);
+    L->vocab_local = c.vocab / tp;
+    if (int32_t rc = expect(L->out_w, L->vocab_local, d, "output.weight")) return rc;
+    if (int32_t rc = expect(L->out_norm, 1, d, "output_norm.weight")) return rc;
+
+    if (int32_t rc = tlc_kvcache_create(ctx, c.n_layers, c.max_batch, c.max_seq, L->kv_heads_local, c.head_dim, &L->cache))
+        return rc;
+    L->max_rows = c.max_prefill > c.max_batch ? c.max_prefill : c.max_batch;
+    if (L->max_rows < 16) L->max_rows = 16;
+    const size_t R = (size_t)L->max_rows;
+    const size_t logits_rows = (size_t)(c.max_batch > 1 ? c.max_batch : 1);
+    struct { void **p; size_t bytes; } bufs[] = {
+        {(void **)&L->x, R * d * 2},      {(void **)&L->x1, R * d * 2},          {(void **)&L->q, R * qd * 2},
+        {(void **)&L->attn, R * qd * 2},  {(void **)&L->act, R * L->ffn_local * 2},
+        {(void **)&L->logits, (c.logits_all_rows ? R : logits_rows) * L->vocab_local * 2},
+        {(void **)&L->ids, R * 4},        {(void **)&L->positions, 64 * 4},      {(void **)&L->next_ids, 64 * 4}};
+    for (auto &b : bufs) {
+        cudaError_t e = cudaMalloc(b.p, b.bytes);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return tlc_fail(TLC_ERR_ALLOCATION, "activation buffer of %zu bytes failed: %s", b.bytes, cudaGetErrorString(e));
+        }
+    }
+    TLC_CUDA(cudaMemsetAsync(L->positions, 0, 64 * 4, ctx->stream));
+    TLC_CUDA(cudaMallocHost(&L->host_ids, R * 4));
+    TLC_CUDA(cudaMallocHost(&L->host_next, 64 * 4));
+    *out = L.release();
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_llama_destroy(tlc_llama *L) {
+    if (!L) return TLC_OK;
+    cudaSetDevice(L->ctx->device);
+    cudaStreamSynchronize(L->ctx->stream);
+    for (auto &g : L->graph)
+        if (g) cudaGraphExecDestroy(g);
+    tlc_kvcache_destroy(L->cache);
+    void *bufs[] = {L->x, L->x1, L->q, L->attn, L->act, L->logits, L->ids, L->positions, L->next_ids};
+    for (void *b : bufs) cudaFree(b);
+    cudaFreeHost(L->host_ids);
+    cudaFreeHost(L->host_next);
+    delete L;
+    return TLC_OK;
+}
+
+// Enqueues one forward pass over m activation rows whose token ids are already
+// in L->ids.  decode == false: the rows are consecutive tokens of sequence 0
+// starting at pos0 (prefill).  decode == true: row r is the next token of
+// sequence r at L->positions[r].
+static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logits, bool sample, bool advance) {
+    tlc_ctx *ctx = L->ctx;
+    const tlc_llama_config &c = L->cfg;
+    TLC_REQUIRE(c.tp_size == 1, TLC_ERR_INVALID_OPERATION,
+                "this build of the runner executes single-GPU models only (tp_size = %d)", c.tp_size);
+    const int d = c.d_model, D = c.head_dim;
+    const int64_t kv_row = (int64_t)L->kv_heads_local * D;
+    {
+        const size_t total = (size_t)m * (d / 8);
+        embed_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
+            static_cast<const uint8_t *>(L->tok_embd->data), L->tok_embd->row_pitch, (int)L->tok_embd->n_rows, d,
+            L->ids, m, L->x);
+        TLC_CHECK_LAUNCH(ctx);
+    }
+    const int *positions = decode ? L->positions : nullptr;
+    const float scale = 1.0f / sqrtf((float)D);
+    for (int l = 0; l < c.n_layers; l++) {
+        const LayerWeights &w = L->layers[l];
+        void *kc = nullptr, *vc = nullptr;
+        tlc_kvcache_layer_ptrs(L->cache, l, &kc, &vc);
+        {
+            tlc_gemv_args a;
+            a.n_out = 3;
+            a.outs[0] = {w.wq, L->q, L->heads_local};
+            a.outs[1] = {w.wk, kc, L->kv_heads_local};
+            a.outs[2] = {w.wv, vc, 0};
+            for (int i = 1; i < 3; i++) {
+                a.outs[i].row_stride = decode ? (int64_t)c.max_seq * kv_row : 0;
+                a.outs[i].pos_stride = kv_row;
+            }
+            a.x = L->x;
+            a.m = m;
+            a.norm_w = w.attn_norm->data;
+            a.eps = c.rms_eps;
+            a.pos_offset = pos0;
+            a.rope_base = c.rope_base;
+            a.positions = positions;
+            if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+        }
+        if (int32_t rc = tlc_launch_attention(ctx, L->cache, l, L->q, L->attn, decode ? m : 1, decode ? 1 : m,
+                                              L->heads_local, pos0, positions, c.max_seq, scale))
+            return rc;
+        {
+            tlc_gemv_args a;
+            a.n_out = 1;
+            a.outs[0] = {w.wo, L->x1, 0};
+            a.x = L->attn;
+            a.m = m;
+            a.epilogue = TLC_EPI_RESIDUAL;
+            a.residual = L->x;
+            if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+        }
+        {
+            tlc_gemv_args a;
+            a.n_out = 2;
+            a.outs[0] = {w.w_gate, L->act, 0};
+            a.outs[1] = {w.w_up, L->act, 0};
+            a.x = L->x1;
+            a.m = m;
+            a.norm_w = w.ffn_norm->data;
+            a.eps = c.rms_eps;
+            a.epilogue = TLC_EPI_SWIGLU;
+            if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+        }
+        {
+            tlc_gemv_args a;
+            a.n_out = 1;
+            a.outs[0] = {w.w_down, L->x, 0};
+            a.x = L->act;
+            a.m = m;
+            a.epilogue = TLC_EPI_RESIDUAL;
+            a.residual = L->x1;
+            if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+        }
+    }
+    {
+        // Logits: every row for a batched decode step, otherwise only the last
+        // prompt token (all rows on request, for parity checks).
+        const int rows = (decode || all_logits) ? m : 1;
+        tlc_gemv_args a;
+        a.n_out = 1;
+        a.outs[0] = {L->out_w, L->logits, 0};
+        a.x = L->x + (size_t)(m - rows) * d;
+        a.m = rows;
+        a.norm_w = L->out_norm->data;
+        a.eps = c.rms_eps;
+        if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+        if (sample) {
+            const int srows = decode ? m : 1;
+            const __half *lg = L->logits + (size_t)(rows - srows) * L->vocab_local;
+            argmax_advance_kernel<<<srows, 1024, 0, ctx->stream>>>(lg, L->vocab_local, L->next_ids, L->ids,
+                                                                   L->positions, advance ? 1 : 0);
+            TLC_CHECK_LAUNCH(ctx);
+        }
+    }
+    return TLC_OK;
+}
+
+static int32_t check_ids(const tlc_llama *L, const int32_t *ids, int n) {
+    for (int i = 0; i < n; i++)
+        TLC_REQUIRE(ids[i] >= 0 && ids[i] < L->cfg.vocab, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d",
+                    ids[i], L->cfg.vocab);
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_llama_prefill(tlc_llama *L, const int32_t *ids_host, int32_t n, int32_t pos0,
+                                     void *logits_host, int32_t all_rows, int32_t *next_id_host) {
+    TLC_REQUIRE(L && ids_host, TLC_ERR_INVALID_OPERATION, "llama_prefill: null pointer");
+    if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    TLC_REQUIRE(n >= 1 && n <= L->max_rows, TLC_ERR_SHAPE_MISMATCH, "prefill of %d tokens (buffers hold %d)", n,
+                L->max_rows);
+    TLC_REQUIRE(pos0 >= 0 && pos0 + n <= L->cfg.max_seq, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d",
+                pos0 + n, L->cfg.max_seq);
+    TLC_REQUIRE(!all_rows || L->cfg.logits_all_rows, TLC_ERR_INVALID_OPERATION,
+                "all-row logits need logits_all_rows in the configuration");
+    if (int32_t rc = check_ids(L, ids_host, n)) return rc;
+    memcpy(L->host_ids, ids_host, (size_t)n * 4);
+    TLC_CUDA(cudaMemcpyAsync(L->ids, L->host_ids, (size_t)n * 4, cudaMemcpyHostToDevice, L->ctx->stream));
+    if (int32_t rc = forward(L, n, false, pos0, all_rows != 0, true, false)) return rc;
+    // Sequence 0 continues after the prompt with the sampled token.
+    const int32_t next_pos = pos0 + n;
+    L->host_next[32] = next_pos;
+    TLC_CUDA(cudaMemcpyAsync(L->positions, &L->host_next[32], 4, cudaMemcpyHostToDevice, L->ctx->stream));
+    TLC_CUDA(cudaMemcpyAsync(L->ids, L->next_ids, 4, cudaMemcpyDeviceToDevice, L->ctx->stream));
+    const int rows = all_rows ? n : 1;
+    if (logits_host)
+        TLC_CUDA(cudaMemcpyAsync(logits_host, L->logits, (size_t)rows * L->vocab_local * 2, cudaMemcpyDeviceToHost,
+                                 L->ctx->stream));
+    TLC_CUDA(cudaMemcpyAsync(L->host_next, L->next_ids, 4, cudaMemcpyDeviceToHost, L->ctx->stream));
+    if (int32_t rc = tlc_synchronize(L->ctx)) return rc;
+    if (next_id_host) *next_id_host = L->host_next[0];
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_llama_set_state(tlc_llama *L, int32_t batch, const int32_t *ids_host,
+                                       const int32_t *positions_host) {
+    TLC_REQUIRE(L && ids_host && positions_host, TLC_ERR_INVALID_OPERATION, "llama_set_state: null pointer");
+    if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    TLC_REQUIRE(batch >= 1 && batch <= L->cfg.max_batch, TLC_ERR_SHAPE_MISMATCH, "batch %d (max %d)", batch,
+                L->cfg.max_batch);
+    if (int32_t rc = check_ids(L, ids_host, batch)) return rc;
+    for (int i = 0; i < batch; i++)
+        TLC_REQUIRE(positions_host[i] >= 0 && positions_host[i] < L->cfg.max_seq, TLC_ERR_INDEX,
+                    "Index out of bounds: index %d, size %d", positions_host[i], L->cfg.max_seq);
+    TLC_CUDA(cudaStreamSynchronize(L->ctx->stream));  // earlier steps may still read ids/positions
+    TLC_CUDA(cudaMemcpy(L->ids, ids_host, (size_t)batch * 4, cudaMemcpyHostToDevice));
+    TLC_CUDA(cudaMemcpy(L->positions, positions_host, (size_t)batch * 4, cudaMemcpyHostToDevice));
+    return TLC_OK;
+}
+
+// Enqueues `steps` greedy decode steps for `batch` sequences (graph replay);
+// nothing is read back.
+extern "C" int32_t tlc_llama_decode_enqueue(tlc_llama *L, int32_t batch, int32_t steps) {
+    TLC_REQUIRE(L, TLC_ERR_INVALID_OPERATION, "llama_decode: null handle");
+    if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    TLC_REQUIRE(batch >= 1 && batch <= L->cfg.max_batch, TLC_ERR_SHAPE_MISMATCH, "batch %d (max %d)", batch,
+                L->cfg.max_batch);
+    tlc_ctx *ctx = L->ctx;
+    if (!L->graph[batch] && !L->cfg.no_graph) {
+        // Warm every kernel configuration (function attributes, scratch growth)
+        // outside the capture, on a throw-away step that does not advance.
+        if (int32_t rc = forward(L, batch, true, 0, false, true, false)) return rc;
+        TLC_CUDA(cudaStreamSynchronize(ctx->stream));
+        const uint64_t launches_before = ctx->launches;
+        TLC_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        int32_t rc = forward(L, batch, true, 0, false, true, true);
+        cudaGraph_t g = nullptr;
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+        L->launches_per_step = (int)(ctx->launches - launches_before);
+        ctx->launches = launches_before;
+        if (rc) {
+            if (g) cudaGraphDestroy(g);
+            return rc;
+        }
+        if (e != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+        e = cudaGraphInstantiate(&L->graph[batch], g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+    }
+    for (int s = 0; s < steps; s++) {
+        if (L->cfg.no_graph) {
+            if (int32_t rc = forward(L, batch, true, 0, false, true, true)) return rc;
+        } else {
+            TLC_CUDA(cudaGraphLaunch(L->graph[batch], ctx->stream));
+            ctx->launches += (uint64_t)L->launches_per_step;
+        }
+    }
+    return TLC_OK;
+}
+
+// One decode step through host buffers: uploads the token ids (NULL: continue
+// with the tokens sampled by the previous step), runs the step, and returns the
+// sampled tokens and, on request, the logits [batch, vocab].
+extern "C" int32_t tlc_llama_decode_host(tlc_llama *L, int32_t batch, const int32_t *ids_host,
+                                         int32_t *next_ids_host, void *logits_host) {
+    TLC_REQUIRE(L && next_ids_host, TLC_ERR_INVALID_OPERATION, "llama_decode_host: null pointer");
+    if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    TLC_REQUIRE(batch >= 1 && batch <= L->cfg.max_batch, TLC_ERR_SHAPE_MISMATCH, "batch %d (max %d)", batch,
+                L->cfg.max_batch);
+    if (ids_host) {
+        if (int32_t rc = check_ids(L, ids_host, batch)) return rc;
+        memcpy(L->host_ids, ids_host, (size_t)batch * 4);
+        TLC_CUDA(cudaMemcpyAsync(L->ids, L->host_ids, (size_t)batch * 4, cudaMemcpyHostToDevice, L->ctx->stream));
+    }
+    if (int32_t rc = tlc_llama_decode_enqueue(L, batch, 1)) return rc;
+    if (logits_host)
+        TLC_CUDA(cudaMemcpyAsync(logits_host, L->logits, (size_t)batch * L->vocab_local * 2, cudaMemcpyDeviceToHost,
+                                 L->ctx->stream));
+    TLC_CUDA(cudaMemcpyAsync(L->host_next, L->next_ids, (size_t)batch * 4, cudaMemcpyDeviceToHost, L->ctx->stream));
+    if (int32_t rc = tlc_synchronize(L->ctx)) return rc;
+    memcpy(next_ids_host, L->host_next, (size_t)batch * 4);
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_llama_read_state(tlc_llama *L, int32_t batch, int32_t *next_ids_host,
+                                        int32_t *positions_host) {
+    TLC_REQUIRE(L, TLC_ERR_INVALID_OPERATION, "llama_read_state: null handle");
+    if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    TLC_REQUIRE(batch >= 1 && batch <= 64, TLC_ERR_SHAPE_MISMATCH, "batch %d", batch);
+    if (next_ids_host) {
+        if (int32_t rc = tlc_download(L->ctx, next_ids_host, L->next_ids, (size_t)batch * 4)) return rc;
+    }
+    if (positions_host) {
+        if (int32_t rc = tlc_download(L->ctx, positions_host, L->positions, (size_t)batch * 4)) return rc;
+    }
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_llama_launches_per_step(tlc_llama *L) { return L ? L->launches_per_step : 0; }
+extern "C" tlc_kvcache *tlc_llama_cache(tlc_llama *L) { return L ? L->cache : nullptr; }

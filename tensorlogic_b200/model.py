@@ -1,0 +1,239 @@
+"""GGUF models and the LLaMA forward pass (host-side mirror).
+
+    load_model(path)          src/interpreter/builtin_model.rs:106-131
+    get_tensor(model, name)   src/interpreter/builtin_model.rs:203-246
+    Llama.prefill / decode    the TL script debug/chat_demo_with_kvcache.tl:136-296
+                              (LlamaModel::forward itself is a stub upstream,
+                              src/model/llama.rs:257-266)
+
+Weights stay in HBM as GGUF blocks; nothing here computes on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+from . import _lib, synth
+from ._lib import LlamaConfig, TensorError, check
+from .api import Device, QTensor
+
+
+@dataclass
+class LlamaArch:
+    """LlamaConfig (src/model/llama.rs:14-42); the defaults are TinyLlama-1.1B's."""
+    n_layers: int = 22
+    d_model: int = 2048
+    n_heads: int = 32
+    n_kv_heads: int = 4
+    head_dim: int = 64
+    ffn_dim: int = 5632
+    vocab: int = 32000
+    rms_eps: float = 1e-5
+    rope_base: int = 10000
+
+    def tensor_shapes(self) -> dict:
+        """GGUF tensor names -> (rows, cols) in the loader's [out, in] order."""
+        d, qd, kvd = self.d_model, self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        shapes = {"token_embd.weight": (self.vocab, d), "output_norm.weight": (1, d), "output.weight": (self.vocab, d)}
+        for l in range(self.n_layers):
+            p = f"blk.{l}."
+            shapes.update({p + "attn_norm.weight": (1, d), p + "attn_q.weight": (qd, d), p + "attn_k.weight": (kvd, d),
+                           p + "attn_v.weight": (kvd, d), p + "attn_output.weight": (d, qd),
+                           p + "ffn_norm.weight": (1, d), p + "ffn_gate.weight": (self.ffn_dim, d),
+                           p + "ffn_up.weight": (self.ffn_dim, d), p + "ffn_down.weight": (d, self.ffn_dim)})
+        return shapes
+
+
+TINYLLAMA = LlamaArch()
+LLAMA2_7B = LlamaArch(32, 4096, 32, 32, 128, 11008, 32000)
+LLAMA2_70B = LlamaArch(80, 8192, 64, 8, 128, 28672, 32000)
+
+_ROW_SPLIT = ("attn_q.weight", "attn_k.weight", "attn_v.weight", "ffn_gate.weight", "ffn_up.weight")
+_COL_SPLIT = ("attn_output.weight", "ffn_down.weight")
+
+
+def split_for(name: str) -> int:
+    if name.endswith(_ROW_SPLIT) or name == "output.weight":
+        return _lib.SPLIT_ROWS
+    if name.endswith(_COL_SPLIT):
+        return _lib.SPLIT_COLS
+    return _lib.SPLIT_NONE
+
+
+class Model:
+    """Model<T> = name -> tensor map (src/model/mod.rs:39-45), tensors resident on the device."""
+
+    def __init__(self, dev: Device, handle: Optional[C.c_void_p] = None):
+        self.dev = dev
+        if handle is None:
+            handle = C.c_void_p()
+            check(dev.lib.tlc_model_create(dev.handle, C.byref(handle)))
+        self.handle = handle
+
+    def __del__(self):
+        try:
+            if self.handle and self.dev.handle:
+                self.dev.lib.tlc_model_destroy(self.handle)
+            self.handle = None
+        except Exception:
+            pass
+
+    def add(self, name: str, t: QTensor) -> None:
+        check(self.dev.lib.tlc_model_add(self.handle, name.encode(), t.handle))
+        t.handle = None  # ownership moved to the model
+
+    def get_tensor(self, name: str) -> QTensor:
+        h = C.c_void_p()
+        check(self.dev.lib.tlc_model_get(self.handle, name.encode(), C.byref(h)))
+        t = QTensor(self.dev, h)
+        t._owner = self
+        t.__class__ = _BorrowedQTensor
+        return t
+
+    def names(self) -> list[str]:
+        n = self.dev.lib.tlc_model_tensor_count(self.handle)
+        return [self.dev.lib.tlc_model_tensor_name(self.handle, i).decode() for i in range(n)]
+
+    def meta(self, key: str):
+        v = C.c_double()
+        rc = self.dev.lib.tlc_model_meta_num(self.handle, key.encode(), C.byref(v))
+        if rc == _lib.OK:
+            return v.value
+        s = self.dev.lib.tlc_model_meta_str(self.handle, key.encode())
+        return s.decode() if s is not None else None
+
+
+class _BorrowedQTensor(QTensor):
+    """A QTensor whose storage belongs to a Model."""
+
+    def __del__(self):
+        self.handle = None
+
+
+def load_model(dev: Device, path: str, tp_rank: int = 0, tp_size: int = 1) -> Model:
+    h = C.c_void_p()
+    check(dev.lib.tlc_model_load_gguf(dev.handle, str(path).encode(), tp_rank, tp_size, C.byref(h)))
+    return Model(dev, h)
+
+
+def get_tensor(model: Model, name: str) -> QTensor:
+    return model.get_tensor(name)
+
+
+def synthetic_host_weights(arch: LlamaArch, seed: int, qtype: int = _lib.TYPE_Q4_0) -> dict:
+    """Seeded synthetic weights as host arrays: name -> (ggml_type, array).
+
+    Linear weights are Q4_0/Q8_0 blocks from the counter-based generator;
+    embeddings f16 N(0,1)*0.02 and norm weights f16 1 + N(0, 0.02).
+    """
+    out = {}
+    for name, (rows, cols) in arch.tensor_shapes().items():
+        if name.endswith("norm.weight"):
+            out[name] = (_lib.TYPE_F16, synth.norm_weight(seed, name, cols).reshape(1, cols))
+        elif name == "token_embd.weight":
+            out[name] = (_lib.TYPE_F16, synth.embedding_table(seed, name, rows, cols))
+        else:
+            out[name] = (qtype, synth.blocks(qtype, seed, synth.tensor_id(name), rows, cols))
+    return out
+
+
+def synthetic_model(dev: Device, arch: LlamaArch, seed: int, qtype: int = _lib.TYPE_Q4_0, tp_rank: int = 0,
+                    tp_size: int = 1) -> Model:
+    """The same weights as ``synthetic_host_weights``; the quantized ones are generated on the device."""
+    m = Model(dev)
+    for name, (rows, cols) in arch.tensor_shapes().items():
+        if name.endswith("norm.weight"):
+            t = QTensor.from_blocks(dev, _lib.TYPE_F16, 1, cols, synth.norm_weight(seed, name, cols))
+        elif name == "token_embd.weight":
+            t = QTensor.from_blocks(dev, _lib.TYPE_F16, rows, cols, synth.embedding_table(seed, name, rows, cols))
+        else:
+            t = QTensor.synthetic(dev, qtype, rows, cols, seed, synth.tensor_id(name), tp_rank, tp_size,
+                                  split_for(name) if tp_size > 1 else _lib.SPLIT_NONE)
+        m.add(name, t)
+    return m
+
+
+def model_from_host(dev: Device, weights: dict, tp_rank: int = 0, tp_size: int = 1) -> Model:
+    m = Model(dev)
+    for name, (gtype, arr) in weights.items():
+        arr = np.ascontiguousarray(arr)
+        if gtype in (_lib.TYPE_F16, _lib.TYPE_F32):
+            rows, cols = (1, arr.size) if arr.ndim == 1 else arr.shape
+        else:
+            rows, cols = arr.shape[0], arr.shape[1] * 32
+        split = split_for(name) if tp_size > 1 and rows > 1 else _lib.SPLIT_NONE
+        m.add(name, QTensor.from_blocks(dev, gtype, rows, cols, arr, tp_rank, tp_size, split))
+    return m
+
+
+class Llama:
+    """Prefill + greedy decode over a Model with LLaMA tensor names."""
+
+    def __init__(self, dev: Device, model: Model, arch: LlamaArch, max_seq: int = 2048, max_batch: int = 1,
+                 max_prefill: int = 512, logits_all_rows: bool = False, use_graph: bool = True, tp_rank: int = 0,
+                 tp_size: int = 1):
+        self.dev, self.model, self.arch = dev, model, arch
+        self.max_batch = max_batch
+        cfg = LlamaConfig(arch.n_layers, arch.d_model, arch.n_heads, arch.n_kv_heads, arch.head_dim, arch.ffn_dim,
+                          arch.vocab, arch.rms_eps, arch.rope_base, max_seq, max_batch, max_prefill, tp_rank, tp_size,
+                          int(logits_all_rows), int(not use_graph))
+        h = C.c_void_p()
+        check(dev.lib.tlc_llama_create(dev.handle, model.handle, C.byref(cfg), C.byref(h)))
+        self.handle = h
+        self.vocab_local = arch.vocab // max(tp_size, 1)
+
+    def __del__(self):
+        try:
+            if self.handle and self.dev.handle:
+                self.dev.lib.tlc_llama_destroy(self.handle)
+            self.handle = None
+        except Exception:
+            pass
+
+    def prefill(self, ids, pos0: int = 0, return_logits: bool = True, all_rows: bool = False):
+        """Returns (next_token, logits or None); logits are [1 or n, vocab] f16."""
+        ids = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)
+        rows = ids.size if all_rows else 1
+        logits = np.empty((rows, self.vocab_local), np.float16) if return_logits else None
+        nxt = C.c_int32()
+        check(self.dev.lib.tlc_llama_prefill(self.handle, ids.ctypes.data_as(C.POINTER(C.c_int32)), ids.size, pos0,
+                                             logits.ctypes.data if logits is not None else None, int(all_rows),
+                                             C.byref(nxt)))
+        return nxt.value, logits
+
+    def set_state(self, ids, positions) -> None:
+        ids = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)
+        pos = np.ascontiguousarray(positions, dtype=np.int32).reshape(-1)
+        if ids.size != pos.size:
+            raise TensorError(_lib.ERR_SHAPE_MISMATCH, "ids and positions differ in length")
+        check(self.dev.lib.tlc_llama_set_state(self.handle, ids.size, ids.ctypes.data_as(C.POINTER(C.c_int32)),
+                                               pos.ctypes.data_as(C.POINTER(C.c_int32))))
+
+    def decode(self, ids=None, batch: int = 1, return_logits: bool = False):
+        """One greedy step through host buffers.  Returns (next_tokens[batch], logits or None)."""
+        ids_p = None
+        if ids is not None:
+            ids = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)
+            batch = ids.size
+            ids_p = ids.ctypes.data_as(C.POINTER(C.c_int32))
+        nxt = np.empty(batch, np.int32)
+        logits = np.empty((batch, self.vocab_local), np.float16) if return_logits else None
+        check(self.dev.lib.tlc_llama_decode_host(self.handle, batch, ids_p, nxt.ctypes.data_as(C.POINTER(C.c_int32)),
+                                                 logits.ctypes.data if logits is not None else None))
+        return nxt, logits
+
+    def decode_enqueue(self, batch: int, steps: int) -> None:
+        check(self.dev.lib.tlc_llama_decode_enqueue(self.handle, batch, steps))
+
+    def read_state(self, batch: int = 1):
+        nxt, pos = np.empty(batch, np.int32), np.empty(batch, np.int32)
+        check(self.dev.lib.tlc_llama_read_state(self.handle, batch, nxt.ctypes.data_as(C.POINTER(C.c_int32)),
+                                                pos.ctypes.data_as(C.POINTER(C.c_int32))))
+        return nxt, pos
+
+    @property
+    def launches_per_step(self) -> int:
+        return int(self.dev.lib.tlc_llama_launches_per_step(self.handle))

@@ -1,0 +1,124 @@
+"""GPU parity tests of the KV cache and the fused grouped-query attention."""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+# The oracle rounds scores, exponentials and probabilities to f16 exactly where the
+# reference's separate kernels store them; the fused kernel keeps the softmax in f32
+# (it rounds the scores and P the same way).  Outputs agree to ~1e-3; the stated
+# tolerance for the path is 1e-2.
+TOL = 1e-2
+TIGHT = 4e-3
+
+
+def _qkv(seed, I, J, H, Hkv, D):
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((I, H, D)).astype(np.float16)
+    k = rng.standard_normal((J, Hkv, D)).astype(np.float16)
+    v = rng.standard_normal((J, Hkv, D)).astype(np.float16)
+    return q, k, v
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(32, 4, 64), (8, 1, 128), (8, 8, 64), (4, 2, 128), (16, 1, 64)])
+@pytest.mark.parametrize("T", [1, 2, 63, 64, 65, 200, 641, 2048])
+def test_decode_attention(dev, ref, H, Hkv, D, T):
+    """One query at position T-1 over T cached keys (split over several CTAs when T is large)."""
+    from tensorlogic_b200.api import KVCache
+    q, k, v = _qkv(T + H, 1, T, H, Hkv, D)
+    cache = KVCache(dev, 2, Hkv, D, max_seq=2048)
+    cache.append(1, dev.tensor(k), dev.tensor(v))
+    kc, vc = cache.layer_arrays(1)
+    assert np.array_equal(kc.view(np.uint16), k.view(np.uint16)) and np.array_equal(vc.view(np.uint16), v.view(np.uint16))
+    scale = 1.0 / np.sqrt(D)
+    got = cache.attention(1, dev.tensor(q), H, q_pos0=T - 1).numpy()
+    want = ref.attention(q, k, v, scale, q_pos0=T - 1)
+    err = rel_l2(got, want)
+    assert err < TOL and err < TIGHT, err
+    # the device-position form (what a replayed decode graph uses) gives the same result
+    got2 = cache.attention(1, dev.tensor(q), H, positions=np.array([T - 1])).numpy()
+    assert rel_l2(got2, want) < TIGHT
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(32, 4, 64), (8, 8, 64), (8, 1, 128)])
+@pytest.mark.parametrize("I,pos0", [(1, 0), (5, 0), (64, 0), (130, 0), (17, 40), (512, 0)])
+def test_prefill_attention_causal(dev, ref, H, Hkv, D, I, pos0):
+    """I queries at positions pos0.. over pos0+I keys with the causal mask."""
+    from tensorlogic_b200.api import KVCache
+    if I == 512 and D == 128:
+        pytest.skip("covered by the 64-wide case; keeps the CPU oracle time down")
+    J = pos0 + I
+    q, k, v = _qkv(I * 7 + pos0, I, J, H, Hkv, D)
+    cache = KVCache(dev, 1, Hkv, D, max_seq=1024)
+    cache.append(0, dev.tensor(k), dev.tensor(v))
+    got = cache.attention(0, dev.tensor(q), H, q_pos0=pos0).numpy()
+    want = ref.attention(q, k, v, 1.0 / np.sqrt(D), q_pos0=pos0)
+    err = rel_l2(got, want)
+    assert err < TOL and err < TIGHT, err
+    # first query row alone sees only keys 0..pos0
+    first = ref.attention(q[:1], k[:pos0 + 1], v[:pos0 + 1], 1.0 / np.sqrt(D), q_pos0=pos0)
+    assert rel_l2(got[0], first[0]) < TIGHT
+
+
+def test_attention_vs_reference_python_golden(dev, golden):
+    """Against the reference's numpy attention (scripts/reference_impl.py:83-128): full visibility = last query."""
+    from tensorlogic_b200.api import KVCache
+    q, k, v = golden["attn_q"], golden["attn_k"], golden["attn_v"]   # [6, 8, 16], [6, 2, 16]: D=16 is not a
+    # supported head_dim, so embed it in 64 with zero padding (scores and outputs are unchanged)
+    S, H, D = q.shape
+    Hkv = k.shape[1]
+    pad = lambda a: np.concatenate([a, np.zeros(a.shape[:2] + (64 - D,), np.float16)], axis=2)
+    cache = KVCache(dev, 1, Hkv, 64, max_seq=64)
+    cache.append(0, dev.tensor(pad(k)), dev.tensor(pad(v)))
+    got = cache.attention(0, dev.tensor(pad(q[-1:])), H, q_pos0=S - 1, scale=1.0 / np.sqrt(D)).numpy()
+    assert rel_l2(got[0, :, :D], golden["attn_full_out"][-1]) < 4e-3
+    assert np.all(got[0, :, D:] == 0)
+
+
+def test_batched_decode_positions(dev, ref):
+    """Several sequences of different lengths in one launch (batched decode)."""
+    from tensorlogic_b200.api import KVCache
+    H, Hkv, D, B = 16, 2, 64, 3
+    lens = [5, 300, 77]
+    cache = KVCache(dev, 1, Hkv, D, max_seq=512, max_batch=B)
+    rng = np.random.default_rng(0)
+    seqs = []
+    kp, vp = cache.dev.lib.tlc_kvcache_layer_ptrs, None
+    import ctypes as C
+    kptr, vptr = C.c_void_p(), C.c_void_p()
+    from tensorlogic_b200._lib import check
+    check(dev.lib.tlc_kvcache_layer_ptrs(cache.handle, 0, C.byref(kptr), C.byref(vptr)))
+    row = Hkv * D
+    for b, n in enumerate(lens):
+        k = rng.standard_normal((n, Hkv, D)).astype(np.float16)
+        v = rng.standard_normal((n, Hkv, D)).astype(np.float16)
+        seqs.append((k, v))
+        # all but the newest token are already in the cache
+        check(dev.lib.tlc_upload(dev.handle, kptr.value + b * 512 * row * 2, k.ctypes.data, (n - 1) * row * 2))
+        check(dev.lib.tlc_upload(dev.handle, vptr.value + b * 512 * row * 2, v.ctypes.data, (n - 1) * row * 2))
+    dev.synchronize()
+    pos = np.array([n - 1 for n in lens], np.int32)
+    knew = np.stack([s[0][-1] for s in seqs])
+    vnew = np.stack([s[1][-1] for s in seqs])
+    cache.append(0, dev.tensor(knew), dev.tensor(vnew), positions=pos)
+    q = rng.standard_normal((B, H, D)).astype(np.float16)
+    got = cache.attention(0, dev.tensor(q), H, batch=B, positions=pos).numpy()
+    for b, n in enumerate(lens):
+        want = ref.attention(q[b:b + 1], seqs[b][0], seqs[b][1], 1.0 / np.sqrt(D), q_pos0=n - 1)
+        assert rel_l2(got[b], want[0]) < TIGHT, b
+
+
+def test_attention_errors(dev):
+    from tensorlogic_b200.api import KVCache, TensorError
+    cache = KVCache(dev, 1, 2, 64, max_seq=16)
+    q = dev.tensor(np.zeros((1, 6, 64), np.float16))
+    with pytest.raises(TensorError):       # 6 query heads over 2 KV heads: group of 3 unsupported
+        cache.attention(0, q, 6)
+    with pytest.raises(TensorError):       # layer out of range
+        cache.attention(3, dev.tensor(np.zeros((1, 4, 64), np.float16)), 4)
+    with pytest.raises(TensorError):       # more keys than the cache holds
+        cache.attention(0, dev.tensor(np.zeros((1, 4, 64), np.float16)), 4, q_pos0=16)
+    with pytest.raises(TensorError):
+        KVCache(dev, 1, 2, 60)

@@ -100,7 +100,12 @@ def test_config1_sweep(dev, ref, qtype, k, n, m):
     want = ref.linear_q(qtype, raw, n, k, x)
     err = rel_l2(y, want)
     assert err < TOL and err < TIGHT, err
-    assert np.max(np.abs(y.astype(np.float32) - want.astype(np.float32))) < 0.05
+    # element-wise: the oracle rounds each dequantized weight to f16 first (as the
+    # reference's loader does) while the kernel multiplies d*(q-8) exactly, so single
+    # outputs differ by a random-walk of 2^-11 relative errors: small against the
+    # output's rms, whatever the element's own magnitude
+    yf, wf = y.astype(np.float32), want.astype(np.float32)
+    assert np.max(np.abs(yf - wf)) < 2e-3 * max(float(np.max(np.abs(wf))), 1.0)  # ~2 f16 steps of the largest output
 
 
 @pytest.mark.parametrize("qtype", [Q4, Q8])

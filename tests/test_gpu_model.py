@@ -1,0 +1,184 @@
+"""GPU tests of the GGUF loader and of the LLaMA forward pass against the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+from gguf_util import write_gguf
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2  # rel-L2 on logits, the tolerance stated for the full forward
+
+
+def _small_arch():
+    from tensorlogic_b200.model import LlamaArch
+    return LlamaArch(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn_dim=512, vocab=1000)
+
+
+def _ref_model(ref, weights, arch):
+    w = {}
+    for name, (gtype, arr) in weights.items():
+        if gtype == 1:
+            w[name] = arr.reshape(-1) if name.endswith("norm.weight") else arr
+        else:
+            w[name] = (gtype, arr, (arr.shape[0], arr.shape[1] * 32))
+    return ref.RefLlama(w, arch.n_layers, arch.n_heads, arch.n_kv_heads, arch.head_dim, arch.rms_eps, arch.rope_base)
+
+
+@pytest.mark.parametrize("alignment", [32, 64])
+def test_gguf_round_trip(dev, ref, tmp_path, alignment):
+    from tensorlogic_b200.model import load_model, synthetic_host_weights
+    arch = _small_arch()
+    weights = synthetic_host_weights(arch, seed=3, qtype=2)
+    # mix in a Q8_0 and an F32 tensor
+    from tensorlogic_b200 import synth
+    weights["blk.1.ffn_up.weight"] = (8, synth.blocks(8, 3, 99, arch.ffn_dim, arch.d_model))
+    weights["blk.0.attn_norm.weight"] = (0, weights["blk.0.attn_norm.weight"][1].astype(np.float32))
+    path = tmp_path / "m.gguf"
+    write_gguf(path, weights, arch, alignment=alignment)
+    m = load_model(dev, path)
+    assert sorted(m.names()) == sorted(weights)
+    assert m.meta("llama.block_count") == 2 and m.meta("test.u16") == 513 and m.meta("test.flag") == 1
+    assert m.meta("test.note") == "synthetic" and m.meta("test.tokens.length") == 3
+    assert m.meta("general.alignment") in (None, alignment) or alignment == 32
+    for name, (gtype, arr) in weights.items():
+        t = m.get_tensor(name)
+        got = t.dequantize().numpy()
+        if gtype in (2, 8):
+            rows, cols = arr.shape[0], arr.shape[1] * 32
+            assert t.shape == (rows, cols) and t.type == gtype
+            want = ref.dequant(gtype, arr, rows * cols).reshape(rows, cols)
+            assert np.array_equal(t.raw_bytes().reshape(-1), arr.reshape(-1))     # blocks kept verbatim
+        else:
+            want = arr.astype(np.float16).reshape(got.shape)
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), name
+    with pytest.raises(Exception) as e:
+        m.get_tensor("no.such.tensor")
+    assert "not found" in str(e.value)
+
+
+def test_gguf_errors(dev, tmp_path):
+    from tensorlogic_b200.api import TensorError
+    from tensorlogic_b200.model import load_model, synthetic_host_weights
+    arch = _small_arch()
+    weights = {k: v for k, v in synthetic_host_weights(arch, 1).items() if k.startswith(("output", "token"))}
+    good = tmp_path / "g.gguf"
+    write_gguf(good, weights, arch)
+    raw = open(good, "rb").read()
+    cases = {"magic": b"GGUX" + raw[4:], "version": raw[:4] + (9).to_bytes(4, "little") + raw[8:],
+             "truncated_data": raw[:len(raw) - 1000], "truncated_header": raw[:40]}
+    for name, data in cases.items():
+        p = tmp_path / f"{name}.gguf"
+        open(p, "wb").write(data)
+        with pytest.raises(TensorError) as e:
+            load_model(dev, p)
+        assert e.value.kind == "LoadError", name
+    with pytest.raises(TensorError) as e:
+        load_model(dev, tmp_path / "missing.gguf")
+    assert e.value.kind == "LoadError"
+
+
+def test_small_llama_prefill_and_decode(dev, ref, tmp_path):
+    """2-layer model from a GGUF file: all-row prefill logits, then teacher-forced decode steps."""
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.model import Llama, load_model, synthetic_host_weights
+    arch = _small_arch()
+    weights = synthetic_host_weights(arch, seed=5)
+    path = tmp_path / "small.gguf"
+    write_gguf(path, weights, arch)
+    model = load_model(dev, path)
+    llm = Llama(dev, model, arch, max_seq=128, max_prefill=64, logits_all_rows=True)
+    oracle = _ref_model(ref, weights, arch)
+    ids = synth.token_ids(5, "prompt", 37, arch.vocab)
+    nxt, logits = llm.prefill(ids, all_rows=True)
+    want = oracle.forward(ids)
+    assert logits.shape == want.shape == (37, arch.vocab)
+    assert rel_l2(logits, want) < TOL
+    assert rel_l2(logits[-1], want[-1]) < TOL
+    tok = ref.argmax_last(want[-1])
+    assert nxt == ref.argmax_last(logits[-1])
+    for step in range(6):
+        got_next, lg = llm.decode([tok], return_logits=True)   # teacher-forced with the oracle's token
+        w = oracle.forward([tok])
+        assert rel_l2(lg, w) < TOL, step
+        assert got_next[0] == ref.argmax_last(lg[0])
+        tok = ref.argmax_last(w[0])
+    # chunked prefill == one-shot prefill
+    llm2 = Llama(dev, model, arch, max_seq=128, max_prefill=64, logits_all_rows=True)
+    llm2.prefill(ids[:20], pos0=0)
+    _, lg2 = llm2.prefill(ids[20:], pos0=20, all_rows=True)
+    assert rel_l2(lg2, want[20:]) < TOL
+
+
+def test_graph_replay_matches_eager_and_free_running_decode(dev):
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.model import Llama, model_from_host, synthetic_host_weights
+    arch = _small_arch()
+    model = model_from_host(dev, synthetic_host_weights(arch, seed=6))
+    ids = synth.token_ids(6, "prompt", 16, arch.vocab)
+    outs = []
+    for use_graph in (True, False):
+        llm = Llama(dev, model, arch, max_seq=96, max_prefill=16, use_graph=use_graph)
+        first, _ = llm.prefill(ids)
+        toks = [first]
+        for _ in range(5):
+            nxt, lg = llm.decode(None, batch=1, return_logits=True)
+            toks.append(int(nxt[0]))
+        outs.append((toks, lg.copy()))
+    assert outs[0][0] == outs[1][0]
+    assert np.array_equal(outs[0][1].view(np.uint16), outs[1][1].view(np.uint16))
+    # free-running device-side loop == stepping through the host
+    llm = Llama(dev, model, arch, max_seq=96, max_prefill=16)
+    llm.prefill(ids)
+    llm.decode_enqueue(1, 5)
+    nxt, pos = llm.read_state(1)
+    assert int(nxt[0]) == outs[0][0][5] and int(pos[0]) == 16 + 5
+    assert llm.launches_per_step == 5 * arch.n_layers + 3
+
+
+def test_batched_decode_matches_single(dev):
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.model import Llama, model_from_host, synthetic_host_weights
+    arch = _small_arch()
+    model = model_from_host(dev, synthetic_host_weights(arch, seed=7))
+    B = 3
+    prompts = [synth.token_ids(7, f"p{b}", 5 + 4 * b, arch.vocab) for b in range(B)]
+    singles = []
+    for b in range(B):
+        llm = Llama(dev, model, arch, max_seq=64, max_prefill=32)
+        first, _ = llm.prefill(prompts[b])
+        _, lg = llm.decode([first], return_logits=True)
+        singles.append((first, lg[0].copy()))
+    # the batched runner: fill each sequence's cache slot by decoding its prompt token by token
+    llm = Llama(dev, model, arch, max_seq=64, max_batch=B, max_prefill=32)
+    maxlen = max(len(p) for p in prompts)
+    for t in range(maxlen):
+        # sequences whose prompt is exhausted re-feed their last token at the same position (idempotent)
+        ids = [int(p[min(t, len(p) - 1)]) for p in prompts]
+        pos = [min(t, len(p) - 1) for p in prompts]
+        llm.set_state(ids, pos)
+        llm.decode(None, batch=B)
+    llm.set_state([s[0] for s in singles], [len(p) for p in prompts])
+    _, lg = llm.decode(None, batch=B, return_logits=True)
+    for b in range(B):
+        assert rel_l2(lg[b], singles[b][1]) < 2e-3, b
+
+
+def test_tinyllama_shape_step(dev, ref):
+    """Full TinyLlama-1.1B architecture (22 layers, Q4_0): short prompt + one decode step vs the oracle."""
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.model import TINYLLAMA, Llama, synthetic_host_weights, synthetic_model
+    arch = TINYLLAMA
+    model = synthetic_model(dev, arch, seed=2)          # quantized weights generated on the device
+    weights = synthetic_host_weights(arch, seed=2)      # the same bytes on the host for the oracle
+    llm = Llama(dev, model, arch, max_seq=64, max_prefill=16)
+    oracle = _ref_model(ref, weights, arch)
+    ids = synth.token_ids(2, "prompt", 6, arch.vocab)
+    nxt, logits = llm.prefill(ids)
+    want = oracle.forward(ids)
+    assert rel_l2(logits[0], want[-1]) < TOL
+    tok = ref.argmax_last(want[-1])
+    _, lg = llm.decode([tok], return_logits=True)
+    assert rel_l2(lg, oracle.forward([tok])) < TOL
