@@ -1,0 +1,339 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-LLM hot path: Q4_0 decode tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload at N=1 (BASELINE.json configs[2]): TinyLlama-1.1B architecture with
+seeded random Q4_0 weights (f16 embeddings and norms), batch 1, 512-token
+prompt, then greedy decode with an f16 KV cache.  A "step" is one decode step
+(one token).  Prints ONE JSON line.
+
+  value        tokens/s over K steps replayed back to back on the device
+               (token ids, positions and the sampled token stay in HBM), CUDA
+               events on the library's stream;
+  e2e          the same K steps through the host-buffer entry point
+               tlc_llama_decode_host: per step the token id goes up from pinned
+               memory and the sampled token comes back, with a stream sync;
+  roofline     the dominant kernel (the fused dequant-GEMV): algorithmic bytes
+               per launch / its average launch duration, timed by replaying only
+               the step's GEMV launches between two CUDA events;
+  cpu_baseline the CPU oracle's restatement of the reference's literal CPU
+               path (single thread, f16 running sum), on a bounded sample.
+
+With --gpus N > 1 (launched under torchrun) every rank decodes its own replica
+of the model: the runner is single-GPU in this build and tensor parallelism is
+not wired in yet, so the line says parallelism "replicas" and scaling "weak".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT_TOKENS = 512
+SEED = 2
+METRIC = "q4_0_decode_tokens_per_s"
+
+
+def tinyllama_bytes_per_token(arch, context: int) -> int:
+    """Algorithmic HBM bytes of one decode step: every Q4_0 weight once, norm weights, one
+    embedding row, the KV cache of `context` tokens read and one position written."""
+    d, qd, kvd, f = arch.d_model, arch.n_heads * arch.head_dim, arch.n_kv_heads * arch.head_dim, arch.ffn_dim
+    q4 = lambda n, k: n * (k // 32) * 18
+    layer = q4(qd, d) + 2 * q4(kvd, d) + q4(d, qd) + 2 * q4(f, d) + q4(d, f)
+    weights = arch.n_layers * layer + q4(arch.vocab, d)
+    norms = (2 * arch.n_layers + 1) * d * 2
+    kv = arch.n_layers * 2 * kvd * 2 * (context + 1)
+    return weights + norms + d * 2 + kv
+
+
+def gemv_bytes_per_step(arch, m: int = 1) -> tuple[int, int]:
+    """(algorithmic bytes, launches) of the GEMV launches of one decode step:
+    N*(K/32)*18 + 2*M*K + 2*M*N per linear, summed per fused launch."""
+    d, qd, kvd, f = arch.d_model, arch.n_heads * arch.head_dim, arch.n_kv_heads * arch.head_dim, arch.ffn_dim
+    lin = lambda n, k: n * (k // 32) * 18 + 2 * m * n
+    x = lambda k: 2 * m * k
+    layer = (lin(qd, d) + 2 * lin(kvd, d) + x(d)) + (lin(d, qd) + x(qd)) + (2 * lin(f, d) + x(d)) + (lin(d, f) + x(f))
+    return arch.n_layers * layer + lin(arch.vocab, d) + x(d), 4 * arch.n_layers + 1
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus: int):
+    """Under torchrun: NCCL process group for the barrier and the max-over-ranks reduction."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def cpu_baseline(arch, seed: int, budget_s: float = 12.0) -> dict:
+    """The reference's CPU path on a bounded sample, scaled to tokens/s.
+
+    Restated by oracle/tl_ref.c: GGUF dequantization (src/model/formats/gguf.rs:68-112) happens
+    once at load upstream and is not timed; per token the linears run as transpose + matmul_cpu with
+    an f16 running sum on one thread (src/ops/matmul.rs:201-228, :293-297).  The sample is the seven
+    linears of one layer plus a slice of lm_head rows; a token costs n_layers * layer + lm_head.
+    """
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import tl_ref as ref
+    from tensorlogic_b200 import synth
+    d, qd, kvd, f = arch.d_model, arch.n_heads * arch.head_dim, arch.n_kv_heads * arch.head_dim, arch.ffn_dim
+    shapes = [("attn_q", qd, d), ("attn_k", kvd, d), ("attn_v", kvd, d), ("attn_output", d, qd), ("ffn_gate", f, d),
+              ("ffn_up", f, d), ("ffn_down", d, f)]
+    ws = []
+    for name, n, k in shapes:
+        raw = synth.blocks(2, seed, synth.tensor_id(f"blk.0.{name}.weight"), n, k)
+        ws.append((ref.dequant(2, raw, n * k).reshape(n, k), synth.activations(seed, f"cpu.{name}", (1, k))))
+    head_rows = 4000
+    raw = synth.blocks(2, seed, synth.tensor_id("output.weight"), head_rows, d)
+    head = ref.dequant(2, raw, head_rows * d).reshape(head_rows, d)
+    xh = synth.activations(seed, "cpu.head", (1, d))
+    t_layer, t_head, reps = 0.0, 0.0, 0
+    t_start = time.perf_counter()
+    while reps < 1 or (time.perf_counter() - t_start) < budget_s:
+        t0 = time.perf_counter()
+        for w, x in ws:
+            ref.linear_literal(x, w)
+        t1 = time.perf_counter()
+        ref.linear_literal(xh, head)
+        t2 = time.perf_counter()
+        t_layer += t1 - t0
+        t_head += t2 - t1
+        reps += 1
+    t_token = arch.n_layers * (t_layer / reps) + (t_head / reps) * (arch.vocab / head_rows)
+    # the multi-threaded f32-accumulating variant (no counterpart upstream), for context
+    t0 = time.perf_counter()
+    for w, x in ws:
+        ref.linear_f32acc(x, w)
+    ref.linear_f32acc(xh, head)
+    t_mt_layer = time.perf_counter() - t0
+    macs_sample = sum(w.size for w, _ in ws) + head.size
+    macs_token = arch.n_layers * sum(w.size for w, _ in ws) + arch.vocab * d
+    return {"value": 1.0 / t_token, "unit": "tokens/s", "cores": 1, "kind": "port",
+            "sample": (f"{reps}x (7 linears of one layer + {head_rows} lm_head rows), literal f16-accumulate matmul on "
+                       f"pre-dequantized f16 weights, scaled to {arch.n_layers} layers + {arch.vocab} lm_head rows; "
+                       f"attention, norms and sampling not counted (favours the CPU)"),
+            "f16c": bool(ref.uses_f16c()), "host_cores_available": os.cpu_count(),
+            "mt_f32acc_tokens_per_s": (macs_sample / macs_token) / t_mt_layer, "mt_threads": ref.num_threads()}
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    """--impl reference: the reference's own CPU implementation of the path (no GPU work)."""
+    if rank != 0:
+        return
+    from tensorlogic_b200.model import TINYLLAMA
+    arch = TINYLLAMA
+    # each "step" is a bounded sample of one token's work; the whole run stays within minutes
+    steps = max(1, args.steps)
+    budget = min(150.0, 1.2 * (args.warmup + steps)) if steps > 1 else 12.0
+    t0 = time.perf_counter()
+    base = cpu_baseline(arch, SEED, budget_s=max(6.0, budget))
+    elapsed = time.perf_counter() - t0
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / base["value"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "tinyllama-1.1b q4_0 decode, batch 1 (BASELINE configs[2])",
+                   "note": "reference CPU path (transpose + f16-accumulating matmul_cpu, 1 thread), "
+                           "bounded sample per step extrapolated to a token", "wall_s": round(elapsed, 1)},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank: int, world: int, local: int) -> None:
+    import torch
+    from tensorlogic_b200.api import Device
+    from tensorlogic_b200.model import TINYLLAMA, Llama, synthetic_model
+    from tensorlogic_b200 import synth
+    arch = TINYLLAMA
+    K, W = args.steps, max(args.warmup, 3)
+    dev = Device(local)
+    model = synthetic_model(dev, arch, SEED)
+    max_seq = PROMPT_TOKENS + 2 * (K + W) + 64
+    llm = Llama(dev, model, arch, max_seq=max_seq, max_batch=1, max_prefill=PROMPT_TOKENS)
+    stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local))
+    ids = synth.token_ids(SEED, f"prompt.{rank}", PROMPT_TOKENS, arch.vocab)
+
+    def barrier():
+        dev.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    first, _ = llm.prefill(ids, return_logits=False)
+
+    # ---- device-resident decode: K graph replays between two events ----
+    llm.decode_enqueue(1, W)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = dev.launch_count
+    with ClockSampler(local) as clocks:
+        e0.record(stream)
+        llm.decode_enqueue(1, K)
+        e1.record(stream)
+        barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    gpu_launches = dev.launch_count - launches0
+    tok_s = world * K / (ms / 1e3)
+    _, pos = llm.read_state(1)
+    context_mid = int(pos[0]) - K // 2
+
+    # ---- end to end through host buffers ----
+    tok = int(llm.read_state(1)[0][0])
+    for _ in range(W):
+        tok = int(llm.decode([tok])[0][0])
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        tok = int(llm.decode([tok])[0][0])
+    dev.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+    e2e_tok_s = world * K / (e2e_ms / 1e3)
+
+    # ---- dominant kernel: replay only the GEMV launches of a step ----
+    llm.decode_enqueue(1, W, parts=1)
+    dev.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    llm.decode_enqueue(1, K, parts=1)
+    g1.record(stream)
+    dev.synchronize()
+    gemv_bytes, gemv_launches = gemv_bytes_per_step(arch)
+    assert llm.launches(1) == gemv_launches, (llm.launches(1), gemv_launches)
+    gemv_us = g0.elapsed_time(g1) * 1e3 / (K * gemv_launches)
+    bytes_per_launch = gemv_bytes / gemv_launches
+    achieved = bytes_per_launch / (gemv_us * 1e-6) / 1e9
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    step_bytes = tinyllama_bytes_per_token(arch, context_mid)
+
+    if rank != 0:
+        return
+    base = cpu_baseline(arch, SEED) if world == 1 else None
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "tinyllama-1.1b q4_0 decode, batch 1, 512-token prompt (BASELINE configs[2])",
+                   "context_tokens_mid_run": context_mid, "parallelism": "single" if world == 1 else f"replicas x{world}",
+                   "l2": "weights of one step (582 MB) exceed the 126 MB L2: every step re-reads them from HBM",
+                   "step_hbm_bytes": step_bytes, "step_hbm_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
+                   "launches_per_step": llm.launches(7), "seed": SEED},
+        "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
+                "ms_per_step": e2e_ms / K},
+        "gpu_launches": int(gpu_launches),
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q4_0> (fused dequant-GEMV, M=1)",
+                     "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                     "frac": achieved / peak, "bytes_per_launch": bytes_per_launch, "us_per_launch": gemv_us,
+                     "launches_per_step": gemv_launches, "traffic": None},
+    }
+    if base is not None:
+        line["cpu_baseline"] = base
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        dist_setup(args.gpus)
+    try:
+        run_ours(args, rank, world, local)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            if dist.is_initialized():
+                dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

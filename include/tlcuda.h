@@ -153,17 +153,18 @@ TLC_API int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows, i
                                    int32_t tp_size, int32_t split, tlc_qtensor **out);
 /* Same, but the shard is filled on the device from the counter-based
  * generator of the benchmark configurations (weights too large to stage on
- * the host).  Only Q4_0 / Q8_0. */
+ * the host).  Only Q4_0 / Q8_0.  Block scales are U[0.002, 0.02] * 2^scale_log2. */
 TLC_API int32_t tlc_qtensor_create_synthetic(tlc_ctx *ctx, int32_t type, int64_t n_rows,
                                              int64_t n_cols, uint64_t seed, uint64_t tensor_id,
-                                             int32_t tp_rank, int32_t tp_size, int32_t split,
-                                             tlc_qtensor **out);
+                                             int32_t scale_log2, int32_t tp_rank, int32_t tp_size,
+                                             int32_t split, tlc_qtensor **out);
 /* The same generator on the host (no GPU needed): writes n_blocks consecutive
  * blocks of the full tensor, starting at block index first_block (row-major
  * block order), into out_host.  No counterpart upstream: the reference has no
  * synthetic weights; this exists so that benchmark inputs are reproducible. */
 TLC_API int32_t tlc_synth_blocks_host(int32_t type, uint64_t seed, uint64_t tensor_id,
-                                      int64_t first_block, int64_t n_blocks, void *out_host);
+                                      int32_t scale_log2, int64_t first_block, int64_t n_blocks,
+                                      void *out_host);
 TLC_API int32_t tlc_qtensor_destroy(tlc_qtensor *qt);
 /* Local (per-rank) shape and storage.  row_pitch is the distance in bytes
  * between rows in HBM: the GGUF row size rounded up to 16 (equal to it, i.e.
@@ -352,8 +353,14 @@ TLC_API int32_t tlc_llama_decode_host(tlc_llama *l, int32_t batch, const int32_t
 TLC_API int32_t tlc_llama_decode_enqueue(tlc_llama *l, int32_t batch, int32_t steps);
 TLC_API int32_t tlc_llama_read_state(tlc_llama *l, int32_t batch, int32_t *next_ids_host,
                                      int32_t *positions_host);
-/* Kernels one decode step launches (for launch accounting). */
-TLC_API int32_t tlc_llama_launches_per_step(tlc_llama *l);
+/* The same, replaying only some of the step's launches, for per-kernel timing:
+ * parts is a mask of 1 (the quantized linears), 2 (attention), 4 (embedding
+ * gather + sampling); tokens and positions are left untouched unless parts == 7. */
+TLC_API int32_t tlc_llama_decode_enqueue_parts(tlc_llama *l, int32_t batch, int32_t steps,
+                                               int32_t parts);
+/* Kernels one decode step launches for a parts mask (7 = whole step), known
+ * once such a step has been enqueued. */
+TLC_API int32_t tlc_llama_launches_per_step(tlc_llama *l, int32_t parts);
 TLC_API tlc_kvcache *tlc_llama_cache(tlc_llama *l);
 
 #ifdef __cplusplus

@@ -173,11 +173,46 @@ TLREF_API size_t tlref_dequant_q8_0(const uint8_t *data, size_t nbytes, size_t n
 /* Matmul / linear.                                                           */
 /* ------------------------------------------------------------------------- */
 
+/* The same loop with the CPU's F16C conversion instructions, which the `half`
+ * crate also uses on x86-64 when the CPU has them (runtime detection); results
+ * are bit-identical to the software conversions above (the tests check). */
+#if defined(__x86_64__)
+#include <immintrin.h>
+__attribute__((target("f16c"))) static void matmul_f16acc_f16c(const uint16_t *a, const uint16_t *b,
+                                                                uint16_t *c, int m, int k, int n) {
+    for (int i = 0; i < m; i++) {
+        for (int j = 0; j < n; j++) {
+            uint16_t sum = 0;
+            for (int p = 0; p < k; p++) {
+                float fa = _cvtsh_ss(a[(size_t)i * k + p]), fb = _cvtsh_ss(b[(size_t)p * n + j]);
+                uint16_t prod = _cvtss_sh(fa * fb, _MM_FROUND_TO_NEAREST_INT);
+                sum = _cvtss_sh(_cvtsh_ss(sum) + _cvtsh_ss(prod), _MM_FROUND_TO_NEAREST_INT);
+            }
+            c[(size_t)i * n + j] = sum;
+        }
+    }
+}
+static int have_f16c(void) { return __builtin_cpu_supports("f16c"); }
+#else
+static int have_f16c(void) { return 0; }
+#endif
+
+static int g_allow_f16c = 1;
+/* Tests switch the hardware path off to compare it with the software one. */
+TLREF_API void tlref_set_f16c(int enable) { g_allow_f16c = enable; }
+TLREF_API int tlref_uses_f16c(void) { return g_allow_f16c && have_f16c(); }
+
 /* Literal CPU matmul: follows Tensor::matmul_cpu, src/ops/matmul.rs:201-228.
  * C[m,n] = A[m,k] * B[k,n]; the running sum is an f16: every step rounds the
  * product to f16, then the sum to f16.  Single thread, as upstream. */
 TLREF_API void tlref_matmul_f16acc(const uint16_t *a, const uint16_t *b, uint16_t *c,
                                    int m, int k, int n) {
+#if defined(__x86_64__)
+    if (g_allow_f16c && have_f16c()) {
+        matmul_f16acc_f16c(a, b, c, m, k, n);
+        return;
+    }
+#endif
     for (int i = 0; i < m; i++) {
         for (int j = 0; j < n; j++) {
             uint16_t sum = 0;

@@ -55,6 +55,8 @@ def _load() -> C.CDLL:
                                    C.c_float, C.c_int, C.c_int]),
         "tlref_argmax_last": (C.c_int, [u16p, C.c_int]),
         "tlref_num_threads": (C.c_int, []),
+        "tlref_set_f16c": (None, [C.c_int]),
+        "tlref_uses_f16c": (C.c_int, []),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -255,6 +257,15 @@ def argmax_last(logits: np.ndarray) -> int:
 
 def num_threads() -> int:
     return int(lib().tlref_num_threads())
+
+
+def set_f16c(enable: bool) -> None:
+    """Allow / forbid the hardware f16 conversions in the literal matmul (bit-identical either way)."""
+    lib().tlref_set_f16c(int(enable))
+
+
+def uses_f16c() -> bool:
+    return bool(lib().tlref_uses_f16c())
 
 
 # --------------------------------------------------------------------------

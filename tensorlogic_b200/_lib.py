@@ -76,8 +76,8 @@ PROTOTYPES = {
     "tlc_host_alloc": (i32, [sz, P(vp)]),
     "tlc_host_free": (i32, [vp]),
     "tlc_qtensor_create": (i32, [vp, i32, i64, i64, vp, sz, i32, i32, i32, P(vp)]),
-    "tlc_qtensor_create_synthetic": (i32, [vp, i32, i64, i64, u64, u64, i32, i32, i32, P(vp)]),
-    "tlc_synth_blocks_host": (i32, [i32, u64, u64, i64, i64, vp]),
+    "tlc_qtensor_create_synthetic": (i32, [vp, i32, i64, i64, u64, u64, i32, i32, i32, i32, P(vp)]),
+    "tlc_synth_blocks_host": (i32, [i32, u64, u64, i32, i64, i64, vp]),
     "tlc_qtensor_destroy": (i32, [vp]),
     "tlc_qtensor_info": (i32, [vp, P(i32), P(i64), P(i64), P(sz), P(vp)]),
     "tlc_dequant": (i32, [vp, vp, vp]),
@@ -122,7 +122,8 @@ PROTOTYPES = {
     "tlc_llama_decode_host": (i32, [vp, i32, P(i32), P(i32), vp]),
     "tlc_llama_decode_enqueue": (i32, [vp, i32, i32]),
     "tlc_llama_read_state": (i32, [vp, i32, P(i32), P(i32)]),
-    "tlc_llama_launches_per_step": (i32, [vp]),
+    "tlc_llama_decode_enqueue_parts": (i32, [vp, i32, i32, i32]),
+    "tlc_llama_launches_per_step": (i32, [vp, i32]),
     "tlc_llama_cache": (vp, [vp]),
 }
 

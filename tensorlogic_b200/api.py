@@ -164,10 +164,10 @@ class QTensor:
 
     @classmethod
     def synthetic(cls, dev: Device, qtype: int, n_rows: int, n_cols: int, seed: int, tensor_id: int,
-                  tp_rank: int = 0, tp_size: int = 1, split: int = _lib.SPLIT_NONE) -> "QTensor":
+                  tp_rank: int = 0, tp_size: int = 1, split: int = _lib.SPLIT_NONE, scale_log2: int = 0) -> "QTensor":
         h = C.c_void_p()
-        check(dev.lib.tlc_qtensor_create_synthetic(dev.handle, qtype, n_rows, n_cols, seed, tensor_id, tp_rank,
-                                                   tp_size, split, C.byref(h)))
+        check(dev.lib.tlc_qtensor_create_synthetic(dev.handle, qtype, n_rows, n_cols, seed, tensor_id, scale_log2,
+                                                   tp_rank, tp_size, split, C.byref(h)))
         return cls(dev, h)
 
     def __del__(self):

@@ -422,17 +422,29 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
     const size_t smem = (size_t)4 * kTileKeys * (D + 8) * sizeof(__half);
     const size_t smem_o = (size_t)4 * 16 * D * sizeof(float);
     const size_t smem_bytes = smem > smem_o ? smem : smem_o;
-    if (D == 64) {
-        attention_kernel<64><<<grid, kAttnThreads, smem_bytes, ctx->stream>>>(p);
-    } else {
-        static bool configured[64] = {};
-        if (!configured[ctx->device & 63]) {
+    // All kernels of a decode step ask for the same (maximal) shared-memory
+    // carve-out: switching the L1/shared split between consecutive launches
+    // makes the SMs drain first.
+    static bool configured[2][64] = {};
+    const int di = D == 64 ? 0 : 1;
+    if (!configured[di][ctx->device & 63]) {
+        if (D == 64) {
+            TLC_CUDA(cudaFuncSetAttribute(attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem_bytes));
+            TLC_CUDA(cudaFuncSetAttribute(attention_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          cudaSharedmemCarveoutMaxShared));
+        } else {
             TLC_CUDA(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem_bytes));
-            configured[ctx->device & 63] = true;
+            TLC_CUDA(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          cudaSharedmemCarveoutMaxShared));
         }
-        attention_kernel<128><<<grid, kAttnThreads, smem_bytes, ctx->stream>>>(p);
+        configured[di][ctx->device & 63] = true;
     }
+    if (D == 64)
+        attention_kernel<64><<<grid, kAttnThreads, smem_bytes, ctx->stream>>>(p);
+    else
+        attention_kernel<128><<<grid, kAttnThreads, smem_bytes, ctx->stream>>>(p);
     TLC_CHECK_LAUNCH(ctx);
     return TLC_OK;
 }

@@ -626,6 +626,8 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p, size_t smem_fixed) {
     if (!configured[ctx->device & 63]) {
         TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)budget));
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 63] = true;
     }
     gemv_mma_kernel<QT, NT><<<grid, kThreads, smem, ctx->stream>>>(p);

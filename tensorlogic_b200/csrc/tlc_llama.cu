@@ -46,8 +46,8 @@ struct tlc_llama {
     int32_t *ids, *positions, *next_ids;
     int32_t *host_ids;  // pinned staging
     int32_t *host_next;
-    cudaGraphExec_t graph[65];  // decode graph per batch size
-    int launches_per_step = 0;
+    std::map<int, cudaGraphExec_t> graph;  // decode graphs keyed by batch * 8 + parts
+    int launches_in[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // kernels per step, by parts mask
     int heads_local, kv_heads_local, ffn_local, vocab_local;
 };
 
@@ -144,7 +144,6 @@ extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_ll
                 TLC_ERR_SHAPE_MISMATCH, "heads %d / kv heads %d / ffn %d do not divide over %d ranks", c.n_heads,
                 c.n_kv_heads, c.ffn_dim, tp);
     std::unique_ptr<tlc_llama> L(new tlc_llama());
-    memset(L->graph, 0, sizeof(L->graph));
     L->ctx = ctx;
     L->cfg = c;
     L->cfg.tp_size = tp;
@@ -203,6 +202,11 @@ extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_ll
             return tlc_fail(TLC_ERR_ALLOCATION, "activation buffer of %zu bytes failed: %s", b.bytes, cudaGetErrorString(e));
         }
     }
+    // Same shared-memory carve-out as the GEMV and attention kernels they run between.
+    TLC_CUDA(cudaFuncSetAttribute(embed_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  cudaSharedmemCarveoutMaxShared));
+    TLC_CUDA(cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  cudaSharedmemCarveoutMaxShared));
     TLC_CUDA(cudaMemsetAsync(L->positions, 0, 64 * 4, ctx->stream));
     TLC_CUDA(cudaMallocHost(&L->host_ids, R * 4));
     TLC_CUDA(cudaMallocHost(&L->host_next, 64 * 4));
@@ -215,7 +219,7 @@ extern "C" int32_t tlc_llama_destroy(tlc_llama *L) {
     cudaSetDevice(L->ctx->device);
     cudaStreamSynchronize(L->ctx->stream);
     for (auto &g : L->graph)
-        if (g) cudaGraphExecDestroy(g);
+        if (g.second) cudaGraphExecDestroy(g.second);
     tlc_kvcache_destroy(L->cache);
     void *bufs[] = {L->x, L->x1, L->q, L->attn, L->act, L->logits, L->ids, L->positions, L->next_ids};
     for (void *b : bufs) cudaFree(b);
@@ -229,14 +233,17 @@ extern "C" int32_t tlc_llama_destroy(tlc_llama *L) {
 // in L->ids.  decode == false: the rows are consecutive tokens of sequence 0
 // starting at pos0 (prefill).  decode == true: row r is the next token of
 // sequence r at L->positions[r].
-static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logits, bool sample, bool advance) {
+// `parts` selects which launches are issued (1: the quantized linears, 2: the
+// attention, 4: embedding gather and sampling); 7 is the whole step.
+static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logits, bool sample, bool advance,
+                       int parts = 7) {
     tlc_ctx *ctx = L->ctx;
     const tlc_llama_config &c = L->cfg;
     TLC_REQUIRE(c.tp_size == 1, TLC_ERR_INVALID_OPERATION,
                 "this build of the runner executes single-GPU models only (tp_size = %d)", c.tp_size);
     const int d = c.d_model, D = c.head_dim;
     const int64_t kv_row = (int64_t)L->kv_heads_local * D;
-    {
+    if (parts & 4) {
         const size_t total = (size_t)m * (d / 8);
         embed_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
             static_cast<const uint8_t *>(L->tok_embd->data), L->tok_embd->row_pitch, (int)L->tok_embd->n_rows, d,
@@ -249,7 +256,7 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         const LayerWeights &w = L->layers[l];
         void *kc = nullptr, *vc = nullptr;
         tlc_kvcache_layer_ptrs(L->cache, l, &kc, &vc);
-        {
+        if (parts & 1) {
             tlc_gemv_args a;
             a.n_out = 3;
             a.outs[0] = {w.wq, L->q, L->heads_local};
@@ -268,10 +275,11 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
             a.positions = positions;
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
         }
-        if (int32_t rc = tlc_launch_attention(ctx, L->cache, l, L->q, L->attn, decode ? m : 1, decode ? 1 : m,
-                                              L->heads_local, pos0, positions, c.max_seq, scale))
-            return rc;
-        {
+        if (parts & 2)
+            if (int32_t rc = tlc_launch_attention(ctx, L->cache, l, L->q, L->attn, decode ? m : 1, decode ? 1 : m,
+                                                  L->heads_local, pos0, positions, c.max_seq, scale))
+                return rc;
+        if (parts & 1) {
             tlc_gemv_args a;
             a.n_out = 1;
             a.outs[0] = {w.wo, L->x1, 0};
@@ -281,7 +289,7 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
             a.residual = L->x;
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
         }
-        {
+        if (parts & 1) {
             tlc_gemv_args a;
             a.n_out = 2;
             a.outs[0] = {w.w_gate, L->act, 0};
@@ -293,7 +301,7 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
             a.epilogue = TLC_EPI_SWIGLU;
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
         }
-        {
+        if (parts & 1) {
             tlc_gemv_args a;
             a.n_out = 1;
             a.outs[0] = {w.w_down, L->x, 0};
@@ -315,8 +323,9 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         a.m = rows;
         a.norm_w = L->out_norm->data;
         a.eps = c.rms_eps;
-        if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
-        if (sample) {
+        if (parts & 1)
+            if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+        if (sample && (parts & 4)) {
             const int srows = decode ? m : 1;
             const __half *lg = L->logits + (size_t)(rows - srows) * L->vocab_local;
             argmax_advance_kernel<<<srows, 1024, 0, ctx->stream>>>(lg, L->vocab_local, L->next_ids, L->ids,
@@ -380,43 +389,59 @@ extern "C" int32_t tlc_llama_set_state(tlc_llama *L, int32_t batch, const int32_
 }
 
 // Enqueues `steps` greedy decode steps for `batch` sequences (graph replay);
-// nothing is read back.
-extern "C" int32_t tlc_llama_decode_enqueue(tlc_llama *L, int32_t batch, int32_t steps) {
+// nothing is read back.  parts != 7 replays only some of the step's launches
+// (for per-kernel timing) and leaves tokens and positions untouched.
+static int32_t decode_enqueue(tlc_llama *L, int32_t batch, int32_t steps, int parts) {
     TLC_REQUIRE(L, TLC_ERR_INVALID_OPERATION, "llama_decode: null handle");
     if (int32_t rc = tlc_enter(L->ctx)) return rc;
     TLC_REQUIRE(batch >= 1 && batch <= L->cfg.max_batch, TLC_ERR_SHAPE_MISMATCH, "batch %d (max %d)", batch,
                 L->cfg.max_batch);
+    TLC_REQUIRE(parts >= 1 && parts <= 7, TLC_ERR_INVALID_OPERATION, "decode parts mask %d", parts);
     tlc_ctx *ctx = L->ctx;
-    if (!L->graph[batch] && !L->cfg.no_graph) {
+    const bool advance = parts == 7;
+    const int key = batch * 8 + parts;
+    if (!L->graph.count(key) && !L->cfg.no_graph) {
         // Warm every kernel configuration (function attributes, scratch growth)
         // outside the capture, on a throw-away step that does not advance.
-        if (int32_t rc = forward(L, batch, true, 0, false, true, false)) return rc;
+        if (int32_t rc = forward(L, batch, true, 0, false, true, false, parts)) return rc;
         TLC_CUDA(cudaStreamSynchronize(ctx->stream));
         const uint64_t launches_before = ctx->launches;
         TLC_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-        int32_t rc = forward(L, batch, true, 0, false, true, true);
+        int32_t rc = forward(L, batch, true, 0, false, true, advance, parts);
         cudaGraph_t g = nullptr;
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
-        L->launches_per_step = (int)(ctx->launches - launches_before);
+        L->launches_in[parts] = (int)(ctx->launches - launches_before);
         ctx->launches = launches_before;
         if (rc) {
             if (g) cudaGraphDestroy(g);
             return rc;
         }
         if (e != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
-        e = cudaGraphInstantiate(&L->graph[batch], g, 0);
+        cudaGraphExec_t ge = nullptr;
+        e = cudaGraphInstantiate(&ge, g, 0);
         cudaGraphDestroy(g);
         if (e != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+        L->graph[key] = ge;
     }
     for (int s = 0; s < steps; s++) {
         if (L->cfg.no_graph) {
-            if (int32_t rc = forward(L, batch, true, 0, false, true, true)) return rc;
+            const uint64_t before = ctx->launches;
+            if (int32_t rc = forward(L, batch, true, 0, false, true, advance, parts)) return rc;
+            L->launches_in[parts] = (int)(ctx->launches - before);
         } else {
-            TLC_CUDA(cudaGraphLaunch(L->graph[batch], ctx->stream));
-            ctx->launches += (uint64_t)L->launches_per_step;
+            TLC_CUDA(cudaGraphLaunch(L->graph[key], ctx->stream));
+            ctx->launches += (uint64_t)L->launches_in[parts];
         }
     }
     return TLC_OK;
+}
+
+extern "C" int32_t tlc_llama_decode_enqueue(tlc_llama *L, int32_t batch, int32_t steps) {
+    return decode_enqueue(L, batch, steps, 7);
+}
+
+extern "C" int32_t tlc_llama_decode_enqueue_parts(tlc_llama *L, int32_t batch, int32_t steps, int32_t parts) {
+    return decode_enqueue(L, batch, steps, parts);
 }
 
 // One decode step through host buffers: uploads the token ids (NULL: continue
@@ -457,5 +482,7 @@ extern "C" int32_t tlc_llama_read_state(tlc_llama *L, int32_t batch, int32_t *ne
     return TLC_OK;
 }
 
-extern "C" int32_t tlc_llama_launches_per_step(tlc_llama *L) { return L ? L->launches_per_step : 0; }
+extern "C" int32_t tlc_llama_launches_per_step(tlc_llama *L, int32_t parts) {
+    return L && parts >= 1 && parts <= 7 ? L->launches_in[parts] : 0;
+}
 extern "C" tlc_kvcache *tlc_llama_cache(tlc_llama *L) { return L ? L->cache : nullptr; }

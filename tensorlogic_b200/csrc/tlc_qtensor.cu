@@ -66,23 +66,17 @@ __global__ void copy_rows_f16_kernel(const uint8_t *__restrict__ data, size_t ro
 // ---------------------------------------------------------------------------
 __global__ void synth_blocks_kernel(uint8_t *__restrict__ data, size_t row_pitch, int type,
                                     int blocks_per_row, int64_t n_rows, int64_t row0, int64_t bc0,
-                                    int64_t full_blocks_per_row, uint64_t key) {
+                                    int64_t full_blocks_per_row, uint64_t key, int scale_log2) {
     int64_t lb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (lb >= n_rows * blocks_per_row) return;
     int64_t row = lb / blocks_per_row;
     int bc = (int)(lb % blocks_per_row);
     uint64_t gb = (uint64_t)((row0 + row) * full_blocks_per_row + bc0 + bc);
-    if (type == TLC_TYPE_Q4_0) {
-        uint8_t tmp[18];
-        tlc_synth_q4_0_block(key, gb, tmp);
-        uint8_t *dst = data + row * row_pitch + (size_t)bc * 18;
-        for (int i = 0; i < 18; i++) dst[i] = tmp[i];
-    } else {
-        uint8_t tmp[34];
-        tlc_synth_q8_0_block(key, gb, tmp);
-        uint8_t *dst = data + row * row_pitch + (size_t)bc * 34;
-        for (int i = 0; i < 34; i++) dst[i] = tmp[i];
-    }
+    // The block is written straight to its (2-byte aligned) place in HBM.
+    if (type == TLC_TYPE_Q4_0)
+        tlc_synth_q4_0_block(key, gb, scale_log2, data + row * row_pitch + (size_t)bc * 18);
+    else
+        tlc_synth_q8_0_block(key, gb, scale_log2, data + row * row_pitch + (size_t)bc * 34);
 }
 
 // ---------------------------------------------------------------------------
@@ -210,8 +204,9 @@ extern "C" int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows
 }
 
 extern "C" int32_t tlc_qtensor_create_synthetic(tlc_ctx *ctx, int32_t type, int64_t n_rows, int64_t n_cols,
-                                                uint64_t seed, uint64_t tensor_id, int32_t tp_rank,
-                                                int32_t tp_size, int32_t split, tlc_qtensor **out) {
+                                                uint64_t seed, uint64_t tensor_id, int32_t scale_log2,
+                                                int32_t tp_rank, int32_t tp_size, int32_t split,
+                                                tlc_qtensor **out) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
     TLC_REQUIRE(out, TLC_ERR_INVALID_OPERATION, "tlc_qtensor_create_synthetic: null pointer");
     *out = nullptr;
@@ -234,7 +229,7 @@ extern "C" int32_t tlc_qtensor_create_synthetic(tlc_ctx *ctx, int32_t type, int6
     int64_t grid = (total + threads - 1) / threads;
     synth_blocks_kernel<<<(unsigned)grid, threads, 0, ctx->stream>>>(
         static_cast<uint8_t *>(qt->data), qt->row_pitch, type, bpr, rows, row0, col0 / 32, n_cols / 32,
-        tlc_synth_key(seed, tensor_id));
+        tlc_synth_key(seed, tensor_id), scale_log2);
     ctx->launches++;
     e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -246,8 +241,8 @@ extern "C" int32_t tlc_qtensor_create_synthetic(tlc_ctx *ctx, int32_t type, int6
     return TLC_OK;
 }
 
-extern "C" int32_t tlc_synth_blocks_host(int32_t type, uint64_t seed, uint64_t tensor_id, int64_t first_block,
-                                         int64_t n_blocks, void *out_host) {
+extern "C" int32_t tlc_synth_blocks_host(int32_t type, uint64_t seed, uint64_t tensor_id, int32_t scale_log2,
+                                         int64_t first_block, int64_t n_blocks, void *out_host) {
     TLC_REQUIRE(type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0, TLC_ERR_INVALID_OPERATION,
                 "synthetic weights exist for Q4_0 and Q8_0 only (got type %d)", type);
     TLC_REQUIRE(out_host && first_block >= 0 && n_blocks >= 0, TLC_ERR_INVALID_OPERATION,
@@ -257,9 +252,9 @@ extern "C" int32_t tlc_synth_blocks_host(int32_t type, uint64_t seed, uint64_t t
     const size_t bb = tlc_block_bytes(type);
     for (int64_t i = 0; i < n_blocks; i++) {
         if (type == TLC_TYPE_Q4_0)
-            tlc_synth_q4_0_block(key, (uint64_t)(first_block + i), o + (size_t)i * bb);
+            tlc_synth_q4_0_block(key, (uint64_t)(first_block + i), scale_log2, o + (size_t)i * bb);
         else
-            tlc_synth_q8_0_block(key, (uint64_t)(first_block + i), o + (size_t)i * bb);
+            tlc_synth_q8_0_block(key, (uint64_t)(first_block + i), scale_log2, o + (size_t)i * bb);
     }
     return TLC_OK;
 }

@@ -4,7 +4,9 @@
 //
 //   key        = mix64(mix64(seed) ^ tensor_id)
 //   r(i)       = mix64(key + i)
-//   Q4_0 block b: d = f16_rne(float(2000 + r(3b) % 18001) * 1e-6f)   (U[0.002, 0.02])
+//   Q4_0 block b: d = f16_rne(float(2000 + r(3b) % 18001) * 1e-6f * 2^scale_log2)
+//                 (U[0.002, 0.02] for scale_log2 = 0; deep random-weight models use
+//                 negative exponents so that activations stay inside the f16 range)
 //                 qs[0..7] = bytes of r(3b+1), qs[8..15] = bytes of r(3b+2)  (little endian)
 //   Q8_0 block b: d as above from r(9b); q[4j..4j+3] = ((u16 * 255) >> 16) - 127 over
 //                 the four 16-bit fields of r(9b+1+j), j = 0..7      (U{-127..127})
@@ -24,7 +26,7 @@ __host__ __device__ inline uint64_t tlc_synth_key(uint64_t seed, uint64_t tensor
     return tlc_mix64(tlc_mix64(seed) ^ tensor_id);
 }
 
-__host__ __device__ inline uint16_t tlc_synth_scale_bits(uint64_t r) {
+__host__ __device__ inline uint16_t tlc_synth_scale_bits(uint64_t r, int scale_log2) {
     float v = (float)(uint32_t)(2000u + (uint32_t)(r % 18001ull));
 #ifdef __CUDA_ARCH__
     float d = __fmul_rn(v, 1e-6f);
@@ -32,12 +34,13 @@ __host__ __device__ inline uint16_t tlc_synth_scale_bits(uint64_t r) {
     volatile float dv = v * 1e-6f;
     float d = dv;
 #endif
-    __half h = __float2half_rn(d);
-    return __half_as_ushort(h);
+    d = ldexpf(d, scale_log2);  // exact: a power-of-two factor
+    const __half_raw h = __float2half_rn(d);
+    return h.x;
 }
 
-__host__ __device__ inline void tlc_synth_q4_0_block(uint64_t key, uint64_t b, uint8_t *out18) {
-    uint16_t d = tlc_synth_scale_bits(tlc_mix64(key + 3 * b));
+__host__ __device__ inline void tlc_synth_q4_0_block(uint64_t key, uint64_t b, int scale_log2, uint8_t *out18) {
+    uint16_t d = tlc_synth_scale_bits(tlc_mix64(key + 3 * b), scale_log2);
     out18[0] = (uint8_t)(d & 0xFF);
     out18[1] = (uint8_t)(d >> 8);
     uint64_t r1 = tlc_mix64(key + 3 * b + 1), r2 = tlc_mix64(key + 3 * b + 2);
@@ -47,8 +50,8 @@ __host__ __device__ inline void tlc_synth_q4_0_block(uint64_t key, uint64_t b, u
     }
 }
 
-__host__ __device__ inline void tlc_synth_q8_0_block(uint64_t key, uint64_t b, uint8_t *out34) {
-    uint16_t d = tlc_synth_scale_bits(tlc_mix64(key + 9 * b));
+__host__ __device__ inline void tlc_synth_q8_0_block(uint64_t key, uint64_t b, int scale_log2, uint8_t *out34) {
+    uint16_t d = tlc_synth_scale_bits(tlc_mix64(key + 9 * b), scale_log2);
     out34[0] = (uint8_t)(d & 0xFF);
     out34[1] = (uint8_t)(d >> 8);
     for (int j = 0; j < 8; j++) {

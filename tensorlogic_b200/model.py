@@ -123,11 +123,27 @@ def get_tensor(model: Model, name: str) -> QTensor:
     return model.get_tensor(name)
 
 
+def weight_scale_log2(qtype: int, cols: int, residual_writer: bool = False) -> int:
+    """Power-of-two factor applied to the block scales of a model's linear weights.
+
+    Blocks with d ~ U[0.002, 0.02] have rms 0.0565 (Q4_0) / 0.89 (Q8_0), so a linear over K inputs
+    amplifies by rms*sqrt(K) (2.6x at K=2048 for Q4_0); stacked 22 or 80 times with residuals the f16
+    activations overflow (the CPU oracle shows inf at layer 15 of the TinyLlama shape).  Full-model
+    configurations therefore scale d by the power of two that brings that gain closest to 1; the
+    single-linear configurations keep the unscaled range.  The projections that write into the
+    residual stream (attn_output, ffn_down) get a further 2^-2: uniform nibbles have mean 7.5 - 8,
+    so every weight row carries a small negative mean that accumulates layer after layer.
+    """
+    rms = 0.0565 if qtype == _lib.TYPE_Q4_0 else 0.892
+    return -int(round(float(np.log2(rms * np.sqrt(cols))))) - (2 if residual_writer else 0)
+
+
 def synthetic_host_weights(arch: LlamaArch, seed: int, qtype: int = _lib.TYPE_Q4_0) -> dict:
     """Seeded synthetic weights as host arrays: name -> (ggml_type, array).
 
-    Linear weights are Q4_0/Q8_0 blocks from the counter-based generator;
-    embeddings f16 N(0,1)*0.02 and norm weights f16 1 + N(0, 0.02).
+    Linear weights are Q4_0/Q8_0 blocks from the counter-based generator (block scales
+    U[0.002, 0.02] * 2^weight_scale_log2); embeddings f16 N(0,1)*0.02 and norm weights
+    f16 1 + N(0, 0.02).
     """
     out = {}
     for name, (rows, cols) in arch.tensor_shapes().items():
@@ -136,7 +152,8 @@ def synthetic_host_weights(arch: LlamaArch, seed: int, qtype: int = _lib.TYPE_Q4
         elif name == "token_embd.weight":
             out[name] = (_lib.TYPE_F16, synth.embedding_table(seed, name, rows, cols))
         else:
-            out[name] = (qtype, synth.blocks(qtype, seed, synth.tensor_id(name), rows, cols))
+            out[name] = (qtype, synth.blocks(qtype, seed, synth.tensor_id(name), rows, cols,
+                                             scale_log2=weight_scale_log2(qtype, cols, name.endswith(_COL_SPLIT))))
     return out
 
 
@@ -151,7 +168,8 @@ def synthetic_model(dev: Device, arch: LlamaArch, seed: int, qtype: int = _lib.T
             t = QTensor.from_blocks(dev, _lib.TYPE_F16, rows, cols, synth.embedding_table(seed, name, rows, cols))
         else:
             t = QTensor.synthetic(dev, qtype, rows, cols, seed, synth.tensor_id(name), tp_rank, tp_size,
-                                  split_for(name) if tp_size > 1 else _lib.SPLIT_NONE)
+                                  split_for(name) if tp_size > 1 else _lib.SPLIT_NONE,
+                                  scale_log2=weight_scale_log2(qtype, cols, name.endswith(_COL_SPLIT)))
         m.add(name, t)
     return m
 
@@ -225,8 +243,13 @@ class Llama:
                                                  logits.ctypes.data if logits is not None else None))
         return nxt, logits
 
-    def decode_enqueue(self, batch: int, steps: int) -> None:
-        check(self.dev.lib.tlc_llama_decode_enqueue(self.handle, batch, steps))
+    def decode_enqueue(self, batch: int, steps: int, parts: int = 7) -> None:
+        """Enqueue greedy steps on the device; parts (1 linears | 2 attention | 4 gather+sample) != 7
+        replays only those launches, for per-kernel timing."""
+        if parts == 7:
+            check(self.dev.lib.tlc_llama_decode_enqueue(self.handle, batch, steps))
+        else:
+            check(self.dev.lib.tlc_llama_decode_enqueue_parts(self.handle, batch, steps, parts))
 
     def read_state(self, batch: int = 1):
         nxt, pos = np.empty(batch, np.int32), np.empty(batch, np.int32)
@@ -234,6 +257,9 @@ class Llama:
                                                 pos.ctypes.data_as(C.POINTER(C.c_int32))))
         return nxt, pos
 
+    def launches(self, parts: int = 7) -> int:
+        return int(self.dev.lib.tlc_llama_launches_per_step(self.handle, parts))
+
     @property
     def launches_per_step(self) -> int:
-        return int(self.dev.lib.tlc_llama_launches_per_step(self.handle))
+        return self.launches(7)

@@ -44,13 +44,15 @@ def _r(k: np.uint64, idx: np.ndarray) -> np.ndarray:
         return mix64(np.uint64(k) + idx.astype(np.uint64))
 
 
-def _scale_bits(r: np.ndarray) -> np.ndarray:
+def _scale_bits(r: np.ndarray, scale_log2: int = 0) -> np.ndarray:
     v = (np.uint64(2000) + r % np.uint64(18001)).astype(np.float32)
     d = (v * np.float32(1e-6)).astype(np.float32)
+    d = np.ldexp(d, scale_log2).astype(np.float32)  # exact power-of-two factor
     return d.astype(np.float16).view(np.uint16)
 
 
-def q4_0_blocks(seed: int, tid: int, n_rows: int, n_cols: int, row0: int = 0, rows: int | None = None) -> np.ndarray:
+def q4_0_blocks(seed: int, tid: int, n_rows: int, n_cols: int, row0: int = 0, rows: int | None = None,
+                scale_log2: int = 0) -> np.ndarray:
     """uint8 [rows, n_cols/32, 18]: the blocks of rows [row0, row0+rows) of the full tensor."""
     assert n_cols % 32 == 0
     rows = n_rows - row0 if rows is None else rows
@@ -58,7 +60,7 @@ def q4_0_blocks(seed: int, tid: int, n_rows: int, n_cols: int, row0: int = 0, ro
     b = (np.arange(rows * bpr, dtype=np.uint64) + np.uint64(row0 * bpr))
     k = key(seed, tid)
     with np.errstate(over="ignore"):
-        d = _scale_bits(_r(k, np.uint64(3) * b))
+        d = _scale_bits(_r(k, np.uint64(3) * b), scale_log2)
         r1 = _r(k, np.uint64(3) * b + np.uint64(1))
         r2 = _r(k, np.uint64(3) * b + np.uint64(2))
     out = np.empty((rows * bpr, 18), np.uint8)
@@ -68,7 +70,8 @@ def q4_0_blocks(seed: int, tid: int, n_rows: int, n_cols: int, row0: int = 0, ro
     return out.reshape(rows, bpr, 18)
 
 
-def q8_0_blocks(seed: int, tid: int, n_rows: int, n_cols: int, row0: int = 0, rows: int | None = None) -> np.ndarray:
+def q8_0_blocks(seed: int, tid: int, n_rows: int, n_cols: int, row0: int = 0, rows: int | None = None,
+                scale_log2: int = 0) -> np.ndarray:
     """uint8 [rows, n_cols/32, 34]."""
     assert n_cols % 32 == 0
     rows = n_rows - row0 if rows is None else rows
@@ -77,7 +80,7 @@ def q8_0_blocks(seed: int, tid: int, n_rows: int, n_cols: int, row0: int = 0, ro
     k = key(seed, tid)
     out = np.empty((rows * bpr, 34), np.uint8)
     with np.errstate(over="ignore"):
-        out[:, 0:2] = _scale_bits(_r(k, np.uint64(9) * b)).astype("<u2").view(np.uint8).reshape(-1, 2)
+        out[:, 0:2] = _scale_bits(_r(k, np.uint64(9) * b), scale_log2).astype("<u2").view(np.uint8).reshape(-1, 2)
         for j in range(8):
             r = _r(k, np.uint64(9) * b + np.uint64(1 + j))
             u = r.astype("<u8").view("<u2").reshape(-1, 4).astype(np.int64)

@@ -64,14 +64,23 @@ def test_host_generator_matches_numpy(lib, qtype, bb):
     n_rows, n_cols = 6, 256
     want = synth.blocks(qtype, seed, tid, n_rows, n_cols)
     got = np.empty((n_rows * (n_cols // 32), bb), np.uint8)
-    assert lib.tlc_synth_blocks_host(qtype, seed, tid, 0, got.shape[0], got.ctypes.data) == 0
+    assert lib.tlc_synth_blocks_host(qtype, seed, tid, 0, 0, got.shape[0], got.ctypes.data) == 0
     assert np.array_equal(got.reshape(want.shape), want)
     # a shard generated on its own equals the slice of the whole
     part = synth.blocks(qtype, seed, tid, n_rows, n_cols, row0=2, rows=3)
     assert np.array_equal(part, want[2:5])
     got2 = np.empty((3 * 8, bb), np.uint8)
-    assert lib.tlc_synth_blocks_host(qtype, seed, tid, 2 * 8, 24, got2.ctypes.data) == 0
+    assert lib.tlc_synth_blocks_host(qtype, seed, tid, 0, 2 * 8, 24, got2.ctypes.data) == 0
     assert np.array_equal(got2.reshape(part.shape), part)
+    # scaled variant: d * 2^-2, same quantized values
+    sc = synth.blocks(qtype, seed, tid, n_rows, n_cols, scale_log2=-2)
+    got3 = np.empty_like(got)
+    assert lib.tlc_synth_blocks_host(qtype, seed, tid, -2, 0, got3.shape[0], got3.ctypes.data) == 0
+    assert np.array_equal(got3.reshape(sc.shape), sc)
+    assert np.array_equal(sc[..., 2:], want[..., 2:])
+    d0 = want[..., :2].copy().view(np.float16).astype(np.float32)
+    d2 = sc[..., :2].copy().view(np.float16).astype(np.float32)
+    assert np.allclose(d2, d0 / 4, rtol=1e-3)
 
 
 def test_synthetic_distributions():

@@ -135,7 +135,8 @@ def test_ragged_shapes(dev, ref, qtype, n, k, m):
     y = linear(dev.tensor(x), w).numpy()
     want = ref.linear_q(qtype, raw, n, k, x)
     assert y.shape == (m, n)
-    assert rel_l2(y, want) < TIGHT
+    # a handful of outputs cannot average out the oracle's f16 rounding of each weight
+    assert rel_l2(y, want) < (TIGHT if n * m >= 64 else TOL)
 
 
 def test_more_than_16_rows_is_chunked(dev, ref):

@@ -237,3 +237,15 @@ def test_embedding_bounds(ref):
     assert np.array_equal(ref.embedding(t, [2, 0]), t[[2, 0]])
     with pytest.raises(IndexError):
         ref.embedding(t, [4])
+
+
+def test_literal_matmul_hardware_and_software_conversions_agree(ref):
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal((2, 300)) * 3).astype(np.float16)
+    w = rng.uniform(-0.3, 0.3, (17, 300)).astype(np.float16)
+    ref.set_f16c(True)
+    hw = ref.linear_literal(x, w)
+    ref.set_f16c(False)
+    sw = ref.linear_literal(x, w)
+    ref.set_f16c(True)
+    assert np.array_equal(hw.view(np.uint16), sw.view(np.uint16))
