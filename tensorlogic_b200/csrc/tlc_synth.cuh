@@ -39,26 +39,32 @@ __host__ __device__ inline uint16_t tlc_synth_scale_bits(uint64_t r, int scale_l
     return h.x;
 }
 
+// Blocks are assembled in 64-bit words and emitted as 16-bit units: a block
+// always starts on a 2-byte boundary (18- and 34-byte blocks, 16-byte aligned
+// rows), so no store ever touches a neighbouring block's bytes.
+__host__ __device__ inline void tlc_synth_put16(uint8_t *dst, uint64_t w, int n_units) {
+    uint16_t *d16 = reinterpret_cast<uint16_t *>(dst);
+    for (int i = 0; i < n_units; i++) d16[i] = (uint16_t)(w >> (16 * i));
+}
+
 __host__ __device__ inline void tlc_synth_q4_0_block(uint64_t key, uint64_t b, int scale_log2, uint8_t *out18) {
-    uint16_t d = tlc_synth_scale_bits(tlc_mix64(key + 3 * b), scale_log2);
-    out18[0] = (uint8_t)(d & 0xFF);
-    out18[1] = (uint8_t)(d >> 8);
-    uint64_t r1 = tlc_mix64(key + 3 * b + 1), r2 = tlc_mix64(key + 3 * b + 2);
-    for (int i = 0; i < 8; i++) {
-        out18[2 + i] = (uint8_t)(r1 >> (8 * i));
-        out18[10 + i] = (uint8_t)(r2 >> (8 * i));
-    }
+    const uint64_t d = tlc_synth_scale_bits(tlc_mix64(key + 3 * b), scale_log2);
+    const uint64_t r1 = tlc_mix64(key + 3 * b + 1), r2 = tlc_mix64(key + 3 * b + 2);
+    tlc_synth_put16(out18, d | (r1 << 16), 4);                 // d, qs[0..5]
+    tlc_synth_put16(out18 + 8, (r1 >> 48) | (r2 << 16), 4);    // qs[6..13]
+    tlc_synth_put16(out18 + 16, r2 >> 48, 1);                  // qs[14..15]
 }
 
 __host__ __device__ inline void tlc_synth_q8_0_block(uint64_t key, uint64_t b, int scale_log2, uint8_t *out34) {
-    uint16_t d = tlc_synth_scale_bits(tlc_mix64(key + 9 * b), scale_log2);
-    out34[0] = (uint8_t)(d & 0xFF);
-    out34[1] = (uint8_t)(d >> 8);
+    const uint64_t d = tlc_synth_scale_bits(tlc_mix64(key + 9 * b), scale_log2);
+    tlc_synth_put16(out34, d, 1);
     for (int j = 0; j < 8; j++) {
-        uint64_t r = tlc_mix64(key + 9 * b + 1 + j);
+        const uint64_t r = tlc_mix64(key + 9 * b + 1 + j);
+        uint64_t q4 = 0;
         for (int i = 0; i < 4; i++) {
-            uint32_t u = (uint32_t)((r >> (16 * i)) & 0xFFFF);
-            out34[2 + 4 * j + i] = (uint8_t)(int8_t)((int)((u * 255u) >> 16) - 127);
+            const uint32_t u = (uint32_t)((r >> (16 * i)) & 0xFFFF);
+            q4 |= (uint64_t)(uint8_t)(int8_t)((int)((u * 255u) >> 16) - 127) << (8 * i);
         }
+        tlc_synth_put16(out34 + 2 + 4 * j, q4, 2);
     }
 }
