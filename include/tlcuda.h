@@ -273,6 +273,31 @@ TLC_API int32_t tlc_attention(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer, c
                               int32_t q_pos0, const int32_t *positions_dev, int32_t max_keys,
                               float scale);
 
+/* Decode attention that allocates nothing (no counterpart in the reference: it
+ * exists for hosts of this library that cannot request device memory while
+ * they decode -- a CUDA-graph capture in progress, a serving loop that must
+ * not hit the device-wide synchronisation of cudaMalloc, or a process whose
+ * memory manager owns all of HBM).  Same computation as tlc_attention with
+ * positions_dev (one query per sequence), on caller-owned buffers:
+ *   q, out        [batch, n_heads, head_dim] f16
+ *   k/v_cache_dev [batch, max_seq, n_kv_heads, head_dim] f16 (one layer)
+ * launched on `stream` (a cudaStream_t) of the CURRENT device.  The split-key
+ * partial results and ticket counters live in a 2 MiB + 4 KiB array inside the
+ * library image, per GPU, for the life of the process; a call is rejected
+ * (TLC_ERR_BUFFER_EXHAUSTED) when batch * n_heads * splits * (head_dim + 2) * 4
+ * bytes exceed 2 MiB (splits = key splits the launch uses, about 2 * SMs /
+ * (batch * n_kv_heads), at most max_keys / 64) or batch * n_kv_heads exceeds 1024.  The first call on a
+ * device looks the array's address up (cudaGetSymbolAddress) and sets kernel
+ * attributes; make that first call before any stream capture.  All calls on a
+ * device share the array: two calls that overlap on the GPU (different
+ * streams) race; calls on one stream are safe.  Never calls cudaMalloc /
+ * cudaFree or any allocating routine. */
+TLC_API int32_t tlc_attention_decode_static(void *stream, const void *q_dev, const void *k_cache_dev,
+                                            const void *v_cache_dev, void *out_dev, int32_t batch,
+                                            int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                                            int32_t max_seq, const int32_t *positions_dev,
+                                            int32_t max_keys, float scale);
+
 /* ---- GGUF models ----------------------------------------------------------- */
 
 /* load_model(path) (src/interpreter/builtin_model.rs:106-131 -> Model::load,

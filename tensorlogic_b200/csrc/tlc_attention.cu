@@ -529,3 +529,120 @@ extern "C" int32_t tlc_attention(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer
     return tlc_launch_attention(ctx, cache, layer, q_dev, out_dev, batch, n_queries, n_heads, q_pos0,
                                 positions_dev, max_keys, scale);
 }
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Some hosts of this library run the decode step from places where device
+// memory cannot be requested: inside a CUDA-graph capture or a latency-critical
+// serving loop (cudaMalloc synchronises the device and is illegal while
+// capturing), or under a memory manager that owns every byte of HBM and hands
+// the library nothing.  tlc_attention() above grows a scratch block with
+// cudaMalloc when the split-key partials do not fit.  This variant keeps the
+// partials and the ticket counters in a fixed array inside the library image
+// instead: kStaticScratchBytes of device memory per GPU that loads the library,
+// held until the process exits.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticPartialBytes = (size_t)2 << 20;  // split-key partials (max, sum, O)
+constexpr size_t kStaticTicketBytes = 4096;              // one int per (sequence, KV head)
+constexpr size_t kStaticScratchBytes = kStaticPartialBytes + kStaticTicketBytes;
+
+static __device__ __align__(256) unsigned char g_static_attention_scratch[kStaticScratchBytes];
+
+struct StaticSetup {
+    bool done = false;
+    unsigned char *scratch = nullptr;  // device address of g_static_attention_scratch on that device
+    int sm_count = 0;
+};
+StaticSetup g_static_setup[64];
+
+}  // namespace
+
+extern "C" int32_t tlc_attention_decode_static(void *stream, const void *q_dev, const void *k_cache_dev,
+                                               const void *v_cache_dev, void *out_dev, int32_t batch,
+                                               int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                                               int32_t max_seq, const int32_t *positions_dev, int32_t max_keys,
+                                               float scale) {
+    TLC_REQUIRE(q_dev && k_cache_dev && v_cache_dev && out_dev && positions_dev, TLC_ERR_INVALID_OPERATION,
+                "attention_decode_static: null pointer");
+    TLC_REQUIRE(batch >= 1 && n_heads >= 1 && n_kv_heads >= 1 && n_heads % n_kv_heads == 0, TLC_ERR_SHAPE_MISMATCH,
+                "attention_decode_static: batch %d, %d query heads over %d KV heads", batch, n_heads, n_kv_heads);
+    const int G = n_heads / n_kv_heads, D = head_dim;
+    TLC_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8 || G == 16, TLC_ERR_INVALID_OPERATION,
+                "attention: group size %d unsupported (1, 2, 4, 8, 16)", G);
+    TLC_REQUIRE(D == 64 || D == 128, TLC_ERR_INVALID_OPERATION, "attention: head_dim %d unsupported (64, 128)", D);
+    TLC_REQUIRE(max_keys >= 1 && max_keys <= max_seq, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d", max_keys,
+                max_seq);
+    int device = 0;
+    TLC_CUDA(cudaGetDevice(&device));
+    TLC_REQUIRE(device >= 0 && device < 64, TLC_ERR_DEVICE, "device ordinal %d out of range", device);
+    StaticSetup &su = g_static_setup[device];
+    const size_t smem = (size_t)4 * kTileKeys * (D + 8) * sizeof(__half);
+    const size_t smem_o = (size_t)4 * 16 * D * sizeof(float);
+    const size_t smem_bytes = smem > smem_o ? smem : smem_o;
+    if (!su.done) {
+        // First call on this device (which is the current one): in host code the
+        // array's name is only a stand-in, the kernel needs its device address.
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_attention_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            cudaGetLastError();
+            return tlc_fail(TLC_ERR_CUDA, "cudaGetSymbolAddress(static attention scratch) failed on device %d: %s",
+                            device, cudaGetErrorString(e));
+        }
+        TLC_CUDA(cudaDeviceGetAttribute(&su.sm_count, cudaDevAttrMultiProcessorCount, device));
+        TLC_CUDA(cudaFuncSetAttribute(attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)((size_t)4 * kTileKeys * (64 + 8) * sizeof(__half))));
+        TLC_CUDA(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)((size_t)4 * kTileKeys * (128 + 8) * sizeof(__half))));
+        su.scratch = static_cast<unsigned char *>(p);
+        su.done = true;
+    }
+
+    AttnParams p{};
+    p.q = static_cast<const __half *>(q_dev);
+    p.kc = static_cast<const __half *>(k_cache_dev);
+    p.vc = static_cast<const __half *>(v_cache_dev);
+    p.out = static_cast<__half *>(out_dev);
+    p.I = 1;
+    p.H = n_heads;
+    p.Hkv = n_kv_heads;
+    p.G = G;
+    p.Tmax = max_seq;
+    p.q_pos0 = 0;
+    p.positions = positions_dev;
+    p.scale = scale;
+    p.q_tiles = 1;
+    const int tiles = (max_keys + kTileKeys - 1) / kTileKeys;
+    const int want = (2 * su.sm_count + batch * n_kv_heads - 1) / (batch * n_kv_heads);
+    int nsplit = tiles < want ? tiles : want;
+    if (nsplit < 1) nsplit = 1;
+    if (nsplit > 64) nsplit = 64;
+    p.nsplit = nsplit;
+    p.keys_per_split = ((tiles + nsplit - 1) / nsplit) * kTileKeys;
+    const size_t rows = (size_t)batch * n_heads;
+    const size_t ml = rows * nsplit * 2 * sizeof(float), po = rows * nsplit * D * sizeof(float);
+    TLC_REQUIRE(nsplit == 1 || ml + po <= kStaticPartialBytes, TLC_ERR_BUFFER_EXHAUSTED,
+                "attention_decode_static: %d sequences x %d heads x %d key splits need %zu bytes of partials, the "
+                "built-in scratch holds %zu; use tlc_attention or a smaller batch",
+                batch, n_heads, nsplit, ml + po, kStaticPartialBytes);
+    TLC_REQUIRE((size_t)batch * n_kv_heads * sizeof(int) <= kStaticTicketBytes, TLC_ERR_BUFFER_EXHAUSTED,
+                "attention_decode_static: %d x %d (sequence, KV head) pairs exceed the %zu built-in tickets", batch,
+                n_kv_heads, kStaticTicketBytes / sizeof(int));
+    p.part_ml = reinterpret_cast<float *>(su.scratch);
+    p.part_o = reinterpret_cast<float *>(su.scratch + ml);
+    p.counters = reinterpret_cast<int *>(su.scratch + kStaticPartialBytes);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left; only the tickets must start at zero.
+    TLC_CUDA(cudaMemsetAsync(p.counters, 0, (size_t)batch * n_kv_heads * sizeof(int), st));
+    dim3 grid(nsplit, n_kv_heads, batch);
+    if (D == 64)
+        attention_kernel<64><<<grid, kAttnThreads, smem_bytes, st>>>(p);
+    else
+        attention_kernel<128><<<grid, kAttnThreads, smem_bytes, st>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    return TLC_OK;
+}
