@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     __shared__ float sm_m[4][16], sm_l[4][16];
     __shared__ int sm_last;
 
+    tlc_pdl_prologue();  // q and the cache rows of this step come from the previous kernel
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int b = blockIdx.z, hk = blockIdx.y;
@@ -441,10 +442,12 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
         }
         configured[di][ctx->device & 63] = true;
     }
-    if (D == 64)
-        attention_kernel<64><<<grid, kAttnThreads, smem_bytes, ctx->stream>>>(p);
-    else
-        attention_kernel<128><<<grid, kAttnThreads, smem_bytes, ctx->stream>>>(p);
+    cudaError_t le = D == 64 ? tlc_launch_pdl(ctx, attention_kernel<64>, grid, dim3(kAttnThreads), smem_bytes, p)
+                             : tlc_launch_pdl(ctx, attention_kernel<128>, grid, dim3(kAttnThreads), smem_bytes, p);
+    if (le != cudaSuccess) {
+        cudaGetLastError();
+        return tlc_fail(TLC_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(le));
+    }
     TLC_CHECK_LAUNCH(ctx);
     return TLC_OK;
 }

@@ -3,6 +3,7 @@
 // Takes the place of MetalDevice (src/device/metal_device.rs), BufferPool
 // (src/device/buffer_pool.rs) and MetalBuffer's copies
 // (src/device/metal_buffer.rs) of the TensorLogic project.
+#include <cstdlib>
 #include <cstring>
 
 #include "tlc_internal.h"
@@ -71,6 +72,10 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     }
     memset(ctx->host_status, 0, sizeof(tlc_dev_status));
     ctx->n_tickets = 16384;
+    const char *no_pdl = getenv("TLC_NO_PDL");
+    ctx->use_pdl = !(no_pdl && no_pdl[0] == '1');
+    if (const char *e = getenv("TLC_PDL_MODE")) ctx->pdl_mode = atoi(e);
+    if (const char *e = getenv("TLC_PDL_SMALL")) ctx->pdl_small = atoi(e) != 0;
     *out = ctx;
     return TLC_OK;
 }

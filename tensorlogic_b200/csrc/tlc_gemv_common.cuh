@@ -1,0 +1,175 @@
+// Shared pieces of the fused dequant-GEMV: launch parameters, block-format
+// traits and the PTX wrappers (mbarrier, bulk async copy, mma.sync, programmatic
+// dependent launch).
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "tlc_internal.h"
+
+namespace tlc_gemv {
+
+constexpr int kRows = 16;  // rows of W per slab (the M of m16n8k16)
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+template <int QT> struct QTraits;
+template <> struct QTraits<TLC_TYPE_Q4_0> {
+    static constexpr int BB = 18;         // bytes per block
+    static constexpr int KCB = 64;        // blocks per ring stage and row (1152 B)
+    static constexpr int PAIR_WORDS = 9;  // 32-bit words per (even, odd) block pair
+    static constexpr float OFFSET = 8.0f;
+};
+template <> struct QTraits<TLC_TYPE_Q8_0> {
+    static constexpr int BB = 34;
+    static constexpr int KCB = 32;  // 1088 B
+    static constexpr int PAIR_WORDS = 17;
+    static constexpr float OFFSET = 128.0f;
+};
+
+// Shared-memory distance between the rows of a stage: the smallest odd
+// multiple of 16 bytes that holds a row segment, so that the 8 row groups of a
+// warp-wide 32-bit load fall into 8 different bank quads.
+__host__ __device__ constexpr int stage_pitch(int seg_bytes) {
+    int units = (seg_bytes + 15) / 16;
+    return (units | 1) * 16;
+}
+
+struct GemvTensor {
+    const uint8_t *w;
+    size_t pitch;
+    int n;  // rows of W (outputs)
+    __half *y;
+    int rope_heads;
+    int head_dim;
+    long long row_stride;  // elements between the outputs of consecutive activation rows
+    long long pos_stride;  // elements per position (0 unless the destination is a KV cache)
+};
+
+struct GemvParams {
+    GemvTensor t[3];
+    int n_out;
+    int slabs[3];
+    int total_units;
+    int subs;      // slabs per unit (2 for the gate/up pair)
+    int k;
+    int nblk;      // k / 32
+    int nblk_pad;  // rounded up to even
+    int nchunks;   // ring stages per slab
+    int m;
+    const __half *x;
+    const __half *norm_w;
+    float eps;
+    int epilogue;
+    const __half *bias;
+    const __half *residual;
+    int pos_offset;
+    float rope_base;
+    const int *positions;
+    int nstages;
+    int pdl_mode;  // 1: let the next kernel be scheduled at once, 2: only when this CTA's last slab is done
+    tlc_dev_status *status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kWaitLimit polls, records where, and raises the
+// CTA's abort flag; once that flag is up every later wait only polls briefly
+// (long enough for copies already in flight to land) so the kernel drains and
+// returns instead of hanging.  The result is made warp-uniform by the callers.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          tlc_dev_status *status, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint32_t limit = *abort_flag ? 4096u : kWaitLimit;
+    for (uint32_t i = 0; i < limit; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    *abort_flag = 1;
+    if (atomicCAS(&status->code, 0, 1) == 0) status->where = where;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void consumer_bar() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+// Programmatic dependent launch: let the next kernel of the stream be scheduled
+// now (it may start fetching its weights), and wait for the previous kernel's
+// results before touching anything it wrote.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                         const float (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]),
+          "f"(c[3]));
+}
+
+// Integer fragments of one block for rows g (w0*) and g+8 (w1*).
+//   Q4_0: one 32-bit word of nibbles per row; every nibble is moved to the
+//   lowest mantissa bits, so all fragments carry the same 2^-24 and the
+//   activations need no per-slot scaling.
+//     a1: elems {4t, 4t+2 | 16+4t, 18+4t}   a2: elems {4t+1, 4t+3 | 17+4t, 19+4t}
+//   Q8_0: two words of int8 per row, biased to unsigned ((q+128) * 2^-24).
+//     a1: elems {8t, 8t+1 | 8t+2, 8t+3}     a2: elems {8t+4, 8t+5 | 8t+6, 8t+7}
+template <int QT>
+__device__ __forceinline__ void unpack(const uint32_t (&w0)[2], const uint32_t (&w1)[2], uint32_t (&a1)[4],
+                                       uint32_t (&a2)[4]) {
+    if (QT == TLC_TYPE_Q4_0) {
+        a1[0] = w0[0] & 0x000F000Fu;
+        a1[1] = w1[0] & 0x000F000Fu;
+        a1[2] = (w0[0] >> 4) & 0x000F000Fu;
+        a1[3] = (w1[0] >> 4) & 0x000F000Fu;
+        a2[0] = (w0[0] >> 8) & 0x000F000Fu;
+        a2[1] = (w1[0] >> 8) & 0x000F000Fu;
+        a2[2] = (w0[0] >> 12) & 0x000F000Fu;
+        a2[3] = (w1[0] >> 12) & 0x000F000Fu;
+    } else {
+        const uint32_t u0 = w0[0] ^ 0x80808080u, v0 = w1[0] ^ 0x80808080u;
+        const uint32_t u1 = w0[1] ^ 0x80808080u, v1 = w1[1] ^ 0x80808080u;
+        a1[0] = __byte_perm(u0, 0, 0x4140);
+        a1[1] = __byte_perm(v0, 0, 0x4140);
+        a1[2] = __byte_perm(u0, 0, 0x4342);
+        a1[3] = __byte_perm(v0, 0, 0x4342);
+        a2[0] = __byte_perm(u1, 0, 0x4140);
+        a2[1] = __byte_perm(v1, 0, 0x4140);
+        a2[2] = __byte_perm(u1, 0, 0x4342);
+        a2[3] = __byte_perm(v1, 0, 0x4342);
+    }
+}
+
+}  // namespace tlc_gemv

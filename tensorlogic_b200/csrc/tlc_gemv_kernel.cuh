@@ -1,0 +1,394 @@
+// The fused dequant-GEMV kernel.  See tlc_gemv.cu for the design notes.
+#pragma once
+
+#include "tlc_gemv_common.cuh"
+
+namespace tlc_gemv {
+
+// Shared-memory layout (bytes from the start of dynamic shared memory):
+//   0    full[8], empty[8] mbarriers
+//   128  abort flag
+//   256  sum-of-squares partials [16 activation rows][8 warps]
+//   768  red   [2][8 warps][16 rows][MP] f32   cross-warp reduction, double buffered
+//   ...  cinit [nblk_pad][NT][4 quad lanes] float4  accumulator start per block
+//   ...  xzero one zero uint4 (B fragment of activation rows that do not exist)
+//   ...  xperm [nblk_pad][m][4 quad lanes] uint4    activations in fragment order
+//   ...  ring  [stages][16 rows][PITCH]             raw weight bytes (128-byte aligned)
+__host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt) {
+    size_t s = 768;
+    s += (size_t)2 * kConsumerWarps * kRows * (8 * nt) * sizeof(float);
+    s += (size_t)nblk_pad * nt * 4 * sizeof(float4);
+    s += sizeof(uint4);
+    s += (size_t)nblk_pad * m * 4 * sizeof(uint4);
+    s += 128;  // ring alignment slack
+    return s;
+}
+
+template <int QT, int NT>
+__global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams p) {
+    using T = QTraits<QT>;
+    constexpr int MP = 8 * NT;  // padded activation rows
+    constexpr int PITCH = stage_pitch(T::KCB * T::BB);
+    constexpr int STAGE_BYTES = kRows * PITCH;
+    constexpr int PW = T::PAIR_WORDS;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *empty = full + kMaxStages;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 128);
+    float *sq_part = reinterpret_cast<float *>(smem + 256);
+    float *red = reinterpret_cast<float *>(smem + 768);
+    float4 *cinit = reinterpret_cast<float4 *>(red + 2 * kConsumerWarps * kRows * MP);
+    uint4 *xzero = reinterpret_cast<uint4 *>(cinit + (size_t)p.nblk_pad * NT * 4);
+    uint4 *xperm = xzero + 1;
+    uint8_t *stages = reinterpret_cast<uint8_t *>(xperm + (size_t)p.nblk_pad * p.m * 4);
+    stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(stages) + 127) & ~(uintptr_t)127);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int S = p.nstages;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumerWarps);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    // The next kernel of the stream may be scheduled from here on: its producer
+    // warps only read weights, everything else waits for this grid to finish.
+    if (p.pdl_mode == 1) pdl_launch_dependents();
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------ producer ------------------------------
+        // Weights are never written by a kernel, so the ring starts filling
+        // before the previous kernel of the stream has finished.
+        uint32_t it = 0;
+        for (int unit = blockIdx.x; unit < p.total_units; unit += gridDim.x) {
+            for (int sub = 0; sub < p.subs; sub++) {
+                int ti = 0, sl = unit;
+                if (p.subs == 2) {
+                    ti = sub;
+                } else {
+                    if (sl >= p.slabs[0]) { sl -= p.slabs[0]; ti = 1; }
+                    if (ti == 1 && sl >= p.slabs[1]) { sl -= p.slabs[1]; ti = 2; }
+                }
+                const uint8_t *wbase = ti == 0 ? p.t[0].w : ti == 1 ? p.t[1].w : p.t[2].w;
+                const size_t wpitch = ti == 0 ? p.t[0].pitch : ti == 1 ? p.t[1].pitch : p.t[2].pitch;
+                const int wn = ti == 0 ? p.t[0].n : ti == 1 ? p.t[1].n : p.t[2].n;
+                const int rows_valid = min(kRows, wn - sl * kRows);
+                for (int c = 0; c < p.nchunks; c++, it++) {
+                    const int s = it % S;
+                    const uint32_t par = ((it / S) & 1u) ^ 1u;
+                    // On a timeout the producer stops issuing copies; the consumers'
+                    // own bounded waits then end the CTA.
+                    if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], par, abort_flag, p.status, 1))) return;
+                    const int kcb = min(T::KCB, p.nblk - c * T::KCB);
+                    const uint32_t bytes_row = (uint32_t)((kcb * T::BB + 15) & ~15);
+                    if (lane == 0) mbar_expect_tx(&full[s], bytes_row * (uint32_t)rows_valid);
+                    __syncwarp();
+                    if (lane < rows_valid) {
+                        const uint8_t *src = wbase + (size_t)(sl * kRows + lane) * wpitch + (size_t)c * (T::KCB * T::BB);
+                        bulk_g2s(stages + (size_t)s * STAGE_BYTES + lane * PITCH, src, bytes_row, &full[s]);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // -------------------------------- consumers --------------------------------
+    const int ctid = tid;  // 0..kConsumerThreads-1
+    const bool do_norm = p.norm_w != nullptr;
+    pdl_wait();  // the activations (and residual) come from the previous kernel
+
+    // (a) sum of squares per activation row: every thread takes 8-element chunks.
+    if (do_norm) {
+        for (int m = 0; m < p.m; m++) {
+            const __half *xr = p.x + (size_t)m * p.k;
+            float sq = 0.f;
+            for (int k = ctid * 8; k < p.k; k += kConsumerThreads * 8) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(xr + k);
+                const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 v = __half22float2(h[j]);
+                    sq = fmaf(v.x, v.x, sq);
+                    sq = fmaf(v.y, v.y, sq);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) sq_part[m * kConsumerWarps + warp] = sq;
+        }
+    }
+    for (int i = ctid; i < p.nblk_pad * NT * 4; i += kConsumerThreads) cinit[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ctid == 0) *xzero = make_uint4(0, 0, 0, 0);
+    consumer_bar();
+
+    // (b) activations into fragment order + accumulator start values.  Item =
+    // (block b, activation row m, quad lane t); the 4 t-items of a (b, m) are
+    // adjacent lanes, so a 2-step shuffle gives the block sum.
+    //   Q4_0 fragment order: {4t, 4t+2, 16+4t, 18+4t | 4t+1, 4t+3, 17+4t, 19+4t}
+    //   Q8_0 fragment order: {8t .. 8t+7}
+    {
+        const int items = p.nblk_pad * p.m * 4;
+        const int rounds = (items + kConsumerThreads - 1) / kConsumerThreads;
+        for (int r = 0; r < rounds; r++) {
+            const int idx = ctid + r * kConsumerThreads;
+            const bool live = idx < items;
+            const int t = idx & 3;
+            const int bm = idx >> 2;
+            const int b = live ? bm / p.m : 0;
+            const int m = live ? bm % p.m : 0;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = 0.f;
+            if (live && b < p.nblk) {
+                const __half *xr = p.x + (size_t)m * p.k + b * 32;
+                float inv = 1.f;
+                if (do_norm) {
+                    float ss = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; w++) ss += sq_part[m * kConsumerWarps + w];
+                    inv = 1.0f / sqrtf(ss / (float)p.k + p.eps);
+                }
+                __half raw[8], nw[8];
+                if (QT == TLC_TYPE_Q4_0) {
+                    *reinterpret_cast<uint2 *>(&raw[0]) = *reinterpret_cast<const uint2 *>(xr + 4 * t);
+                    *reinterpret_cast<uint2 *>(&raw[4]) = *reinterpret_cast<const uint2 *>(xr + 16 + 4 * t);
+                    if (do_norm) {
+                        const __half *wr = p.norm_w + b * 32;
+                        *reinterpret_cast<uint2 *>(&nw[0]) = *reinterpret_cast<const uint2 *>(wr + 4 * t);
+                        *reinterpret_cast<uint2 *>(&nw[4]) = *reinterpret_cast<const uint2 *>(wr + 16 + 4 * t);
+                    }
+                } else {
+                    *reinterpret_cast<uint4 *>(&raw[0]) = *reinterpret_cast<const uint4 *>(xr + 8 * t);
+                    if (do_norm)
+                        *reinterpret_cast<uint4 *>(&nw[0]) = *reinterpret_cast<const uint4 *>(p.norm_w + b * 32 + 8 * t);
+                }
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    f[j] = __half2float(raw[j]);
+                    // f16((x * inv) * w): two separately rounded f32 multiplies, then RNE
+                    // (Tensor::rms_norm_cpu, src/ops/normalization.rs:236-240).
+                    if (do_norm)
+                        f[j] = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(f[j], inv), __half2float(nw[j]))));
+                }
+                if (QT == TLC_TYPE_Q4_0) {
+                    v[0] = f[0]; v[1] = f[2]; v[2] = f[4]; v[3] = f[6];
+                    v[4] = f[1]; v[5] = f[3]; v[6] = f[5]; v[7] = f[7];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = f[j];
+                }
+            }
+            float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            if (live) {
+                const __half2 h0 = __floats2half2_rn(v[0], v[1]);  // exact: v[] are f16 values
+                const __half2 h1 = __floats2half2_rn(v[2], v[3]);
+                const __half2 h2 = __floats2half2_rn(v[4], v[5]);
+                const __half2 h3 = __floats2half2_rn(v[6], v[7]);
+                uint4 o;
+                o.x = *reinterpret_cast<const uint32_t *>(&h0);
+                o.y = *reinterpret_cast<const uint32_t *>(&h1);
+                o.z = *reinterpret_cast<const uint32_t *>(&h2);
+                o.w = *reinterpret_cast<const uint32_t *>(&h3);
+                xperm[idx] = o;
+                if (t == 0) {
+                    // Column m of the 16x8 tile sits in the C fragment of quad lane (m%8)/2,
+                    // components m%2 (row g) and m%2 + 2 (row g+8).
+                    const float cv = -T::OFFSET * 5.9604644775390625e-08f * s;  // * 2^-24
+                    float *cf = reinterpret_cast<float *>(&cinit[(b * NT + (m >> 3)) * 4 + ((m & 7) >> 1)]);
+                    cf[m & 1] = cv;
+                    cf[(m & 1) + 2] = cv;
+                }
+            }
+        }
+    }
+    consumer_bar();
+
+    // (c) main loop
+    const int g = lane >> 2, t = lane & 3;
+    // Loop-invariant addressing of this lane's B fragments: activation row nt*8+g.
+    const uint4 *xp_base[NT];
+    int xp_stride[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const bool has = nt * 8 + g < p.m;
+        xp_base[nt] = has ? xperm + (nt * 8 + g) * 4 + t : xzero;
+        xp_stride[nt] = has ? p.m * 4 : 0;
+    }
+    const float4 *ci_base = cinit + t;
+    const int seg_lo = g * PITCH, seg_hi = (g + 8) * PITCH;
+
+    uint32_t it = 0;
+    int slab_count = 0;
+    __half hold = __float2half(0.f);  // gate value kept between the two slabs of a gate/up unit
+
+    for (int unit = blockIdx.x; unit < p.total_units; unit += gridDim.x) {
+        for (int sub = 0; sub < p.subs; sub++, slab_count++) {
+            int ti = 0, sl = unit;
+            if (p.subs == 2) {
+                ti = sub;
+            } else {
+                if (sl >= p.slabs[0]) { sl -= p.slabs[0]; ti = 1; }
+                if (ti == 1 && sl >= p.slabs[1]) { sl -= p.slabs[1]; ti = 2; }
+            }
+            float acc[4 * NT];
+#pragma unroll
+            for (int i = 0; i < 4 * NT; i++) acc[i] = 0.f;
+
+            for (int c = 0; c < p.nchunks; c++, it++) {
+                const int s = it % S;
+                const uint32_t par = (it / S) & 1u;
+                // A wait that ran out skips the math but keeps the barrier protocol
+                // going, so every warp still reaches the same bar.sync calls.
+                const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], par, abort_flag, p.status, 2));
+                const int kcb = min(T::KCB, p.nblk - c * T::KCB);
+                const int npairs = ready ? (kcb + 1) >> 1 : 0;
+                const uint8_t *st = stages + (size_t)s * STAGE_BYTES;
+                const uint32_t *seg_g = reinterpret_cast<const uint32_t *>(st + seg_lo);
+                const uint32_t *seg_g8 = reinterpret_cast<const uint32_t *>(st + seg_hi);
+
+                // One (even, odd) block pair: 2 blocks x 16 rows.  Pair pr starts at
+                // word PW*pr of the 4-byte aligned row segment; the even block's qs
+                // bytes sit 2 bytes past a word boundary, hence the funnel shifts.
+                auto do_pair = [&](int pr) {
+                    const uint32_t *q0 = seg_g + PW * pr, *q1 = seg_g8 + PW * pr;
+                    const __half *h0 = reinterpret_cast<const __half *>(q0), *h1 = reinterpret_cast<const __half *>(q1);
+                    uint32_t we0[2], we1[2], wo0[2], wo1[2];
+                    if (QT == TLC_TYPE_Q4_0) {
+                        we0[0] = __funnelshift_r(q0[t], q0[t + 1], 16);
+                        we1[0] = __funnelshift_r(q1[t], q1[t + 1], 16);
+                        wo0[0] = q0[5 + t];
+                        wo1[0] = q1[5 + t];
+                        we0[1] = we1[1] = wo0[1] = wo1[1] = 0;
+                    } else {
+                        const uint32_t a0 = q0[2 * t], a1 = q0[2 * t + 1], a2 = q0[2 * t + 2];
+                        const uint32_t b0 = q1[2 * t], b1 = q1[2 * t + 1], b2 = q1[2 * t + 2];
+                        we0[0] = __funnelshift_r(a0, a1, 16);
+                        we0[1] = __funnelshift_r(a1, a2, 16);
+                        we1[0] = __funnelshift_r(b0, b1, 16);
+                        we1[1] = __funnelshift_r(b1, b2, 16);
+                        wo0[0] = q0[9 + 2 * t];
+                        wo0[1] = q0[10 + 2 * t];
+                        wo1[0] = q1[9 + 2 * t];
+                        wo1[1] = q1[10 + 2 * t];
+                    }
+                    const float de0 = __half2float(h0[0]), de1 = __half2float(h1[0]);
+                    float do0 = __half2float(h0[T::BB / 2]), do1 = __half2float(h1[T::BB / 2]);
+                    if (2 * pr + 1 >= kcb) {  // odd tail block does not exist
+                        do0 = 0.f;
+                        do1 = 0.f;
+                    }
+                    const int b = c * T::KCB + 2 * pr;
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        uint32_t a1[4], a2[4];
+                        if (e == 0) unpack<QT>(we0, we1, a1, a2);
+                        else unpack<QT>(wo0, wo1, a1, a2);
+                        const float dlo = e == 0 ? de0 : do0, dhi = e == 0 ? de1 : do1;
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            const uint4 xp = xp_base[nt][(b + e) * xp_stride[nt]];
+                            const float4 ci = ci_base[((b + e) * NT + nt) * 4];
+                            const float cc[4] = {ci.x, ci.y, ci.z, ci.w};
+                            float d1[4], d2[4];
+                            mma16816(d1, a1, xp.x, xp.y, cc);
+                            mma16816(d2, a2, xp.z, xp.w, d1);
+                            acc[nt * 4 + 0] = fmaf(dlo, d2[0], acc[nt * 4 + 0]);
+                            acc[nt * 4 + 1] = fmaf(dlo, d2[1], acc[nt * 4 + 1]);
+                            acc[nt * 4 + 2] = fmaf(dhi, d2[2], acc[nt * 4 + 2]);
+                            acc[nt * 4 + 3] = fmaf(dhi, d2[3], acc[nt * 4 + 3]);
+                        }
+                    }
+                };
+                if (npairs == T::KCB / 2) {
+#pragma unroll
+                    for (int i = 0; i < T::KCB / 2 / kConsumerWarps; i++) do_pair(warp + i * kConsumerWarps);
+                } else {
+                    for (int pr = warp; pr < npairs; pr += kConsumerWarps) do_pair(pr);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+            }
+
+            // (d) cross-warp reduction and epilogue
+            if (p.pdl_mode == 2 && unit + (int)gridDim.x >= p.total_units && sub == p.subs - 1) pdl_launch_dependents();
+            float *rbuf = red + (size_t)(slab_count & 1) * (kConsumerWarps * kRows * MP);
+            float *mine = rbuf + warp * (kRows * MP);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                *reinterpret_cast<float2 *>(&mine[g * MP + nt * 8 + 2 * t]) = make_float2(acc[nt * 4 + 0], acc[nt * 4 + 1]);
+                *reinterpret_cast<float2 *>(&mine[(g + 8) * MP + nt * 8 + 2 * t]) =
+                    make_float2(acc[nt * 4 + 2], acc[nt * 4 + 3]);
+            }
+            consumer_bar();
+            if (ctid < kRows * MP) {
+                const int col = ctid >> 4, row = ctid & 15;
+                const int n = sl * kRows + row;
+                const int wn = ti == 0 ? p.t[0].n : ti == 1 ? p.t[1].n : p.t[2].n;
+                auto total = [&](int r_) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; w++) v += rbuf[w * (kRows * MP) + r_ * MP + col];
+                    return v * 16777216.0f;  // undo the 2^-24 of the integer fragments
+                };
+                if (col < p.m && n < wn) {
+                    __half *yout = ti == 0 ? p.t[0].y : ti == 1 ? p.t[1].y : p.t[2].y;
+                    const long long rstride = ti == 0 ? p.t[0].row_stride : ti == 1 ? p.t[1].row_stride : p.t[2].row_stride;
+                    const long long pstride = ti == 0 ? p.t[0].pos_stride : ti == 1 ? p.t[1].pos_stride : p.t[2].pos_stride;
+                    const int rheads = ti == 0 ? p.t[0].rope_heads : ti == 1 ? p.t[1].rope_heads : p.t[2].rope_heads;
+                    const int hdim = ti == 0 ? p.t[0].head_dim : ti == 1 ? p.t[1].head_dim : p.t[2].head_dim;
+                    __half h = __float2half_rn(total(row));
+                    const size_t oidx = (size_t)col * wn + n;  // dense [m, N] index (residual, act)
+                    const int pos = p.positions ? p.positions[col] : p.pos_offset + col;
+                    // Where this output goes: dense rows by default; a KV-cache destination
+                    // addresses rows by (sequence, position) instead.
+                    const size_t yidx = (size_t)((long long)col * rstride + (long long)pos * pstride) + n;
+                    if (rheads > 0) {
+                        // Interleaved RoPE on the f16-rounded projection
+                        // (rope_f16, shaders/unified.metal:2355-2417).
+                        const __half hp = __float2half_rn(total(row ^ 1));
+                        const int dim = n % hdim;
+                        const int pair = dim >> 1;
+                        const float x0 = __half2float((dim & 1) ? hp : h);
+                        const float x1 = __half2float((dim & 1) ? h : hp);
+                        const float exponent = (float)(2 * pair) / (float)hdim;
+                        const float freq = 1.0f / powf(p.rope_base, exponent);
+                        const float theta = (float)(unsigned)pos * freq;
+                        const float cs = cosf(theta), sn = sinf(theta);
+                        const float r = (dim & 1) ? __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs))
+                                                  : __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+                        yout[yidx] = __float2half_rn(r);
+                    } else if (p.epilogue == TLC_EPI_RESIDUAL) {
+                        yout[yidx] = __hadd(h, p.residual[oidx]);
+                    } else if (p.epilogue == TLC_EPI_SWIGLU) {
+                        if (sub == 0) {
+                            hold = h;
+                        } else {
+                            // s = sigmoid(g) (f32, RNE); a = g*s; act = a*u: three
+                            // f16 roundings as in debug/chat_demo_with_kvcache.tl:26-41.
+                            const float gf = __half2float(hold);
+                            const __half sg = __float2half_rn(1.0f / (1.0f + expf(-gf)));
+                            const __half a = __hmul(hold, sg);
+                            p.t[0].y[oidx] = __hmul(a, h);
+                        }
+                    } else {
+                        if (p.bias) h = __hadd(h, p.bias[n]);
+                        yout[yidx] = h;
+                    }
+                }
+            }
+        }
+    }
+}
+
+}  // namespace tlc_gemv

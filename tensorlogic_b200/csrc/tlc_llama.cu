@@ -55,6 +55,7 @@ namespace {
 
 __global__ void embed_kernel(const uint8_t *__restrict__ table, size_t pitch, int vocab, int d,
                              const int *__restrict__ ids, int m, __half *__restrict__ y) {
+    tlc_pdl_prologue();  // ids are written by the previous step's sampling kernel
     const int vec = d >> 3;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)m * vec) return;
@@ -72,6 +73,7 @@ __global__ void argmax_advance_kernel(const __half *__restrict__ logits, int voc
                                       int *__restrict__ ids, int *__restrict__ positions, int advance) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    tlc_pdl_prologue();  // the logits come from the previous kernel
     const int b = blockIdx.x;
     const __half *row = logits + (size_t)b * vocab;
     float best = -INFINITY;
@@ -245,9 +247,10 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
     const int64_t kv_row = (int64_t)L->kv_heads_local * D;
     if (parts & 4) {
         const size_t total = (size_t)m * (d / 8);
-        embed_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
-            static_cast<const uint8_t *>(L->tok_embd->data), L->tok_embd->row_pitch, (int)L->tok_embd->n_rows, d,
-            L->ids, m, L->x);
+        cudaError_t le = tlc_launch_pdl(ctx, embed_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
+                                        static_cast<const uint8_t *>(L->tok_embd->data), L->tok_embd->row_pitch,
+                                        (int)L->tok_embd->n_rows, d, (const int *)L->ids, m, L->x);
+        if (le != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "embedding launch failed: %s", cudaGetErrorString(le));
         TLC_CHECK_LAUNCH(ctx);
     }
     const int *positions = decode ? L->positions : nullptr;
@@ -328,8 +331,9 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         if (sample && (parts & 4)) {
             const int srows = decode ? m : 1;
             const __half *lg = L->logits + (size_t)(rows - srows) * L->vocab_local;
-            argmax_advance_kernel<<<srows, 1024, 0, ctx->stream>>>(lg, L->vocab_local, L->next_ids, L->ids,
-                                                                   L->positions, advance ? 1 : 0);
+            cudaError_t le = tlc_launch_pdl(ctx, argmax_advance_kernel, dim3(srows), dim3(1024), 0, lg, L->vocab_local,
+                                            (int *)L->next_ids, (int *)L->ids, (int *)L->positions, advance ? 1 : 0);
+            if (le != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "sampling launch failed: %s", cudaGetErrorString(le));
             TLC_CHECK_LAUNCH(ctx);
         }
     }
