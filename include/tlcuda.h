@@ -383,6 +383,30 @@ TLC_API int32_t tlc_llama_read_state(tlc_llama *l, int32_t batch, int32_t *next_
  * gather + sampling); tokens and positions are left untouched unless parts == 7. */
 TLC_API int32_t tlc_llama_decode_enqueue_parts(tlc_llama *l, int32_t batch, int32_t steps,
                                                int32_t parts);
+/* ---- tensor parallelism ----------------------------------------------------- */
+
+/* No counterpart in the reference (it has no multi-GPU code).  One process per
+ * GPU; the 128-byte id made by rank 0 (tlc_comm_unique_id) is handed to the
+ * other ranks by the caller (a file, MPI, torch.distributed ...).  NCCL is
+ * loaded at run time; TLC_ERR_COMM if it is missing or a call fails. */
+typedef struct tlc_comm tlc_comm;
+TLC_API int32_t tlc_comm_unique_id(void *out128);
+TLC_API int32_t tlc_comm_init(tlc_ctx *ctx, const void *id128, int32_t rank, int32_t world,
+                              tlc_comm **out);
+TLC_API int32_t tlc_comm_destroy(tlc_comm *comm);
+TLC_API int32_t tlc_comm_rank(tlc_comm *comm);
+TLC_API int32_t tlc_comm_size(tlc_comm *comm);
+/* In-place sum of `count` f16 values over the ranks (after the row-parallel
+ * attn_output / ffn_down projections), enqueued on the context's stream. */
+TLC_API int32_t tlc_allreduce_f16(tlc_ctx *ctx, tlc_comm *comm, void *buf_dev, size_t count);
+/* recv[rank * count ...] = every rank's `count` f16 values (logit shards). */
+TLC_API int32_t tlc_allgather_f16(tlc_ctx *ctx, tlc_comm *comm, const void *send_dev,
+                                  void *recv_dev, size_t count);
+/* Joins a runner created with tp_size > 1 to its communicator; required before
+ * the first prefill / decode of a sharded model.  Logits handed back to the
+ * host are full [rows, vocab] rows on every rank. */
+TLC_API int32_t tlc_llama_set_comm(tlc_llama *l, tlc_comm *comm);
+
 /* Kernels one decode step launches for a parts mask (7 = whole step), known
  * once such a step has been enqueued. */
 TLC_API int32_t tlc_llama_launches_per_step(tlc_llama *l, int32_t parts);

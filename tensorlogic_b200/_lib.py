@@ -126,6 +126,14 @@ PROTOTYPES = {
     "tlc_llama_decode_enqueue_parts": (i32, [vp, i32, i32, i32]),
     "tlc_llama_launches_per_step": (i32, [vp, i32]),
     "tlc_llama_cache": (vp, [vp]),
+    "tlc_comm_unique_id": (i32, [vp]),
+    "tlc_comm_init": (i32, [vp, vp, i32, i32, P(vp)]),
+    "tlc_comm_destroy": (i32, [vp]),
+    "tlc_comm_rank": (i32, [vp]),
+    "tlc_comm_size": (i32, [vp]),
+    "tlc_allreduce_f16": (i32, [vp, vp, vp, sz]),
+    "tlc_allgather_f16": (i32, [vp, vp, vp, vp, sz]),
+    "tlc_llama_set_comm": (i32, [vp, vp]),
 }
 
 _lib = None

@@ -30,6 +30,11 @@ extern "C" int32_t tlc_kvcache_destroy(tlc_kvcache *);
 extern "C" int32_t tlc_kvcache_layer_ptrs(tlc_kvcache *, int32_t, void **, void **);
 struct tlc_model;
 extern "C" int32_t tlc_model_get(tlc_model *, const char *, tlc_qtensor **);
+struct tlc_comm;
+extern "C" int32_t tlc_allreduce_f16(tlc_ctx *, tlc_comm *, void *, size_t);
+extern "C" int32_t tlc_allgather_f16(tlc_ctx *, tlc_comm *, const void *, void *, size_t);
+extern "C" int32_t tlc_comm_size(tlc_comm *);
+extern "C" int32_t tlc_comm_rank(tlc_comm *);
 
 struct LayerWeights {
     tlc_qtensor *attn_norm, *wq, *wk, *wv, *wo, *ffn_norm, *w_gate, *w_up, *w_down;
@@ -43,6 +48,10 @@ struct tlc_llama {
     tlc_kvcache *cache;
     int max_rows;  // rows of the activation buffers
     __half *x, *x1, *q, *attn, *act, *logits;
+    __half *part = nullptr;         // tensor parallel: this rank's partial [rows, d] before the all-reduce
+    __half *logits_full = nullptr;  // tensor parallel: gathered logits [rank][rows][vocab / tp]
+    tlc_comm *comm = nullptr;
+    int last_logit_rows = 1;
     int32_t *ids, *positions, *next_ids;
     int32_t *host_ids;  // pinned staging
     int32_t *host_next;
@@ -69,20 +78,25 @@ __global__ void embed_kernel(const uint8_t *__restrict__ table, size_t pitch, in
 // maximal index, like Iterator::max_by in temperature_sample's greedy arm
 // (src/interpreter/builtin_sampling.rs:176-181).  Also feeds the sampled token
 // back as the next input and advances the sequence position.
-__global__ void argmax_advance_kernel(const __half *__restrict__ logits, int vocab, int *__restrict__ next_ids,
-                                      int *__restrict__ ids, int *__restrict__ positions, int advance) {
+// With tensor parallelism the logits arrive as gathered vocabulary shards
+// [shard][row][vocab_per_shard]; token index = shard * vocab_per_shard + i.
+__global__ void argmax_advance_kernel(const __half *__restrict__ logits, int vocab, int shards, int rows,
+                                      int *__restrict__ next_ids, int *__restrict__ ids,
+                                      int *__restrict__ positions, int advance) {
     __shared__ float sv[32];
     __shared__ int si[32];
     tlc_pdl_prologue();  // the logits come from the previous kernel
     const int b = blockIdx.x;
-    const __half *row = logits + (size_t)b * vocab;
     float best = -INFINITY;
     int bi = -1;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = __half2float(row[i]);
-        if (bi < 0 || !(v < best)) {  // v >= best (or unordered): later index wins
-            best = v;
-            bi = i;
+    for (int sh = 0; sh < shards; sh++) {
+        const __half *row = logits + ((size_t)sh * rows + b) * vocab;
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const float v = __half2float(row[i]);
+            if (bi < 0 || !(v < best)) {  // v >= best (or unordered): later index wins
+                best = v;
+                bi = sh * vocab + i;
+            }
         }
     }
     auto better = [](float v, int i, float bv, int bidx) {
@@ -196,8 +210,11 @@ extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_ll
         {(void **)&L->x, R * d * 2},      {(void **)&L->x1, R * d * 2},          {(void **)&L->q, R * qd * 2},
         {(void **)&L->attn, R * qd * 2},  {(void **)&L->act, R * L->ffn_local * 2},
         {(void **)&L->logits, (c.logits_all_rows ? R : logits_rows) * L->vocab_local * 2},
-        {(void **)&L->ids, R * 4},        {(void **)&L->positions, 64 * 4},      {(void **)&L->next_ids, 64 * 4}};
+        {(void **)&L->ids, R * 4},        {(void **)&L->positions, 64 * 4},      {(void **)&L->next_ids, 64 * 4},
+        {(void **)&L->part, tp > 1 ? R * d * 2 : 0},
+        {(void **)&L->logits_full, tp > 1 ? (c.logits_all_rows ? R : logits_rows) * (size_t)c.vocab * 2 : 0}};
     for (auto &b : bufs) {
+        if (b.bytes == 0) continue;
         cudaError_t e = cudaMalloc(b.p, b.bytes);
         if (e != cudaSuccess) {
             cudaGetLastError();
@@ -223,7 +240,8 @@ extern "C" int32_t tlc_llama_destroy(tlc_llama *L) {
     for (auto &g : L->graph)
         if (g.second) cudaGraphExecDestroy(g.second);
     tlc_kvcache_destroy(L->cache);
-    void *bufs[] = {L->x, L->x1, L->q, L->attn, L->act, L->logits, L->ids, L->positions, L->next_ids};
+    void *bufs[] = {L->x, L->x1, L->q, L->attn, L->act, L->logits, L->ids, L->positions, L->next_ids,
+                    L->part, L->logits_full};
     for (void *b : bufs) cudaFree(b);
     cudaFreeHost(L->host_ids);
     cudaFreeHost(L->host_next);
@@ -241,8 +259,9 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
                        int parts = 7) {
     tlc_ctx *ctx = L->ctx;
     const tlc_llama_config &c = L->cfg;
-    TLC_REQUIRE(c.tp_size == 1, TLC_ERR_INVALID_OPERATION,
-                "this build of the runner executes single-GPU models only (tp_size = %d)", c.tp_size);
+    const bool tp = c.tp_size > 1;
+    TLC_REQUIRE(!tp || L->comm, TLC_ERR_COMM, "tensor-parallel model (tp_size = %d) has no communicator: call "
+                "tlc_llama_set_comm first", c.tp_size);
     const int d = c.d_model, D = c.head_dim;
     const int64_t kv_row = (int64_t)L->kv_heads_local * D;
     if (parts & 4) {
@@ -285,12 +304,19 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         if (parts & 1) {
             tlc_gemv_args a;
             a.n_out = 1;
-            a.outs[0] = {w.wo, L->x1, 0};
+            a.outs[0] = {w.wo, tp ? L->part : L->x1, 0};
             a.x = L->attn;
             a.m = m;
-            a.epilogue = TLC_EPI_RESIDUAL;
-            a.residual = L->x;
+            if (!tp) {
+                a.epilogue = TLC_EPI_RESIDUAL;
+                a.residual = L->x;
+            }
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+            if (tp) {
+                // Row-parallel projection: sum the ranks' partial products, then the residual add.
+                if (int32_t rc = tlc_allreduce_f16(ctx, L->comm, L->part, (size_t)m * d)) return rc;
+                if (int32_t rc = tlc_add(ctx, L->x, L->part, L->x1, (size_t)m * d)) return rc;
+            }
         }
         if (parts & 1) {
             tlc_gemv_args a;
@@ -307,12 +333,18 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         if (parts & 1) {
             tlc_gemv_args a;
             a.n_out = 1;
-            a.outs[0] = {w.w_down, L->x, 0};
+            a.outs[0] = {w.w_down, tp ? L->part : L->x, 0};
             a.x = L->act;
             a.m = m;
-            a.epilogue = TLC_EPI_RESIDUAL;
-            a.residual = L->x1;
+            if (!tp) {
+                a.epilogue = TLC_EPI_RESIDUAL;
+                a.residual = L->x1;
+            }
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+            if (tp) {
+                if (int32_t rc = tlc_allreduce_f16(ctx, L->comm, L->part, (size_t)m * d)) return rc;
+                if (int32_t rc = tlc_add(ctx, L->x1, L->part, L->x, (size_t)m * d)) return rc;
+            }
         }
     }
     {
@@ -326,17 +358,51 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         a.m = rows;
         a.norm_w = L->out_norm->data;
         a.eps = c.rms_eps;
-        if (parts & 1)
+        if (parts & 1) {
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
+            // Column-parallel lm_head: gather the vocabulary shards [rank][rows][vocab / tp].
+            if (tp)
+                if (int32_t rc = tlc_allgather_f16(ctx, L->comm, L->logits, L->logits_full, (size_t)rows * L->vocab_local))
+                    return rc;
+        }
+        L->last_logit_rows = rows;
         if (sample && (parts & 4)) {
             const int srows = decode ? m : 1;
-            const __half *lg = L->logits + (size_t)(rows - srows) * L->vocab_local;
+            const __half *lg = (tp ? L->logits_full : L->logits) + (size_t)(rows - srows) * L->vocab_local;
             cudaError_t le = tlc_launch_pdl(ctx, argmax_advance_kernel, dim3(srows), dim3(1024), 0, lg, L->vocab_local,
-                                            (int *)L->next_ids, (int *)L->ids, (int *)L->positions, advance ? 1 : 0);
+                                            c.tp_size, rows, (int *)L->next_ids, (int *)L->ids, (int *)L->positions,
+                                            advance ? 1 : 0);
             if (le != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "sampling launch failed: %s", cudaGetErrorString(le));
             TLC_CHECK_LAUNCH(ctx);
         }
     }
+    return TLC_OK;
+}
+
+// Enqueues the copy of the last forward's logits to host memory as [rows, vocab]
+// (with tensor parallelism the gathered shards are interleaved into full rows).
+static int32_t copy_logits(tlc_llama *L, void *logits_host, int rows) {
+    const size_t vl = (size_t)L->vocab_local;
+    if (L->cfg.tp_size == 1) {
+        TLC_CUDA(cudaMemcpyAsync(logits_host, L->logits, (size_t)rows * vl * 2, cudaMemcpyDeviceToHost, L->ctx->stream));
+        return TLC_OK;
+    }
+    const size_t vocab = (size_t)L->cfg.vocab;
+    for (int r = 0; r < L->cfg.tp_size; r++)
+        TLC_CUDA(cudaMemcpy2DAsync(static_cast<char *>(logits_host) + r * vl * 2, vocab * 2,
+                                   L->logits_full + (size_t)r * rows * vl, vl * 2, vl * 2, (size_t)rows,
+                                   cudaMemcpyDeviceToHost, L->ctx->stream));
+    return TLC_OK;
+}
+
+// Tensor parallelism: the communicator that joins this rank's runner to the
+// others (tlc_comm_init).  Must be set before the first prefill / decode.
+extern "C" int32_t tlc_llama_set_comm(tlc_llama *L, tlc_comm *comm) {
+    TLC_REQUIRE(L && comm, TLC_ERR_INVALID_OPERATION, "llama_set_comm: null pointer");
+    TLC_REQUIRE(tlc_comm_size(comm) == L->cfg.tp_size && tlc_comm_rank(comm) == L->cfg.tp_rank, TLC_ERR_COMM,
+                "communicator is rank %d of %d, the model is shard %d of %d", tlc_comm_rank(comm), tlc_comm_size(comm),
+                L->cfg.tp_rank, L->cfg.tp_size);
+    L->comm = comm;
     return TLC_OK;
 }
 
@@ -368,8 +434,7 @@ extern "C" int32_t tlc_llama_prefill(tlc_llama *L, const int32_t *ids_host, int3
     TLC_CUDA(cudaMemcpyAsync(L->ids, L->next_ids, 4, cudaMemcpyDeviceToDevice, L->ctx->stream));
     const int rows = all_rows ? n : 1;
     if (logits_host)
-        TLC_CUDA(cudaMemcpyAsync(logits_host, L->logits, (size_t)rows * L->vocab_local * 2, cudaMemcpyDeviceToHost,
-                                 L->ctx->stream));
+        if (int32_t rc = copy_logits(L, logits_host, rows)) return rc;
     TLC_CUDA(cudaMemcpyAsync(L->host_next, L->next_ids, 4, cudaMemcpyDeviceToHost, L->ctx->stream));
     if (int32_t rc = tlc_synchronize(L->ctx)) return rc;
     if (next_id_host) *next_id_host = L->host_next[0];
@@ -464,8 +529,7 @@ extern "C" int32_t tlc_llama_decode_host(tlc_llama *L, int32_t batch, const int3
     }
     if (int32_t rc = tlc_llama_decode_enqueue(L, batch, 1)) return rc;
     if (logits_host)
-        TLC_CUDA(cudaMemcpyAsync(logits_host, L->logits, (size_t)batch * L->vocab_local * 2, cudaMemcpyDeviceToHost,
-                                 L->ctx->stream));
+        if (int32_t rc = copy_logits(L, logits_host, batch)) return rc;
     TLC_CUDA(cudaMemcpyAsync(L->host_next, L->next_ids, (size_t)batch * 4, cudaMemcpyDeviceToHost, L->ctx->stream));
     if (int32_t rc = tlc_synchronize(L->ctx)) return rc;
     memcpy(next_ids_host, L->host_next, (size_t)batch * 4);

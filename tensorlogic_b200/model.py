@@ -211,6 +211,12 @@ class Llama:
         except Exception:
             pass
 
+    def set_comm(self, comm) -> None:
+        """Tensor parallelism: join this rank's runner to its communicator (tensorlogic_b200.comm.Comm)."""
+        check(self.dev.lib.tlc_llama_set_comm(self.handle, comm.handle))
+        self._comm = comm  # keep it alive
+        self.vocab_local = self.arch.vocab  # logits handed back to the host are full rows
+
     def prefill(self, ids, pos0: int = 0, return_logits: bool = True, all_rows: bool = False):
         """Returns (next_token, logits or None); logits are [1 or n, vocab] f16."""
         ids = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)
