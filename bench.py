@@ -20,9 +20,11 @@ prompt, then greedy decode with an f16 KV cache.  A "step" is one decode step
   cpu_baseline the CPU oracle's restatement of the reference's literal CPU
                path (single thread, f16 running sum), on a bounded sample.
 
-With --gpus N > 1 (launched under torchrun) every rank decodes its own replica
-of the model: the runner is single-GPU in this build and tensor parallelism is
-not wired in yet, so the line says parallelism "replicas" and scaling "weak".
+With --gpus N > 1 (launched under torchrun, one process per GPU) the workload is
+BASELINE.json configs[4]: Llama-2-70B-shape Q4_0 decode, tensor-parallel over
+the N GPUs with an NCCL all-reduce after the row-parallel projections (TinyLlama
+has 4 KV heads and cannot be split 8 ways).  The line names that workload and
+says scaling "strong"; it is a different workload from the N=1 line.
 """
 from __future__ import annotations
 
@@ -311,12 +313,126 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def llama_bytes_per_step(arch, tp: int, batch: int, context: int) -> int:
+    """Algorithmic HBM bytes one rank moves per decode step: its shard of every Q4_0 weight once,
+    plus its KV heads' cache of `context` positions per sequence."""
+    d, qd, kvd, f = arch.d_model, arch.n_heads * arch.head_dim, arch.n_kv_heads * arch.head_dim, arch.ffn_dim
+    q4 = lambda n, k: n * (k // 32) * 18
+    layer = q4(qd, d) + 2 * q4(kvd, d) + q4(d, qd) + 2 * q4(f, d) + q4(d, f)
+    weights = (arch.n_layers * layer + q4(arch.vocab, d)) // tp
+    kv = arch.n_layers * 2 * (kvd // tp) * 2 * (context + 1) * batch
+    return weights + kv
+
+
+def run_tp(args, rank: int, world: int, local: int) -> None:
+    """N > 1: Llama-2-70B-shape Q4_0 decode, tensor-parallel over the N GPUs (BASELINE configs[4]):
+    column-parallel q/k/v/gate/up/lm_head, row-parallel o/down with an NCCL all-reduce after each,
+    2048 positions already in the KV cache (filled with random f16 on the device)."""
+    import torch
+    import torch.distributed as dist
+    from tensorlogic_b200.api import Device
+    from tensorlogic_b200.comm import Comm, unique_id
+    from tensorlogic_b200.model import LLAMA2_70B, Llama, synthetic_model
+    arch, batch, context = LLAMA2_70B, args.batch, 2048
+    K, W = args.steps, max(args.warmup, 3)
+    dev = Device(local)
+    box = [unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0, device=torch.device("cuda", local))
+    comm = Comm(dev, box[0], rank, world)
+    model = synthetic_model(dev, arch, SEED, tp_rank=rank, tp_size=world, device_embeddings=True)
+    max_seq = context + 2 * (K + W) + 64
+    llm = Llama(dev, model, arch, max_seq=max_seq, max_batch=batch, max_prefill=16, tp_rank=rank, tp_size=world)
+    llm.set_comm(comm)
+    llm.fill_cache_random(SEED)
+    llm.set_state([(7 + 13 * b) % arch.vocab for b in range(batch)], [context] * batch)
+    stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local))
+
+    def barrier():
+        dev.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        t = torch.tensor([ms], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    llm.decode_enqueue(batch, W)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = dev.launch_count
+    with ClockSampler(local) as clocks:
+        e0.record(stream)
+        llm.decode_enqueue(batch, K)
+        e1.record(stream)
+        barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    gpu_launches = dev.launch_count - launches0
+    tok_s = batch * K / (ms / 1e3)
+
+    # end to end: token ids up from the host, sampled tokens back, every step, on every rank
+    toks = llm.read_state(batch)[0]
+    for _ in range(W):
+        toks = llm.decode(toks)[0]
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        toks = llm.decode(toks)[0]
+    dev.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+
+    # dominant kernel: the GEMV launches of a step, replayed alone (no collectives in that graph)
+    llm.decode_enqueue(batch, W, parts=1)
+    dev.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record(stream)
+    llm.decode_enqueue(batch, K, parts=1)
+    g1.record(stream)
+    dev.synchronize()
+    gemv_ms = max_over_ranks(g0.elapsed_time(g1))
+    if rank != 0:
+        return
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak, peak_src = (float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)") \
+        if os.path.exists(peaks_path) else (6650.0, "fallback")
+    d, qd, kvd, f = arch.d_model, arch.n_heads * arch.head_dim, arch.n_kv_heads * arch.head_dim, arch.ffn_dim
+    q4 = lambda n, k: n * (k // 32) * 18
+    wbytes = (arch.n_layers * (q4(qd, d) + 2 * q4(kvd, d) + q4(d, qd) + 2 * q4(f, d) + q4(d, f)) + q4(arch.vocab, d)) // world
+    gemv_launches = 4 * arch.n_layers + 1
+    # parts=1 in a sharded model also issues the collectives that follow o/down and lm_head
+    us = gemv_ms * 1e3 / (K * gemv_launches)
+    achieved = wbytes / gemv_launches / (us * 1e-6) / 1e9
+    step_bytes = llama_bytes_per_step(arch, world, batch, context + W + K // 2)
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"llama-2-70b-shape q4_0 decode, TP{world}, batch {batch}, 2048-token context "
+                               f"(BASELINE configs[4]); NOT the N=1 workload (tinyllama, configs[2])",
+                   "parallelism": f"tp{world}", "batch": batch, "collectives_per_step": 2 * arch.n_layers + 1,
+                   "allreduce_bytes": batch * d * 2, "step_hbm_bytes_per_gpu": step_bytes,
+                   "step_hbm_gbs_per_gpu": step_bytes / (ms / K * 1e-3) / 1e9,
+                   "l2": "per-GPU weights (GBs) exceed the 126 MB L2", "launches_per_step": llm.launches(7), "seed": SEED},
+        "e2e": {"value": batch * K / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
+                "d2h_bytes_per_step": 4 * batch, "ms_per_step": e2e_ms / K},
+        "gpu_launches": int(gpu_launches),
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q4_0> (per-rank shard; time includes the NCCL "
+                     "collectives interleaved with the GEMV launches)", "achieved": achieved, "peak": peak,
+                     "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
+                     "bytes_per_launch": wbytes / gemv_launches, "us_per_launch": us,
+                     "launches_per_step": gemv_launches, "traffic": None},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1, help="decode batch of the tensor-parallel (N > 1) workload")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -327,7 +443,10 @@ def main() -> None:
     if world > 1:
         dist_setup(args.gpus)
     try:
-        run_ours(args, rank, world, local)
+        if world > 1:
+            run_tp(args, rank, world, local)
+        else:
+            run_ours(args, rank, world, local)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -165,6 +165,14 @@ TLC_API int32_t tlc_qtensor_create_synthetic(tlc_ctx *ctx, int32_t type, int64_t
 TLC_API int32_t tlc_synth_blocks_host(int32_t type, uint64_t seed, uint64_t tensor_id,
                                       int32_t scale_log2, int64_t first_block, int64_t n_blocks,
                                       void *out_host);
+/* Device-side f16 N(mean, std) fill from the same generator (embedding tables
+ * and pre-filled KV caches of the large benchmark shapes).  No counterpart in
+ * the reference. */
+TLC_API int32_t tlc_fill_normal_f16(tlc_ctx *ctx, void *dst_dev, size_t n, uint64_t seed,
+                                    uint64_t tensor_id, float mean, float std);
+TLC_API int32_t tlc_qtensor_create_normal_f16(tlc_ctx *ctx, int64_t n_rows, int64_t n_cols,
+                                              uint64_t seed, uint64_t tensor_id, float mean,
+                                              float std, tlc_qtensor **out);
 TLC_API int32_t tlc_qtensor_destroy(tlc_qtensor *qt);
 /* Local (per-rank) shape and storage.  row_pitch is the distance in bytes
  * between rows in HBM: the GGUF row size rounded up to 16 (equal to it, i.e.

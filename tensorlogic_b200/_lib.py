@@ -78,6 +78,8 @@ PROTOTYPES = {
     "tlc_qtensor_create": (i32, [vp, i32, i64, i64, vp, sz, i32, i32, i32, P(vp)]),
     "tlc_qtensor_create_synthetic": (i32, [vp, i32, i64, i64, u64, u64, i32, i32, i32, i32, P(vp)]),
     "tlc_synth_blocks_host": (i32, [i32, u64, u64, i32, i64, i64, vp]),
+    "tlc_fill_normal_f16": (i32, [vp, vp, sz, u64, u64, f32, f32]),
+    "tlc_qtensor_create_normal_f16": (i32, [vp, i64, i64, u64, u64, f32, f32, P(vp)]),
     "tlc_qtensor_destroy": (i32, [vp]),
     "tlc_qtensor_info": (i32, [vp, P(i32), P(i64), P(i64), P(sz), P(vp)]),
     "tlc_dequant": (i32, [vp, vp, vp]),

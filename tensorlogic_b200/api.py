@@ -170,6 +170,14 @@ class QTensor:
                                                    tp_rank, tp_size, split, C.byref(h)))
         return cls(dev, h)
 
+    @classmethod
+    def normal_f16(cls, dev: Device, n_rows: int, n_cols: int, seed: int, tensor_id: int, mean: float = 0.0,
+                   std: float = 1.0) -> "QTensor":
+        """f16 tensor filled on the device with N(mean, std) (large benchmark tensors only)."""
+        h = C.c_void_p()
+        check(dev.lib.tlc_qtensor_create_normal_f16(dev.handle, n_rows, n_cols, seed, tensor_id, mean, std, C.byref(h)))
+        return cls(dev, h)
+
     def __del__(self):
         try:
             if self.handle and self.dev.handle:

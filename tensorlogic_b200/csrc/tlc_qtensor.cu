@@ -259,6 +259,50 @@ extern "C" int32_t tlc_synth_blocks_host(int32_t type, uint64_t seed, uint64_t t
     return TLC_OK;
 }
 
+// f16 N(mean, std) from the same counter-based uniforms (Box-Muller); used for
+// device-side filling of large f16 tensors of the benchmark configurations
+// (embedding tables, a pre-filled KV cache).  Not bit-matched with the host
+// generator's f64 Box-Muller: parity tests always upload host-generated f16 data.
+__global__ void fill_normal_f16_kernel(__half *__restrict__ out, size_t n, uint64_t key, float mean, float std) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t r1 = tlc_mix64(key + 2 * i), r2 = tlc_mix64(key + 2 * i + 1);
+    const float u1 = ((float)(r1 >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = ((float)(r2 >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+    out[i] = __float2half_rn(mean + std * z);
+}
+
+extern "C" int32_t tlc_fill_normal_f16(tlc_ctx *ctx, void *dst_dev, size_t n, uint64_t seed, uint64_t tensor_id,
+                                       float mean, float std) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(dst_dev, TLC_ERR_INVALID_OPERATION, "fill_normal_f16: null pointer");
+    if (n == 0) return TLC_OK;
+    fill_normal_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(
+        static_cast<__half *>(dst_dev), n, tlc_synth_key(seed, tensor_id), mean, std);
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_qtensor_create_normal_f16(tlc_ctx *ctx, int64_t n_rows, int64_t n_cols, uint64_t seed,
+                                                 uint64_t tensor_id, float mean, float std, tlc_qtensor **out) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(out, TLC_ERR_INVALID_OPERATION, "qtensor_create_normal_f16: null pointer");
+    *out = nullptr;
+    TLC_REQUIRE(n_rows > 0 && n_cols > 0 && n_cols % 8 == 0, TLC_ERR_INVALID_DIMENSION,
+                "f16 tensor shape [%lld, %lld] (columns must be a multiple of 8)", (long long)n_rows, (long long)n_cols);
+    tlc_qtensor *qt = nullptr;
+    if (int32_t rc = alloc_qtensor(ctx, TLC_TYPE_F16, n_rows, n_cols, n_rows, n_cols, 0, 1, TLC_SPLIT_NONE, &qt)) return rc;
+    // n_cols % 8 == 0 makes the row pitch equal to the row size: one flat fill.
+    if (int32_t rc = tlc_fill_normal_f16(ctx, qt->data, (size_t)n_rows * n_cols, seed, tensor_id, mean, std)) {
+        cudaFree(qt->data);
+        delete qt;
+        return rc;
+    }
+    *out = qt;
+    return TLC_OK;
+}
+
 extern "C" int32_t tlc_qtensor_destroy(tlc_qtensor *qt) {
     if (!qt) return TLC_OK;
     cudaSetDevice(qt->ctx->device);

@@ -158,12 +158,18 @@ def synthetic_host_weights(arch: LlamaArch, seed: int, qtype: int = _lib.TYPE_Q4
 
 
 def synthetic_model(dev: Device, arch: LlamaArch, seed: int, qtype: int = _lib.TYPE_Q4_0, tp_rank: int = 0,
-                    tp_size: int = 1) -> Model:
-    """The same weights as ``synthetic_host_weights``; the quantized ones are generated on the device."""
+                    tp_size: int = 1, device_embeddings: bool = False) -> Model:
+    """The same weights as ``synthetic_host_weights``; the quantized ones are generated on the device.
+
+    device_embeddings: fill the f16 embedding table on the device too (same distribution, different
+    samples than the host generator) -- for the large shapes whose 0.5 GB table is slow to make in numpy.
+    """
     m = Model(dev)
     for name, (rows, cols) in arch.tensor_shapes().items():
         if name.endswith("norm.weight"):
             t = QTensor.from_blocks(dev, _lib.TYPE_F16, 1, cols, synth.norm_weight(seed, name, cols))
+        elif name == "token_embd.weight" and device_embeddings:
+            t = QTensor.normal_f16(dev, rows, cols, seed, synth.tensor_id(name), 0.0, 0.02)
         elif name == "token_embd.weight":
             t = QTensor.from_blocks(dev, _lib.TYPE_F16, rows, cols, synth.embedding_table(seed, name, rows, cols))
         else:
@@ -195,6 +201,7 @@ class Llama:
                  tp_size: int = 1):
         self.dev, self.model, self.arch = dev, model, arch
         self.max_batch = max_batch
+        self._max_seq, self._tp_size = max_seq, tp_size
         cfg = LlamaConfig(arch.n_layers, arch.d_model, arch.n_heads, arch.n_kv_heads, arch.head_dim, arch.ffn_dim,
                           arch.vocab, arch.rms_eps, arch.rope_base, max_seq, max_batch, max_prefill, tp_rank, tp_size,
                           int(logits_all_rows), int(not use_graph))
@@ -248,6 +255,18 @@ class Llama:
         check(self.dev.lib.tlc_llama_decode_host(self.handle, batch, ids_p, nxt.ctypes.data_as(C.POINTER(C.c_int32)),
                                                  logits.ctypes.data if logits is not None else None))
         return nxt, logits
+
+    def fill_cache_random(self, seed: int, std: float = 1.0) -> None:
+        """Fill the whole KV cache with f16 N(0, std) on the device: stands in for a context that is
+        'already in the cache' (BASELINE config 4) without running a 2048-token prefill."""
+        cache = self.dev.lib.tlc_llama_cache(self.handle)
+        kv_local = self.arch.n_kv_heads // max(self._tp_size, 1)
+        n = self.max_batch * self._max_seq * kv_local * self.arch.head_dim
+        for l in range(self.arch.n_layers):
+            kp, vp_ = C.c_void_p(), C.c_void_p()
+            check(self.dev.lib.tlc_kvcache_layer_ptrs(cache, l, C.byref(kp), C.byref(vp_)))
+            check(self.dev.lib.tlc_fill_normal_f16(self.dev.handle, kp, n, seed, 2 * l, 0.0, std))
+            check(self.dev.lib.tlc_fill_normal_f16(self.dev.handle, vp_, n, seed, 2 * l + 1, 0.0, std))
 
     def decode_enqueue(self, batch: int, steps: int, parts: int = 7) -> None:
         """Enqueue greedy steps on the device; parts (1 linears | 2 attention | 4 gather+sample) != 7
