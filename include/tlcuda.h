@@ -81,6 +81,16 @@ TLC_API const char *tlc_version(void);
  * TLC_ERR_DEVICE when no CUDA device is present. */
 TLC_API int32_t tlc_init(int32_t ordinal, tlc_ctx **out);
 TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
+/* Runtime switches the reference reads from the environment (TL_PERF, TL_DEBUG,
+ * src/device/kernel_executor.rs:33-41); here by name:
+ *   "gemm_min_m"  activation rows from which quantized linears run as the
+ *                 tcgen05 GEMM (0 = decide from the shape);
+ *   "gemm_tile"   0 = pick the GEMM tile from the shape; 11, 12, 22 force
+ *                 128x128, 128x256 or 256x256 (activation rows x weight rows);
+ *   "pdl"         programmatic dependent launch on (1) / off (0);
+ *   "pdl_mode"    1 = let the successor start at once, 2 = after the last slab.
+ * Unknown names fail with TLC_ERR_INVALID_OPERATION. */
+TLC_API int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value);
 /* MetalDevice::name (metal_device.rs:89). */
 TLC_API int32_t tlc_device_name(tlc_ctx *ctx, char *buf, size_t buflen);
 /* recommended_max_working_set_size / current_allocated_size and the pre-load

@@ -39,6 +39,10 @@ class Device:
         self.handle = h
         self.ordinal = ordinal
 
+    def set_option(self, name: str, value: int) -> None:
+        """Runtime switch by name (tlc_set_option): "gemm_min_m", "pdl", "pdl_mode"."""
+        check(self.lib.tlc_set_option(self.handle, name.encode(), int(value)))
+
     def close(self) -> None:
         if self.handle:
             self.lib.tlc_destroy(self.handle)

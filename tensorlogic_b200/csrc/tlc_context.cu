@@ -76,7 +76,26 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     ctx->use_pdl = !(no_pdl && no_pdl[0] == '1');
     if (const char *e = getenv("TLC_PDL_MODE")) ctx->pdl_mode = atoi(e);
     if (const char *e = getenv("TLC_PDL_SMALL")) ctx->pdl_small = atoi(e) != 0;
+    if (const char *e = getenv("TLC_GEMM_MIN_M")) ctx->gemm_min_m = atoi(e);
     *out = ctx;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value) {
+    TLC_REQUIRE(ctx && name, TLC_ERR_INVALID_OPERATION, "set_option: null pointer");
+    const std::string n(name);
+    if (n == "gemm_min_m")
+        ctx->gemm_min_m = (int)value;
+    else if (n == "gemm_tile") {
+        TLC_REQUIRE(value == 0 || value == 11 || value == 12 || value == 22, TLC_ERR_INVALID_OPERATION,
+                    "set_option: gemm_tile must be 0, 11, 12 or 22");
+        ctx->gemm_tile = (int)value;
+    } else if (n == "pdl")
+        ctx->use_pdl = value != 0;
+    else if (n == "pdl_mode")
+        ctx->pdl_mode = (int)value;
+    else
+        return tlc_fail(TLC_ERR_INVALID_OPERATION, "set_option: unknown option '%s'", name);
     return TLC_OK;
 }
 

@@ -1,0 +1,432 @@
+// Kernel body and launcher of the tcgen05 dequant-GEMM (see tlc_gemm_kernel.cuh).
+#include <type_traits>
+
+#include "tlc_gemm_kernel.cuh"
+
+using namespace tlc_gemm;
+
+namespace {
+
+// Dequantizes the two blocks of one K step of one weight row (`cur`: the 9 / 17
+// 32-bit words that hold them) into the row's eight 16-byte pieces of the
+// swizzled tile at `bt` (`piece`: their byte offsets).
+template <int QT>
+__device__ __forceinline__ void dequant_step(const uint32_t *cur, uint8_t *bt, const uint32_t (&piece)[8]) {
+    if (QT == TLC_TYPE_Q4_0) {
+        // 36 bytes: d0 | qs0[16] | d1 | qs1[16]; the even block's qs sit 2 bytes past a word boundary
+        const __half2 bias = __float2half2_rn(1032.f);  // 1024 (magic) + 8
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            uint32_t q[4];
+            __half d;
+            if (e == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) q[j] = __funnelshift_r(cur[j], cur[j + 1], 16);
+                d = __ushort_as_half((unsigned short)(cur[0] & 0xFFFFu));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) q[j] = cur[5 + j];
+                d = __ushort_as_half((unsigned short)(cur[4] >> 16));
+            }
+            const __half2 d2 = __half2half2(d);
+            uint4 c[4];
+            c[0] = dequant8(q[0] & 0x0F0F0F0Fu, q[1] & 0x0F0F0F0Fu, bias, d2);                // elems 0..7
+            c[1] = dequant8(q[2] & 0x0F0F0F0Fu, q[3] & 0x0F0F0F0Fu, bias, d2);                // 8..15
+            c[2] = dequant8((q[0] >> 4) & 0x0F0F0F0Fu, (q[1] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 16..23
+            c[3] = dequant8((q[2] >> 4) & 0x0F0F0F0Fu, (q[3] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 24..31
+#pragma unroll
+            for (int j = 0; j < 4; j++) *reinterpret_cast<uint4 *>(bt + piece[4 * e + j]) = c[j];
+        }
+    } else {
+        // 68 bytes: d0 | q0[32] | d1 | q1[32]
+        const __half2 bias = __float2half2_rn(1152.f);  // 1024 (magic) + 128 (sign flip)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            uint32_t q[8];
+            __half d;
+            if (e == 0) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) q[j] = __funnelshift_r(cur[j], cur[j + 1], 16) ^ 0x80808080u;
+                d = __ushort_as_half((unsigned short)(cur[0] & 0xFFFFu));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) q[j] = cur[9 + j] ^ 0x80808080u;
+                d = __ushort_as_half((unsigned short)(cur[8] >> 16));
+            }
+            const __half2 d2 = __half2half2(d);
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                *reinterpret_cast<uint4 *>(bt + piece[4 * e + j]) = dequant8(q[2 * j], q[2 * j + 1], bias, d2);
+        }
+    }
+}
+
+// B producer of one weight row.  The row's raw blocks are fetched in groups of
+// nine 16-byte pieces -- Q4_0: 8 blocks = four K steps (144 bytes); Q8_0: 4
+// blocks = two K steps (136 bytes, which start 0 or 8 bytes into the first
+// piece) -- one group ahead of their use, so the global-memory latency is
+// spread over a group's worth of K steps.
+template <int QT, int STAGES, int STAGE_BYTES>
+__device__ __forceinline__ void produce_b(const GemmParams &p, uint8_t *btiles, uint64_t *full, uint64_t *empty,
+                                          volatile int *abort_flag, int n0, int row, int KT, int lane) {
+    constexpr int BB = QT == TLC_TYPE_Q4_0 ? 18 : 34;
+    constexpr int RAW_WORDS = 2 * BB / 4;           // 32-bit words of the two blocks of one K step
+    constexpr int SPG = QT == TLC_TYPE_Q4_0 ? 4 : 2;  // K steps per group
+    constexpr int GV4 = 9;                           // 16-byte pieces per group
+    const bool row_ok = n0 + row < p.n;
+    const uint4 *wrow4 = reinterpret_cast<const uint4 *>(p.w + (size_t)(n0 + (row_ok ? row : 0)) * p.w_pitch);
+    // Rows past N load nothing: a zero scale makes every value of the tile row zero.
+    const int limit_v4 = row_ok ? (int)(p.w_pitch >> 4) : 0;
+    uint4 nxt4[GV4], cur4[GV4];
+    auto load_group = [&](int g) {
+        const int start = QT == TLC_TYPE_Q4_0 ? 9 * g : (17 * g) >> 1;
+#pragma unroll
+        for (int i = 0; i < GV4; i++) {
+            const int idx = start + i;  // the last group may end in the row's padding
+            nxt4[i] = idx < limit_v4 ? __ldg(wrow4 + idx) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    // byte offsets of the eight 16-byte pieces of this row under the 128-byte swizzle
+    uint32_t piece[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) piece[j] = (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4));
+    const int n_groups = (KT + SPG - 1) / SPG;
+    // WOFF: word of the group's first block inside cur4 (odd Q8_0 groups start 8 bytes in)
+    auto process = [&](int g, auto woff_c) {
+        constexpr int WOFF = decltype(woff_c)::value;
+#pragma unroll
+        for (int st = 0; st < SPG; st++) {
+            const int kt = g * SPG + st;
+            if (kt >= KT) break;
+            uint32_t cur[RAW_WORDS];
+#pragma unroll
+            for (int i = 0; i < RAW_WORDS; i++) {
+                const int wi = WOFF + st * RAW_WORDS + i;
+                const uint4 v = cur4[wi >> 2];
+                cur[i] = (wi & 3) == 0 ? v.x : (wi & 3) == 1 ? v.y : (wi & 3) == 2 ? v.z : v.w;
+            }
+            const int s = kt % STAGES;
+            mbar_wait(&empty[s], ((kt / STAGES) & 1u) ^ 1u, abort_flag, p.status, 11);
+            dequant_step<QT>(cur, btiles + (size_t)s * STAGE_BYTES, piece);
+            fence_async_proxy();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+    };
+    load_group(0);
+#pragma unroll 1
+    for (int g = 0; g < n_groups; g += 2) {
+#pragma unroll
+        for (int i = 0; i < GV4; i++) cur4[i] = nxt4[i];
+        if (g + 1 < n_groups) load_group(g + 1);
+        process(g, std::integral_constant<int, 0>{});
+        if (g + 1 < n_groups) {
+#pragma unroll
+            for (int i = 0; i < GV4; i++) cur4[i] = nxt4[i];
+            if (g + 2 < n_groups) load_group(g + 2);
+            process(g + 1, std::integral_constant<int, QT == TLC_TYPE_Q4_0 ? 0 : 2>{});
+        }
+    }
+}
+
+// One 32-column piece of the epilogue for one activation row: f16 rounding of
+// the accumulators `r`, then RoPE / bias / residual as the launch asks, store.
+__device__ __forceinline__ void epilogue_piece(const GemmParams &p, const uint32_t (&r)[32], int row, int pos, int nb,
+                                               __half *ybase) {
+    __align__(16) __half h[32];
+#pragma unroll
+    for (int e = 0; e < 32; e++) h[e] = __float2half_rn(__uint_as_float(r[e]));
+    if (p.head_dim > 0) {
+        // Interleaved RoPE on the f16-rounded projection (rope_f16,
+        // shaders/unified.metal:2355-2417); a pair never straddles this
+        // thread's 32 columns because heads start at even columns.
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+            const int pair = ((nb + e) % p.head_dim) >> 1;
+            const float exponent = (float)(2 * pair) / (float)p.head_dim;
+            const float freq = 1.0f / powf(p.rope_base, exponent);
+            const float theta = (float)(unsigned)pos * freq;
+            const float cs = cosf(theta), sn = sinf(theta);
+            const float x0 = __half2float(h[e]), x1 = __half2float(h[e + 1]);
+            h[e] = __float2half_rn(__fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn)));
+            h[e + 1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs)));
+        }
+    }
+    const bool whole = nb + 32 <= p.n;
+    const bool vec_ok = p.vec_ok != 0;
+    if (p.bias) {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            if (whole || nb + e < p.n) h[e] = __hadd(h[e], p.bias[nb + e]);
+    }
+    if (p.residual) {
+        const __half *rrow = p.residual + (size_t)row * p.n + nb;
+        if (whole && vec_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                const uint4 rv = *reinterpret_cast<const uint4 *>(rrow + 8 * v);
+                const __half *rh = reinterpret_cast<const __half *>(&rv);
+#pragma unroll
+                for (int e = 0; e < 8; e++) h[8 * v + e] = __hadd(h[8 * v + e], rh[e]);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; e++)
+                if (nb + e < p.n) h[e] = __hadd(h[e], rrow[e]);
+        }
+    }
+    if (whole && vec_ok) {
+#pragma unroll
+        for (int v = 0; v < 4; v++)
+            *reinterpret_cast<uint4 *>(ybase + nb + 8 * v) = *reinterpret_cast<const uint4 *>(h + 8 * v);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            if (nb + e < p.n) ybase[nb + e] = h[e];
+    }
+}
+
+template <int QT, int MT, int NT>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmParams p) {
+    constexpr int BN = 128 * NT;
+    constexpr int A_BYTES = 128 * MT * 128, B_BYTES = BN * 128;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int kStages = stages_for(MT, NT);
+    constexpr uint32_t TMEM_COLS = MT * BN;  // 128, 256 or 512: a power of two
+    constexpr uint32_t IDESC = idesc_for(BN);
+    constexpr int MMA_WARP = 12;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(tiles + (size_t)kStages * STAGE_BYTES);
+    uint64_t *empty = full + kStages;
+    uint64_t *accum_bar = empty + kStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(accum_bar + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * 128 * MT;
+    const int KT = p.k / kBK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full[s], 4 + 4 * NT);  // A-loader warps + working B-producer warps
+            mbar_init(&empty[s], 1);          // tcgen05.commit
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    tlc_pdl_prologue();  // x (and residual) come from the previous kernel of the stream
+
+    if (warp >= 4 && warp < 4 + 4 * NT) {
+        produce_b<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, n0, tid - 128, KT, lane);
+    } else if (warp < 4) {
+        // ------------------------------ A loaders ------------------------------
+        auto issue = [&](int j) {
+            const int s = j % kStages;
+            mbar_wait(&empty[s], ((j / kStages) & 1u) ^ 1u, abort_flag, p.status, 12);
+            const uint32_t abase = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+            // 8 consecutive threads copy the 128 bytes of one row.
+#pragma unroll
+            for (int it = 0; it < 8 * MT; it++) {
+                const int row = it * 16 + (tid >> 3), c = tid & 7;
+                const bool ok = m0 + row < p.m;
+                const __half *src = p.x + (size_t)(ok ? m0 + row : 0) * p.k + (size_t)j * kBK + c * 8;
+                cp_async16(abase + row * 128 + ((c ^ (row & 7)) << 4), src, ok);
+            }
+        };
+        constexpr int kAhead = kStages - 1;
+        for (int j = 0; j < kAhead; j++) {
+            if (j < KT) issue(j);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        for (int kt = 0; kt < KT; kt++) {
+            // Hand over stage kt first, then refill the stage the MMA of step
+            // kt-1 is about to free: the hand-over must not wait for that MMA.
+            asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");
+            fence_async_proxy();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[kt % kStages]);
+            const int j = kt + kAhead;
+            if (j < KT) issue(j);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+    } else if (warp == MMA_WARP) {
+        // ------------------------------ MMA issuer ------------------------------
+        for (int kt = 0; kt < KT; kt++) {
+            const int s = kt % kStages;
+            const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (kt / kStages) & 1u, abort_flag, p.status, 14));
+            tc_fence_after();
+            if (lane == 0 && ready) {
+                const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k16 = 0; k16 < kBK / 16; k16++) {
+                    const uint64_t bdesc = make_desc(b_addr + k16 * 32);
+#pragma unroll
+                    for (int i = 0; i < MT; i++)
+                        umma_f16(tmem_base + BN * i, make_desc(a_addr + i * (128 * 128) + k16 * 32), bdesc, IDESC,
+                                 (kt > 0 || k16 > 0) ? 1u : 0u);
+                }
+            }
+            if (lane == 0) umma_commit(&empty[s]);  // arrives when the MMAs above have read the stage
+            __syncwarp();
+        }
+        if (lane == 0) umma_commit(accum_bar);
+        __syncwarp();
+    }
+
+    // ------------------------------ epilogue ------------------------------
+    // Warp w reads tensor-memory lanes 32*(w%4) .. +31 (= activation rows of a
+    // sub-tile); the three warps of a lane quarter take the 32-column pieces in turn.
+    if (warp < MMA_WARP) {
+        mbar_wait(accum_bar, 0, abort_flag, p.status, 13);
+        tc_fence_after();
+        const int wq = warp & 3;
+        constexpr int PIECES = MT * BN / 32;
+#pragma unroll 1
+        for (int pc = warp >> 2; pc < PIECES; pc += 3) {
+            const int i = pc / (BN / 32), c0 = (pc % (BN / 32)) * 32;
+            const int row = m0 + 128 * i + 32 * wq + lane;
+            const bool row_ok = row < p.m;
+            const int pos = !row_ok ? 0 : p.positions ? p.positions[row] : p.pos_offset + row;
+            // Dense rows by default; a KV-cache destination addresses rows by (sequence, position).
+            __half *ybase = p.y + (size_t)((long long)row * p.row_stride + (long long)pos * p.pos_stride);
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(32 * wq) << 16) + (uint32_t)(BN * i + c0), r);
+            if (row_ok && n0 + c0 < p.n) epilogue_piece(p, r, row, pos, n0 + c0, ybase);
+        }
+        tc_fence_before();
+    }
+
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int QT, int MT, int NT>
+int32_t launch_tile(tlc_ctx *ctx, const GemmParams &p) {
+    const size_t smem = smem_bytes(MT, NT);
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem));
+        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared));
+        configured[ctx->device & 63] = true;
+    }
+    const dim3 grid((unsigned)((p.n + 128 * NT - 1) / (128 * NT)), (unsigned)((p.m + 128 * MT - 1) / (128 * MT)));
+    cudaError_t le = tlc_launch_pdl(ctx, gemm_tcgen05_kernel<QT, MT, NT>, grid, dim3(kThreads), smem, p);
+    if (le != cudaSuccess) {
+        cudaGetLastError();
+        return tlc_fail(TLC_ERR_CUDA, "gemm launch failed: %s", cudaGetErrorString(le));
+    }
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
+
+template <int QT>
+int32_t launch_one_t(tlc_ctx *ctx, const GemmParams &p) {
+    // The widest tile that still gives every SM a CTA: 256 x 256 halves the
+    // activation traffic from L2 per MMA against 128 x 128.
+    auto ctas = [&](int mt, int nt) {
+        return (long)((p.n + 128 * nt - 1) / (128 * nt)) * ((p.m + 128 * mt - 1) / (128 * mt));
+    };
+    int tile = ctx->gemm_tile;  // 0: choose; 11 / 12 / 22: forced (tests)
+    if (tile == 0) tile = p.m > 128 && ctas(2, 2) >= ctx->sm_count ? 22 : ctas(1, 2) >= ctx->sm_count ? 12 : 11;
+    if (tile == 22) return launch_tile<QT, 2, 2>(ctx, p);
+    if (tile == 12) return launch_tile<QT, 1, 2>(ctx, p);
+    return launch_tile<QT, 1, 1>(ctx, p);
+}
+
+int32_t launch_one(tlc_ctx *ctx, const GemmParams &p, int type) {
+    return type == TLC_TYPE_Q4_0 ? launch_one_t<TLC_TYPE_Q4_0>(ctx, p) : launch_one_t<TLC_TYPE_Q8_0>(ctx, p);
+}
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+}  // namespace
+
+size_t tlc_gemm_scratch_bytes(int m, int64_t k, int64_t n_swiglu) {
+    return align256((size_t)m * k * 2) + 2 * align256((size_t)m * n_swiglu * 2);
+}
+
+bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a) {
+    const tlc_qtensor *w0 = a.outs[0].w;
+    if (w0->type != TLC_TYPE_Q4_0 && w0->type != TLC_TYPE_Q8_0) return false;
+    if (w0->n_cols % kBK != 0 || w0->n_cols < kBK) return false;
+    if (ctx->gemm_min_m > 0) return a.m >= ctx->gemm_min_m;
+    // Below 17 rows one GEMV pass reads the weights once.  Up to 48 rows the
+    // GEMV's few passes still win unless the weight has enough 128-row tiles
+    // to occupy half of the SMs.
+    int64_t tiles = 0;
+    for (int i = 0; i < a.n_out; i++) tiles = tiles < (a.outs[i].w->n_rows + 128 - 1) / 128 ? (a.outs[i].w->n_rows + 128 - 1) / 128 : tiles;
+    return a.m > (tiles * 2 >= ctx->sm_count ? 16 : 48);
+}
+
+// Same contract as tlc_launch_gemv for m activation rows on the tensor cores:
+// the RMSNorm prologue runs as its own kernel into scratch, every output of a
+// fused multi-projection is its own GEMM, and the SiLU.mul pair is two GEMMs
+// into scratch plus the element-wise kernel.
+int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
+    const tlc_qtensor *w0 = a.outs[0].w;
+    const int64_t k = w0->n_cols;
+    const bool swiglu = a.epilogue == TLC_EPI_SWIGLU;
+    const size_t norm_bytes = a.norm_w ? align256((size_t)a.m * k * 2) : 0;
+    const size_t gu_bytes = swiglu ? align256((size_t)a.m * w0->n_rows * 2) : 0;
+    if (norm_bytes + 2 * gu_bytes > 0)
+        if (int32_t rc = tlc_scratch_reserve(ctx, norm_bytes + 2 * gu_bytes)) return rc;
+    uint8_t *scratch = static_cast<uint8_t *>(ctx->scratch);
+    const __half *x = static_cast<const __half *>(a.x);
+    if (a.norm_w) {
+        if (int32_t rc = tlc_rms_norm(ctx, a.x, a.norm_w, scratch, a.m, (int32_t)k, a.eps)) return rc;
+        x = reinterpret_cast<const __half *>(scratch);
+    }
+    TLC_REQUIRE(((uintptr_t)x & 15) == 0, TLC_ERR_INVALID_OPERATION, "gemm: activations must be 16-byte aligned");
+    for (int i = 0; i < a.n_out; i++) {
+        const tlc_qtensor *w = a.outs[i].w;
+        GemmParams p{};
+        p.w = static_cast<const uint8_t *>(w->data);
+        p.w_pitch = w->row_pitch;
+        p.x = x;
+        p.m = a.m;
+        p.n = (int)w->n_rows;
+        p.k = (int)k;
+        p.status = ctx->dev_status;
+        if (swiglu) {
+            p.y = reinterpret_cast<__half *>(scratch + norm_bytes + (size_t)i * gu_bytes);
+            p.row_stride = p.n;
+        } else {
+            p.y = static_cast<__half *>(a.outs[i].y);
+            p.row_stride = a.outs[i].row_stride >= 0 ? a.outs[i].row_stride : (long long)w->n_rows;
+            p.pos_stride = a.outs[i].pos_stride;
+            p.head_dim = a.outs[i].rope_heads > 0 ? (int)(w->n_rows / a.outs[i].rope_heads) : 0;
+            p.residual = a.epilogue == TLC_EPI_RESIDUAL ? static_cast<const __half *>(a.residual) : nullptr;
+            p.bias = a.epilogue == TLC_EPI_STORE ? static_cast<const __half *>(a.bias) : nullptr;
+        }
+        p.pos_offset = a.pos_offset;
+        p.positions = a.positions;
+        p.rope_base = (float)a.rope_base;
+        p.vec_ok = ((p.row_stride | p.pos_stride | (long long)p.n) & 7) == 0 && ((uintptr_t)p.y & 15) == 0 &&
+                   ((uintptr_t)p.residual & 15) == 0;
+        if (int32_t rc = launch_one(ctx, p, w->type)) return rc;
+    }
+    if (swiglu) {
+        const size_t n = (size_t)a.m * w0->n_rows;
+        return tlc_swiglu(ctx, scratch + norm_bytes, scratch + norm_bytes + gu_bytes, a.outs[0].y, n);
+    }
+    return TLC_OK;
+}

@@ -202,6 +202,8 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
         return TLC_OK;
     }
 
+    if (tlc_gemm_eligible(ctx, a)) return tlc_launch_gemm(ctx, a);
+
     const int max_m = gemv_max_m(ctx, type, (int)k);
     TLC_REQUIRE(max_m >= 1, TLC_ERR_INVALID_OPERATION, "gemv: K = %lld too large for the shared-memory staging",
                 (long long)k);

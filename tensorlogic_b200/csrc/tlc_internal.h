@@ -49,6 +49,10 @@ struct tlc_ctx {
     bool use_pdl = true;
     int pdl_mode = 2;      // TLC_PDL_MODE: when the GEMV lets its successor be scheduled (1 at once, 2 after its last slab; measured: 2 is 1-2 % faster than no PDL, 1 is 10 % slower)
     bool pdl_small = true; // TLC_PDL_SMALL=0: keep PDL off for the non-GEMV kernels
+    // TLC_GEMM_MIN_M: activation rows from which quantized linears run as the
+    // tensor-core GEMM (0: decide from the shape; a huge value keeps the GEMV).
+    int gemm_min_m = 0;
+    int gemm_tile = 0;  // 0: pick the GEMM tile from the shape; 11, 12, 22: force 128x128, 128x256, 256x256
 };
 
 struct tlc_buf {
@@ -172,6 +176,14 @@ struct tlc_gemv_args {
 };
 
 int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a);
+
+// Tensor-core (tcgen05) path of the same contract for many activation rows;
+// tlc_launch_gemv forwards to it when tlc_gemm_eligible says so.
+bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a);
+int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a);
+// Scratch the GEMM path needs for m rows of width k with a fused RMSNorm and a
+// SiLU.mul pair of n_swiglu outputs (reserve it before capturing a graph).
+size_t tlc_gemm_scratch_bytes(int m, int64_t k, int64_t n_swiglu);
 
 struct tlc_kvcache;
 int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const void *q_dev, void *out_dev,

@@ -221,6 +221,12 @@ extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_ll
             return tlc_fail(TLC_ERR_ALLOCATION, "activation buffer of %zu bytes failed: %s", b.bytes, cudaGetErrorString(e));
         }
     }
+    // The tensor-core path of the linears (many rows) works through scratch;
+    // reserve it now so that no allocation happens inside a graph capture.
+    {
+        const int64_t kmax = d > qd ? d : qd;
+        if (int32_t rc = tlc_scratch_reserve(ctx, tlc_gemm_scratch_bytes(L->max_rows, kmax, L->ffn_local))) return rc;
+    }
     // Same shared-memory carve-out as the GEMV and attention kernels they run between.
     TLC_CUDA(cudaFuncSetAttribute(embed_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                   cudaSharedmemCarveoutMaxShared));
