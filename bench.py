@@ -44,6 +44,18 @@ sys.path.insert(0, ROOT)
 PROMPT_TOKENS = 512
 SEED = 2
 METRIC = "q4_0_decode_tokens_per_s"
+L2_BYTES = 126 * 1000 * 1000
+
+
+def load_peaks() -> dict:
+    """Measured roofline denominators (MEASURED_PEAKS.json beside this file), else the pool's fallback figures."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 def tinyllama_bytes_per_token(arch, context: int) -> int:
@@ -426,8 +438,66 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_kernel(args) -> None:
+    """Micro-benchmark of one quantized linear (the profiling target): K launches of
+    tlc_linear over weight copies that together exceed the L2, CUDA events on the
+    library's stream.  m <= 16 runs the fused dequant-GEMV (HBM-bound: GB/s of
+    algorithmic bytes), larger m the tcgen05 dequant-GEMM (tensor-bound: TFLOP/s)."""
+    import torch
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.api import Device, QTensor
+    qtype = {"q4_0": 2, "q8_0": 8}[args.qtype]
+    n, k, m = args.n, args.k, args.m
+    dev = Device(0)
+    peaks = load_peaks()
+    bb = 18 if qtype == 2 else 34
+    w_bytes = n * (k // 32) * bb
+    copies = max(1, min(64, -(-(2 * L2_BYTES) // w_bytes)))
+    ws = [QTensor.synthetic(dev, qtype, n, k, SEED, 100 + i) for i in range(copies)]
+    x = dev.tensor(synth.activations(SEED, "x", (m, k)))
+    y = dev.empty((m, n))
+    stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", 0))
+    lib = dev.lib
+
+    def run(count):
+        for i in range(count):
+            rc = lib.tlc_linear(dev.handle, ws[i % copies].handle, x.ptr, m, k, y.ptr, None)
+            if rc:
+                raise RuntimeError(lib.tlc_last_error().decode())
+
+    run(max(args.warmup, 1))
+    dev.synchronize()
+    l0 = dev.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        run(args.steps)
+        e1.record(stream)
+    dev.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    algo_bytes = w_bytes + 2 * m * k + 2 * m * n
+    flops = 2.0 * m * n * k
+    gemm = m > 16 and (dev.launch_count - l0) == args.steps and k % 64 == 0
+    line = {"kernel": "linear", "qtype": args.qtype, "n": n, "k": k, "m": m, "launches": args.steps,
+            "weight_copies": copies, "us_per_launch": us, "gpu_launches": dev.launch_count - l0}
+    if m <= 16:
+        line["roofline"] = {"bound": "hbm", "achieved": algo_bytes / us / 1e3, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": algo_bytes / us / 1e3 / peaks["hbm_gbs"], "peak_source": peaks["source"]}
+    else:
+        line["roofline"] = {"bound": "tensor", "achieved": flops / us / 1e6, "peak": peaks["bf16_tflops"],
+                            "unit": "TFLOP/s", "frac": flops / us / 1e6 / peaks["bf16_tflops"],
+                            "peak_source": peaks["source"], "path": "tcgen05 gemm" if gemm else "gemv passes"}
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default=None, choices=["linear"],
+                    help="micro-benchmark one kernel instead of the decode workload (see run_kernel)")
+    ap.add_argument("--qtype", default="q4_0", choices=["q4_0", "q8_0"])
+    ap.add_argument("--n", type=int, default=28672)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
@@ -439,6 +509,9 @@ def main() -> None:
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.kernel:
+        run_kernel(args)
         return
     if world > 1:
         dist_setup(args.gpus)
