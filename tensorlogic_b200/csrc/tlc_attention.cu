@@ -21,6 +21,7 @@
 // through shared memory.  For decode the key range of a sequence is split over
 // several CTAs; each writes its partial to global scratch and the last one to
 // finish (atomic ticket) merges them, so no second launch is needed.
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
 #include "tlc_internal.h"
@@ -53,6 +54,8 @@ struct AttnParams {
     float *part_ml;  // [rows][nsplit][2]
     float *part_o;   // [rows][nsplit][D]
     int *counters;   // [B][q_tiles][Hkv], zero between launches
+    int cluster;     // 1: the nsplit CTAs of a tile form a thread-block cluster and merge through
+                     // distributed shared memory instead of global scratch
 };
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
@@ -100,6 +103,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     __half *vs = ks + 2 * TILE;                         // [2][TILE]
     __shared__ float sm_m[4][16], sm_l[4][16];
     __shared__ int sm_last;
+    __shared__ float cl_m[16], cl_l[16];
+    __shared__ __align__(16) float cl_o[16][D];
 
     tlc_pdl_prologue();  // q and the cache rows of this step come from the previous kernel
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -297,6 +302,46 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         return;
     }
 
+    if (p.cluster) {
+        // ---- split keys inside a cluster: partials stay in shared memory, rank 0 reads
+        // its peers' through distributed shared memory ----
+        namespace cg = cooperative_groups;
+        cg::cluster_group cl = cg::this_cluster();
+        if ((tid & 7) == 0) {
+            cl_m[row] = M;
+            cl_l[row] = L;
+        }
+#pragma unroll
+        for (int j = 0; j < DPT; j++) cl_o[row][d0 + j] = acc[j];
+        cl.sync();
+        if (cl.block_rank() == 0 && row_valid) {
+            float Mg = -INFINITY;
+            for (int sp = 0; sp < p.nsplit; sp++) Mg = fmaxf(Mg, cl.map_shared_rank(cl_m, sp)[row]);
+            float Lg = 0.f;
+#pragma unroll
+            for (int j = 0; j < DPT; j++) acc[j] = 0.f;
+            for (int sp = 0; sp < p.nsplit; sp++) {
+                const float ms = cl.map_shared_rank(cl_m, sp)[row];
+                const float wgt = ms == -INFINITY ? 0.f : expf(ms - Mg);
+                Lg += cl.map_shared_rank(cl_l, sp)[row] * wgt;
+                const float *ro = cl.map_shared_rank(&cl_o[0][0], sp) + row * D + d0;
+#pragma unroll
+                for (int j = 0; j < DPT; j += 4) {
+                    const float4 v = *reinterpret_cast<const float4 *>(ro + j);
+                    acc[j] += v.x * wgt;
+                    acc[j + 1] += v.y * wgt;
+                    acc[j + 2] += v.z * wgt;
+                    acc[j + 3] += v.w * wgt;
+                }
+            }
+            const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;
+#pragma unroll
+            for (int j = 0; j < DPT; j++) p.out[out_row * D + d0 + j] = __float2half_rn(acc[j] * inv);
+        }
+        cl.sync();  // peers keep their shared memory alive until rank 0 has read it
+        return;
+    }
+
     // ---- split keys: publish the partial, last CTA of the tile merges ----
     if (row_valid) {
         const size_t pi = out_row * p.nsplit + split;
@@ -404,10 +449,15 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
         if (nsplit < 1) nsplit = 1;
         if (nsplit > 64) nsplit = 64;
     }
+    // Up to 32 key tiles (2048 keys) the splits of a tile fit one thread-block cluster
+    // (8 CTAs, up to 4 tiles each) and merge through distributed shared memory.
+    const bool cluster = I == 1 && nsplit > 1 && (T + kTileKeys - 1) / kTileKeys <= 32;
+    if (cluster && nsplit > 8) nsplit = 8;
     p.nsplit = nsplit;
+    p.cluster = cluster ? 1 : 0;
     const int tiles_total = (T + kTileKeys - 1) / kTileKeys;
     p.keys_per_split = ((tiles_total + nsplit - 1) / nsplit) * kTileKeys;
-    if (nsplit > 1) {
+    if (nsplit > 1 && !cluster) {
         const size_t rows = (size_t)batch * I * n_heads;
         const size_t ml = rows * nsplit * 2 * sizeof(float), po = rows * nsplit * D * sizeof(float);
         // Ticket counters (one per tile, zero between launches: the merging
@@ -442,8 +492,27 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
         }
         configured[di][ctx->device & 63] = true;
     }
-    cudaError_t le = D == 64 ? tlc_launch_pdl(ctx, attention_kernel<64>, grid, dim3(kAttnThreads), smem_bytes, p)
-                             : tlc_launch_pdl(ctx, attention_kernel<128>, grid, dim3(kAttnThreads), smem_bytes, p);
+    cudaError_t le;
+    if (cluster) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kAttnThreads);
+        cfg.dynamicSmemBytes = smem_bytes;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)nsplit;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ctx->use_pdl && ctx->pdl_small ? 2 : 1;
+        le = D == 64 ? cudaLaunchKernelEx(&cfg, attention_kernel<64>, p) : cudaLaunchKernelEx(&cfg, attention_kernel<128>, p);
+    } else {
+        le = D == 64 ? tlc_launch_pdl(ctx, attention_kernel<64>, grid, dim3(kAttnThreads), smem_bytes, p)
+                     : tlc_launch_pdl(ctx, attention_kernel<128>, grid, dim3(kAttnThreads), smem_bytes, p);
+    }
     if (le != cudaSuccess) {
         cudaGetLastError();
         return tlc_fail(TLC_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(le));

@@ -92,41 +92,13 @@ __global__ void linear_generic_kernel(const uint8_t *__restrict__ w, size_t pitc
     }
 }
 
-template <int QT, int NT>
-int32_t launch_mma(tlc_ctx *ctx, GemvParams &p, size_t smem_fixed) {
-    using T = QTraits<QT>;
-    constexpr int PITCH = stage_pitch(T::KCB * T::BB);
-    constexpr size_t STAGE_BYTES = (size_t)kRows * PITCH;
-    const size_t budget = (size_t)ctx->prop.sharedMemPerBlockOptin;
-    TLC_REQUIRE(smem_fixed + 2 * STAGE_BYTES <= budget, TLC_ERR_INVALID_OPERATION,
-                "gemv: activations of %d x %d do not fit in shared memory", p.m, p.k);
-    // Two CTAs per SM (16 consumer warps hide the shared-memory and MMA latency
-    // of the unpack loop) whenever the activations leave room for at least
-    // three ring stages in half of the SM's shared memory.
-    const size_t half = (size_t)ctx->prop.sharedMemPerMultiprocessor / 2 - 1024;
-    const bool fits_half = smem_fixed + 3 * STAGE_BYTES <= half;
-    // Small problems (a few slabs per SM, the decode-sized linears) run one CTA
-    // per SM in half of the shared memory: the other half is then free for the
-    // CTAs of the NEXT kernel of the stream, which programmatic dependent launch
-    // schedules early so that its weight ring fills while this kernel computes.
-    const bool small = p.total_units <= 4 * ctx->sm_count;
-    const bool two = fits_half && !small;
-    const size_t cap = fits_half ? half : budget;
-    const int max_ctas = two ? 2 * ctx->sm_count : ctx->sm_count;
-    int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
-    // No more stages than this CTA will ever fill.
-    long per_cta = ((long)(p.total_units + grid - 1) / grid) * p.subs * p.nchunks;
-    int stages = (int)((cap - smem_fixed) / STAGE_BYTES);
-    if (stages > kMaxStages) stages = kMaxStages;
-    if (stages > per_cta) stages = per_cta < 2 ? 2 : (int)per_cta;
-    p.nstages = stages;
-    p.pdl_mode = ctx->pdl_mode;
-    size_t smem = smem_fixed + (size_t)stages * STAGE_BYTES;
+template <int QT, int NT, int AS>
+int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)budget));
-        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)ctx->prop.sharedMemPerBlockOptin));
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 63] = true;
     }
@@ -140,7 +112,7 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p, size_t smem_fixed) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<QT, NT>, p);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<QT, NT, AS>, p);
     if (le != cudaSuccess) {
         cudaGetLastError();
         return tlc_fail(TLC_ERR_CUDA, "gemv launch failed: %s", cudaGetErrorString(le));
@@ -149,7 +121,52 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p, size_t smem_fixed) {
     return TLC_OK;
 }
 
-size_t gemv_fixed_smem(int nblk_pad, int m, int nt) { return fixed_smem_bytes(nblk_pad, m, nt); }
+template <int QT, int NT>
+int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
+    using T = QTraits<QT>;
+    constexpr int PITCH = stage_pitch(T::KCB * T::BB);
+    constexpr size_t STAGE_BYTES = (size_t)kRows * PITCH;
+    const size_t budget = (size_t)ctx->prop.sharedMemPerBlockOptin;
+    const size_t fixed1 = fixed_smem_bytes(p.nblk_pad, p.m, NT, p.subs);
+    TLC_REQUIRE(fixed1 + 2 * STAGE_BYTES <= budget, TLC_ERR_INVALID_OPERATION,
+                "gemv: activations of %d x %d do not fit in shared memory", p.m, p.k);
+    // Two CTAs per SM (16 consumer warps hide the shared-memory and MMA latency
+    // of the unpack loop) whenever the activations leave room for at least
+    // three ring stages in half of the SM's shared memory.
+    const size_t half = (size_t)ctx->prop.sharedMemPerMultiprocessor / 2 - 1024;
+    const bool fits_half = fixed1 + 3 * STAGE_BYTES <= half;
+    // (Measured on the TinyLlama decode step: keeping small launches at one CTA per
+    // SM, to leave room for the next kernel's early CTAs, costs 8 % against
+    // letting them spread over two CTAs per SM.)
+    const bool two = fits_half;
+    const size_t cap = fits_half ? half : budget;
+    const int max_ctas = two ? 2 * ctx->sm_count : ctx->sm_count;
+    const int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
+    // Accumulator sets per reduction: enough units for about four ring stages
+    // between two cross-warp reductions, as far as this CTA has units and the
+    // shared memory (reduction buffers grow with the sets) allows.
+    const int units_per_cta = (p.total_units + grid - 1) / grid;
+    const int iters_per_unit = p.subs * p.nchunks;
+    int ub = (4 + iters_per_unit - 1) / iters_per_unit;
+    if (ub > units_per_cta) ub = units_per_cta;
+    int as = p.subs;
+    while (as < ub * p.subs && as < (NT == 2 ? 2 : 4)) as *= 2;
+    while (as > p.subs && fixed_smem_bytes(p.nblk_pad, p.m, NT, as) + 3 * STAGE_BYTES > cap) as /= 2;
+    const size_t smem_fixed = fixed_smem_bytes(p.nblk_pad, p.m, NT, as);
+    // No more stages than this CTA will ever fill.
+    const long per_cta = (long)units_per_cta * p.subs * p.nchunks;
+    int stages = (int)((cap - smem_fixed) / STAGE_BYTES);
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages > per_cta) stages = per_cta < 2 ? 2 : (int)per_cta;
+    p.nstages = stages;
+    p.pdl_mode = ctx->pdl_mode;
+    const size_t smem = smem_fixed + (size_t)stages * STAGE_BYTES;
+    if (as == 1) return launch_mma_as<QT, NT, 1>(ctx, p, grid, smem);
+    if (as == 2) return launch_mma_as<QT, NT, 2>(ctx, p, grid, smem);
+    return launch_mma_as<QT, NT, 4>(ctx, p, grid, smem);
+}
+
+size_t gemv_fixed_smem(int nblk_pad, int m, int nt) { return fixed_smem_bytes(nblk_pad, m, nt, 2); }
 
 }  // namespace
 
@@ -251,12 +268,11 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.positions = a.positions ? a.positions + m0 : nullptr;
         p.status = ctx->dev_status;
         const int nt = mc > 8 ? 2 : 1;
-        const size_t fixed = gemv_fixed_smem(p.nblk_pad, mc, nt);
         int32_t rc;
         if (type == TLC_TYPE_Q4_0)
-            rc = nt == 1 ? launch_mma<TLC_TYPE_Q4_0, 1>(ctx, p, fixed) : launch_mma<TLC_TYPE_Q4_0, 2>(ctx, p, fixed);
+            rc = nt == 1 ? launch_mma<TLC_TYPE_Q4_0, 1>(ctx, p) : launch_mma<TLC_TYPE_Q4_0, 2>(ctx, p);
         else
-            rc = nt == 1 ? launch_mma<TLC_TYPE_Q8_0, 1>(ctx, p, fixed) : launch_mma<TLC_TYPE_Q8_0, 2>(ctx, p, fixed);
+            rc = nt == 1 ? launch_mma<TLC_TYPE_Q8_0, 1>(ctx, p) : launch_mma<TLC_TYPE_Q8_0, 2>(ctx, p);
         if (rc) return rc;
     }
     return TLC_OK;

@@ -9,22 +9,22 @@ namespace tlc_gemv {
 //   0    full[8], empty[8] mbarriers
 //   128  abort flag
 //   256  sum-of-squares partials [16 activation rows][8 warps]
-//   768  red   [2][8 warps][16 rows][MP] f32   cross-warp reduction, double buffered
-//   ...  cinit [nblk_pad][NT][4 quad lanes] float4  accumulator start per block
+//   768  red   [2][AS sets][8 warps][16 rows][MP] f32   cross-warp reduction, double buffered
+//   ...  cinit [nblk_pad][NT][4 quad lanes] float2  accumulator start per block (columns 2t, 2t+1)
 //   ...  xzero one zero uint4 (B fragment of activation rows that do not exist)
 //   ...  xperm [nblk_pad][m][4 quad lanes] uint4    activations in fragment order
 //   ...  ring  [stages][16 rows][PITCH]             raw weight bytes (128-byte aligned)
-__host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt) {
+__host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, int as) {
     size_t s = 768;
-    s += (size_t)2 * kConsumerWarps * kRows * (8 * nt) * sizeof(float);
-    s += (size_t)nblk_pad * nt * 4 * sizeof(float4);
+    s += (size_t)2 * as * kConsumerWarps * kRows * (8 * nt) * sizeof(float);
+    s += (size_t)nblk_pad * nt * 4 * sizeof(float2);
     s += sizeof(uint4);
     s += (size_t)nblk_pad * m * 4 * sizeof(uint4);
     s += 128;  // ring alignment slack
     return s;
 }
 
-template <int QT, int NT>
+template <int QT, int NT, int AS>
 __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams p) {
     using T = QTraits<QT>;
     constexpr int MP = 8 * NT;  // padded activation rows
@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 128);
     float *sq_part = reinterpret_cast<float *>(smem + 256);
     float *red = reinterpret_cast<float *>(smem + 768);
-    float4 *cinit = reinterpret_cast<float4 *>(red + 2 * kConsumerWarps * kRows * MP);
+    float2 *cinit = reinterpret_cast<float2 *>(red + 2 * AS * kConsumerWarps * kRows * MP);
     uint4 *xzero = reinterpret_cast<uint4 *>(cinit + (size_t)p.nblk_pad * NT * 4);
     uint4 *xperm = xzero + 1;
     uint8_t *stages = reinterpret_cast<uint8_t *>(xperm + (size_t)p.nblk_pad * p.m * 4);
@@ -67,7 +67,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
         // Weights are never written by a kernel, so the ring starts filling
         // before the previous kernel of the stream has finished.
         uint32_t it = 0;
-        for (int unit = blockIdx.x; unit < p.total_units; unit += gridDim.x) {
+        const int pu_lo = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
+        const int pu_hi = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
+        for (int unit = pu_lo; unit < pu_hi; unit++) {
             for (int sub = 0; sub < p.subs; sub++) {
                 int ti = 0, sl = unit;
                 if (p.subs == 2) {
@@ -125,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
             if (lane == 0) sq_part[m * kConsumerWarps + warp] = sq;
         }
     }
-    for (int i = ctid; i < p.nblk_pad * NT * 4; i += kConsumerThreads) cinit[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = ctid; i < p.nblk_pad * NT * 4; i += kConsumerThreads) cinit[i] = make_float2(0.f, 0.f);
     if (ctid == 0) *xzero = make_uint4(0, 0, 0, 0);
     consumer_bar();
 
@@ -206,8 +208,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                     // components m%2 (row g) and m%2 + 2 (row g+8).
                     const float cv = -T::OFFSET * 5.9604644775390625e-08f * s;  // * 2^-24
                     float *cf = reinterpret_cast<float *>(&cinit[(b * NT + (m >> 3)) * 4 + ((m & 7) >> 1)]);
-                    cf[m & 1] = cv;
-                    cf[(m & 1) + 2] = cv;
+                    cf[m & 1] = cv;  // rows g and g+8 of the tile start from the same value
                 }
             }
         }
@@ -216,35 +217,41 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
 
     // (c) main loop
     const int g = lane >> 2, t = lane & 3;
-    // Loop-invariant addressing of this lane's B fragments: activation row nt*8+g.
-    const uint4 *xp_base[NT];
-    int xp_stride[NT];
+    // Loop-invariant shared-memory addresses (32-bit, explicit ld.shared: a generic
+    // load would go through the global-memory path).  B fragments of activation
+    // row nt*8+g: xperm[(block*m + row)*4 + t]; rows that do not exist read xzero.
+    uint32_t xp_addr[NT], xp_stride[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const bool has = nt * 8 + g < p.m;
-        xp_base[nt] = has ? xperm + (nt * 8 + g) * 4 + t : xzero;
-        xp_stride[nt] = has ? p.m * 4 : 0;
+        xp_addr[nt] = has ? smem_u32(xperm + (nt * 8 + g) * 4 + t) : smem_u32(xzero);
+        xp_stride[nt] = has ? (uint32_t)p.m * 64u : 0u;
     }
-    const float4 *ci_base = cinit + t;
-    const int seg_lo = g * PITCH, seg_hi = (g + 8) * PITCH;
+    const uint32_t ci_addr = smem_u32(cinit + t);
+    const uint32_t stages_addr = smem_u32(stages);
+    const uint32_t seg_lo = g * PITCH, seg_hi = (g + 8) * PITCH;
 
+    // Units of this CTA: a balanced contiguous range.  They are processed in
+    // batches of AS accumulator sets (one set = one 16-row slab; a gate/up unit
+    // takes two), with ONE cross-warp reduction per batch: for short K a slab
+    // is only a few block pairs per warp, and a barrier per slab would dominate.
+    const int u_lo = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
+    const int u_hi = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
+    const int ub = AS / p.subs;  // units per batch
     uint32_t it = 0;
-    int slab_count = 0;
-    __half hold = __float2half(0.f);  // gate value kept between the two slabs of a gate/up unit
+    int batch_count = 0;
 
-    for (int unit = blockIdx.x; unit < p.total_units; unit += gridDim.x) {
-        for (int sub = 0; sub < p.subs; sub++, slab_count++) {
-            int ti = 0, sl = unit;
-            if (p.subs == 2) {
-                ti = sub;
-            } else {
-                if (sl >= p.slabs[0]) { sl -= p.slabs[0]; ti = 1; }
-                if (ti == 1 && sl >= p.slabs[1]) { sl -= p.slabs[1]; ti = 2; }
-            }
-            float acc[4 * NT];
+    for (int u0 = u_lo; u0 < u_hi; u0 += ub, batch_count++) {
+        const int nsets = min(ub, u_hi - u0) * p.subs;
+        float acc[AS][4 * NT];
 #pragma unroll
-            for (int i = 0; i < 4 * NT; i++) acc[i] = 0.f;
+        for (int a = 0; a < AS; a++)
+#pragma unroll
+            for (int i = 0; i < 4 * NT; i++) acc[a][i] = 0.f;
 
+#pragma unroll
+        for (int a = 0; a < AS; a++) {
+            if (a >= nsets) break;
             for (int c = 0; c < p.nchunks; c++, it++) {
                 const int s = it % S;
                 const uint32_t par = (it / S) & 1u;
@@ -253,42 +260,40 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                 const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], par, abort_flag, p.status, 2));
                 const int kcb = min(T::KCB, p.nblk - c * T::KCB);
                 const int npairs = ready ? (kcb + 1) >> 1 : 0;
-                const uint8_t *st = stages + (size_t)s * STAGE_BYTES;
-                const uint32_t *seg_g = reinterpret_cast<const uint32_t *>(st + seg_lo);
-                const uint32_t *seg_g8 = reinterpret_cast<const uint32_t *>(st + seg_hi);
+                const uint32_t row_lo = stages_addr + (uint32_t)s * STAGE_BYTES + seg_lo;
+                const uint32_t row_hi = stages_addr + (uint32_t)s * STAGE_BYTES + seg_hi;
 
-                // One (even, odd) block pair: 2 blocks x 16 rows.  Pair pr starts at
-                // word PW*pr of the 4-byte aligned row segment; the even block's qs
-                // bytes sit 2 bytes past a word boundary, hence the funnel shifts.
+                // One (even, odd) block pair: 2 blocks x 16 rows.  Pair pr starts
+                // 4*PW*pr bytes into the 4-byte aligned row segment; the even block's
+                // qs bytes sit 2 bytes past a word boundary, hence the funnel shifts.
                 auto do_pair = [&](int pr) {
-                    const uint32_t *q0 = seg_g + PW * pr, *q1 = seg_g8 + PW * pr;
-                    const __half *h0 = reinterpret_cast<const __half *>(q0), *h1 = reinterpret_cast<const __half *>(q1);
+                    const uint32_t q0 = row_lo + 4 * PW * pr, q1 = row_hi + 4 * PW * pr;
                     uint32_t we0[2], we1[2], wo0[2], wo1[2];
                     if (QT == TLC_TYPE_Q4_0) {
-                        we0[0] = __funnelshift_r(q0[t], q0[t + 1], 16);
-                        we1[0] = __funnelshift_r(q1[t], q1[t + 1], 16);
-                        wo0[0] = q0[5 + t];
-                        wo1[0] = q1[5 + t];
+                        we0[0] = __funnelshift_r(lds_u32(q0 + 4 * t), lds_u32(q0 + 4 * t + 4), 16);
+                        we1[0] = __funnelshift_r(lds_u32(q1 + 4 * t), lds_u32(q1 + 4 * t + 4), 16);
+                        wo0[0] = lds_u32(q0 + 20 + 4 * t);
+                        wo1[0] = lds_u32(q1 + 20 + 4 * t);
                         we0[1] = we1[1] = wo0[1] = wo1[1] = 0;
                     } else {
-                        const uint32_t a0 = q0[2 * t], a1 = q0[2 * t + 1], a2 = q0[2 * t + 2];
-                        const uint32_t b0 = q1[2 * t], b1 = q1[2 * t + 1], b2 = q1[2 * t + 2];
+                        const uint32_t a0 = lds_u32(q0 + 8 * t), a1 = lds_u32(q0 + 8 * t + 4), a2 = lds_u32(q0 + 8 * t + 8);
+                        const uint32_t b0 = lds_u32(q1 + 8 * t), b1 = lds_u32(q1 + 8 * t + 4), b2 = lds_u32(q1 + 8 * t + 8);
                         we0[0] = __funnelshift_r(a0, a1, 16);
                         we0[1] = __funnelshift_r(a1, a2, 16);
                         we1[0] = __funnelshift_r(b0, b1, 16);
                         we1[1] = __funnelshift_r(b1, b2, 16);
-                        wo0[0] = q0[9 + 2 * t];
-                        wo0[1] = q0[10 + 2 * t];
-                        wo1[0] = q1[9 + 2 * t];
-                        wo1[1] = q1[10 + 2 * t];
+                        wo0[0] = lds_u32(q0 + 36 + 8 * t);
+                        wo0[1] = lds_u32(q0 + 40 + 8 * t);
+                        wo1[0] = lds_u32(q1 + 36 + 8 * t);
+                        wo1[1] = lds_u32(q1 + 40 + 8 * t);
                     }
-                    const float de0 = __half2float(h0[0]), de1 = __half2float(h1[0]);
-                    float do0 = __half2float(h0[T::BB / 2]), do1 = __half2float(h1[T::BB / 2]);
+                    const float de0 = __half2float(lds_f16(q0)), de1 = __half2float(lds_f16(q1));
+                    float do0 = __half2float(lds_f16(q0 + T::BB)), do1 = __half2float(lds_f16(q1 + T::BB));
                     if (2 * pr + 1 >= kcb) {  // odd tail block does not exist
                         do0 = 0.f;
                         do1 = 0.f;
                     }
-                    const int b = c * T::KCB + 2 * pr;
+                    const uint32_t b = (uint32_t)(c * T::KCB + 2 * pr);
 #pragma unroll
                     for (int e = 0; e < 2; e++) {
                         uint32_t a1[4], a2[4];
@@ -297,16 +302,16 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                         const float dlo = e == 0 ? de0 : do0, dhi = e == 0 ? de1 : do1;
 #pragma unroll
                         for (int nt = 0; nt < NT; nt++) {
-                            const uint4 xp = xp_base[nt][(b + e) * xp_stride[nt]];
-                            const float4 ci = ci_base[((b + e) * NT + nt) * 4];
-                            const float cc[4] = {ci.x, ci.y, ci.z, ci.w};
+                            const uint4 xp = lds_u128(xp_addr[nt] + (b + e) * xp_stride[nt]);
+                            const float2 ci = lds_f32x2(ci_addr + ((b + e) * NT + nt) * 32);
+                            const float cc[4] = {ci.x, ci.y, ci.x, ci.y};
                             float d1[4], d2[4];
                             mma16816(d1, a1, xp.x, xp.y, cc);
                             mma16816(d2, a2, xp.z, xp.w, d1);
-                            acc[nt * 4 + 0] = fmaf(dlo, d2[0], acc[nt * 4 + 0]);
-                            acc[nt * 4 + 1] = fmaf(dlo, d2[1], acc[nt * 4 + 1]);
-                            acc[nt * 4 + 2] = fmaf(dhi, d2[2], acc[nt * 4 + 2]);
-                            acc[nt * 4 + 3] = fmaf(dhi, d2[3], acc[nt * 4 + 3]);
+                            acc[a][nt * 4 + 0] = fmaf(dlo, d2[0], acc[a][nt * 4 + 0]);
+                            acc[a][nt * 4 + 1] = fmaf(dlo, d2[1], acc[a][nt * 4 + 1]);
+                            acc[a][nt * 4 + 2] = fmaf(dhi, d2[2], acc[a][nt * 4 + 2]);
+                            acc[a][nt * 4 + 3] = fmaf(dhi, d2[3], acc[a][nt * 4 + 3]);
                         }
                     }
                 };
@@ -319,73 +324,83 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
             }
+        }
 
-            // (d) cross-warp reduction and epilogue
-            if (p.pdl_mode == 2 && unit + (int)gridDim.x >= p.total_units && sub == p.subs - 1) pdl_launch_dependents();
-            float *rbuf = red + (size_t)(slab_count & 1) * (kConsumerWarps * kRows * MP);
-            float *mine = rbuf + warp * (kRows * MP);
+        // (d) cross-warp reduction and epilogue of the batch
+        if (p.pdl_mode == 2 && u0 + ub >= u_hi) pdl_launch_dependents();
+        float *rbuf = red + (size_t)(batch_count & 1) * (AS * kConsumerWarps * kRows * MP);
+#pragma unroll
+        for (int a = 0; a < AS; a++) {
+            if (a >= nsets) break;
+            float *mine = rbuf + (a * kConsumerWarps + warp) * (kRows * MP);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                *reinterpret_cast<float2 *>(&mine[g * MP + nt * 8 + 2 * t]) = make_float2(acc[nt * 4 + 0], acc[nt * 4 + 1]);
+                *reinterpret_cast<float2 *>(&mine[g * MP + nt * 8 + 2 * t]) = make_float2(acc[a][nt * 4 + 0], acc[a][nt * 4 + 1]);
                 *reinterpret_cast<float2 *>(&mine[(g + 8) * MP + nt * 8 + 2 * t]) =
-                    make_float2(acc[nt * 4 + 2], acc[nt * 4 + 3]);
+                    make_float2(acc[a][nt * 4 + 2], acc[a][nt * 4 + 3]);
             }
-            consumer_bar();
-            if (ctid < kRows * MP) {
-                const int col = ctid >> 4, row = ctid & 15;
-                const int n = sl * kRows + row;
-                const int wn = ti == 0 ? p.t[0].n : ti == 1 ? p.t[1].n : p.t[2].n;
-                auto total = [&](int r_) {
-                    float v = 0.f;
+        }
+        consumer_bar();
+        // Outputs of the batch: (unit, row, activation row) items over the consumer threads.
+        const int per_unit = kRows * p.m;
+        for (int item = ctid; item < (nsets / p.subs) * per_unit; item += kConsumerThreads) {
+            const int ui = item / per_unit, rc = item % per_unit;
+            const int col = rc >> 4, row = rc & 15;
+            const int a0 = ui * p.subs;
+            int ti = 0, sl = u0 + ui;
+            if (p.subs == 1) {
+                if (sl >= p.slabs[0]) { sl -= p.slabs[0]; ti = 1; }
+                if (ti == 1 && sl >= p.slabs[1]) { sl -= p.slabs[1]; ti = 2; }
+            }
+            const int n = sl * kRows + row;
+            const int wn = ti == 0 ? p.t[0].n : ti == 1 ? p.t[1].n : p.t[2].n;
+            if (n >= wn) continue;
+            auto total = [&](int set, int r_) {
+                const float *base = rbuf + (size_t)set * kConsumerWarps * (kRows * MP) + r_ * MP + col;
+                float v = 0.f;
 #pragma unroll
-                    for (int w = 0; w < kConsumerWarps; w++) v += rbuf[w * (kRows * MP) + r_ * MP + col];
-                    return v * 16777216.0f;  // undo the 2^-24 of the integer fragments
-                };
-                if (col < p.m && n < wn) {
-                    __half *yout = ti == 0 ? p.t[0].y : ti == 1 ? p.t[1].y : p.t[2].y;
-                    const long long rstride = ti == 0 ? p.t[0].row_stride : ti == 1 ? p.t[1].row_stride : p.t[2].row_stride;
-                    const long long pstride = ti == 0 ? p.t[0].pos_stride : ti == 1 ? p.t[1].pos_stride : p.t[2].pos_stride;
-                    const int rheads = ti == 0 ? p.t[0].rope_heads : ti == 1 ? p.t[1].rope_heads : p.t[2].rope_heads;
-                    const int hdim = ti == 0 ? p.t[0].head_dim : ti == 1 ? p.t[1].head_dim : p.t[2].head_dim;
-                    __half h = __float2half_rn(total(row));
-                    const size_t oidx = (size_t)col * wn + n;  // dense [m, N] index (residual, act)
-                    const int pos = p.positions ? p.positions[col] : p.pos_offset + col;
-                    // Where this output goes: dense rows by default; a KV-cache destination
-                    // addresses rows by (sequence, position) instead.
-                    const size_t yidx = (size_t)((long long)col * rstride + (long long)pos * pstride) + n;
-                    if (rheads > 0) {
-                        // Interleaved RoPE on the f16-rounded projection
-                        // (rope_f16, shaders/unified.metal:2355-2417).
-                        const __half hp = __float2half_rn(total(row ^ 1));
-                        const int dim = n % hdim;
-                        const int pair = dim >> 1;
-                        const float x0 = __half2float((dim & 1) ? hp : h);
-                        const float x1 = __half2float((dim & 1) ? h : hp);
-                        const float exponent = (float)(2 * pair) / (float)hdim;
-                        const float freq = 1.0f / powf(p.rope_base, exponent);
-                        const float theta = (float)(unsigned)pos * freq;
-                        const float cs = cosf(theta), sn = sinf(theta);
-                        const float r = (dim & 1) ? __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs))
-                                                  : __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
-                        yout[yidx] = __float2half_rn(r);
-                    } else if (p.epilogue == TLC_EPI_RESIDUAL) {
-                        yout[yidx] = __hadd(h, p.residual[oidx]);
-                    } else if (p.epilogue == TLC_EPI_SWIGLU) {
-                        if (sub == 0) {
-                            hold = h;
-                        } else {
-                            // s = sigmoid(g) (f32, RNE); a = g*s; act = a*u: three
-                            // f16 roundings as in debug/chat_demo_with_kvcache.tl:26-41.
-                            const float gf = __half2float(hold);
-                            const __half sg = __float2half_rn(1.0f / (1.0f + expf(-gf)));
-                            const __half a = __hmul(hold, sg);
-                            p.t[0].y[oidx] = __hmul(a, h);
-                        }
-                    } else {
-                        if (p.bias) h = __hadd(h, p.bias[n]);
-                        yout[yidx] = h;
-                    }
-                }
+                for (int w = 0; w < kConsumerWarps; w++) v += base[w * (kRows * MP)];
+                return v * 16777216.0f;  // undo the 2^-24 of the integer fragments
+            };
+            __half *yout = ti == 0 ? p.t[0].y : ti == 1 ? p.t[1].y : p.t[2].y;
+            const long long rstride = ti == 0 ? p.t[0].row_stride : ti == 1 ? p.t[1].row_stride : p.t[2].row_stride;
+            const long long pstride = ti == 0 ? p.t[0].pos_stride : ti == 1 ? p.t[1].pos_stride : p.t[2].pos_stride;
+            const int rheads = ti == 0 ? p.t[0].rope_heads : ti == 1 ? p.t[1].rope_heads : p.t[2].rope_heads;
+            const int hdim = ti == 0 ? p.t[0].head_dim : ti == 1 ? p.t[1].head_dim : p.t[2].head_dim;
+            __half h = __float2half_rn(total(a0, row));
+            const size_t oidx = (size_t)col * wn + n;  // dense [m, N] index (residual, act)
+            const int pos = p.positions ? p.positions[col] : p.pos_offset + col;
+            // Where this output goes: dense rows by default; a KV-cache destination
+            // addresses rows by (sequence, position) instead.
+            const size_t yidx = (size_t)((long long)col * rstride + (long long)pos * pstride) + n;
+            if (rheads > 0) {
+                // Interleaved RoPE on the f16-rounded projection
+                // (rope_f16, shaders/unified.metal:2355-2417).
+                const __half hp = __float2half_rn(total(a0, row ^ 1));
+                const int dim = n % hdim;
+                const int pair = dim >> 1;
+                const float x0 = __half2float((dim & 1) ? hp : h);
+                const float x1 = __half2float((dim & 1) ? h : hp);
+                const float exponent = (float)(2 * pair) / (float)hdim;
+                const float freq = 1.0f / powf(p.rope_base, exponent);
+                const float theta = (float)(unsigned)pos * freq;
+                const float cs = cosf(theta), sn = sinf(theta);
+                const float r = (dim & 1) ? __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs))
+                                          : __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+                yout[yidx] = __float2half_rn(r);
+            } else if (p.epilogue == TLC_EPI_RESIDUAL) {
+                yout[yidx] = __hadd(h, p.residual[oidx]);
+            } else if (p.epilogue == TLC_EPI_SWIGLU) {
+                // h = gate; s = sigmoid(g) (f32, RNE); a = g*s; act = a*u: three
+                // f16 roundings as in debug/chat_demo_with_kvcache.tl:26-41.
+                const __half up = __float2half_rn(total(a0 + 1, row));
+                const float gf = __half2float(h);
+                const __half sg = __float2half_rn(1.0f / (1.0f + expf(-gf)));
+                const __half av = __hmul(h, sg);
+                p.t[0].y[oidx] = __hmul(av, up);
+            } else {
+                if (p.bias) h = __hadd(h, p.bias[n]);
+                yout[yidx] = h;
             }
         }
     }
