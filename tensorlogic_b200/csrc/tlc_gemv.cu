@@ -160,6 +160,7 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     if (stages > per_cta) stages = per_cta < 2 ? 2 : (int)per_cta;
     p.nstages = stages;
     p.pdl_mode = ctx->pdl_mode;
+    p.contig = units_per_cta <= 4 ? 1 : 0;
     const size_t smem = smem_fixed + (size_t)stages * STAGE_BYTES;
     if (as == 1) return launch_mma_as<QT, NT, 1>(ctx, p, grid, smem);
     if (as == 2) return launch_mma_as<QT, NT, 2>(ctx, p, grid, smem);

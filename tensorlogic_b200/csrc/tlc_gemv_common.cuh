@@ -70,6 +70,7 @@ struct GemvParams {
     float rope_base;
     const int *positions;
     int nstages;
+    int contig;    // 1: each CTA takes a contiguous range of units, 0: units blockIdx.x, + gridDim.x, ...
     int pdl_mode;  // 1: let the next kernel be scheduled at once, 2: only when this CTA's last slab is done
     tlc_dev_status *status;
 };

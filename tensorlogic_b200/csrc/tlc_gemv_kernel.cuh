@@ -69,7 +69,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
         uint32_t it = 0;
         const int pu_lo = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
         const int pu_hi = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
-        for (int unit = pu_lo; unit < pu_hi; unit++) {
+        const int pcount = p.contig ? pu_hi - pu_lo
+                                    : ((int)p.total_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+        for (int ui = 0; ui < pcount; ui++) {
+            const int unit = p.contig ? pu_lo + ui : (int)blockIdx.x + ui * (int)gridDim.x;
             for (int sub = 0; sub < p.subs; sub++) {
                 int ti = 0, sl = unit;
                 if (p.subs == 2) {
@@ -231,18 +234,22 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
     const uint32_t stages_addr = smem_u32(stages);
     const uint32_t seg_lo = g * PITCH, seg_hi = (g + 8) * PITCH;
 
-    // Units of this CTA: a balanced contiguous range.  They are processed in
-    // batches of AS accumulator sets (one set = one 16-row slab; a gate/up unit
-    // takes two), with ONE cross-warp reduction per batch: for short K a slab
-    // is only a few block pairs per warp, and a barrier per slab would dominate.
+    // Units of this CTA: with only a few per CTA a balanced contiguous range
+    // (1.5 % faster on the TinyLlama decode step), otherwise blockIdx.x,
+    // blockIdx.x + gridDim.x, ... so that neighbouring CTAs stream neighbouring
+    // rows (9 % faster on a 132 MB weight).  They are processed in batches of AS
+    // accumulator sets (one set = one 16-row slab; a gate/up unit takes two) with
+    // ONE cross-warp reduction per batch.
     const int u_lo = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
     const int u_hi = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
+    const int n_mine = p.contig ? u_hi - u_lo
+                                : ((int)p.total_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int ub = AS / p.subs;  // units per batch
     uint32_t it = 0;
     int batch_count = 0;
 
-    for (int u0 = u_lo; u0 < u_hi; u0 += ub, batch_count++) {
-        const int nsets = min(ub, u_hi - u0) * p.subs;
+    for (int i0 = 0; i0 < n_mine; i0 += ub, batch_count++) {
+        const int nsets = min(ub, n_mine - i0) * p.subs;
         float acc[AS][4 * NT];
 #pragma unroll
         for (int a = 0; a < AS; a++)
@@ -327,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
         }
 
         // (d) cross-warp reduction and epilogue of the batch
-        if (p.pdl_mode == 2 && u0 + ub >= u_hi) pdl_launch_dependents();
+        if (p.pdl_mode == 2 && i0 + ub >= n_mine) pdl_launch_dependents();
         float *rbuf = red + (size_t)(batch_count & 1) * (AS * kConsumerWarps * kRows * MP);
 #pragma unroll
         for (int a = 0; a < AS; a++) {
@@ -347,7 +354,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
             const int ui = item / per_unit, rc = item % per_unit;
             const int col = rc >> 4, row = rc & 15;
             const int a0 = ui * p.subs;
-            int ti = 0, sl = u0 + ui;
+            int ti = 0, sl = p.contig ? u_lo + i0 + ui : (int)blockIdx.x + (i0 + ui) * (int)gridDim.x;
             if (p.subs == 1) {
                 if (sl >= p.slabs[0]) { sl -= p.slabs[0]; ti = 1; }
                 if (ti == 1 && sl >= p.slabs[1]) { sl -= p.slabs[1]; ti = 2; }
