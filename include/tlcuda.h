@@ -55,8 +55,11 @@ enum {
     TLC_ERR_COMM = -11              /* collective / communicator failure   */
 };
 
-/* GGUF tensor type ids (src/model/formats/mmap_gguf.rs:30-45). */
-enum { TLC_TYPE_F32 = 0, TLC_TYPE_F16 = 1, TLC_TYPE_Q4_0 = 2, TLC_TYPE_Q8_0 = 8 };
+/* GGUF tensor type ids (src/model/formats/mmap_gguf.rs:30-45).  Q4_0 and Q8_0
+ * stay quantized in device memory; Q6_K (210-byte super-blocks of 256 values) and
+ * F32 are accepted on upload and become F16 tensors, which is what the reference's
+ * loader makes of every type (src/model/formats/gguf.rs:128-253, :413-440). */
+enum { TLC_TYPE_F32 = 0, TLC_TYPE_F16 = 1, TLC_TYPE_Q4_0 = 2, TLC_TYPE_Q8_0 = 8, TLC_TYPE_Q6_K = 14 };
 
 /* How a weight is split across tensor-parallel ranks. */
 enum {

@@ -169,6 +169,53 @@ TLREF_API size_t tlref_dequant_q8_0(const uint8_t *data, size_t nbytes, size_t n
     return produced;
 }
 
+/* Q6_K: follows GGUFLoader::dequantize_q6_k, src/model/formats/gguf.rs:128-218
+ * (the llama.cpp element order; NOT gguf_weight_cache.rs:340-415, which differs).
+ * 210-byte super-block of 256 values: ql[128] low nibbles, qh[64] two high bits,
+ * sc[16] int8 scales, d f16.  Per half of 128 values and l in 0..31:
+ *   q1 = (ql[l] & 15)    | ((qh[l] >> 0) & 3) << 4   -> y[l],      scale sc[l/16 + 0]
+ *   q2 = (ql[l+32] & 15) | ((qh[l] >> 2) & 3) << 4   -> y[l + 32], scale sc[l/16 + 2]
+ *   q3 = (ql[l] >> 4)    | ((qh[l] >> 4) & 3) << 4   -> y[l + 64], scale sc[l/16 + 4]
+ *   q4 = (ql[l+32] >> 4) | ((qh[l] >> 6) & 3) << 4   -> y[l + 96], scale sc[l/16 + 6]
+ * value = f16_rne((d * sc) * (q - 32)) in f32 (both products are exact: 11 + 7 + 6 bits). */
+TLREF_API size_t tlref_dequant_q6_k(const uint8_t *data, size_t nbytes, size_t n_elem,
+                                    uint16_t *out) {
+    const size_t QK = 256, BB = 210;
+    size_t nblocks = (n_elem + QK - 1) / QK;
+    for (size_t i = 0; i < n_elem; i++) out[i] = 0;
+    size_t produced = 0;
+    for (size_t b = 0; b < nblocks; b++) {
+        size_t off = b * BB;
+        if (off + BB > nbytes) break;
+        const uint8_t *ql = data + off, *qh = data + off + 128;
+        const int8_t *sc = (const int8_t *)(data + off + 192);
+        float d = h2f((uint16_t)(data[off + 208] | ((uint16_t)data[off + 209] << 8)));
+        for (size_t n = 0; n < QK; n += 128) {
+            for (size_t l = 0; l < 32; l++) {
+                size_t base = b * QK + n + l;
+                size_t is = l / 16;
+                int q[4];
+                q[0] = (int)((ql[l] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32;
+                q[1] = (int)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+                q[2] = (int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+                q[3] = (int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+                for (int j = 0; j < 4; j++) {
+                    size_t idx = base + 32 * (size_t)j;
+                    if (idx < n_elem) {
+                        float v = d * (float)sc[is + 2 * (size_t)j];
+                        out[idx] = f2h(v * (float)q[j]);
+                        if (idx + 1 > produced) produced = idx + 1;
+                    }
+                }
+            }
+            ql += 64;
+            qh += 32;
+            sc += 8;
+        }
+    }
+    return produced;
+}
+
 /* ------------------------------------------------------------------------- */
 /* Matmul / linear.                                                           */
 /* ------------------------------------------------------------------------- */
@@ -270,12 +317,13 @@ TLREF_API void tlref_linear_f32acc(const uint16_t *x, const uint16_t *w, uint16_
 /* Same parity target, taking the weight as native GGUF blocks: each row is
  * dequantized with the bit-exact dequantizer above (so the f16 weight values
  * are exactly the reference loader's) and contracted with f32 accumulation.
- * qtype: 2 = Q4_0, 8 = Q8_0 (GGUF type ids, mmap_gguf.rs:30-45), 1 = F16. */
+ * qtype: 2 = Q4_0, 8 = Q8_0, 14 = Q6_K (GGUF type ids, mmap_gguf.rs:30-45), 1 = F16. */
 TLREF_API int tlref_linear_q_f32acc(int qtype, const uint8_t *wq, const uint16_t *x,
                                     uint16_t *y, int m, int k, int n, int threads) {
     if (k % 32 != 0 && qtype != 1) return -1;
     size_t row_bytes = qtype == 2 ? (size_t)(k / 32) * 18
                      : qtype == 8 ? (size_t)(k / 32) * 34
+                     : qtype == 14 ? (k % 256 == 0 ? (size_t)(k / 256) * 210 : 0)
                      : qtype == 1 ? (size_t)k * 2 : 0;
     if (!row_bytes) return -2;
     float *xf = (float *)malloc((size_t)m * k * sizeof(float));
@@ -294,6 +342,7 @@ TLREF_API int tlref_linear_q_f32acc(int qtype, const uint8_t *wq, const uint16_t
             const uint8_t *row = wq + (size_t)j * row_bytes;
             if (qtype == 2) tlref_dequant_q4_0(row, row_bytes, (size_t)k, wh);
             else if (qtype == 8) tlref_dequant_q8_0(row, row_bytes, (size_t)k, wh);
+            else if (qtype == 14) tlref_dequant_q6_k(row, row_bytes, (size_t)k, wh);
             else memcpy(wh, row, row_bytes);
             for (int p = 0; p < k; p++) wf[p] = h2f(wh[p]);
             for (int i = 0; i < m; i++) {

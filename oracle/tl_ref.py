@@ -17,7 +17,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libtlref.so")
 
-GGML_F16, GGML_Q4_0, GGML_Q8_0 = 1, 2, 8
+GGML_F16, GGML_Q4_0, GGML_Q8_0, GGML_Q6_K = 1, 2, 8, 14
 
 
 def build(force: bool = False) -> str:
@@ -39,6 +39,7 @@ def _load() -> C.CDLL:
         "tlref_f32_to_f16_n": (None, [f32p, u16p, sz]),
         "tlref_dequant_q4_0": (None, [u8p, sz, sz, u16p]),
         "tlref_dequant_q8_0": (sz, [u8p, sz, sz, u16p]),
+        "tlref_dequant_q6_k": (sz, [u8p, sz, sz, u16p]),
         "tlref_matmul_f16acc": (None, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int]),
         "tlref_linear_literal": (None, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, u16p]),
         "tlref_linear_f32acc": (None, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]),
@@ -111,6 +112,8 @@ def dequant(qtype: int, data: np.ndarray, n_elem: int) -> np.ndarray:
         lib().tlref_dequant_q4_0(_b(data), data.size, n_elem, _h(out))
     elif qtype == GGML_Q8_0:
         lib().tlref_dequant_q8_0(_b(data), data.size, n_elem, _h(out))
+    elif qtype == GGML_Q6_K:
+        lib().tlref_dequant_q6_k(_b(data), data.size, n_elem, _h(out))
     elif qtype == GGML_F16:
         out[:] = data.view(np.float16)[:n_elem]
     else:

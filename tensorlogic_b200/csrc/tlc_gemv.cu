@@ -8,13 +8,13 @@
 // them in the TL scripts (debug/chat_demo_with_kvcache.tl:219-290).
 //
 // Design (memory-bound; the weight bytes are read from HBM exactly once):
-//   * persistent CTAs, one per SM, each walking 16-row slabs of the weight(s);
+//   * persistent CTAs, up to two per SM, each walking 16-row slabs of the weight(s);
 //   * a producer warp streams the raw block bytes of a slab into a shared
 //     memory ring with 16-byte-granular bulk async copies (one per row per
 //     stage) that complete on mbarriers -- no thread ever issues a narrow
 //     global load for weight data, and the ring keeps tens of KB per SM in
 //     flight independent of occupancy;
-//   * four consumer warps unpack nibbles / bytes in registers straight into
+//   * eight consumer warps unpack nibbles / bytes in registers straight into
 //     f16 tensor-core fragments: a 4-bit (8-bit) integer n placed in the low
 //     mantissa bits of a binary16 is the subnormal n * 2^-24, so one AND per
 //     pair of weights yields an exact A fragment; the -8 (-128) offset is
@@ -22,8 +22,8 @@
 //     activations of the block) and the block scale d multiplies the 16x8 block
 //     result in f32;  mma.sync m16n8k16 with f32 accumulation does the dot
 //     products for up to 8 activation rows at no extra cost;
-//   * the K range of a slab is split over the four warps, reduced through
-//     shared memory, and the epilogue (f16 rounding, bias / residual add,
+//   * the K range of a slab is split over the eight warps, reduced through
+//     shared memory (up to four slabs per reduction), and the epilogue (f16 rounding, bias / residual add,
 //     SiLU(gate)*up, interleaved RoPE) is applied before the single store.
 // The activation vector(s) are optionally RMS-normalised on the way into
 // shared memory, where they are kept pre-permuted in fragment order.
@@ -88,6 +88,63 @@ __global__ void linear_generic_kernel(const uint8_t *__restrict__ w, size_t pitc
             __half h = __float2half_rn(acc);
             if (bias) h = __hadd(h, bias[warp]);
             y[(size_t)mm * n_rows + warp] = h;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Dense f16 weights (F16 / F32 files, Q6_K after its load-time dequantization,
+// tied embeddings): one warp per output row, 16-byte loads of the row and of up
+// to 8 activation rows, f32 accumulation, optional bias / residual.  HBM-bound
+// on the 2 bytes per weight; K must be a multiple of 8 and rows 16-byte aligned.
+// ---------------------------------------------------------------------------
+template <int MR>
+__global__ void __launch_bounds__(256) linear_f16_kernel(const uint8_t *__restrict__ w, size_t pitch, int n_rows,
+                                                         int k, const __half *__restrict__ x, int m,
+                                                         __half *__restrict__ y, const __half *__restrict__ bias,
+                                                         const __half *__restrict__ residual) {
+    tlc_pdl_prologue();
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    const uint4 *wr = reinterpret_cast<const uint4 *>(w + (size_t)row * pitch);
+    const int steps = k >> 3;  // 16-byte pieces per row
+    float acc[MR];
+#pragma unroll
+    for (int i = 0; i < MR; i++) acc[i] = 0.f;
+#pragma unroll 4
+    for (int s = lane; s < steps; s += 32) {
+        const uint4 wv = __ldg(wr + s);
+        const __half2 *wh = reinterpret_cast<const __half2 *>(&wv);
+        float2 wf[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) wf[j] = __half22float2(wh[j]);
+#pragma unroll
+        for (int i = 0; i < MR; i++) {
+            if (i < m) {
+                const uint4 xv = *(reinterpret_cast<const uint4 *>(x + (size_t)i * k) + s);
+                const __half2 *xh = reinterpret_cast<const __half2 *>(&xv);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 xf = __half22float2(xh[j]);
+                    acc[i] = fmaf(wf[j].x, xf.x, acc[i]);
+                    acc[i] = fmaf(wf[j].y, xf.y, acc[i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MR; i++) {
+        if (i < m) {
+            float v = acc[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) {
+                __half h = __float2half_rn(v);
+                if (bias) h = __hadd(h, bias[row]);
+                if (residual) h = __hadd(h, residual[(size_t)i * n_rows + row]);
+                y[(size_t)i * n_rows + row] = h;
+            }
         }
     }
 }
@@ -207,16 +264,43 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
                     "gate and up projections must have the same shape");
 
     if (type == TLC_TYPE_F16) {
-        TLC_REQUIRE(a.epilogue == TLC_EPI_STORE && !a.norm_w && a.n_out == 1 && a.outs[0].rope_heads == 0,
-                    TLC_ERR_INVALID_OPERATION, "fused epilogues need a quantized weight");
+        // Dense weights: RMSNorm (if asked for) runs as its own kernel, bias and
+        // residual are applied in the store; RoPE, SiLU.mul and cache addressing
+        // exist on the quantized path only.
+        TLC_REQUIRE(a.epilogue != TLC_EPI_SWIGLU && a.n_out == 1 && a.outs[0].rope_heads == 0 &&
+                        a.outs[0].row_stride < 0 && a.outs[0].pos_stride == 0,
+                    TLC_ERR_INVALID_OPERATION, "fused RoPE / SiLU.mul / cache epilogues need a quantized weight");
+        const __half *x = static_cast<const __half *>(a.x);
+        if (a.norm_w) {
+            if (int32_t rc = tlc_scratch_reserve(ctx, (size_t)a.m * k * 2)) return rc;
+            if (int32_t rc = tlc_rms_norm(ctx, a.x, a.norm_w, ctx->scratch, a.m, (int32_t)k, a.eps)) return rc;
+            x = static_cast<const __half *>(ctx->scratch);
+        }
         const int threads = 256;
-        const int64_t warps = w0->n_rows;
-        unsigned grid = (unsigned)((warps * 32 + threads - 1) / threads);
-        linear_generic_kernel<<<grid, threads, 0, ctx->stream>>>(
-            static_cast<const uint8_t *>(w0->data), w0->row_pitch, type, (int)w0->n_rows, (int)k,
-            static_cast<const __half *>(a.x), a.m, static_cast<__half *>(a.outs[0].y),
-            static_cast<const __half *>(a.bias));
-        TLC_CHECK_LAUNCH(ctx);
+        const unsigned grid = (unsigned)((w0->n_rows * 32 + threads - 1) / threads);
+        const __half *residual = a.epilogue == TLC_EPI_RESIDUAL ? static_cast<const __half *>(a.residual) : nullptr;
+        const bool vec = k % 8 == 0 && w0->row_pitch % 16 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w0->data % 16) == 0;
+        if (!vec) {
+            TLC_REQUIRE(!residual, TLC_ERR_INVALID_OPERATION, "residual epilogue needs 16-byte aligned f16 rows");
+            linear_generic_kernel<<<grid, threads, 0, ctx->stream>>>(
+                static_cast<const uint8_t *>(w0->data), w0->row_pitch, type, (int)w0->n_rows, (int)k, x, a.m,
+                static_cast<__half *>(a.outs[0].y), static_cast<const __half *>(a.bias));
+            TLC_CHECK_LAUNCH(ctx);
+            return TLC_OK;
+        }
+        for (int m0 = 0; m0 < a.m; m0 += 8) {
+            const int mc = a.m - m0 < 8 ? a.m - m0 : 8;
+            cudaError_t le = tlc_launch_pdl(
+                ctx, mc <= 2 ? linear_f16_kernel<2> : linear_f16_kernel<8>, dim3(grid), dim3(threads), 0,
+                static_cast<const uint8_t *>(w0->data), w0->row_pitch, (int)w0->n_rows, (int)k, x + (size_t)m0 * k, mc,
+                static_cast<__half *>(a.outs[0].y) + (size_t)m0 * w0->n_rows, static_cast<const __half *>(a.bias),
+                residual ? residual + (size_t)m0 * w0->n_rows : nullptr);
+            if (le != cudaSuccess) {
+                cudaGetLastError();
+                return tlc_fail(TLC_ERR_CUDA, "f16 linear launch failed: %s", cudaGetErrorString(le));
+            }
+            TLC_CHECK_LAUNCH(ctx);
+        }
         return TLC_OK;
     }
 

@@ -289,6 +289,10 @@ static int32_t parse_gguf(const char *path, tlc_gguf *g) {
             TLC_REQUIRE(t.cols % 32 == 0, TLC_ERR_LOAD, "tensor '%s': %lld columns are not a multiple of 32",
                         t.name.c_str(), (long long)t.cols);
             t.nbytes = (uint64_t)t.rows * (t.cols / 32) * tlc_block_bytes(t.type);
+        } else if (t.type == TLC_TYPE_Q6_K) {
+            TLC_REQUIRE(t.cols % 256 == 0, TLC_ERR_LOAD, "tensor '%s': %lld columns are not a multiple of 256",
+                        t.name.c_str(), (long long)t.cols);
+            t.nbytes = (uint64_t)t.rows * (t.cols / 256) * 210;
         } else {
             t.nbytes = 0;  // unsupported type: listed, but cannot be uploaded
         }
@@ -370,8 +374,9 @@ extern "C" int32_t tlc_model_load_gguf(tlc_ctx *ctx, const char *path, int32_t t
     TLC_REQUIRE(f.good(), TLC_ERR_LOAD, "Failed to open GGUF file '%s': %s", path, strerror(errno));
     std::vector<char> host;
     for (const auto &t : g.tensors) {
-        TLC_REQUIRE(t.type == TLC_TYPE_F32 || t.type == TLC_TYPE_F16 || t.type == TLC_TYPE_Q4_0 || t.type == TLC_TYPE_Q8_0,
-                    TLC_ERR_LOAD, "tensor '%s' has unsupported GGUF type %d (supported: F32, F16, Q4_0, Q8_0)",
+        TLC_REQUIRE(t.type == TLC_TYPE_F32 || t.type == TLC_TYPE_F16 || t.type == TLC_TYPE_Q4_0 ||
+                        t.type == TLC_TYPE_Q8_0 || t.type == TLC_TYPE_Q6_K,
+                    TLC_ERR_LOAD, "tensor '%s' has unsupported GGUF type %d (supported: F32, F16, Q4_0, Q8_0, Q6_K)",
                     t.name.c_str(), t.type);
         host.resize(t.nbytes);
         f.seekg((std::streamoff)t.offset);
@@ -381,6 +386,17 @@ extern "C" int32_t tlc_model_load_gguf(tlc_ctx *ctx, const char *path, int32_t t
         tlc_qtensor *qt = nullptr;
         if (int32_t rc = tlc_qtensor_create(ctx, t.type, t.rows, t.cols, host.data(), t.nbytes, tp_rank, tp_size, split, &qt))
             return rc;
+        // The embedding gather reads f16 rows: a quantized table is dequantized once, here
+        // (the reference dequantizes every tensor at load time).
+        if (t.name == "token_embd.weight" && (qt->type == TLC_TYPE_Q4_0 || qt->type == TLC_TYPE_Q8_0)) {
+            tlc_qtensor *dense = nullptr;
+            if (int32_t rc = tlc_qtensor_to_f16(ctx, qt, &dense)) {
+                tlc_qtensor_destroy(qt);
+                return rc;
+            }
+            tlc_qtensor_destroy(qt);
+            qt = dense;
+        }
         tlc_model_add(model.get(), t.name.c_str(), qt);
     }
     *out = model.release();

@@ -106,6 +106,8 @@ static inline size_t tlc_block_bytes(int32_t type) {
     return type == TLC_TYPE_Q4_0 ? 18 : type == TLC_TYPE_Q8_0 ? 34 : 0;
 }
 
+// A dense F16 copy of a quantized tensor (device-side dequantization).
+int32_t tlc_qtensor_to_f16(tlc_ctx *ctx, tlc_qtensor *qt, tlc_qtensor **out);
 // Makes the context's device current; every entry point calls it first.
 int32_t tlc_enter(tlc_ctx *ctx);
 // Ensures ctx->scratch holds at least `bytes`.

@@ -51,6 +51,39 @@ __global__ void dequant_q8_0_kernel(const uint8_t *__restrict__ data, size_t row
     }
 }
 
+// Q6_K (GGUFLoader::dequantize_q6_k, gguf.rs:128-218, the llama.cpp order): one
+// thread per (row, super-block, half, l) produces the four values l, l+32, l+64,
+// l+96 of its half: q = 4 bits of ql | 2 bits of qh, value = f16_rne((d*sc)*(q-32)).
+// Writes columns [col0, col0 + out_cols) of the row into a dense-pitch f16 tensor.
+__global__ void dequant_q6_k_kernel(const uint8_t *__restrict__ data, int sb_per_row, int64_t n_rows,
+                                    int64_t col0, int64_t out_cols, __half *__restrict__ out, size_t out_pitch) {
+    const int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t total = n_rows * sb_per_row * 64;
+    if (gi >= total) return;
+    const int l = (int)(gi & 31), half = (int)((gi >> 5) & 1);
+    const int64_t sbi = gi >> 6;
+    const int64_t row = sbi / sb_per_row;
+    const int sb = (int)(sbi % sb_per_row);
+    const uint8_t *blk = data + (size_t)sbi * 210;
+    const uint8_t *ql = blk + 64 * half, *qh = blk + 128 + 32 * half;
+    const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * half);
+    const float d = __half2float(__ushort_as_half((unsigned short)(blk[208] | (blk[209] << 8))));
+    const int is = l >> 4;
+    const int h = qh[l];
+    int q[4];
+    q[0] = ((ql[l] & 0xF) | (((h >> 0) & 3) << 4)) - 32;
+    q[1] = ((ql[l + 32] & 0xF) | (((h >> 2) & 3) << 4)) - 32;
+    q[2] = ((ql[l] >> 4) | (((h >> 4) & 3) << 4)) - 32;
+    q[3] = ((ql[l + 32] >> 4) | (((h >> 6) & 3) << 4)) - 32;
+    __half *orow = reinterpret_cast<__half *>(reinterpret_cast<uint8_t *>(out) + (size_t)row * out_pitch);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int64_t col = (int64_t)sb * 256 + 128 * half + l + 32 * j - col0;
+        if (col >= 0 && col < out_cols)
+            orow[col] = __float2half_rn(__fmul_rn(__fmul_rn(d, (float)sc[is + 2 * j]), (float)q[j]));
+    }
+}
+
 __global__ void copy_rows_f16_kernel(const uint8_t *__restrict__ data, size_t row_pitch, int64_t n_cols,
                                      int64_t n_rows, __half *__restrict__ out) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -83,8 +116,9 @@ __global__ void synth_blocks_kernel(uint8_t *__restrict__ data, size_t row_pitch
 
 static int32_t shard_shape(int32_t type, int64_t n_rows, int64_t n_cols, int32_t tp_rank, int32_t tp_size,
                            int32_t split, int64_t *rows, int64_t *cols, int64_t *row0, int64_t *col0) {
-    TLC_REQUIRE(type == TLC_TYPE_F16 || type == TLC_TYPE_F32 || type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0,
-                TLC_ERR_LOAD, "unsupported GGUF tensor type %d (supported: F32, F16, Q4_0, Q8_0)", type);
+    TLC_REQUIRE(type == TLC_TYPE_F16 || type == TLC_TYPE_F32 || type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0 ||
+                    type == TLC_TYPE_Q6_K,
+                TLC_ERR_LOAD, "unsupported GGUF tensor type %d (supported: F32, F16, Q4_0, Q8_0, Q6_K)", type);
     TLC_REQUIRE(n_rows > 0 && n_cols > 0, TLC_ERR_INVALID_DIMENSION, "tensor shape [%lld, %lld] is empty",
                 (long long)n_rows, (long long)n_cols);
     bool quant = type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0;
@@ -162,9 +196,46 @@ extern "C" int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows
     if (int32_t rc = shard_shape(type, n_rows, n_cols, tp_rank, tp_size, split, &rows, &cols, &row0, &col0))
         return rc;
     size_t src_row_bytes = type == TLC_TYPE_F32 ? (size_t)n_cols * 4 : bytes_per_row(type, n_cols);
-    TLC_REQUIRE(bytes >= src_row_bytes * (size_t)n_rows, TLC_ERR_LOAD,
+    TLC_REQUIRE(type == TLC_TYPE_Q6_K || bytes >= src_row_bytes * (size_t)n_rows, TLC_ERR_LOAD,
                 "tensor data too short: %zu bytes for shape [%lld, %lld] (need %zu)", bytes, (long long)n_rows,
                 (long long)n_cols, src_row_bytes * (size_t)n_rows);
+    if (type == TLC_TYPE_Q6_K) {
+        // Dequantized on the device into an F16 tensor (what the reference's loader keeps in memory).
+        TLC_REQUIRE(n_cols % 256 == 0, TLC_ERR_LOAD, "Q6_K tensor needs columns in multiples of 256 (got %lld)",
+                    (long long)n_cols);
+        const int sb_per_row = (int)(n_cols / 256);
+        const size_t q_row_bytes = (size_t)sb_per_row * 210;
+        TLC_REQUIRE(bytes >= q_row_bytes * (size_t)n_rows, TLC_ERR_LOAD,
+                    "tensor data too short: %zu bytes for Q6_K shape [%lld, %lld] (need %zu)", bytes, (long long)n_rows,
+                    (long long)n_cols, q_row_bytes * (size_t)n_rows);
+        tlc_qtensor *qt = nullptr;
+        if (int32_t rc = alloc_qtensor(ctx, TLC_TYPE_F16, rows, cols, n_rows, n_cols, tp_rank, tp_size, split, &qt))
+            return rc;
+        void *tmp = nullptr;
+        cudaError_t e = cudaMalloc(&tmp, q_row_bytes * (size_t)rows);
+        if (e == cudaSuccess) e = cudaMemsetAsync(qt->data, 0, qt->bytes + 16, ctx->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(tmp, static_cast<const uint8_t *>(blocks) + (size_t)row0 * q_row_bytes,
+                                q_row_bytes * (size_t)rows, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) {
+            const int64_t total = rows * sb_per_row * 64;
+            dequant_q6_k_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
+                static_cast<const uint8_t *>(tmp), sb_per_row, rows, col0, cols, static_cast<__half *>(qt->data),
+                qt->row_pitch);
+            ctx->launches++;
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        cudaFree(tmp);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(qt->data);
+            delete qt;
+            return tlc_fail(TLC_ERR_CUDA, "Q6_K upload failed: %s", cudaGetErrorString(e));
+        }
+        *out = qt;
+        return TLC_OK;
+    }
     tlc_qtensor *qt = nullptr;
     if (int32_t rc = alloc_qtensor(ctx, type, rows, cols, n_rows, n_cols, tp_rank, tp_size, split, &qt)) return rc;
 
@@ -319,6 +390,26 @@ extern "C" int32_t tlc_qtensor_info(tlc_qtensor *qt, int32_t *type, int64_t *n_r
     if (n_cols) *n_cols = qt->n_cols;
     if (row_pitch) *row_pitch = qt->row_pitch;
     if (dev_ptr) *dev_ptr = qt->data;
+    return TLC_OK;
+}
+
+// A dense F16 copy of a quantized tensor (same shape and shard).
+int32_t tlc_qtensor_to_f16(tlc_ctx *ctx, tlc_qtensor *qt, tlc_qtensor **out) {
+    TLC_REQUIRE(qt && out, TLC_ERR_INVALID_OPERATION, "qtensor_to_f16: null pointer");
+    TLC_REQUIRE(qt->n_cols % 8 == 0, TLC_ERR_INVALID_DIMENSION, "qtensor_to_f16: %lld columns are not a multiple of 8",
+                (long long)qt->n_cols);
+    tlc_qtensor *dense = nullptr;
+    if (int32_t rc = alloc_qtensor(ctx, TLC_TYPE_F16, qt->n_rows, qt->n_cols, qt->full_rows, qt->full_cols,
+                                   qt->tp_rank, qt->tp_size, qt->split, &dense))
+        return rc;
+    int32_t rc = tlc_dequant(ctx, qt, dense->data);  // pitch == 2 * cols: the dense layout tlc_dequant writes
+    if (!rc) rc = tlc_synchronize(ctx);
+    if (rc) {
+        cudaFree(dense->data);
+        delete dense;
+        return rc;
+    }
+    *out = dense;
     return TLC_OK;
 }
 

@@ -93,6 +93,26 @@ def main() -> None:
     np.savez_compressed(path, **out)
     print(path, {k_: v_.shape for k_, v_ in out.items()})
 
+    # --- Q6_K super-blocks (own file and generator, so the vectors above keep their bytes):
+    # the gguf package's dequantizer = the llama.cpp element order the Rust loader follows ---
+    rng6 = np.random.default_rng(20250614)
+    nsb = 12
+    q6 = rng6.integers(0, 256, (nsb, 210), dtype=np.uint8)
+    d6 = rng6.uniform(1e-4, 2e-3, nsb).astype(np.float16)
+    d6[:3] = np.array([0.0, -7.5e-4, 6.1e-5], np.float16)  # zero, negative, subnormal super-block scales
+    q6[:, 208:210] = d6.view(np.uint8).reshape(-1, 2)
+    q6[3, 192:208] = np.int8(-128).view(np.uint8)          # extreme sub-block scales
+    q6[4, 192:208] = 127
+    q6[5, :192] = 0x00                                     # all quants -32
+    q6[6, :192] = 0xFF                                     # all quants +31
+    out6 = {"q6_k_bytes": q6}
+    out6["q6_k_gguf_f32"] = quants.dequantize(q6.reshape(-1), gguf.GGMLQuantizationType.Q6_K).astype(np.float32)
+    # (scripts/reference_with_gguf.py also has a dequantize_q6_k, with another element order; the
+    # script itself leaves it unused and the Rust loader follows llama.cpp, as the gguf package does.)
+    path6 = os.path.join(HERE, "q6_k.npz")
+    np.savez_compressed(path6, **out6)
+    print(path6, {k_: v_.shape for k_, v_ in out6.items()})
+
 
 if __name__ == "__main__":
     main()

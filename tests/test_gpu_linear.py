@@ -262,8 +262,8 @@ def test_error_behaviour(dev):
     with pytest.raises(TensorError) as e:       # truncated tensor data
         QTensor.from_blocks(dev, Q4, 16, 64, raw.reshape(-1)[:100])
     assert e.value.kind == "LoadError"
-    with pytest.raises(TensorError):            # unsupported type id (Q6_K = 14)
-        QTensor.from_blocks(dev, 14, 16, 256, np.zeros(16 * 210, np.uint8))
+    with pytest.raises(TensorError):            # unsupported type id (Q4_K = 12)
+        QTensor.from_blocks(dev, 12, 16, 256, np.zeros(16 * 144, np.uint8))
     with pytest.raises(TensorError) as e:       # rows do not divide over ranks
         QTensor.from_blocks(dev, Q4, 16, 64, raw, 0, 3, 1)
     assert e.value.kind == "ShapeMismatch"

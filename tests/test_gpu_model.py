@@ -23,7 +23,7 @@ def _ref_model(ref, weights, arch):
         if gtype == 1:
             w[name] = arr.reshape(-1) if name.endswith("norm.weight") else arr
         else:
-            w[name] = (gtype, arr, (arr.shape[0], arr.shape[1] * 32))
+            w[name] = (gtype, arr, (arr.shape[0], arr.shape[1] * (256 if gtype == 14 else 32)))
     return ref.RefLlama(w, arch.n_layers, arch.n_heads, arch.n_kv_heads, arch.head_dim, arch.rms_eps, arch.rope_base)
 
 

@@ -249,3 +249,37 @@ def test_literal_matmul_hardware_and_software_conversions_agree(ref):
     sw = ref.linear_literal(x, w)
     ref.set_f16c(True)
     assert np.array_equal(hw.view(np.uint16), sw.view(np.uint16))
+
+
+def test_q6_k_against_gguf_package(ref):
+    """Q6_K super-blocks: bit-exact with the gguf package's dequantizer (llama.cpp element order,
+    the order GGUFLoader::dequantize_q6_k follows), including zero / negative / subnormal
+    super-block scales, extreme sub-block scales and all-min / all-max quants."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "q6_k.npz"))
+    raw, want = g["q6_k_bytes"], g["q6_k_gguf_f32"]
+    got = ref.dequant(14, raw, raw.shape[0] * 256)
+    with np.errstate(over="ignore"):
+        assert np.array_equal(got.view(np.uint16), want.astype(np.float16).view(np.uint16))
+    # hand-made block: d = 0.5, every sub-block scale 2, ql = 0x21, qh = 0b11100100:
+    #   q1 = 1 | 0<<4 = 1, q2 = 1 | 1<<4 = 17, q3 = 2 | 2<<4 = 34, q4 = 2 | 3<<4 = 50  (minus 32)
+    b = np.zeros(210, np.uint8)
+    b[:128] = 0x21
+    b[128:192] = 0b11100100
+    b[192:208] = 2
+    b[208:210] = np.array([0.5], np.float16).view(np.uint8)
+    out = ref.dequant(14, b, 256).astype(np.float32).reshape(2, 4, 32)
+    for j, q in enumerate((1, 17, 34, 50)):
+        assert np.all(out[:, j, :] == 0.5 * 2 * (q - 32))
+    # truncated data leaves zeros, partial element counts stop early
+    assert np.all(ref.dequant(14, b[:100], 256) == 0)
+    assert ref.dequant(14, b, 40).shape == (40,)
+
+
+def test_q6_k_linear_is_dequant_plus_f16_linear(ref):
+    g = np.load(__import__("os").path.join(__import__("os").path.dirname(__file__), "golden", "q6_k.npz"))
+    raw = g["q6_k_bytes"][7:11]                      # 4 ordinary super-blocks -> W [2, 512]
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((3, 512)).astype(np.float16)
+    w = ref.dequant(14, raw, 1024).reshape(2, 512)
+    assert np.array_equal(ref.linear_q(14, raw, 2, 512, x).view(np.uint16), ref.linear_f32acc(x, w).view(np.uint16))
