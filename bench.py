@@ -338,7 +338,8 @@ def llama_bytes_per_step(arch, tp: int, batch: int, context: int) -> int:
 
 def run_tp(args, rank: int, world: int, local: int) -> None:
     """N > 1: Llama-2-70B-shape Q4_0 decode, tensor-parallel over the N GPUs (BASELINE configs[4]):
-    column-parallel q/k/v/gate/up/lm_head, row-parallel o/down with an NCCL all-reduce after each,
+    column-parallel q/k/v/gate/up/lm_head, row-parallel o/down with an all-reduce after each (one peer-memory
+    kernel fused with the residual add; NCCL with --nccl-allreduce),
     2048 positions already in the KV cache (filled with random f16 on the device)."""
     import torch
     import torch.distributed as dist
@@ -351,6 +352,13 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
     box = [unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0, device=torch.device("cuda", local))
     comm = Comm(dev, box[0], rank, world)
+    if not args.nccl_allreduce:
+        # peer-memory exchange: the [batch, d_model] all-reduces run as one kernel over NVLink
+        def gather(blob):
+            out = [None] * world
+            dist.all_gather_object(out, blob)
+            return out
+        comm.enable_p2p(max(16, batch) * arch.d_model, gather)
     model = synthetic_model(dev, arch, SEED, tp_rank=rank, tp_size=world, device_embeddings=True)
     max_seq = context + 2 * (K + W) + 64
     llm = Llama(dev, model, arch, max_seq=max_seq, max_batch=batch, max_prefill=16, tp_rank=rank, tp_size=world)
@@ -422,7 +430,10 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
         "config": {"workload": f"llama-2-70b-shape q4_0 decode, TP{world}, batch {batch}, 2048-token context "
                                f"(BASELINE configs[4]); NOT the N=1 workload (tinyllama, configs[2])",
                    "parallelism": f"tp{world}", "batch": batch, "collectives_per_step": 2 * arch.n_layers + 1,
-                   "allreduce_bytes": batch * d * 2, "step_hbm_bytes_per_gpu": step_bytes,
+                   "allreduce_bytes": batch * d * 2,
+                   "allreduce": "one-shot peer-memory kernel fused with the residual add" if comm.p2p_ready
+                   else "nccl all-reduce + add kernel",
+                   "step_hbm_bytes_per_gpu": step_bytes,
                    "step_hbm_gbs_per_gpu": step_bytes / (ms / K * 1e-3) / 1e9,
                    "l2": "per-GPU weights (GBs) exceed the 126 MB L2", "launches_per_step": llm.launches(7), "seed": SEED},
         "e2e": {"value": batch * K / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
@@ -503,6 +514,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="decode batch of the tensor-parallel (N > 1) workload")
+    ap.add_argument("--nccl-allreduce", action="store_true",
+                    help="N > 1: keep the all-reduces on NCCL instead of the peer-memory kernel (for comparison)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -426,6 +426,23 @@ TLC_API int32_t tlc_allgather_f16(tlc_ctx *ctx, tlc_comm *comm, const void *send
 /* Joins a runner created with tp_size > 1 to its communicator; required before
  * the first prefill / decode of a sharded model.  Logits handed back to the
  * host are full [rows, vocab] rows on every rank. */
+/* Peer-memory exchange for small all-reduces (one process per GPU on one host,
+ * GPUs connected by NVLink): every rank exports an exchange block
+ * (tlc_comm_p2p_export -> a CUDA IPC handle of TLC_IPC_HANDLE_BYTES bytes), the
+ * host gathers the handles of all ranks in rank order and gives them to
+ * tlc_comm_p2p_import.  From then on tlc_allreduce_residual_f16 runs as ONE
+ * kernel that pushes the partial sums to the peers over NVLink, waits (bounded:
+ * a wait that runs out reports TLC_ERR_TIMEOUT at the next tlc_synchronize) and
+ * sums in rank order, for vectors of up to max_elems values; larger ones, and
+ * communicators without the exchange, use NCCL all-reduce + an add kernel. */
+#define TLC_IPC_HANDLE_BYTES 64
+TLC_API int32_t tlc_comm_p2p_export(tlc_comm *comm, size_t max_elems, void *handle_out);
+TLC_API int32_t tlc_comm_p2p_import(tlc_comm *comm, const void *handles);
+TLC_API int32_t tlc_comm_p2p_ready(tlc_comm *comm);
+/* out = residual + sum over ranks of partial; residual may be null (out = the sum);
+ * partial_dev may be overwritten.  count f16 values on every rank. */
+TLC_API int32_t tlc_allreduce_residual_f16(tlc_ctx *ctx, tlc_comm *comm, void *partial_dev,
+                                           const void *residual_dev, void *out_dev, size_t count);
 TLC_API int32_t tlc_llama_set_comm(tlc_llama *l, tlc_comm *comm);
 
 /* Kernels one decode step launches for a parts mask (7 = whole step), known

@@ -136,6 +136,10 @@ PROTOTYPES = {
     "tlc_comm_size": (i32, [vp]),
     "tlc_allreduce_f16": (i32, [vp, vp, vp, sz]),
     "tlc_allgather_f16": (i32, [vp, vp, vp, vp, sz]),
+    "tlc_comm_p2p_export": (i32, [vp, sz, vp]),
+    "tlc_comm_p2p_import": (i32, [vp, vp]),
+    "tlc_comm_p2p_ready": (i32, [vp]),
+    "tlc_allreduce_residual_f16": (i32, [vp, vp, vp, vp, vp, sz]),
     "tlc_llama_set_comm": (i32, [vp, vp]),
 }
 

@@ -3,6 +3,8 @@
 The reference has nothing of the kind.  Rank 0 makes a 128-byte id with
 ``unique_id()``; the caller ships it to the other ranks (torch.distributed, a
 pipe, a file) and every rank calls ``Comm(dev, id, rank, world)``.
+``enable_p2p`` then maps the ranks' exchange blocks into one another (CUDA IPC)
+so that the small all-reduces of a decode step run as one kernel over NVLink.
 """
 from __future__ import annotations
 
@@ -40,6 +42,31 @@ class Comm:
             self.close()
         except Exception:
             pass
+
+    def enable_p2p(self, max_elems: int, gather) -> None:
+        """Sets up the peer-memory exchange for all-reduces of up to ``max_elems`` f16 values.
+
+        ``gather(blob: bytes) -> list[bytes]`` must return every rank's blob in rank order (for
+        instance ``torch.distributed.all_gather_object``); it carries the 64-byte CUDA IPC handles."""
+        buf = C.create_string_buffer(64)
+        check(self.dev.lib.tlc_comm_p2p_export(self.handle, max_elems, buf))
+        blobs = gather(buf.raw)
+        if len(blobs) != self.world or any(len(b) != 64 for b in blobs):
+            raise ValueError("gather() must return one 64-byte handle per rank")
+        check(self.dev.lib.tlc_comm_p2p_import(self.handle, C.create_string_buffer(b"".join(blobs), 64 * self.world)))
+
+    @property
+    def p2p_ready(self) -> bool:
+        return bool(self.dev.lib.tlc_comm_p2p_ready(self.handle))
+
+    def all_reduce_residual(self, partial: Tensor, residual: Tensor | None = None) -> Tensor:
+        """residual + sum over the ranks of ``partial`` (which may be overwritten); one peer-memory
+        kernel when the exchange is enabled and the vector fits, NCCL + add otherwise."""
+        out = self.dev.empty(partial.shape)
+        check(self.dev.lib.tlc_allreduce_residual_f16(self.dev.handle, self.handle, partial.ptr,
+                                                      residual.ptr if residual is not None else None, out.ptr,
+                                                      partial.size))
+        return out
 
     def all_reduce(self, t: Tensor) -> Tensor:
         """In-place f16 sum over the ranks."""

@@ -64,10 +64,150 @@ NcclApi &nccl() {
 
 }  // namespace
 
+namespace {
+
+// ---------------------------------------------------------------------------
+// One-shot all-reduce over NVLink peer memory, fused with the residual add.
+//
+// The row-parallel projections of a decode step leave [M, d] f16 partial sums
+// on every rank (16 KB for M = 1, d = 8192): far too small for a ring, and a
+// library all-reduce costs tens of microseconds per call, 160 times per step
+// at 80 layers.  Here every rank owns an exchange block that its peers map
+// through CUDA IPC.  One kernel per all-reduce, kChunks CTAs, each on its own
+// slice of the vector and its own flags, so no CTA waits for another CTA of
+// the same GPU:
+//   1. store the slice of the local partial into slot [parity][rank] of every
+//      peer's block (plain 16-byte stores over NVLink), fence, then store the
+//      sequence number into flag [rank][chunk] of every peer (release);
+//   2. wait (bounded) until the flags of all peers in the local block carry
+//      that sequence number (acquire);
+//   3. sum the world partials in rank order in f32 (the local one straight
+//      from the GEMV's output, the others from the local block), round to f16
+//      once, add the residual, store.  Every rank computes bit-identical sums.
+// Two slots alternate by sequence parity: a rank can be at most one all-reduce
+// ahead of a peer, because finishing one needs every peer's flag for it.  The
+// sequence number lives in device memory (one per chunk), so a CUDA graph that
+// replays the same launch keeps counting.
+// ---------------------------------------------------------------------------
+constexpr int kP2pChunks = 8;
+constexpr int kP2pMaxWorld = 8;
+constexpr size_t kP2pFlagsOffset = 0;     // uint32 [world][kP2pChunks], written by peers
+constexpr size_t kP2pSeqOffset = 1024;    // uint32 [kP2pChunks], local
+constexpr size_t kP2pDataOffset = 4096;   // f16 [2][world][max_elems], written by peers
+constexpr uint32_t kP2pSpinLimit = 1u << 22;
+
+struct P2pParams {
+    uint8_t *peer[kP2pMaxWorld];  // exchange blocks, peer[rank] is the local one
+    const __half *partial;        // [n] this rank's partial sums
+    const __half *residual;       // [n] or null
+    __half *out;                  // [n]
+    int rank, world;
+    uint32_t n, max_elems;
+    tlc_dev_status *status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) allreduce_residual_kernel(const P2pParams p) {
+    __shared__ int timed_out;
+    tlc_pdl_prologue();  // the partial sums come from the previous kernel of the stream
+    const int tid = threadIdx.x, chunk = blockIdx.x;
+    const uint32_t per = ((p.n + kP2pChunks * 8 - 1) / (kP2pChunks * 8)) * 8;  // elements per chunk, multiple of 8
+    const uint32_t lo = min(p.n, chunk * per), hi = min(p.n, lo + per);
+    uint8_t *local = p.peer[p.rank];
+    uint32_t *seq = reinterpret_cast<uint32_t *>(local + kP2pSeqOffset) + chunk;
+    const uint32_t s = *seq + 1;
+    const uint32_t parity = s & 1u;
+    if (tid == 0) timed_out = 0;
+
+    // 1. push this rank's slice to every peer
+    const size_t slot_mine = ((size_t)parity * p.world + p.rank) * p.max_elems;
+    for (int r = 0; r < p.world; r++) {
+        if (r == p.rank) continue;
+        __half *dst = reinterpret_cast<__half *>(p.peer[r] + kP2pDataOffset) + slot_mine;
+        for (uint32_t i = lo + 8 * tid; i < hi; i += 8 * blockDim.x)
+            *reinterpret_cast<uint4 *>(dst + i) = *reinterpret_cast<const uint4 *>(p.partial + i);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < p.world && tid != p.rank)
+        st_release_sys(reinterpret_cast<uint32_t *>(p.peer[tid] + kP2pFlagsOffset) + p.rank * kP2pChunks + chunk, s);
+
+    // 2. wait for every peer's slice
+    if (tid < p.world && tid != p.rank) {
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(local + kP2pFlagsOffset) + tid * kP2pChunks + chunk;
+        bool ok = false;
+        for (uint32_t it = 0; it < kP2pSpinLimit; it++) {
+            if ((int32_t)(ld_acquire_sys(flag) - s) >= 0) {
+                ok = true;
+                break;
+            }
+            __nanosleep(32);
+        }
+        if (!ok) {
+            timed_out = 1;
+            if (atomicCAS(&p.status->code, 0, 3) == 0) p.status->where = 100 + tid;
+        }
+    }
+    __syncthreads();
+
+    // 3. sum in rank order, add the residual
+    if (!timed_out) {
+        const __half *slots = reinterpret_cast<const __half *>(local + kP2pDataOffset) + (size_t)parity * p.world * p.max_elems;
+        for (uint32_t i = lo + 8 * tid; i < hi; i += 8 * blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] = 0.f;
+            for (int r = 0; r < p.world; r++) {
+                const uint4 v = r == p.rank ? *reinterpret_cast<const uint4 *>(p.partial + i)
+                                            : __ldcg(reinterpret_cast<const uint4 *>(slots + (size_t)r * p.max_elems + i));
+                const __half2 *h = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __half22float2(h[j]);
+                    acc[2 * j] += f.x;
+                    acc[2 * j + 1] += f.y;
+                }
+            }
+            __align__(16) __half o[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) o[j] = __float2half_rn(acc[j]);
+            if (p.residual) {
+                const uint4 rv = *reinterpret_cast<const uint4 *>(p.residual + i);
+                const __half *rh = reinterpret_cast<const __half *>(&rv);
+#pragma unroll
+                for (int j = 0; j < 8; j++) o[j] = __hadd(rh[j], o[j]);
+            }
+            *reinterpret_cast<uint4 *>(p.out + i) = *reinterpret_cast<const uint4 *>(o);
+        }
+    }
+    if (tid == 0) *seq = s;
+}
+
+__global__ void add_f16_kernel(const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ y,
+                               size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = __hadd(a[i], b[i]);
+}
+
+}  // namespace
+
 struct tlc_comm {
     tlc_ctx *ctx;
     ncclComm_t comm;
     int rank, world;
+    // peer-memory exchange (tlc_comm_p2p_export / _import)
+    uint8_t *p2p_local = nullptr;
+    uint8_t *p2p_peer[kP2pMaxWorld] = {};
+    size_t p2p_max_elems = 0;
+    bool p2p_ready = false;
 };
 
 #define TLC_NCCL(expr)                                                                              \
@@ -100,7 +240,12 @@ extern "C" int32_t tlc_comm_init(tlc_ctx *ctx, const void *id128, int32_t rank, 
     memcpy(&id, id128, sizeof(id));
     ncclComm_t c = nullptr;
     TLC_NCCL(api.CommInitRank(&c, world, id, rank));
-    *out = new tlc_comm{ctx, c, rank, world};
+    tlc_comm *cm = new tlc_comm();
+    cm->ctx = ctx;
+    cm->comm = c;
+    cm->rank = rank;
+    cm->world = world;
+    *out = cm;
     return TLC_OK;
 }
 
@@ -108,6 +253,9 @@ extern "C" int32_t tlc_comm_destroy(tlc_comm *comm) {
     if (!comm) return TLC_OK;
     cudaSetDevice(comm->ctx->device);
     cudaStreamSynchronize(comm->ctx->stream);
+    for (int r = 0; r < comm->world && r < kP2pMaxWorld; r++)
+        if (comm->p2p_ready && r != comm->rank && comm->p2p_peer[r]) cudaIpcCloseMemHandle(comm->p2p_peer[r]);
+    if (comm->p2p_local) cudaFree(comm->p2p_local);
     if (nccl().CommDestroy) nccl().CommDestroy(comm->comm);
     delete comm;
     return TLC_OK;
@@ -141,5 +289,116 @@ extern "C" int32_t tlc_allgather_f16(tlc_ctx *ctx, tlc_comm *comm, const void *s
     }
     TLC_NCCL(nccl().AllGather(send_dev, recv_dev, count, ncclFloat16, comm->comm, ctx->stream));
     ctx->launches++;
+    return TLC_OK;
+}
+
+// ---- peer-memory exchange ----------------------------------------------------
+
+// Allocates this rank's exchange block for all-reduces of up to max_elems f16
+// values and writes its CUDA IPC handle (TLC_IPC_HANDLE_BYTES bytes) to handle_out.
+extern "C" int32_t tlc_comm_p2p_export(tlc_comm *comm, size_t max_elems, void *handle_out) {
+    TLC_REQUIRE(comm && handle_out, TLC_ERR_INVALID_OPERATION, "comm_p2p_export: null pointer");
+    if (int32_t rc = tlc_enter(comm->ctx)) return rc;
+    TLC_REQUIRE(comm->world <= kP2pMaxWorld, TLC_ERR_COMM, "peer-memory all-reduce supports up to %d ranks (got %d)",
+                kP2pMaxWorld, comm->world);
+    TLC_REQUIRE(!comm->p2p_local, TLC_ERR_INVALID_OPERATION, "comm_p2p_export: already exported");
+    TLC_REQUIRE(max_elems > 0 && max_elems % 8 == 0, TLC_ERR_INVALID_DIMENSION,
+                "comm_p2p_export: capacity %zu is not a positive multiple of 8", max_elems);
+    static_assert(sizeof(cudaIpcMemHandle_t) == TLC_IPC_HANDLE_BYTES, "IPC handle size");
+    const size_t bytes = kP2pDataOffset + (size_t)2 * comm->world * max_elems * sizeof(__half);
+    void *blk = nullptr;
+    cudaError_t e = cudaMalloc(&blk, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return tlc_fail(TLC_ERR_ALLOCATION, "exchange block of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    }
+    TLC_CUDA(cudaMemset(blk, 0, bytes));
+    TLC_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, blk);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(blk);
+        return tlc_fail(TLC_ERR_COMM, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle_out, &h, sizeof(h));
+    comm->p2p_local = static_cast<uint8_t *>(blk);
+    comm->p2p_max_elems = max_elems;
+    return TLC_OK;
+}
+
+// Maps the peers' exchange blocks: `handles` holds world handles in rank order
+// (every rank's tlc_comm_p2p_export output, gathered by the host).
+extern "C" int32_t tlc_comm_p2p_import(tlc_comm *comm, const void *handles) {
+    TLC_REQUIRE(comm && handles, TLC_ERR_INVALID_OPERATION, "comm_p2p_import: null pointer");
+    if (int32_t rc = tlc_enter(comm->ctx)) return rc;
+    TLC_REQUIRE(comm->p2p_local && !comm->p2p_ready, TLC_ERR_INVALID_OPERATION,
+                "comm_p2p_import: export first, import once");
+    const uint8_t *hs = static_cast<const uint8_t *>(handles);
+    for (int r = 0; r < comm->world; r++) {
+        if (r == comm->rank) {
+            comm->p2p_peer[r] = comm->p2p_local;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, hs + (size_t)r * TLC_IPC_HANDLE_BYTES, sizeof(h));
+        void *ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            for (int q = 0; q < r; q++)
+                if (q != comm->rank && comm->p2p_peer[q]) cudaIpcCloseMemHandle(comm->p2p_peer[q]);
+            return tlc_fail(TLC_ERR_COMM, "cudaIpcOpenMemHandle for rank %d failed: %s", r, cudaGetErrorString(e));
+        }
+        comm->p2p_peer[r] = static_cast<uint8_t *>(ptr);
+    }
+    comm->p2p_ready = true;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_comm_p2p_ready(tlc_comm *comm) { return comm && comm->p2p_ready ? 1 : 0; }
+
+// out = residual + sum over ranks of partial (f32 sum in rank order, one f16
+// rounding, then the f16 add).  `partial_dev` may be overwritten.  Runs as one
+// peer-memory kernel when the exchange is set up and the vector fits; as NCCL
+// all-reduce + add otherwise.
+extern "C" int32_t tlc_allreduce_residual_f16(tlc_ctx *ctx, tlc_comm *comm, void *partial_dev,
+                                              const void *residual_dev, void *out_dev, size_t count) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(comm && partial_dev && out_dev, TLC_ERR_INVALID_OPERATION, "allreduce_residual: null pointer");
+    TLC_REQUIRE(comm->ctx->device == ctx->device, TLC_ERR_DEVICE, "allreduce: communicator lives on another device");
+    if (count == 0) return TLC_OK;
+    const bool aligned = count % 8 == 0 && ((uintptr_t)partial_dev | (uintptr_t)out_dev | (uintptr_t)residual_dev) % 16 == 0;
+    if (comm->world > 1 && comm->p2p_ready && aligned && count <= comm->p2p_max_elems) {
+        P2pParams p{};
+        for (int r = 0; r < comm->world; r++) p.peer[r] = comm->p2p_peer[r];
+        p.partial = static_cast<const __half *>(partial_dev);
+        p.residual = static_cast<const __half *>(residual_dev);
+        p.out = static_cast<__half *>(out_dev);
+        p.rank = comm->rank;
+        p.world = comm->world;
+        p.n = (uint32_t)count;
+        p.max_elems = (uint32_t)comm->p2p_max_elems;
+        p.status = ctx->dev_status;
+        cudaError_t le = tlc_launch_pdl(ctx, allreduce_residual_kernel, dim3(kP2pChunks), dim3(256), 0, p);
+        if (le != cudaSuccess) {
+            cudaGetLastError();
+            return tlc_fail(TLC_ERR_CUDA, "all-reduce launch failed: %s", cudaGetErrorString(le));
+        }
+        TLC_CHECK_LAUNCH(ctx);
+        return TLC_OK;
+    }
+    if (comm->world > 1) {
+        TLC_NCCL(nccl().AllReduce(partial_dev, partial_dev, count, ncclFloat16, ncclSum, comm->comm, ctx->stream));
+        ctx->launches++;
+    }
+    if (residual_dev) {
+        add_f16_kernel<<<(unsigned)((count + 255) / 256), 256, 0, ctx->stream>>>(
+            static_cast<const __half *>(residual_dev), static_cast<const __half *>(partial_dev),
+            static_cast<__half *>(out_dev), count);
+        TLC_CHECK_LAUNCH(ctx);
+    } else if (out_dev != partial_dev) {
+        TLC_CUDA(cudaMemcpyAsync(out_dev, partial_dev, count * 2, cudaMemcpyDeviceToDevice, ctx->stream));
+    }
     return TLC_OK;
 }

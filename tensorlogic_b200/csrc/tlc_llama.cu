@@ -320,8 +320,7 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
             if (tp) {
                 // Row-parallel projection: sum the ranks' partial products, then the residual add.
-                if (int32_t rc = tlc_allreduce_f16(ctx, L->comm, L->part, (size_t)m * d)) return rc;
-                if (int32_t rc = tlc_add(ctx, L->x, L->part, L->x1, (size_t)m * d)) return rc;
+                if (int32_t rc = tlc_allreduce_residual_f16(ctx, L->comm, L->part, L->x, L->x1, (size_t)m * d)) return rc;
             }
         }
         if (parts & 1) {
@@ -348,8 +347,7 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
             }
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
             if (tp) {
-                if (int32_t rc = tlc_allreduce_f16(ctx, L->comm, L->part, (size_t)m * d)) return rc;
-                if (int32_t rc = tlc_add(ctx, L->x1, L->part, L->x, (size_t)m * d)) return rc;
+                if (int32_t rc = tlc_allreduce_residual_f16(ctx, L->comm, L->part, L->x1, L->x, (size_t)m * d)) return rc;
             }
         }
     }

@@ -4,8 +4,9 @@
         --master-port 29511 tests/tp_parity.py
 
 Every rank builds its shard of a small LLaMA (weights split Megatron-style), joins
-the NCCL communicator, runs prefill + greedy decode, and compares its logits with
-the CPU oracle's unsharded forward (rank 0 prints PASS/FAIL; exit code says the same).
+the communicator (NCCL + the peer-memory exchange), checks the fused all-reduce +
+residual kernel against a host sum, runs prefill + greedy decode, and compares its
+logits with the CPU oracle's unsharded forward (rank 0 prints PASS/FAIL; exit code says the same).
 The id of the communicator travels over torch.distributed's gloo backend.
 """
 import os
@@ -34,10 +35,39 @@ def main() -> int:
     dist.broadcast_object_list(box, src=0)
     comm = Comm(dev, box[0], rank, world)
 
+    def gather(blob):
+        out = [None] * world
+        dist.all_gather_object(out, blob)
+        return out
+
+    # residual + all-reduce before and after the peer-memory exchange exists (NCCL + add, then one kernel)
+    rng = np.random.default_rng(100 + rank)
+    ok = True
+    for phase in ("nccl", "p2p", "p2p-too-large"):
+        if phase == "p2p":
+            comm.enable_p2p(4096, gather)
+            ok &= comm.p2p_ready
+        for rep, n in enumerate((8, 40, 1024, 4096, 4096, 2048) if phase != "p2p-too-large" else (8192,)):
+            part = rng.standard_normal(n).astype(np.float16)
+            res = np.random.default_rng(7 * rep + n).standard_normal(n).astype(np.float16)  # same on every rank
+            parts = gather(part.tobytes())
+            acc = np.zeros(n, np.float32)
+            for b in parts:                                   # rank order, f32, one rounding
+                acc += np.frombuffer(b, np.float16).astype(np.float32)
+            want_sum = acc.astype(np.float16)
+            got = comm.all_reduce_residual(dev.tensor(part), dev.tensor(res)).numpy()
+            got_sum = comm.all_reduce_residual(dev.tensor(part)).numpy()
+            if phase == "nccl" or phase == "p2p-too-large":   # the library's own f16 summation order
+                ok &= bool(np.allclose(got_sum.astype(np.float32), acc, rtol=2e-3, atol=2e-3))
+            else:
+                ok &= bool(np.array_equal(got_sum.view(np.uint16), want_sum.view(np.uint16)))
+                ok &= bool(np.array_equal(got.view(np.uint16), (res + want_sum).view(np.uint16)))
+    dev.synchronize()
+
     # all-reduce / all-gather on their own
     t = dev.tensor(np.full((3, 5), rank + 1, np.float16))
     comm.all_reduce(t)
-    ok = bool(np.all(t.numpy() == np.float16(world * (world + 1) / 2)))
+    ok &= bool(np.all(t.numpy() == np.float16(world * (world + 1) / 2)))
     g = comm.all_gather(dev.tensor(np.full((4,), rank, np.float16))).numpy()
     ok &= bool(np.array_equal(g, np.repeat(np.arange(world, dtype=np.float16), 4).reshape(world, 4)))
 
