@@ -143,13 +143,15 @@ def dist_setup(n_gpus: int):
     return rank, world, local
 
 
-def cpu_baseline(arch, seed: int, budget_s: float = 12.0) -> dict:
+def cpu_baseline(arch, seed: int, budget_s: float = 12.0, row_div: int = 1) -> dict:
     """The reference's CPU path on a bounded sample, scaled to tokens/s.
 
     Restated by oracle/tl_ref.c: GGUF dequantization (src/model/formats/gguf.rs:68-112) happens
     once at load upstream and is not timed; per token the linears run as transpose + matmul_cpu with
     an f16 running sum on one thread (src/ops/matmul.rs:201-228, :293-297).  The sample is the seven
     linears of one layer plus a slice of lm_head rows; a token costs n_layers * layer + lm_head.
+    row_div > 1 takes only every row_div-th part of each linear's rows (the cost is linear in the
+    rows) so that the 70B shape stays a bounded sample too.
     """
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import tl_ref as ref
@@ -159,6 +161,7 @@ def cpu_baseline(arch, seed: int, budget_s: float = 12.0) -> dict:
               ("ffn_up", f, d), ("ffn_down", d, f)]
     ws = []
     for name, n, k in shapes:
+        n = max(16, n // row_div)
         raw = synth.blocks(2, seed, synth.tensor_id(f"blk.0.{name}.weight"), n, k)
         ws.append((ref.dequant(2, raw, n * k).reshape(n, k), synth.activations(seed, f"cpu.{name}", (1, k))))
     head_rows = 4000
@@ -177,7 +180,7 @@ def cpu_baseline(arch, seed: int, budget_s: float = 12.0) -> dict:
         t_layer += t1 - t0
         t_head += t2 - t1
         reps += 1
-    t_token = arch.n_layers * (t_layer / reps) + (t_head / reps) * (arch.vocab / head_rows)
+    t_token = arch.n_layers * (t_layer / reps) * row_div + (t_head / reps) * (arch.vocab / head_rows)
     # the multi-threaded f32-accumulating variant (no counterpart upstream), for context
     t0 = time.perf_counter()
     for w, x in ws:
@@ -185,9 +188,10 @@ def cpu_baseline(arch, seed: int, budget_s: float = 12.0) -> dict:
     ref.linear_f32acc(xh, head)
     t_mt_layer = time.perf_counter() - t0
     macs_sample = sum(w.size for w, _ in ws) + head.size
-    macs_token = arch.n_layers * sum(w.size for w, _ in ws) + arch.vocab * d
+    macs_token = arch.n_layers * sum(w.size for w, _ in ws) * row_div + arch.vocab * d
     return {"value": 1.0 / t_token, "unit": "tokens/s", "cores": 1, "kind": "port",
-            "sample": (f"{reps}x (7 linears of one layer + {head_rows} lm_head rows), literal f16-accumulate matmul on "
+            "sample": (f"{reps}x (7 linears of one layer{f', 1/{row_div} of their rows' if row_div > 1 else ''} + {head_rows} "
+                       f"lm_head rows), literal f16-accumulate matmul on "
                        f"pre-dequantized f16 weights, scaled to {arch.n_layers} layers + {arch.vocab} lm_head rows; "
                        f"attention, norms and sampling not counted (favours the CPU)"),
             "f16c": bool(ref.uses_f16c()), "host_cores_available": os.cpu_count(),
@@ -198,19 +202,24 @@ def run_reference(args, rank: int, world: int) -> None:
     """--impl reference: the reference's own CPU implementation of the path (no GPU work)."""
     if rank != 0:
         return
-    from tensorlogic_b200.model import TINYLLAMA
-    arch = TINYLLAMA
+    from tensorlogic_b200.model import LLAMA2_70B, TINYLLAMA
+    # the same workload as this repo's arm at that N: TinyLlama at N = 1, the 70B shape beyond
+    big = args.gpus > 1
+    arch = LLAMA2_70B if big else TINYLLAMA
     # each "step" is a bounded sample of one token's work; the whole run stays within minutes
     steps = max(1, args.steps)
     budget = min(150.0, 1.2 * (args.warmup + steps)) if steps > 1 else 12.0
     t0 = time.perf_counter()
-    base = cpu_baseline(arch, SEED, budget_s=max(6.0, budget))
+    base = cpu_baseline(arch, SEED, budget_s=max(6.0, budget), row_div=16 if big else 1)
     elapsed = time.perf_counter() - t0
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / base["value"],
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "tinyllama-1.1b q4_0 decode, batch 1 (BASELINE configs[2])",
+        "higher_is_better": True, "scaling": "strong" if big else "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": "llama-2-70b-shape q4_0 decode, batch 1 (BASELINE configs[4]); the reference has no "
+                               "multi-GPU path: one host process" if big else
+                               "tinyllama-1.1b q4_0 decode, batch 1 (BASELINE configs[2])",
                    "note": "reference CPU path (transpose + f16-accumulating matmul_cpu, 1 thread), "
                            "bounded sample per step extrapolated to a token", "wall_s": round(elapsed, 1)},
         "cpu_baseline": base,

@@ -399,6 +399,19 @@ TLC_API int32_t tlc_llama_decode_host(tlc_llama *l, int32_t batch, const int32_t
 TLC_API int32_t tlc_llama_decode_enqueue(tlc_llama *l, int32_t batch, int32_t steps);
 TLC_API int32_t tlc_llama_read_state(tlc_llama *l, int32_t batch, int32_t *next_ids_host,
                                      int32_t *positions_host);
+/* Sampling of the runner (src/interpreter/builtin_sampling.rs:66-250).  temperature
+ * <= 1e-4 is greedy, the default.  Otherwise every step draws the next token as
+ * temperature_sample does -- f32 logits / temperature, softmax, first index whose
+ * running probability sum exceeds a uniform draw -- on the device; the draw is a
+ * pure function of (seed, position of the token fed to the step, sequence index),
+ * tlc_sample_uniform_host gives the same number on the host. */
+TLC_API int32_t tlc_llama_set_sampling(tlc_llama *l, float temperature, uint64_t seed);
+TLC_API float tlc_sample_uniform_host(uint64_t seed, uint32_t position, uint32_t sequence);
+/* The temperature_sample builtin on its own: logits_dev [rows, vocab] f16, one
+ * uniform draw in [0, 1) per row from the caller (upstream: rand::thread_rng()),
+ * sampled ids to the host.  uniforms_host may be NULL when temperature <= 1e-4. */
+TLC_API int32_t tlc_temperature_sample(tlc_ctx *ctx, const void *logits_dev, int32_t rows, int32_t vocab,
+                                       float temperature, const float *uniforms_host, int32_t *ids_host);
 /* The same, replaying only some of the step's launches, for per-kernel timing:
  * parts is a mask of 1 (the quantized linears), 2 (attention), 4 (embedding
  * gather + sampling); tokens and positions are left untouched unless parts == 7. */

@@ -564,6 +564,43 @@ TLREF_API int tlref_argmax_last(const uint16_t *logits, int n) {
     return best;
 }
 
+/* Temperature sample: follows temperature_sample_cpu,
+ * src/interpreter/builtin_sampling.rs:131-220, with the uniform draw passed in
+ * (upstream: rand::thread_rng().gen::<f32>()).  Logits widened to f32; T <= 1e-4
+ * is the greedy arm; otherwise scaled = x / T, softmax with the maximum
+ * subtracted (f32, sums in index order), probabilities divided by the sum, then
+ * the first index whose running sum exceeds u; the last index if none does.
+ * cdf_out (optional, n floats) receives the running sums. */
+TLREF_API int tlref_temperature_sample(const uint16_t *logits, int n, float temperature, float u,
+                                       float *cdf_out) {
+    if (temperature <= 0.0001f) return tlref_argmax_last(logits, n);
+    float *p = (float *)malloc((size_t)n * sizeof(float));
+    float mx = -INFINITY;
+    for (int i = 0; i < n; i++) {
+        p[i] = h2f(logits[i]) / temperature;
+        if (p[i] > mx) mx = p[i];  /* f32::max fold */
+    }
+    float sum = 0.0f;
+    for (int i = 0; i < n; i++) {
+        p[i] = expf(p[i] - mx);
+        sum += p[i];
+    }
+    int idx = n - 1;
+    int found = 0;
+    float cum = 0.0f;
+    for (int i = 0; i < n; i++) {
+        cum += p[i] / sum;
+        if (cdf_out) cdf_out[i] = cum;
+        if (!found && u < cum) {
+            idx = i;
+            found = 1;
+            if (!cdf_out) break;
+        }
+    }
+    free(p);
+    return idx;
+}
+
 TLREF_API int tlref_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -55,6 +55,7 @@ def _load() -> C.CDLL:
         "tlref_attention": (None, [u16p, u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_float, C.c_int, C.c_int]),
         "tlref_argmax_last": (C.c_int, [u16p, C.c_int]),
+        "tlref_temperature_sample": (C.c_int, [u16p, C.c_int, C.c_float, C.c_float, C.POINTER(C.c_float)]),
         "tlref_num_threads": (C.c_int, []),
         "tlref_set_f16c": (None, [C.c_int]),
         "tlref_uses_f16c": (C.c_int, []),
@@ -256,6 +257,15 @@ def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, q_pos0:
 def argmax_last(logits: np.ndarray) -> int:
     logits = _f16(logits).reshape(-1)
     return int(lib().tlref_argmax_last(_h(logits), logits.size))
+
+
+def temperature_sample(logits: np.ndarray, temperature: float, u: float, return_cdf: bool = False):
+    """temperature_sample(logits, T) with the uniform draw u passed in; optionally also the running sums."""
+    logits = _f16(logits).reshape(-1)
+    cdf = np.empty(logits.size, np.float32) if return_cdf else None
+    idx = int(lib().tlref_temperature_sample(_h(logits), logits.size, temperature, u,
+                                             cdf.ctypes.data_as(C.POINTER(C.c_float)) if return_cdf else None))
+    return (idx, cdf) if return_cdf else idx
 
 
 def num_threads() -> int:

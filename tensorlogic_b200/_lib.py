@@ -129,6 +129,9 @@ PROTOTYPES = {
     "tlc_llama_decode_enqueue_parts": (i32, [vp, i32, i32, i32]),
     "tlc_llama_launches_per_step": (i32, [vp, i32]),
     "tlc_llama_cache": (vp, [vp]),
+    "tlc_llama_set_sampling": (i32, [vp, f32, u64]),
+    "tlc_sample_uniform_host": (f32, [u64, u32, u32]),
+    "tlc_temperature_sample": (i32, [vp, vp, i32, i32, f32, P(f32), P(i32)]),
     "tlc_comm_unique_id": (i32, [vp]),
     "tlc_comm_init": (i32, [vp, vp, i32, i32, P(vp)]),
     "tlc_comm_destroy": (i32, [vp]),

@@ -292,6 +292,27 @@ def softmax(x: Tensor, dim: int = -1) -> Tensor:
     return y
 
 
+def temperature_sample(logits: Tensor, temperature: float = 1.0, uniforms=None) -> np.ndarray:
+    """temperature_sample(logits, T) for every row of ``logits`` [rows, vocab]: sampled token ids.
+
+    ``uniforms``: one draw in [0, 1) per row (the reference draws ``rand::thread_rng().gen::<f32>()``
+    itself; here the caller owns the randomness).  temperature <= 1e-4 is greedy and needs none."""
+    vocab = logits.shape[-1]
+    rows = logits.size // vocab
+    ids = np.empty(rows, np.int32)
+    u = None
+    if temperature > 1e-4:
+        if uniforms is None:
+            raise TensorError(_lib.ERR_INVALID_OPERATION, "temperature_sample() needs one uniform draw per row")
+        u = np.ascontiguousarray(np.atleast_1d(uniforms), dtype=np.float32)
+        if u.size != rows:
+            raise TensorError(_lib.ERR_SHAPE_MISMATCH, f"temperature_sample: {u.size} draws for {rows} rows")
+    check(logits.dev.lib.tlc_temperature_sample(logits.dev.handle, logits.ptr, rows, vocab, float(temperature),
+                                                u.ctypes.data_as(C.POINTER(C.c_float)) if u is not None else None,
+                                                ids.ctypes.data_as(C.POINTER(C.c_int32))))
+    return ids
+
+
 def embedding(table: Tensor, ids) -> Tensor:
     if table.ndim != 2:
         raise TensorError(_lib.ERR_INVALID_OPERATION, "embedding table must be 2D [vocab, d]")

@@ -23,6 +23,7 @@
 #include <memory>
 
 #include "tlc_internal.h"
+#include "tlc_synth.cuh"
 
 struct tlc_kvcache;
 extern "C" int32_t tlc_kvcache_create(tlc_ctx *, int32_t, int32_t, int32_t, int32_t, int32_t, tlc_kvcache **);
@@ -58,6 +59,8 @@ struct tlc_llama {
     std::map<int, cudaGraphExec_t> graph;  // decode graphs keyed by batch * 8 + parts
     int launches_in[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // kernels per step, by parts mask
     int heads_local, kv_heads_local, ffn_local, vocab_local;
+    float temperature = 0.f;   // <= 1e-4: greedy
+    uint64_t sample_seed = 0;  // uniform draws: counter-based, keyed by (seed, position, sequence)
 };
 
 namespace {
@@ -142,6 +145,99 @@ __global__ void argmax_advance_kernel(const __half *__restrict__ logits, int voc
         }
     }
 }
+
+}  // namespace
+
+// Uniform draw in [0, 1) with 24 bits, a pure function of (seed, position, sequence).
+__host__ __device__ inline float tlc_sample_uniform(uint64_t seed, uint32_t pos, uint32_t seq) {
+    const uint64_t r = tlc_mix64(tlc_mix64(seed ^ 0x73616d706c65ull) + ((uint64_t)pos << 20) + seq);
+    return (float)(r >> 40) * (1.0f / 16777216.0f);
+}
+
+// Temperature sample + step bookkeeping, one CTA per sequence: the arithmetic of
+// temperature_sample_cpu (src/interpreter/builtin_sampling.rs:185-217) -- logits
+// widened to f32 and divided by the temperature, softmax with the maximum
+// subtracted, first index whose running probability sum exceeds the uniform
+// draw, the last index if none does -- with the sums formed in parallel: every
+// thread owns a contiguous run of the vocabulary, a block-wide scan gives each
+// run its starting sum, and the comparison is made against u * total instead of
+// dividing every probability (the f32 rounding differs from the sequential sum
+// only for draws within ~1e-6 of a boundary).
+// u comes from `uniforms[b]` when given, else from tlc_sample_uniform.
+__global__ void __launch_bounds__(1024) sample_advance_kernel(const __half *__restrict__ logits, int vocab, int shards,
+                                                              int rows, float temperature, uint64_t seed,
+                                                              const float *__restrict__ uniforms, int fixed_pos,
+                                                              int *__restrict__ next_ids, int *__restrict__ ids,
+                                                              int *__restrict__ positions, int advance) {
+    __shared__ float red[32];
+    __shared__ float warp_sum[32];
+    __shared__ int found_min;
+    tlc_pdl_prologue();  // the logits come from the previous kernel
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int V = vocab * shards;
+    const int seg = (V + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int lo = min(V, tid * seg), hi = min(V, lo + seg);
+    auto logit = [&](int j) {  // token j of the gathered shards
+        const int sh = j / vocab, i = j - sh * vocab;
+        return __half2float(logits[((size_t)sh * rows + b) * vocab + i]) / temperature;
+    };
+    float mx = -INFINITY;
+    for (int j = lo; j < hi; j++) mx = fmaxf(mx, logit(j));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[warp] = mx;
+    if (tid == 0) found_min = V - 1;  // "default to last token"
+    __syncthreads();
+    mx = red[lane];  // blockDim.x == 1024: 32 warps
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float local = 0.f;
+    for (int j = lo; j < hi; j++) local += expf(logit(j) - mx);
+    // inclusive scan of the per-thread sums: within the warp, then across warps
+    float incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    float wbase = 0.f, total = 0.f;
+    {
+        float w = warp_sum[lane], wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += t;
+        }
+        total = __shfl_sync(0xffffffffu, wi, 31);
+        wbase = __shfl_sync(0xffffffffu, wi - w, warp);  // exclusive sum of the warps before this one
+    }
+    const int pos = fixed_pos >= 0 ? fixed_pos : positions ? positions[b] : 0;  // position of the token fed to this step
+    const float u = uniforms ? uniforms[b] : tlc_sample_uniform(seed, (uint32_t)pos, (uint32_t)b);
+    const float target = u * total;
+    float run = wbase + incl - local;  // sum of everything before this thread's run
+    if (target < run + local) {
+        for (int j = lo; j < hi; j++) {
+            run += expf(logit(j) - mx);
+            if (target < run) {
+                atomicMin(&found_min, j);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const int tok = found_min;
+        next_ids[b] = tok;
+        if (advance) {
+            ids[b] = tok;
+            positions[b] += 1;
+        }
+    }
+}
+
+namespace {
 
 int32_t get(tlc_model *m, const std::string &name, tlc_qtensor **out) { return tlc_model_get(m, name.c_str(), out); }
 
@@ -373,9 +469,14 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         if (sample && (parts & 4)) {
             const int srows = decode ? m : 1;
             const __half *lg = (tp ? L->logits_full : L->logits) + (size_t)(rows - srows) * L->vocab_local;
-            cudaError_t le = tlc_launch_pdl(ctx, argmax_advance_kernel, dim3(srows), dim3(1024), 0, lg, L->vocab_local,
-                                            c.tp_size, rows, (int *)L->next_ids, (int *)L->ids, (int *)L->positions,
-                                            advance ? 1 : 0);
+            cudaError_t le =
+                L->temperature > 0.0001f
+                    ? tlc_launch_pdl(ctx, sample_advance_kernel, dim3(srows), dim3(1024), 0, lg, L->vocab_local,
+                                     c.tp_size, rows, L->temperature, L->sample_seed, (const float *)nullptr,
+                                     decode ? -1 : pos0 + m - 1, (int *)L->next_ids, (int *)L->ids, (int *)L->positions, advance ? 1 : 0)
+                    : tlc_launch_pdl(ctx, argmax_advance_kernel, dim3(srows), dim3(1024), 0, lg, L->vocab_local,
+                                     c.tp_size, rows, (int *)L->next_ids, (int *)L->ids, (int *)L->positions,
+                                     advance ? 1 : 0);
             if (le != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "sampling launch failed: %s", cudaGetErrorString(le));
             TLC_CHECK_LAUNCH(ctx);
         }
@@ -552,6 +653,59 @@ extern "C" int32_t tlc_llama_read_state(tlc_llama *L, int32_t batch, int32_t *ne
         if (int32_t rc = tlc_download(L->ctx, positions_host, L->positions, (size_t)batch * 4)) return rc;
     }
     return TLC_OK;
+}
+
+// Sampling of prefill / decode: temperature <= 1e-4 is greedy (the default).
+// Otherwise tokens are drawn as temperature_sample does, with uniform draws that
+// are a pure function of (seed, position of the sampled token, sequence index):
+// a run is reproducible and tensor-parallel ranks draw the same tokens.
+extern "C" int32_t tlc_llama_set_sampling(tlc_llama *L, float temperature, uint64_t seed) {
+    TLC_REQUIRE(L, TLC_ERR_INVALID_OPERATION, "llama_set_sampling: null pointer");
+    TLC_REQUIRE(temperature >= 0.f && temperature == temperature, TLC_ERR_INVALID_OPERATION,
+                "temperature must be >= 0 (got %f)", (double)temperature);
+    if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    TLC_CUDA(cudaStreamSynchronize(L->ctx->stream));
+    // captured decode graphs hold the old sampling kernel and its arguments
+    for (auto &g : L->graph)
+        if (g.second) cudaGraphExecDestroy(g.second);
+    L->graph.clear();
+    L->temperature = temperature;
+    L->sample_seed = seed;
+    return TLC_OK;
+}
+
+extern "C" float tlc_sample_uniform_host(uint64_t seed, uint32_t position, uint32_t sequence) {
+    return tlc_sample_uniform(seed, position, sequence);
+}
+
+// temperature_sample(logits, T) as a builtin: logits_dev [rows, vocab] f16, one
+// uniform draw per row from the caller (upstream draws rand::thread_rng().gen::<f32>()),
+// the sampled ids come back to the host (the builtin returns an Integer).
+extern "C" int32_t tlc_temperature_sample(tlc_ctx *ctx, const void *logits_dev, int32_t rows, int32_t vocab,
+                                          float temperature, const float *uniforms_host, int32_t *ids_host) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(logits_dev && ids_host && (uniforms_host || temperature <= 0.0001f), TLC_ERR_INVALID_OPERATION,
+                "temperature_sample: null pointer");
+    TLC_REQUIRE(rows >= 1 && vocab >= 1, TLC_ERR_INVALID_DIMENSION, "temperature_sample: bad shape [%d, %d]", rows, vocab);
+    tlc_buf *ub = nullptr, *ib = nullptr;
+    int32_t rc = tlc_alloc(ctx, (size_t)rows * 4, &ib);
+    if (!rc) rc = tlc_alloc(ctx, (size_t)rows * 4, &ub);
+    if (!rc && temperature > 0.0001f) rc = tlc_upload(ctx, tlc_buf_ptr(ub), uniforms_host, (size_t)rows * 4);
+    if (!rc) {
+        if (temperature > 0.0001f)
+            sample_advance_kernel<<<rows, 1024, 0, ctx->stream>>>(
+                static_cast<const __half *>(logits_dev), vocab, 1, rows, temperature, 0, (const float *)tlc_buf_ptr(ub),
+                -1, (int *)tlc_buf_ptr(ib), nullptr, nullptr, 0);
+        else
+            argmax_advance_kernel<<<rows, 1024, 0, ctx->stream>>>(static_cast<const __half *>(logits_dev), vocab, 1, rows,
+                                                                   (int *)tlc_buf_ptr(ib), nullptr, nullptr, 0);
+        ctx->launches++;
+        if (cudaGetLastError() != cudaSuccess) rc = tlc_fail(TLC_ERR_CUDA, "sampling launch failed");
+    }
+    if (!rc) rc = tlc_download(ctx, ids_host, tlc_buf_ptr(ib), (size_t)rows * 4);
+    tlc_free(ub);
+    tlc_free(ib);
+    return rc;
 }
 
 extern "C" int32_t tlc_llama_launches_per_step(tlc_llama *L, int32_t parts) {

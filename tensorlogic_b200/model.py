@@ -224,6 +224,15 @@ class Llama:
         self._comm = comm  # keep it alive
         self.vocab_local = self.arch.vocab  # logits handed back to the host are full rows
 
+    def set_sampling(self, temperature: float = 0.0, seed: int = 0) -> None:
+        """temperature <= 1e-4: greedy (default).  Otherwise temperature_sample on the device, with
+        uniform draws that depend only on (seed, position, sequence): see ``sample_uniform``."""
+        check(self.dev.lib.tlc_llama_set_sampling(self.handle, float(temperature), int(seed)))
+
+    def sample_uniform(self, seed: int, position: int, sequence: int = 0) -> float:
+        """The draw the device uses for the token fed at ``position`` of ``sequence``."""
+        return float(self.dev.lib.tlc_sample_uniform_host(int(seed), int(position), int(sequence)))
+
     def prefill(self, ids, pos0: int = 0, return_logits: bool = True, all_rows: bool = False):
         """Returns (next_token, logits or None); logits are [1 or n, vocab] f16."""
         ids = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)

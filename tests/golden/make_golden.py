@@ -1,9 +1,8 @@
-"""Generates tests/golden/reference_py.npz from the reference's own Python code.
+"""Generates tests/golden/reference_py.npz and q6_k.npz from the reference's own Python code.
 
-Run in a container that has the TensorLogic checkout (path in TL_REFERENCE,
-default /root/reference):
+Run where the TensorLogic checkout is available, with its path in TL_REFERENCE:
 
-    python tests/golden/make_golden.py
+    TL_REFERENCE=<path to the tensorlogic checkout> python tests/golden/make_golden.py
 
 It imports the reference's numpy implementation of the TinyLlama layer
 (scripts/reference_impl.py, scripts/reference_with_gguf.py) and the `gguf`
@@ -22,10 +21,12 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("TL_REFERENCE", "/root/reference")
+REF = os.environ.get("TL_REFERENCE")
 
 
 def main() -> None:
+    if not REF or not os.path.isdir(os.path.join(REF, "scripts")):
+        raise SystemExit("set TL_REFERENCE to the path of the tensorlogic checkout")
     sys.path.insert(0, os.path.join(REF, "scripts"))
     import reference_impl as ri  # noqa: E402
     import reference_with_gguf as rg  # noqa: E402

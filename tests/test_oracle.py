@@ -283,3 +283,36 @@ def test_q6_k_linear_is_dequant_plus_f16_linear(ref):
     x = rng.standard_normal((3, 512)).astype(np.float16)
     w = ref.dequant(14, raw, 1024).reshape(2, 512)
     assert np.array_equal(ref.linear_q(14, raw, 2, 512, x).view(np.uint16), ref.linear_f32acc(x, w).view(np.uint16))
+
+
+def test_temperature_sample_kats(ref):
+    """The reference's sampling tests (src/interpreter/builtin_sampling.rs:555-790), through the oracle."""
+    # test_temperature_sample_greedy / _zero_equivalence: T = 0 picks the maximum, whatever the draw
+    lg = np.array([1.0, 2.0, 0.5, 3.0, 1.5, 10.0, 2.5, 0.1], np.float16)
+    for u in (0.0, 0.3, 0.999):
+        assert ref.temperature_sample(lg, 0.0, u) == 5
+    # test_softmax_probabilities_sum_to_one / test_exp_numerical_stability: large logits stay finite
+    big = np.array([1000.0, 1001.0, 1000.5], np.float16)
+    idx, cdf = ref.temperature_sample(big, 1.0, 0.5, return_cdf=True)
+    assert np.all(np.isfinite(cdf)) and abs(cdf[-1] - 1.0) < 1e-5 and idx == 1
+    # test_temperature_scaling_effects: lower temperature -> more mass on the maximum
+    lg4 = np.array([1.0, 2.0, 3.0, 0.5], np.float16)
+    mass = []
+    for t in (0.5, 1.0, 2.0):
+        _, cdf = ref.temperature_sample(lg4, t, 0.0, return_cdf=True)
+        p = np.diff(np.concatenate([[0.0], cdf]))
+        assert int(np.argmax(p)) == 2
+        mass.append(p[2])
+    assert mass[0] > mass[1] > mass[2]
+    # the draw walks the cumulative sums; u at or above the final sum falls back to the last index
+    _, cdf = ref.temperature_sample(lg4, 1.0, 0.0, return_cdf=True)
+    assert ref.temperature_sample(lg4, 1.0, 0.0) == 0
+    assert ref.temperature_sample(lg4, 1.0, float(cdf[0]) + 1e-4) == 1
+    assert ref.temperature_sample(lg4, 1.0, 0.99999994) == 3
+    # distribution check against the exact softmax
+    rng = np.random.default_rng(3)
+    lg = (rng.standard_normal(50) * 2).astype(np.float16)
+    cnt = np.bincount([ref.temperature_sample(lg, 0.7, float(u)) for u in rng.random(20000, np.float32)], minlength=50)
+    p = np.exp(lg.astype(np.float64) / 0.7)
+    p /= p.sum()
+    assert np.abs(cnt / 20000 - p).max() < 0.015
