@@ -449,9 +449,11 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
         if (nsplit < 1) nsplit = 1;
         if (nsplit > 64) nsplit = 64;
     }
-    // Up to 32 key tiles (2048 keys) the splits of a tile fit one thread-block cluster
-    // (8 CTAs, up to 4 tiles each) and merge through distributed shared memory.
-    const bool cluster = I == 1 && nsplit > 1 && (T + kTileKeys - 1) / kTileKeys <= 32;
+    // Up to 128 key tiles (8192 keys) the splits of a tile form one thread-block cluster
+    // (8 CTAs, up to 16 tiles each, walked with the double-buffered tile loop) and merge
+    // through distributed shared memory; beyond that, up to 64 independent splits and the
+    // global-memory merge.
+    const bool cluster = I == 1 && nsplit > 1 && (T + kTileKeys - 1) / kTileKeys <= 128;
     if (cluster && nsplit > 8) nsplit = 8;
     p.nsplit = nsplit;
     p.cluster = cluster ? 1 : 0;

@@ -42,6 +42,22 @@ def test_decode_attention(dev, ref, H, Hkv, D, T):
     assert rel_l2(got2, want) < TIGHT
 
 
+@pytest.mark.parametrize("H,Hkv,D,T,cap", [(8, 1, 128, 4100, 8192), (32, 4, 64, 9000, 9216), (8, 1, 64, 2184, 2200)])
+def test_decode_attention_long_context(dev, ref, H, Hkv, D, T, cap):
+    """Contexts past 2048 keys: cluster splits that walk several tiles (up to 8192 keys of capacity), and
+    the global-memory merge beyond; the capacity of the cache, not the position, picks the path when
+    the position lives on the device."""
+    from tensorlogic_b200.api import KVCache
+    q, k, v = _qkv(T + H, 1, T, H, Hkv, D)
+    cache = KVCache(dev, 1, Hkv, D, max_seq=cap)
+    cache.append(0, dev.tensor(k), dev.tensor(v))
+    want = ref.attention(q, k, v, 1.0 / np.sqrt(D), q_pos0=T - 1)
+    got = cache.attention(0, dev.tensor(q), H, q_pos0=T - 1).numpy()
+    assert rel_l2(got, want) < TIGHT
+    got2 = cache.attention(0, dev.tensor(q), H, positions=np.array([T - 1])).numpy()
+    assert rel_l2(got2, want) < TIGHT
+
+
 @pytest.mark.parametrize("H,Hkv,D", [(32, 4, 64), (8, 8, 64), (8, 1, 128)])
 @pytest.mark.parametrize("I,pos0", [(1, 0), (5, 0), (64, 0), (130, 0), (17, 40), (512, 0)])
 def test_prefill_attention_causal(dev, ref, H, Hkv, D, I, pos0):

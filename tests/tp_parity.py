@@ -58,7 +58,9 @@ def main() -> int:
             got = comm.all_reduce_residual(dev.tensor(part), dev.tensor(res)).numpy()
             got_sum = comm.all_reduce_residual(dev.tensor(part)).numpy()
             if phase == "nccl" or phase == "p2p-too-large":   # the library's own f16 summation order
-                ok &= bool(np.allclose(got_sum.astype(np.float32), acc, rtol=2e-3, atol=2e-3))
+                # f16 partial sums inside the library: a few f16 roundings of values up to ~world * 3
+                ok &= bool(np.allclose(got_sum.astype(np.float32), acc, rtol=1e-2, atol=8e-3 * world))
+                ok &= bool(np.allclose(got.astype(np.float32), acc + res.astype(np.float32), rtol=1e-2, atol=8e-3 * world))
             else:
                 ok &= bool(np.array_equal(got_sum.view(np.uint16), want_sum.view(np.uint16)))
                 ok &= bool(np.array_equal(got.view(np.uint16), (res + want_sum).view(np.uint16)))
@@ -106,8 +108,12 @@ def main() -> int:
     all_lg = [None] * world
     dist.all_gather_object(all_lg, (lg.tobytes(), int(got[0])))
     ok &= all(a == all_lg[0] for a in all_lg)
+    flags = [None] * world
+    dist.all_gather_object(flags, bool(ok))
     if rank == 0:
-        ok &= max(errs) < 1e-2
+        if not all(flags):
+            print(f"per-rank checks: {flags}", flush=True)
+        ok = all(flags) and max(errs) < 1e-2
         print(f"tp={world} rel-L2 of logits vs oracle: {['%.2e' % e for e in errs]}  {'PASS' if ok else 'FAIL'}",
               flush=True)
     flag = [bool(ok)]
