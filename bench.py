@@ -45,6 +45,9 @@ PROMPT_TOKENS = 512
 SEED = 2
 METRIC = "q4_0_decode_tokens_per_s"
 L2_BYTES = 126 * 1000 * 1000
+# DRAM bytes per GEMV launch of the N=1 workload, from one ncu capture of this command
+# (profiles/tinyllama_decode_launches.md): 586.92 MB read + ~0 written over the 89 launches of a step.
+NCU_GEMV_TRAFFIC_PER_LAUNCH = 586.92e6 / 89
 
 
 def load_peaks() -> dict:
@@ -327,7 +330,9 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q4_0> (fused dequant-GEMV, M=1)",
                      "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                      "frac": achieved / peak, "bytes_per_launch": bytes_per_launch, "us_per_launch": gemv_us,
-                     "launches_per_step": gemv_launches, "traffic": None},
+                     "launches_per_step": gemv_launches, "traffic": NCU_GEMV_TRAFFIC_PER_LAUNCH,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum over the 89 GEMV launches "
+                                       "of one decode step / 89 (profiles/tinyllama_decode_launches.md)"},
     }
     if base is not None:
         line["cpu_baseline"] = base
