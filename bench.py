@@ -515,8 +515,91 @@ def run_kernel(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args, rank: int, world: int, local: int) -> None:
+    """--workload prefill: BASELINE configs[3], Llama-2-7B-shape Q4_0 prefill of 2048 tokens.  The
+    per-layer linears run as the tcgen05 dequant-GEMM; with N > 1 GPUs (torchrun) the weights are
+    sharded column/row-parallel and the o / down partial sums are all-reduced (NCCL: 16 MB vectors).
+    A step is one whole prefill; value = prompt tokens per second, roofline = tensor FLOP/s of the
+    linears (2 * weights * tokens per step) against the measured bf16 peak."""
+    import torch
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.api import Device
+    from tensorlogic_b200.model import LLAMA2_7B, Llama, synthetic_model
+    arch, tokens = LLAMA2_7B, 2048
+    K, W = args.steps, max(args.warmup, 3)
+    dev = Device(local)
+    comm = None
+    if world > 1:
+        import torch.distributed as dist
+        from tensorlogic_b200.comm import Comm, unique_id
+        box = [unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, device=torch.device("cuda", local))
+        comm = Comm(dev, box[0], rank, world)
+    model = synthetic_model(dev, arch, SEED, tp_rank=rank if world > 1 else 0, tp_size=world, device_embeddings=True)
+    llm = Llama(dev, model, arch, max_seq=tokens + 8, max_batch=1, max_prefill=tokens, tp_rank=rank if world > 1 else 0,
+                tp_size=world)
+    if comm is not None:
+        llm.set_comm(comm)
+    ids = synth.token_ids(SEED, "prefill.prompt", tokens, arch.vocab)
+    stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local))
+
+    def barrier():
+        dev.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        llm.prefill(ids, return_logits=False)
+    barrier()
+    l0 = dev.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for _ in range(K):
+            llm.prefill(ids, return_logits=False)   # ids up, 2048-token forward, sampled token down
+        e1.record(stream)
+        barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank != 0:
+        return
+    peaks = load_peaks()
+    weights = sum(r * c for n, (r, c) in arch.tensor_shapes().items()
+                  if not n.endswith("norm.weight") and n not in ("token_embd.weight", "output.weight"))
+    flops = 2.0 * weights * tokens  # lm_head runs for the last row only
+    tflops = flops / (ms / K * 1e-3) / 1e12 / world
+    line = {
+        "metric": "q4_0_prefill_tokens_per_s", "value": tokens * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "llama-2-7b-shape q4_0 prefill, 2048 tokens, batch 1 (BASELINE configs[3])",
+                   "parallelism": "single" if world == 1 else f"tp{world}",
+                   "l2": "3.6 GB of weights per pass exceed the 126 MB L2", "seed": SEED},
+        "e2e": {"value": tokens * K / (wall_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": tokens * 4,
+                "d2h_bytes_per_step": 4, "ms_per_step": wall_ms / K},
+        "gpu_launches": int(dev.launch_count - l0),
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<Q4_0> (dequant-GEMM of the layer linears)",
+                     "achieved": tflops, "peak": peaks["bf16_tflops_sustained"], "peak_source": peaks["source"] +
+                     " (sustained: the kernel runs inside a long step)", "unit": "TFLOP/s",
+                     "frac": tflops / peaks["bf16_tflops_sustained"], "flops_per_step": flops, "traffic": None,
+                     "note": "whole-step time: attention, norms, SiLU.mul and all-reduces are inside it"},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: the headline workload (default); prefill: Llama-2-7B-shape 2048-token prefill")
     ap.add_argument("--kernel", default=None, choices=["linear"],
                     help="micro-benchmark one kernel instead of the decode workload (see run_kernel)")
     ap.add_argument("--qtype", default="q4_0", choices=["q4_0", "q8_0"])
@@ -543,7 +626,9 @@ def main() -> None:
     if world > 1:
         dist_setup(args.gpus)
     try:
-        if world > 1:
+        if args.workload == "prefill":
+            run_prefill(args, rank, world, local)
+        elif world > 1:
             run_tp(args, rank, world, local)
         else:
             run_ours(args, rank, world, local)

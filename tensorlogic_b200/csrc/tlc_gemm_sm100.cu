@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * BN, m0 = blockIdx.y * 128 * MT;
-    const int KT = p.k / kBK;
+    const int KT = (p.k + kBK - 1) / kBK;  // K is a multiple of 32: the last step may hold one block only
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
@@ -241,8 +241,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
 #pragma unroll
             for (int it = 0; it < 8 * MT; it++) {
                 const int row = it * 16 + (tid >> 3), c = tid & 7;
-                const bool ok = m0 + row < p.m;
-                const __half *src = p.x + (size_t)(ok ? m0 + row : 0) * p.k + (size_t)j * kBK + c * 8;
+                // rows past M and, in a last step of one block, columns past K are zero-filled
+                const bool ok = m0 + row < p.m && j * kBK + c * 8 < p.k;
+                const __half *src = p.x + (ok ? (size_t)(m0 + row) * p.k + (size_t)j * kBK + c * 8 : 0);
                 cp_async16(abase + row * 128 + ((c ^ (row & 7)) << 4), src, ok);
             }
         };
@@ -340,13 +341,22 @@ int32_t launch_tile(tlc_ctx *ctx, const GemmParams &p) {
 
 template <int QT>
 int32_t launch_one_t(tlc_ctx *ctx, const GemmParams &p) {
-    // The widest tile that still gives every SM a CTA: 256 x 256 halves the
-    // activation traffic from L2 per MMA against 128 x 128.
+    // Tile choice: 256 x 256 halves the activation traffic from L2 per MMA against 128 x 128
+    // (measured on wide weights: about 930 / 760 / 580 TFLOP/s for 256x256 / 128x256 / 128x128),
+    // but a tile shape only pays if its CTAs fill the SMs: score = relative tile speed x the
+    // fraction of SM slots the last wave leaves busy.
     auto ctas = [&](int mt, int nt) {
         return (long)((p.n + 128 * nt - 1) / (128 * nt)) * ((p.m + 128 * mt - 1) / (128 * mt));
     };
+    auto score = [&](int mt, int nt, double speed) {
+        const long c = ctas(mt, nt), sms = ctx->sm_count;
+        return speed * (double)c / (double)(((c + sms - 1) / sms) * sms);
+    };
     int tile = ctx->gemm_tile;  // 0: choose; 11 / 12 / 22: forced (tests)
-    if (tile == 0) tile = p.m > 128 && ctas(2, 2) >= ctx->sm_count ? 22 : ctas(1, 2) >= ctx->sm_count ? 12 : 11;
+    if (tile == 0) {
+        const double s22 = p.m > 128 ? score(2, 2, 1.0) : 0.0, s12 = score(1, 2, 0.8), s11 = score(1, 1, 0.6);
+        tile = s22 >= s12 && s22 >= s11 ? 22 : s12 >= s11 ? 12 : 11;
+    }
     if (tile == 22) return launch_tile<QT, 2, 2>(ctx, p);
     if (tile == 12) return launch_tile<QT, 1, 2>(ctx, p);
     return launch_tile<QT, 1, 1>(ctx, p);
@@ -367,7 +377,9 @@ size_t tlc_gemm_scratch_bytes(int m, int64_t k, int64_t n_swiglu) {
 bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a) {
     const tlc_qtensor *w0 = a.outs[0].w;
     if (w0->type != TLC_TYPE_Q4_0 && w0->type != TLC_TYPE_Q8_0) return false;
-    if (w0->n_cols % kBK != 0 || w0->n_cols < kBK) return false;
+    // K in whole blocks; an odd block count ends in a K step whose second block is the row's
+    // zero padding (rows are padded to 16 bytes with zeros at upload) against zero-filled activations
+    if (w0->n_cols % 32 != 0 || w0->n_cols < kBK) return false;
     if (ctx->gemm_min_m > 0) return a.m >= ctx->gemm_min_m;
     // Below 17 rows one GEMV pass reads the weights once.  Up to 48 rows the
     // GEMV's few passes still win unless the weight has enough 128-row tiles

@@ -141,6 +141,22 @@ __global__ void embedding_scalar_kernel(const __half *__restrict__ table, const 
     y[i] = table[(size_t)ids[r] * d + c];
 }
 
+// Eight elements per thread (16-byte accesses) for the large element-wise passes of a prefill.
+__global__ void swiglu_vec8_kernel(const uint4 *__restrict__ g, const uint4 *__restrict__ u, uint4 *__restrict__ y,
+                                   size_t n8) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const uint4 gv = g[i], uv = u[i];
+    const __half *gh = reinterpret_cast<const __half *>(&gv), *uh = reinterpret_cast<const __half *>(&uv);
+    __align__(16) __half o[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const __half s = __float2half_rn(1.0f / (1.0f + expf(-__half2float(gh[j]))));
+        o[j] = __hmul(__hmul(gh[j], s), uh[j]);
+    }
+    y[i] = *reinterpret_cast<const uint4 *>(o);
+}
+
 inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
 
 }  // namespace
@@ -199,7 +215,19 @@ extern "C" int32_t tlc_rope(tlc_ctx *ctx, const void *x_dev, void *y_dev, int32_
 TLC_ELEMENTWISE_1(tlc_sigmoid, sigmoid_kernel)
 TLC_ELEMENTWISE_2(tlc_mul, mul_kernel)
 TLC_ELEMENTWISE_2(tlc_add, add_kernel)
-TLC_ELEMENTWISE_2(tlc_swiglu, swiglu_kernel)
+extern "C" int32_t tlc_swiglu(tlc_ctx *ctx, const void *a_dev, const void *b_dev, void *y_dev, size_t n) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(a_dev && b_dev && y_dev, TLC_ERR_INVALID_OPERATION, "tlc_swiglu: null pointer");
+    if (n == 0) return TLC_OK;
+    if (n % 8 == 0 && (((uintptr_t)a_dev | (uintptr_t)b_dev | (uintptr_t)y_dev) & 15) == 0)
+        swiglu_vec8_kernel<<<blocks_for(n / 8, 256), 256, 0, ctx->stream>>>(
+            static_cast<const uint4 *>(a_dev), static_cast<const uint4 *>(b_dev), static_cast<uint4 *>(y_dev), n / 8);
+    else
+        swiglu_kernel<<<blocks_for(n, 256), 256, 0, ctx->stream>>>(
+            static_cast<const __half *>(a_dev), static_cast<const __half *>(b_dev), static_cast<__half *>(y_dev), n);
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
 
 extern "C" int32_t tlc_softmax(tlc_ctx *ctx, const void *x_dev, void *y_dev, int32_t rows, int32_t last_dim) {
     if (int32_t rc = tlc_enter(ctx)) return rc;

@@ -77,7 +77,8 @@ def test_edge_scales_through_gemm(dev, ref, golden, qtype):
 
 @pytest.mark.parametrize("qtype", [Q4, Q8])
 @pytest.mark.parametrize("n,k,m", [(128, 64, 128), (130, 128, 37), (2048, 2048, 128), (256, 5632, 100),
-                                   (4000, 2048, 17), (5632, 2048, 700), (96, 4096, 513)])
+                                   (4000, 2048, 17), (5632, 2048, 700), (96, 4096, 513),
+                                   (200, 96, 130), (64, 1376, 40)])
 def test_gemm_matches_oracle(dev, ref, qtype, n, k, m):
     from tensorlogic_b200.api import QTensor, linear
     raw = _weights(qtype, n, k, seed=12, name=f"g{n}x{k}")
@@ -147,7 +148,7 @@ def test_default_dispatch(dev, ref):
         x = _x(m, k, seed=14, name=f"d{m}")
         y = linear(dev.tensor(x), w).numpy()
         assert rel_l2(y, ref.linear_q(Q4, raw, n, k, x)) < TIGHT, m
-    # K not a multiple of 64 cannot use the GEMM tile and stays on the chunked GEMV
+    # an odd number of blocks (K = 96): the last K step of the GEMM holds one block and zero padding
     n, k, m = 64, 96, 80
     raw = _weights(Q4, n, k, seed=15)
     x = _x(m, k, seed=15)
