@@ -383,6 +383,183 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     }
 }
 
+// Prefill variant: one CTA owns 64 (query, head) rows that share a KV head -- the G
+// query heads of the group times 64/G query positions -- and walks the keys in tiles
+// of 64.  Each of the 4 warps takes 16 ROWS against the whole tile (the decode kernel
+// above gives each warp 16 KEYS of the tile instead): a K/V tile fetched from L2 now
+// serves 64 rows, a quarter of the traffic of the 16-row tiling, and a row's softmax
+// statistics stay inside one warp, so there is nothing to merge at the end.  Same
+// arithmetic: f16 roundings of the scores (einsum output, then the f16 multiply by the
+// scale) and of P, online softmax and O accumulation in f32.
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads) attention_prefill_kernel(const AttnParams p) {
+    constexpr int PITCH = D + 8;
+    constexpr int TILE = kTileKeys * PITCH;
+    constexpr int KSTEPS = D / 16;
+    constexpr int NDT = D / 8;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __half *ks = reinterpret_cast<__half *>(smem_raw);  // [2][TILE]
+    __half *vs = ks + 2 * TILE;                         // [2][TILE]
+
+    tlc_pdl_prologue();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int b = blockIdx.z, hk = blockIdx.y, qt = blockIdx.x;
+    const int G = p.G, RQ = 64 / G;
+    const int pos0 = p.q_pos0;
+    const int T = pos0 + p.I;
+    // rows of this warp: r_lo = 16*warp + g, r_hi = r_lo + 8; r -> (query qt*RQ + r/G, head hk*G + r%G)
+    const int r_lo = 16 * warp + g, r_hi = r_lo + 8;
+    const int qi_lo = qt * RQ + r_lo / G, qi_hi = qt * RQ + r_hi / G;
+    const int head_lo = hk * G + r_lo % G, head_hi = hk * G + r_hi % G;
+    const bool valid_lo = qi_lo < p.I, valid_hi = qi_hi < p.I;
+    const int rpos_lo = pos0 + qi_lo, rpos_hi = pos0 + qi_hi;
+    // last key any row of this warp may see (warp-uniform): rows 16*warp .. 16*warp+15
+    const int warp_last_q = min(p.I - 1, qt * RQ + (16 * warp + 15) / G);
+    const int warp_end = pos0 + warp_last_q + 1;
+    const int last_q = min(p.I, (qt + 1) * RQ) - 1;
+    const int k_end = min(T, pos0 + last_q + 1);
+    const int ntiles = (k_end + kTileKeys - 1) / kTileKeys;
+
+    uint32_t qa[KSTEPS][4];
+    {
+        const __half *q_lo = p.q + ((size_t)(b * p.I + (valid_lo ? qi_lo : 0)) * p.H + head_lo) * D;
+        const __half *q_hi = p.q + ((size_t)(b * p.I + (valid_hi ? qi_hi : 0)) * p.H + head_hi) * D;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; kk++) {
+            qa[kk][0] = valid_lo ? *reinterpret_cast<const uint32_t *>(q_lo + 16 * kk + 2 * t) : 0u;
+            qa[kk][1] = valid_hi ? *reinterpret_cast<const uint32_t *>(q_hi + 16 * kk + 2 * t) : 0u;
+            qa[kk][2] = valid_lo ? *reinterpret_cast<const uint32_t *>(q_lo + 16 * kk + 8 + 2 * t) : 0u;
+            qa[kk][3] = valid_hi ? *reinterpret_cast<const uint32_t *>(q_hi + 16 * kk + 8 + 2 * t) : 0u;
+        }
+    }
+    const __half *kbase = p.kc + ((size_t)b * p.Tmax * p.Hkv + hk) * D;
+    const __half *vbase = p.vc + ((size_t)b * p.Tmax * p.Hkv + hk) * D;
+    const size_t key_stride = (size_t)p.Hkv * D;
+    auto load_tile = [&](int tile, int stage) {
+        const int j0 = tile * kTileKeys;
+        constexpr int CHUNKS = kTileKeys * (D / 8);
+#pragma unroll
+        for (int c = tid; c < CHUNKS; c += kAttnThreads) {
+            const int key = c / (D / 8), part = c % (D / 8);
+            const bool ok = j0 + key < k_end;
+            const size_t off = (size_t)(ok ? j0 + key : 0) * key_stride + part * 8;
+            cp_async16(ks + stage * TILE + key * PITCH + part * 8, kbase + off, ok);
+            cp_async16(vs + stage * TILE + key * PITCH + part * 8, vbase + off, ok);
+        }
+        cp_async_commit();
+    };
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[NDT][4];
+#pragma unroll
+    for (int i = 0; i < NDT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const __half scale_h = __float2half_rn(p.scale);
+
+    if (ntiles > 0) load_tile(0, 0);
+    for (int tile = 0; tile < ntiles; tile++) {
+        const int stage = tile & 1;
+        if (tile + 1 < ntiles) {
+            load_tile(tile + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int j0 = tile * kTileKeys;
+        if (j0 < warp_end) {  // causal: tiles past this warp's last row are skipped
+            const __half *kt = ks + stage * TILE;
+            const __half *vt = vs + stage * TILE;
+            float s[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; kk++) {
+#pragma unroll
+                for (int np = 0; np < 4; np++) {  // two n8 tiles (16 keys) per ldmatrix.x4
+                    uint32_t r[4];
+                    const int mi = lane >> 3;
+                    ldsm_x4(r, kt + (16 * np + (mi >> 1) * 8 + (lane & 7)) * PITCH + 16 * kk + (mi & 1) * 8);
+                    mma16816(s[2 * np], qa[kk], r[0], r[1]);
+                    mma16816(s[2 * np + 1], qa[kk], r[2], r[3]);
+                }
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int key = j0 + nt * 8 + 2 * t + (e & 1);
+                    const int rpos = e < 2 ? rpos_lo : rpos_hi;
+                    float v = __half2float(__hmul(__float2half_rn(s[nt][e]), scale_h));
+                    if (key >= k_end || key > rpos) v = -INFINITY;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float corr[2], msafe[2];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_run[h], mx[h]);
+                msafe[h] = m_new == -INFINITY ? 0.f : m_new;
+                corr[h] = expf(m_run[h] - msafe[h]);
+                m_run[h] = m_new;
+            }
+            float psum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float pv = expf(s[nt][e] - msafe[e >> 1]);
+                    s[nt][e] = pv;
+                    psum[e >> 1] += pv;
+                }
+            l_run[0] = l_run[0] * corr[0] + psum[0];
+            l_run[1] = l_run[1] * corr[1] + psum[1];
+#pragma unroll
+            for (int i = 0; i < NDT; i++) {
+                o[i][0] *= corr[0];
+                o[i][1] *= corr[0];
+                o[i][2] *= corr[1];
+                o[i][3] *= corr[1];
+            }
+#pragma unroll
+            for (int kp = 0; kp < 4; kp++) {  // 16 keys of the tile per step
+                uint32_t pa[4];
+                pa[0] = pack_half2(s[2 * kp][0], s[2 * kp][1]);
+                pa[1] = pack_half2(s[2 * kp][2], s[2 * kp][3]);
+                pa[2] = pack_half2(s[2 * kp + 1][0], s[2 * kp + 1][1]);
+                pa[3] = pack_half2(s[2 * kp + 1][2], s[2 * kp + 1][3]);
+#pragma unroll
+                for (int jd = 0; jd < KSTEPS; jd++) {
+                    uint32_t r[4];
+                    const int mi = lane >> 3;
+                    ldsm_x4_trans(r, vt + (16 * kp + (mi & 1) * 8 + (lane & 7)) * PITCH + 16 * jd + (mi >> 1) * 8);
+                    mma16816(o[2 * jd], pa, r[0], r[1]);
+                    mma16816(o[2 * jd + 1], pa, r[2], r[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    const float inv_lo = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f, inv_hi = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
+    __half *out_lo = p.out + ((size_t)(b * p.I + (valid_lo ? qi_lo : 0)) * p.H + head_lo) * D;
+    __half *out_hi = p.out + ((size_t)(b * p.I + (valid_hi ? qi_hi : 0)) * p.H + head_hi) * D;
+#pragma unroll
+    for (int i = 0; i < NDT; i++) {
+        if (valid_lo)
+            *reinterpret_cast<__half2 *>(out_lo + 8 * i + 2 * t) = __floats2half2_rn(o[i][0] * inv_lo, o[i][1] * inv_lo);
+        if (valid_hi)
+            *reinterpret_cast<__half2 *>(out_hi + 8 * i + 2 * t) = __floats2half2_rn(o[i][2] * inv_hi, o[i][3] * inv_hi);
+    }
+}
+
 // cache.append for the unfused surface: rows of K/V [m, Hkv*D] go to position
 // pos(row) of sequence seq(row).
 __global__ void kv_append_kernel(const __half *__restrict__ k, const __half *__restrict__ v,
@@ -438,6 +615,38 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
     p.q_pos0 = q_pos0;
     p.positions = positions_dev;
     p.scale = scale;
+    if (I > 1) {
+        // Prefill: 64-row tiles, the warps split the rows (attention_prefill_kernel).
+        p.nsplit = 1;
+        const int RQ64 = 64 / G;
+        p.q_tiles = (I + RQ64 - 1) / RQ64;
+        const size_t smem_pf = (size_t)4 * kTileKeys * (D + 8) * sizeof(__half);
+        static bool configured_pf[2][64] = {};
+        const int dj = D == 64 ? 0 : 1;
+        if (!configured_pf[dj][ctx->device & 63]) {
+            if (D == 64) {
+                TLC_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)smem_pf));
+                TLC_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<64>,
+                                              cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            } else {
+                TLC_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)smem_pf));
+                TLC_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<128>,
+                                              cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            }
+            configured_pf[dj][ctx->device & 63] = true;
+        }
+        const dim3 grid_pf(p.q_tiles, Hkv, batch);
+        cudaError_t le = D == 64 ? tlc_launch_pdl(ctx, attention_prefill_kernel<64>, grid_pf, dim3(kAttnThreads), smem_pf, p)
+                                 : tlc_launch_pdl(ctx, attention_prefill_kernel<128>, grid_pf, dim3(kAttnThreads), smem_pf, p);
+        if (le != cudaSuccess) {
+            cudaGetLastError();
+            return tlc_fail(TLC_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(le));
+        }
+        TLC_CHECK_LAUNCH(ctx);
+        return TLC_OK;
+    }
     const int RQ = 16 / G;
     p.q_tiles = (I + RQ - 1) / RQ;
     // Decode: split the keys so that about two CTAs per SM are busy.
