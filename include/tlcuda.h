@@ -90,10 +90,18 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *                 tcgen05 GEMM (0 = decide from the shape);
  *   "gemm_tile"   0 = pick the GEMM tile from the shape; 11, 12, 22 force
  *                 128x128, 128x256 or 256x256 (activation rows x weight rows);
+ *   "wait_limit_ms" how long a device-side wait (mbarrier, peer flag) may last before the
+ *                 kernel gives up and the next tlc_synchronize returns TLC_ERR_TIMEOUT;
  *   "pdl"         programmatic dependent launch on (1) / off (0);
  *   "pdl_mode"    1 = let the successor start at once, 2 = after the last slab.
  * Unknown names fail with TLC_ERR_INVALID_OPERATION. */
 TLC_API int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value);
+/* Failure-detection self-test.  Enqueues a kernel whose device-side wait can never be
+ * satisfied -- kind 0: an mbarrier nothing arrives on (the wait of the GEMV / GEMM
+ * pipelines); kind 1: the peer flags of the all-reduce with no peer present.  The wait
+ * gives up after the "wait_limit_ms" option (default 2000), the kernel returns, and the
+ * next tlc_synchronize reports TLC_ERR_TIMEOUT once; the context stays usable. */
+TLC_API int32_t tlc_selftest_wait_timeout(tlc_ctx *ctx, int32_t kind);
 /* MetalDevice::name (metal_device.rs:89). */
 TLC_API int32_t tlc_device_name(tlc_ctx *ctx, char *buf, size_t buflen);
 /* recommended_max_working_set_size / current_allocated_size and the pre-load

@@ -60,6 +60,7 @@ PROTOTYPES = {
     "tlc_init": (i32, [i32, P(vp)]),
     "tlc_destroy": (i32, [vp]),
     "tlc_set_option": (i32, [vp, C.c_char_p, i64]),
+    "tlc_selftest_wait_timeout": (i32, [vp, i32]),
     "tlc_device_name": (i32, [vp, C.c_char_p, sz]),
     "tlc_mem_info": (i32, [vp, P(sz), P(sz)]),
     "tlc_sm_count": (i32, [vp, P(i32)]),

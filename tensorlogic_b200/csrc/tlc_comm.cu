@@ -94,7 +94,6 @@ constexpr int kP2pMaxWorld = 8;
 constexpr size_t kP2pFlagsOffset = 0;     // uint32 [world][kP2pChunks], written by peers
 constexpr size_t kP2pSeqOffset = 1024;    // uint32 [kP2pChunks], local
 constexpr size_t kP2pDataOffset = 4096;   // f16 [2][world][max_elems], written by peers
-constexpr uint32_t kP2pSpinLimit = 1u << 22;
 
 struct P2pParams {
     uint8_t *peer[kP2pMaxWorld];  // exchange blocks, peer[rank] is the local one
@@ -104,6 +103,7 @@ struct P2pParams {
     int rank, world;
     uint32_t n, max_elems;
     tlc_dev_status *status;
+    uint64_t wait_ns;  // how long the wait for the peers may last
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
@@ -144,13 +144,14 @@ __global__ void __launch_bounds__(256) allreduce_residual_kernel(const P2pParams
     if (tid < p.world && tid != p.rank) {
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(local + kP2pFlagsOffset) + tid * kP2pChunks + chunk;
         bool ok = false;
-        for (uint32_t it = 0; it < kP2pSpinLimit; it++) {
+        const uint64_t t0 = tlc_globaltimer_ns();
+        do {
             if ((int32_t)(ld_acquire_sys(flag) - s) >= 0) {
                 ok = true;
                 break;
             }
             __nanosleep(32);
-        }
+        } while (tlc_globaltimer_ns() - t0 < p.wait_ns);
         if (!ok) {
             timed_out = 1;
             if (atomicCAS(&p.status->code, 0, 3) == 0) p.status->where = 100 + tid;
@@ -380,6 +381,7 @@ extern "C" int32_t tlc_allreduce_residual_f16(tlc_ctx *ctx, tlc_comm *comm, void
         p.n = (uint32_t)count;
         p.max_elems = (uint32_t)comm->p2p_max_elems;
         p.status = ctx->dev_status;
+        p.wait_ns = ctx->wait_ns;
         cudaError_t le = tlc_launch_pdl(ctx, allreduce_residual_kernel, dim3(kP2pChunks), dim3(256), 0, p);
         if (le != cudaSuccess) {
             cudaGetLastError();
@@ -400,5 +402,42 @@ extern "C" int32_t tlc_allreduce_residual_f16(tlc_ctx *ctx, tlc_comm *comm, void
     } else if (out_dev != partial_dev) {
         TLC_CUDA(cudaMemcpyAsync(out_dev, partial_dev, count * 2, cudaMemcpyDeviceToDevice, ctx->stream));
     }
+    return TLC_OK;
+}
+
+// Failure-detection self-test (no second GPU, no communicator needed): the
+// all-reduce kernel runs as "rank 0 of 2" over two exchange blocks on this GPU;
+// nothing ever plays rank 1, so the wait for its flags runs out after the
+// context's limit, the status word is set and the kernel returns.
+int32_t tlc_selftest_peer_wait(tlc_ctx *ctx) {
+    const size_t n = 1024, bytes = kP2pDataOffset + (size_t)2 * 2 * n * sizeof(__half);
+    uint8_t *blk[2] = {nullptr, nullptr};
+    __half *vec = nullptr;
+    TLC_CUDA(cudaMalloc(&blk[0], bytes));
+    TLC_CUDA(cudaMalloc(&blk[1], bytes));
+    TLC_CUDA(cudaMalloc(&vec, 2 * n * sizeof(__half)));
+    TLC_CUDA(cudaMemsetAsync(blk[0], 0, bytes, ctx->stream));
+    TLC_CUDA(cudaMemsetAsync(blk[1], 0, bytes, ctx->stream));
+    TLC_CUDA(cudaMemsetAsync(vec, 0, 2 * n * sizeof(__half), ctx->stream));
+    P2pParams p{};
+    p.peer[0] = blk[0];
+    p.peer[1] = blk[1];
+    p.partial = vec;
+    p.residual = nullptr;
+    p.out = vec + n;
+    p.rank = 0;
+    p.world = 2;
+    p.n = (uint32_t)n;
+    p.max_elems = (uint32_t)n;
+    p.status = ctx->dev_status;
+    p.wait_ns = ctx->wait_ns;
+    allreduce_residual_kernel<<<kP2pChunks, 256, 0, ctx->stream>>>(p);
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(blk[0]);
+    cudaFree(blk[1]);
+    cudaFree(vec);
+    if (e != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "self-test launch failed: %s", cudaGetErrorString(e));
     return TLC_OK;
 }

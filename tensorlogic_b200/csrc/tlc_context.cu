@@ -86,7 +86,10 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
     const std::string n(name);
     if (n == "gemm_min_m")
         ctx->gemm_min_m = (int)value;
-    else if (n == "gemm_tile") {
+    else if (n == "wait_limit_ms") {
+        TLC_REQUIRE(value >= 1 && value <= 60000, TLC_ERR_INVALID_OPERATION, "set_option: wait_limit_ms must be 1..60000");
+        ctx->wait_ns = (uint64_t)value * 1000000ull;
+    } else if (n == "gemm_tile") {
         TLC_REQUIRE(value == 0 || value == 11 || value == 12 || value == 22, TLC_ERR_INVALID_OPERATION,
                     "set_option: gemm_tile must be 0, 11, 12 or 22");
         ctx->gemm_tile = (int)value;
@@ -97,6 +100,12 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
     else
         return tlc_fail(TLC_ERR_INVALID_OPERATION, "set_option: unknown option '%s'", name);
     return TLC_OK;
+}
+
+extern "C" int32_t tlc_selftest_wait_timeout(tlc_ctx *ctx, int32_t kind) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(kind == 0 || kind == 1, TLC_ERR_INVALID_OPERATION, "selftest_wait_timeout: kind %d (0 or 1)", kind);
+    return kind == 0 ? tlc_selftest_mbarrier_wait(ctx) : tlc_selftest_peer_wait(ctx);
 }
 
 extern "C" int32_t tlc_destroy(tlc_ctx *ctx) {

@@ -40,7 +40,6 @@ namespace tlc_gemm {
 
 constexpr int kBK = 64;  // K elements per stage (one 128-byte swizzle row)
 constexpr int kThreads = 416;
-constexpr uint32_t kWaitLimit = 1u << 22;
 
 struct GemmParams {
     const uint8_t *w;  // blocks, row-major [N, K/32]
@@ -59,6 +58,7 @@ struct GemmParams {
     float rope_base;
     int vec_ok;  // strides, N and pointers allow 16-byte stores
     tlc_dev_status *status;
+    uint64_t wait_ns;  // how long a wait may last before the kernel gives up
 };
 
 // Ring depth for a tile of 128*mt x 128*nt: stages of 16 KB per sub-tile.
@@ -84,11 +84,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          tlc_dev_status *status, int where) {
+                                          tlc_dev_status *status, int where, uint64_t wait_ns) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint32_t limit = *abort_flag ? 4096u : kWaitLimit;
-    for (uint32_t i = 0; i < limit; i++)
+    const uint64_t limit = *abort_flag ? 20000ull : wait_ns;
+    const uint64_t t0 = tlc_globaltimer_ns();
+    do {
         if (mbar_try_wait(bar, parity)) return true;
+    } while (tlc_globaltimer_ns() - t0 < limit);
     *abort_flag = 1;
     if (atomicCAS(&status->code, 0, 2) == 0) status->where = where;
     return false;

@@ -106,7 +106,7 @@ __device__ __forceinline__ void produce_b(const GemmParams &p, uint8_t *btiles, 
                 cur[i] = (wi & 3) == 0 ? v.x : (wi & 3) == 1 ? v.y : (wi & 3) == 2 ? v.z : v.w;
             }
             const int s = kt % STAGES;
-            mbar_wait(&empty[s], ((kt / STAGES) & 1u) ^ 1u, abort_flag, p.status, 11);
+            mbar_wait(&empty[s], ((kt / STAGES) & 1u) ^ 1u, abort_flag, p.status, 11, p.wait_ns);
             dequant_step<QT>(cur, btiles + (size_t)s * STAGE_BYTES, piece);
             fence_async_proxy();
             __syncwarp();
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
         // ------------------------------ A loaders ------------------------------
         auto issue = [&](int j) {
             const int s = j % kStages;
-            mbar_wait(&empty[s], ((j / kStages) & 1u) ^ 1u, abort_flag, p.status, 12);
+            mbar_wait(&empty[s], ((j / kStages) & 1u) ^ 1u, abort_flag, p.status, 12, p.wait_ns);
             const uint32_t abase = smem_u32(tiles + (size_t)s * STAGE_BYTES);
             // 8 consecutive threads copy the 128 bytes of one row.
 #pragma unroll
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
         // ------------------------------ MMA issuer ------------------------------
         for (int kt = 0; kt < KT; kt++) {
             const int s = kt % kStages;
-            const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (kt / kStages) & 1u, abort_flag, p.status, 14));
+            const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (kt / kStages) & 1u, abort_flag, p.status, 14, p.wait_ns));
             tc_fence_after();
             if (lane == 0 && ready) {
                 const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
     // Warp w reads tensor-memory lanes 32*(w%4) .. +31 (= activation rows of a
     // sub-tile); the three warps of a lane quarter take the 32-column pieces in turn.
     if (warp < MMA_WARP) {
-        mbar_wait(accum_bar, 0, abort_flag, p.status, 13);
+        mbar_wait(accum_bar, 0, abort_flag, p.status, 13, p.wait_ns);
         tc_fence_after();
         const int wq = warp & 3;
         constexpr int PIECES = MT * BN / 32;
@@ -418,6 +418,7 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.n = (int)w->n_rows;
         p.k = (int)k;
         p.status = ctx->dev_status;
+        p.wait_ns = ctx->wait_ns;
         if (swiglu) {
             p.y = reinterpret_cast<__half *>(scratch + norm_bytes + (size_t)i * gu_bytes);
             p.row_stride = p.n;

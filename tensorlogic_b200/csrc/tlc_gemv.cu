@@ -228,6 +228,29 @@ size_t gemv_fixed_smem(int nblk_pad, int m, int nt) { return fixed_smem_bytes(nb
 
 }  // namespace
 
+// Failure-detection self-test: a CTA waits on an mbarrier that nothing ever
+// completes, through the same bounded wait the GEMV uses.  The wait runs out
+// after the context's limit, the status word is set and the kernel returns.
+namespace {
+__global__ void selftest_mbarrier_wait_kernel(tlc_dev_status *status, uint64_t wait_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    mbar_wait(&bar, 0, &abort_flag, status, 99, wait_ns);
+}
+}  // namespace
+
+int32_t tlc_selftest_mbarrier_wait(tlc_ctx *ctx) {
+    selftest_mbarrier_wait_kernel<<<1, 32, 0, ctx->stream>>>(ctx->dev_status, ctx->wait_ns);
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
+
 // Largest number of activation rows one launch can take for this K.
 static int gemv_max_m(tlc_ctx *ctx, int type, int k) {
     const int nblk_pad = ((k / 32) + 1) & ~1;
@@ -352,6 +375,7 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.rope_base = (float)a.rope_base;
         p.positions = a.positions ? a.positions + m0 : nullptr;
         p.status = ctx->dev_status;
+        p.wait_ns = ctx->wait_ns;
         const int nt = mc > 8 ? 2 : 1;
         int32_t rc;
         if (type == TLC_TYPE_Q4_0)

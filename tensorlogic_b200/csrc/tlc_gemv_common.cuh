@@ -14,7 +14,6 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 8;
-constexpr uint32_t kWaitLimit = 1u << 22;
 
 template <int QT> struct QTraits;
 template <> struct QTraits<TLC_TYPE_Q4_0> {
@@ -73,6 +72,7 @@ struct GemvParams {
     int contig;    // 1: each CTA takes a contiguous range of units, 0: units blockIdx.x, + gridDim.x, ...
     int pdl_mode;  // 1: let the next kernel be scheduled at once, 2: only when this CTA's last slab is done
     tlc_dev_status *status;
+    uint64_t wait_ns;  // how long a wait may last before the kernel gives up
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -99,17 +99,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after kWaitLimit polls, records where, and raises the
+// Bounded wait: gives up after wait_ns nanoseconds, records where, and raises the
 // CTA's abort flag; once that flag is up every later wait only polls briefly
 // (long enough for copies already in flight to land) so the kernel drains and
 // returns instead of hanging.  The result is made warp-uniform by the callers.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          tlc_dev_status *status, int where) {
+                                          tlc_dev_status *status, int where, uint64_t wait_ns) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint32_t limit = *abort_flag ? 4096u : kWaitLimit;
-    for (uint32_t i = 0; i < limit; i++) {
+    const uint64_t limit = *abort_flag ? 20000ull : wait_ns;
+    const uint64_t t0 = tlc_globaltimer_ns();
+    do {
         if (mbar_try_wait(bar, parity)) return true;
-    }
+    } while (tlc_globaltimer_ns() - t0 < limit);
     *abort_flag = 1;
     if (atomicCAS(&status->code, 0, 1) == 0) status->where = where;
     return false;

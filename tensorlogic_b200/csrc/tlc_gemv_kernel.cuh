@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                     const uint32_t par = ((it / S) & 1u) ^ 1u;
                     // On a timeout the producer stops issuing copies; the consumers'
                     // own bounded waits then end the CTA.
-                    if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], par, abort_flag, p.status, 1))) return;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], par, abort_flag, p.status, 1, p.wait_ns))) return;
                     const int kcb = min(T::KCB, p.nblk - c * T::KCB);
                     const uint32_t bytes_row = (uint32_t)((kcb * T::BB + 15) & ~15);
                     if (lane == 0) mbar_expect_tx(&full[s], bytes_row * (uint32_t)rows_valid);
@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                 const uint32_t par = (it / S) & 1u;
                 // A wait that ran out skips the math but keeps the barrier protocol
                 // going, so every warp still reaches the same bar.sync calls.
-                const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], par, abort_flag, p.status, 2));
+                const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], par, abort_flag, p.status, 2, p.wait_ns));
                 const int kcb = min(T::KCB, p.nblk - c * T::KCB);
                 const int npairs = ready ? (kcb + 1) >> 1 : 0;
                 const uint32_t row_lo = stages_addr + (uint32_t)s * STAGE_BYTES + seg_lo;

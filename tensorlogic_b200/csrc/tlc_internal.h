@@ -52,6 +52,9 @@ struct tlc_ctx {
     // TLC_GEMM_MIN_M: activation rows from which quantized linears run as the
     // tensor-core GEMM (0: decide from the shape; a huge value keeps the GEMV).
     int gemm_min_m = 0;
+    // How long a device-side wait (mbarrier, peer flag) may last before the kernel gives up,
+    // sets the status word and drains; option "wait_limit_ms".
+    uint64_t wait_ns = 2000000000ull;
     int gemm_tile = 0;  // 0: pick the GEMM tile from the shape; 11, 12, 22: force 128x128, 128x256, 256x256
 };
 
@@ -108,6 +111,9 @@ static inline size_t tlc_block_bytes(int32_t type) {
 
 // A dense F16 copy of a quantized tensor (device-side dequantization).
 int32_t tlc_qtensor_to_f16(tlc_ctx *ctx, tlc_qtensor *qt, tlc_qtensor **out);
+// Failure-detection self-tests: launch a kernel whose bounded wait must run out.
+int32_t tlc_selftest_mbarrier_wait(tlc_ctx *ctx);
+int32_t tlc_selftest_peer_wait(tlc_ctx *ctx);
 // Makes the context's device current; every entry point calls it first.
 int32_t tlc_enter(tlc_ctx *ctx);
 // Ensures ctx->scratch holds at least `bytes`.
@@ -134,6 +140,11 @@ inline cudaError_t tlc_launch_pdl(tlc_ctx *ctx, void (*kernel)(KArgs...), dim3 g
 }
 
 #ifdef __CUDACC__
+__device__ __forceinline__ uint64_t tlc_globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 // Device side of the above: let the successor be scheduled, then wait for the
 // predecessor's results.  Both are no-ops for a kernel launched the plain way.
 __device__ __forceinline__ void tlc_pdl_prologue() {

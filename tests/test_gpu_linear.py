@@ -283,3 +283,25 @@ def test_pool_reuse_and_stats(dev):
     del big, t2
     dev.pool_trim(0)
     assert dev.pool_stats()["total_pooled"] == 0
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_bounded_wait_reports_timeout_and_context_survives(dev, ref, kind):
+    """Failure detection without a fault: a device-side wait that nothing satisfies (an mbarrier of the
+    GEMV pipeline; the peer flags of the all-reduce) runs out, the kernel returns, synchronize reports it
+    once, and the next launch on the same context works."""
+    from tensorlogic_b200 import _lib
+    from tensorlogic_b200.api import QTensor, TensorError, check, linear
+    dev.set_option("wait_limit_ms", 40)
+    try:
+        check(dev.lib.tlc_selftest_wait_timeout(dev.handle, kind))
+        with pytest.raises(TensorError) as e:
+            dev.synchronize()
+        assert e.value.code == _lib.ERR_TIMEOUT
+        dev.synchronize()                      # reported once, then clear
+    finally:
+        dev.set_option("wait_limit_ms", 2000)
+    raw = _weights(Q4, 64, 256, seed=31)
+    x = _x(2, 256, seed=31)
+    y = linear(dev.tensor(x), QTensor.from_blocks(dev, Q4, 64, 256, raw)).numpy()
+    assert rel_l2(y, ref.linear_q(Q4, raw, 64, 256, x)) < TIGHT
