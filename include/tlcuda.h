@@ -338,6 +338,21 @@ TLC_API int32_t tlc_attention_decode_static(void *stream, const void *q_dev, con
  * output: rows; attn_output/ffn_down: columns). */
 TLC_API int32_t tlc_model_load_gguf(tlc_ctx *ctx, const char *path, int32_t tp_rank,
                                     int32_t tp_size, tlc_model **out);
+/* Lazy weight cache: GGUFWeightCache (src/model/gguf_weight_cache.rs:45-262, :418-441;
+ * builtins load_weight_cache_gguf_f16 / _f32 and get_weight, builtin_model.rs:330-414).
+ * Opens the file and reads its tensor table; tlc_weight_cache_get uploads a tensor on
+ * first use and keeps at most `capacity` tensors, least recently used evicted first.
+ * Cached tensors keep their GGUF quantization; a tensor returned by _get belongs to
+ * the cache and stays valid until it is evicted, or the cache is cleared or closed.
+ * Unknown names fail with TLC_ERR_LOAD "Weight not found: <name>". */
+typedef struct tlc_weight_cache tlc_weight_cache;
+TLC_API int32_t tlc_weight_cache_open(tlc_ctx *ctx, const char *path, int64_t capacity, tlc_weight_cache **out);
+TLC_API int32_t tlc_weight_cache_close(tlc_weight_cache *cache);
+TLC_API int32_t tlc_weight_cache_get(tlc_weight_cache *cache, const char *name, tlc_qtensor **out);
+TLC_API int32_t tlc_weight_cache_contains(tlc_weight_cache *cache, const char *name);
+TLC_API int32_t tlc_weight_cache_clear(tlc_weight_cache *cache);
+TLC_API int32_t tlc_weight_cache_stats(tlc_weight_cache *cache, int64_t *len, int64_t *capacity, uint64_t *hits,
+                                       uint64_t *misses, uint64_t *evictions);
 /* MmapGGUFLoader::new (src/model/formats/mmap_gguf.rs:120, header walk
  * :187-275): parses header, metadata and tensor table only -- no device needed.
  * Per tensor: reversed [rows, cols], GGUF type id, absolute file offset and

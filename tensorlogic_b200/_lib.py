@@ -133,6 +133,12 @@ PROTOTYPES = {
     "tlc_llama_set_sampling": (i32, [vp, f32, u64]),
     "tlc_sample_uniform_host": (f32, [u64, u32, u32]),
     "tlc_temperature_sample": (i32, [vp, vp, i32, i32, f32, P(f32), P(i32)]),
+    "tlc_weight_cache_open": (i32, [vp, C.c_char_p, i64, P(vp)]),
+    "tlc_weight_cache_close": (i32, [vp]),
+    "tlc_weight_cache_get": (i32, [vp, C.c_char_p, P(vp)]),
+    "tlc_weight_cache_contains": (i32, [vp, C.c_char_p]),
+    "tlc_weight_cache_clear": (i32, [vp]),
+    "tlc_weight_cache_stats": (i32, [vp, P(i64), P(i64), P(u64), P(u64), P(u64)]),
     "tlc_comm_unique_id": (i32, [vp]),
     "tlc_comm_init": (i32, [vp, vp, i32, i32, P(vp)]),
     "tlc_comm_destroy": (i32, [vp]),

@@ -42,7 +42,8 @@ constexpr int kBK = 64;  // K elements per stage (one 128-byte swizzle row)
 constexpr int kThreads = 416;
 
 struct GemmParams {
-    const uint8_t *w;  // blocks, row-major [N, K/32]
+    const uint8_t *w;   // blocks, row-major [N, K/32]
+    const uint8_t *w2;  // second weight of the SiLU.mul pair (same shape and pitch) or null
     size_t w_pitch;
     const __half *x;         // [M, K]
     __half *y;               // [M, N]

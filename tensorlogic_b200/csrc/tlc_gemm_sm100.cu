@@ -68,13 +68,15 @@ __device__ __forceinline__ void dequant_step(const uint32_t *cur, uint8_t *bt, c
 // spread over a group's worth of K steps.
 template <int QT, int STAGES, int STAGE_BYTES>
 __device__ __forceinline__ void produce_b(const GemmParams &p, uint8_t *btiles, uint64_t *full, uint64_t *empty,
-                                          volatile int *abort_flag, int n0, int row, int KT, int lane) {
+                                          volatile int *abort_flag, const uint8_t *wbase, int wrow, int row, int KT,
+                                          int lane) {
     constexpr int BB = QT == TLC_TYPE_Q4_0 ? 18 : 34;
     constexpr int RAW_WORDS = 2 * BB / 4;           // 32-bit words of the two blocks of one K step
     constexpr int SPG = QT == TLC_TYPE_Q4_0 ? 4 : 2;  // K steps per group
     constexpr int GV4 = 9;                           // 16-byte pieces per group
-    const bool row_ok = n0 + row < p.n;
-    const uint4 *wrow4 = reinterpret_cast<const uint4 *>(p.w + (size_t)(n0 + (row_ok ? row : 0)) * p.w_pitch);
+    // `row`: row of the tile this thread fills; `wrow`: the weight row it holds (of `wbase`)
+    const bool row_ok = wrow < p.n;
+    const uint4 *wrow4 = reinterpret_cast<const uint4 *>(wbase + (size_t)(row_ok ? wrow : 0) * p.w_pitch);
     // Rows past N load nothing: a zero scale makes every value of the tile row zero.
     const int limit_v4 = row_ok ? (int)(p.w_pitch >> 4) : 0;
     uint4 nxt4[GV4], cur4[GV4];
@@ -186,8 +188,12 @@ __device__ __forceinline__ void epilogue_piece(const GemmParams &p, const uint32
     }
 }
 
-template <int QT, int MT, int NT>
+// SW: the SiLU.mul pair.  The weight tile holds 128 rows of the gate weight (tile rows
+// 0-127) and the same 128 rows of the up weight (tile rows 128-255); the epilogue reads
+// both accumulators and stores silu(gate) * up for the 128 output columns of the CTA.
+template <int QT, int MT, int NT, bool SW>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmParams p) {
+    static_assert(!SW || NT == 2, "the gate/up pair fills a 256-row weight tile");
     constexpr int BN = 128 * NT;
     constexpr int A_BYTES = 128 * MT * 128, B_BYTES = BN * 128;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -205,7 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * 128 * MT;
+    const int n0 = blockIdx.x * (SW ? 128 : BN), m0 = blockIdx.y * 128 * MT;
     const int KT = (p.k + kBK - 1) / kBK;  // K is a multiple of 32: the last step may hold one block only
 
     if (tid == 0) {
@@ -230,7 +236,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
     tlc_pdl_prologue();  // x (and residual) come from the previous kernel of the stream
 
     if (warp >= 4 && warp < 4 + 4 * NT) {
-        produce_b<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, n0, tid - 128, KT, lane);
+        const int trow = tid - 128;  // row of the weight tile
+        const uint8_t *wbase = SW && trow >= 128 ? p.w2 : p.w;
+        const int wrow = SW ? n0 + (trow & 127) : n0 + trow;
+        produce_b<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, wbase, wrow, trow, KT, lane);
     } else if (warp < 4) {
         // ------------------------------ A loaders ------------------------------
         auto issue = [&](int j) {
@@ -295,10 +304,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
         mbar_wait(accum_bar, 0, abort_flag, p.status, 13, p.wait_ns);
         tc_fence_after();
         const int wq = warp & 3;
-        constexpr int PIECES = MT * BN / 32;
+        constexpr int OUT_COLS = SW ? 128 : BN;  // output columns of the CTA
+        constexpr int PIECES = MT * OUT_COLS / 32;
 #pragma unroll 1
         for (int pc = warp >> 2; pc < PIECES; pc += 3) {
-            const int i = pc / (BN / 32), c0 = (pc % (BN / 32)) * 32;
+            const int i = pc / (OUT_COLS / 32), c0 = (pc % (OUT_COLS / 32)) * 32;
             const int row = m0 + 128 * i + 32 * wq + lane;
             const bool row_ok = row < p.m;
             const int pos = !row_ok ? 0 : p.positions ? p.positions[row] : p.pos_offset + row;
@@ -306,7 +316,34 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
             __half *ybase = p.y + (size_t)((long long)row * p.row_stride + (long long)pos * p.pos_stride);
             uint32_t r[32];
             tmem_ld32(tmem_base + ((uint32_t)(32 * wq) << 16) + (uint32_t)(BN * i + c0), r);
-            if (row_ok && n0 + c0 < p.n) epilogue_piece(p, r, row, pos, n0 + c0, ybase);
+            if (SW) {
+                // s = sigmoid(g) (f32, RNE); a = g*s; act = a*u: three f16 roundings as in
+                // debug/chat_demo_with_kvcache.tl:26-41 (the GEMV's SiLU.mul epilogue does the same)
+                uint32_t ru[32];
+                tmem_ld32(tmem_base + ((uint32_t)(32 * wq) << 16) + (uint32_t)(BN * i + 128 + c0), ru);
+                if (row_ok && n0 + c0 < p.n) {
+                    __align__(16) __half h[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        const __half gate = __float2half_rn(__uint_as_float(r[e]));
+                        const __half up = __float2half_rn(__uint_as_float(ru[e]));
+                        const __half sg = __float2half_rn(1.0f / (1.0f + expf(-__half2float(gate))));
+                        h[e] = __hmul(__hmul(gate, sg), up);
+                    }
+                    const int nb = n0 + c0;
+                    if (nb + 32 <= p.n && p.vec_ok) {
+#pragma unroll
+                        for (int v = 0; v < 4; v++)
+                            *reinterpret_cast<uint4 *>(ybase + nb + 8 * v) = *reinterpret_cast<const uint4 *>(h + 8 * v);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; e++)
+                            if (nb + e < p.n) ybase[nb + e] = h[e];
+                    }
+                }
+            } else if (row_ok && n0 + c0 < p.n) {
+                epilogue_piece(p, r, row, pos, n0 + c0, ybase);
+            }
         }
         tc_fence_before();
     }
@@ -318,19 +355,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
     }
 }
 
-template <int QT, int MT, int NT>
+template <int QT, int MT, int NT, bool SW = false>
 int32_t launch_tile(tlc_ctx *ctx, const GemmParams &p) {
     const size_t smem = smem_bytes(MT, NT);
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem));
-        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT, SW>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 63] = true;
     }
-    const dim3 grid((unsigned)((p.n + 128 * NT - 1) / (128 * NT)), (unsigned)((p.m + 128 * MT - 1) / (128 * MT)));
-    cudaError_t le = tlc_launch_pdl(ctx, gemm_tcgen05_kernel<QT, MT, NT>, grid, dim3(kThreads), smem, p);
+    const int out_cols = SW ? 128 : 128 * NT;  // output columns per CTA
+    const dim3 grid((unsigned)((p.n + out_cols - 1) / out_cols), (unsigned)((p.m + 128 * MT - 1) / (128 * MT)));
+    cudaError_t le = tlc_launch_pdl(ctx, gemm_tcgen05_kernel<QT, MT, NT, SW>, grid, dim3(kThreads), smem, p);
     if (le != cudaSuccess) {
         cudaGetLastError();
         return tlc_fail(TLC_ERR_CUDA, "gemm launch failed: %s", cudaGetErrorString(le));
@@ -362,7 +400,20 @@ int32_t launch_one_t(tlc_ctx *ctx, const GemmParams &p) {
     return launch_tile<QT, 1, 1>(ctx, p);
 }
 
+// The gate/up pair: 128 output columns per CTA (a 256-row weight tile), one or two token sub-tiles.
+template <int QT>
+int32_t launch_pair_t(tlc_ctx *ctx, const GemmParams &p) {
+    auto ctas = [&](int mt) { return (long)((p.n + 127) / 128) * ((p.m + 128 * mt - 1) / (128 * mt)); };
+    auto score = [&](int mt, double speed) {
+        const long c = ctas(mt), sms = ctx->sm_count;
+        return speed * (double)c / (double)(((c + sms - 1) / sms) * sms);
+    };
+    const bool two = ctx->gemm_tile == 22 || (ctx->gemm_tile == 0 && p.m > 128 && score(2, 1.0) >= score(1, 0.8));
+    return two ? launch_tile<QT, 2, 2, true>(ctx, p) : launch_tile<QT, 1, 2, true>(ctx, p);
+}
+
 int32_t launch_one(tlc_ctx *ctx, const GemmParams &p, int type) {
+    if (p.w2) return type == TLC_TYPE_Q4_0 ? launch_pair_t<TLC_TYPE_Q4_0>(ctx, p) : launch_pair_t<TLC_TYPE_Q8_0>(ctx, p);
     return type == TLC_TYPE_Q4_0 ? launch_one_t<TLC_TYPE_Q4_0>(ctx, p) : launch_one_t<TLC_TYPE_Q8_0>(ctx, p);
 }
 
@@ -371,7 +422,8 @@ inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 }  // namespace
 
 size_t tlc_gemm_scratch_bytes(int m, int64_t k, int64_t n_swiglu) {
-    return align256((size_t)m * k * 2) + 2 * align256((size_t)m * n_swiglu * 2);
+    (void)n_swiglu;  // the SiLU.mul pair is fused into the GEMM epilogue and needs no scratch
+    return align256((size_t)m * k * 2);
 }
 
 bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a) {
@@ -391,16 +443,15 @@ bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a) {
 
 // Same contract as tlc_launch_gemv for m activation rows on the tensor cores:
 // the RMSNorm prologue runs as its own kernel into scratch, every output of a
-// fused multi-projection is its own GEMM, and the SiLU.mul pair is two GEMMs
-// into scratch plus the element-wise kernel.
+// fused multi-projection is its own GEMM, and the SiLU.mul pair is one GEMM whose
+// weight tile holds gate and up rows side by side.
 int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
     const tlc_qtensor *w0 = a.outs[0].w;
     const int64_t k = w0->n_cols;
     const bool swiglu = a.epilogue == TLC_EPI_SWIGLU;
     const size_t norm_bytes = a.norm_w ? align256((size_t)a.m * k * 2) : 0;
-    const size_t gu_bytes = swiglu ? align256((size_t)a.m * w0->n_rows * 2) : 0;
-    if (norm_bytes + 2 * gu_bytes > 0)
-        if (int32_t rc = tlc_scratch_reserve(ctx, norm_bytes + 2 * gu_bytes)) return rc;
+    if (norm_bytes > 0)
+        if (int32_t rc = tlc_scratch_reserve(ctx, norm_bytes)) return rc;
     uint8_t *scratch = static_cast<uint8_t *>(ctx->scratch);
     const __half *x = static_cast<const __half *>(a.x);
     if (a.norm_w) {
@@ -408,7 +459,9 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
         x = reinterpret_cast<const __half *>(scratch);
     }
     TLC_REQUIRE(((uintptr_t)x & 15) == 0, TLC_ERR_INVALID_OPERATION, "gemm: activations must be 16-byte aligned");
-    for (int i = 0; i < a.n_out; i++) {
+    // The SiLU.mul pair is ONE launch: gate and up rows share the weight tile of a CTA.
+    const int n_launch = swiglu ? 1 : a.n_out;
+    for (int i = 0; i < n_launch; i++) {
         const tlc_qtensor *w = a.outs[i].w;
         GemmParams p{};
         p.w = static_cast<const uint8_t *>(w->data);
@@ -419,11 +472,13 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.k = (int)k;
         p.status = ctx->dev_status;
         p.wait_ns = ctx->wait_ns;
+        p.y = static_cast<__half *>(a.outs[i].y);
         if (swiglu) {
-            p.y = reinterpret_cast<__half *>(scratch + norm_bytes + (size_t)i * gu_bytes);
+            TLC_REQUIRE(a.outs[1].w->row_pitch == w->row_pitch, TLC_ERR_SHAPE_MISMATCH,
+                        "gate and up projections must have the same layout");
+            p.w2 = static_cast<const uint8_t *>(a.outs[1].w->data);
             p.row_stride = p.n;
         } else {
-            p.y = static_cast<__half *>(a.outs[i].y);
             p.row_stride = a.outs[i].row_stride >= 0 ? a.outs[i].row_stride : (long long)w->n_rows;
             p.pos_stride = a.outs[i].pos_stride;
             p.head_dim = a.outs[i].rope_heads > 0 ? (int)(w->n_rows / a.outs[i].rope_heads) : 0;
@@ -436,10 +491,6 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.vec_ok = ((p.row_stride | p.pos_stride | (long long)p.n) & 7) == 0 && ((uintptr_t)p.y & 15) == 0 &&
                    ((uintptr_t)p.residual & 15) == 0;
         if (int32_t rc = launch_one(ctx, p, w->type)) return rc;
-    }
-    if (swiglu) {
-        const size_t n = (size_t)a.m * w0->n_rows;
-        return tlc_swiglu(ctx, scratch + norm_bytes, scratch + norm_bytes + gu_bytes, a.outs[0].y, n);
     }
     return TLC_OK;
 }

@@ -402,3 +402,119 @@ extern "C" int32_t tlc_model_load_gguf(tlc_ctx *ctx, const char *path, int32_t t
     *out = model.release();
     return TLC_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Lazy weight cache: GGUFWeightCache (src/model/gguf_weight_cache.rs:45-262,
+// :418-441; builtins load_weight_cache_gguf_f16/_f32 and get_weight,
+// src/interpreter/builtin_model.rs:330-414).  The file's tensor table is read
+// once; a tensor is read from the file and uploaded on its first get_weight and
+// then kept under an LRU policy with a capacity counted in tensors, as upstream.
+// Unlike upstream the cached tensors stay quantized (Q4_0 / Q8_0 blocks) in
+// device memory, and an evicted tensor is freed once the caller's work on the
+// stream has been waited for.
+// ---------------------------------------------------------------------------
+#include <list>
+
+struct tlc_weight_cache {
+    tlc_ctx *ctx;
+    tlc_gguf file;
+    size_t capacity;
+    std::list<std::string> lru;  // most recently used first
+    std::map<std::string, std::pair<tlc_qtensor *, std::list<std::string>::iterator>> entries;
+    uint64_t hits = 0, misses = 0, evictions = 0;
+};
+
+extern "C" int32_t tlc_weight_cache_open(tlc_ctx *ctx, const char *path, int64_t capacity, tlc_weight_cache **out) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(path && out, TLC_ERR_INVALID_OPERATION, "weight_cache_open: null pointer");
+    *out = nullptr;
+    // LruCache::new(NonZeroUsize::new(capacity).unwrap()) panics on 0 upstream
+    TLC_REQUIRE(capacity >= 1, TLC_ERR_INVALID_OPERATION, "cache capacity must be at least 1 (got %lld)",
+                (long long)capacity);
+    std::unique_ptr<tlc_weight_cache> c(new tlc_weight_cache());
+    c->ctx = ctx;
+    c->capacity = (size_t)capacity;
+    if (int32_t rc = parse_gguf(path, &c->file)) return rc;
+    *out = c.release();
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_weight_cache_clear(tlc_weight_cache *c) {
+    if (!c) return TLC_OK;
+    cudaSetDevice(c->ctx->device);
+    cudaStreamSynchronize(c->ctx->stream);  // kernels may still read the cached weights
+    for (auto &e : c->entries) tlc_qtensor_destroy(e.second.first);
+    c->entries.clear();
+    c->lru.clear();
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_weight_cache_close(tlc_weight_cache *c) {
+    if (!c) return TLC_OK;
+    tlc_weight_cache_clear(c);
+    delete c;
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_weight_cache_contains(tlc_weight_cache *c, const char *name) {
+    if (!c || !name) return 0;
+    for (const auto &t : c->file.tensors)
+        if (t.name == name) return 1;
+    return 0;
+}
+
+// cache_stats(): (tensors held, capacity); plus hit / miss / eviction counters.
+extern "C" int32_t tlc_weight_cache_stats(tlc_weight_cache *c, int64_t *len, int64_t *capacity, uint64_t *hits,
+                                          uint64_t *misses, uint64_t *evictions) {
+    TLC_REQUIRE(c, TLC_ERR_INVALID_OPERATION, "weight_cache_stats: null pointer");
+    if (len) *len = (int64_t)c->entries.size();
+    if (capacity) *capacity = (int64_t)c->capacity;
+    if (hits) *hits = c->hits;
+    if (misses) *misses = c->misses;
+    if (evictions) *evictions = c->evictions;
+    return TLC_OK;
+}
+
+// get_weight(name): the tensor stays owned by the cache and valid until it is
+// evicted (capacity further get_weight calls for other names) or the cache is
+// cleared / closed.
+extern "C" int32_t tlc_weight_cache_get(tlc_weight_cache *c, const char *name, tlc_qtensor **out) {
+    TLC_REQUIRE(c && name && out, TLC_ERR_INVALID_OPERATION, "weight_cache_get: null pointer");
+    if (int32_t rc = tlc_enter(c->ctx)) return rc;
+    *out = nullptr;
+    auto hit = c->entries.find(name);
+    if (hit != c->entries.end()) {
+        c->hits++;
+        c->lru.splice(c->lru.begin(), c->lru, hit->second.second);
+        *out = hit->second.first;
+        return TLC_OK;
+    }
+    const GGUFTensor *t = nullptr;
+    for (const auto &cand : c->file.tensors)
+        if (cand.name == name) t = &cand;
+    TLC_REQUIRE(t, TLC_ERR_LOAD, "Weight not found: %s", name);
+    TLC_REQUIRE(t->nbytes > 0, TLC_ERR_LOAD, "Unsupported quantization type: %d", t->type);
+    c->misses++;
+    std::ifstream f(c->file.path, std::ios::binary);
+    TLC_REQUIRE(f.good(), TLC_ERR_LOAD, "Failed to open GGUF file '%s': %s", c->file.path.c_str(), strerror(errno));
+    std::vector<char> host(t->nbytes);
+    f.seekg((std::streamoff)t->offset);
+    f.read(host.data(), (std::streamsize)t->nbytes);
+    TLC_REQUIRE((bool)f, TLC_ERR_LOAD, "Failed to load tensor data: short read on '%s'", name);
+    tlc_qtensor *qt = nullptr;
+    if (int32_t rc = tlc_qtensor_create(c->ctx, t->type, t->rows, t->cols, host.data(), t->nbytes, 0, 1, TLC_SPLIT_NONE, &qt))
+        return rc;
+    if (c->entries.size() >= c->capacity) {
+        // evict the least recently used tensor, once nothing on the stream can still read it
+        cudaStreamSynchronize(c->ctx->stream);
+        const std::string victim = c->lru.back();
+        c->lru.pop_back();
+        tlc_qtensor_destroy(c->entries[victim].first);
+        c->entries.erase(victim);
+        c->evictions++;
+    }
+    c->lru.push_front(name);
+    c->entries[name] = {qt, c->lru.begin()};
+    *out = qt;
+    return TLC_OK;
+}

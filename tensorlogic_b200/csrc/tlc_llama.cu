@@ -13,9 +13,14 @@
 //   [rms_norm + gate/up linears + silu*mul]                         1 launch
 //   [down projection + residual add]                                1 launch
 //
-// then [rms_norm + lm_head] and an on-device greedy sample.  Token ids,
-// positions and the sampled token live in device memory, so a decode step has
-// no host-dependent kernel argument and is replayed as a CUDA graph.
+// then [rms_norm + lm_head] and an on-device sample (greedy, or temperature
+// sampling with counter-based draws).  Token ids, positions and the sampled
+// token live in device memory, so a decode step has no host-dependent kernel
+// argument and is replayed as a CUDA graph.  A prompt of many tokens takes the
+// same path with the linears on the tcgen05 GEMM (norms and SiLU.mul then run
+// as their own kernels).  With tensor parallelism the o and down projections
+// produce partial sums that one peer-memory kernel all-reduces and adds to the
+// residual, and the vocabulary shards of the logits are all-gathered.
 // RoPE takes the true position of every token (the reference's decode branch
 // calls rope() with its default offset 0, chat_demo_with_kvcache.tl:236,:244).
 #include <cmath>

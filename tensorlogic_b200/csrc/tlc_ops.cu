@@ -18,10 +18,25 @@ __global__ void rms_norm_kernel(const __half *__restrict__ x, const __half *__re
     __shared__ float inv_s;
     const __half *xr = x + (size_t)blockIdx.x * d;
     __half *yr = y + (size_t)blockIdx.x * d;
+    // 16-byte accesses when the row allows it (d a multiple of 8, 16-byte aligned pointers)
+    const bool vec = (d & 7) == 0 && ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0);
     float sq = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = __half2float(xr[i]);
-        sq = fmaf(v, v, sq);
+    if (vec) {
+        for (int i = threadIdx.x; i < (d >> 3); i += blockDim.x) {
+            const uint4 raw = reinterpret_cast<const uint4 *>(xr)[i];
+            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 v = __half22float2(h[j]);
+                sq = fmaf(v.x, v.x, sq);
+                sq = fmaf(v.y, v.y, sq);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float v = __half2float(xr[i]);
+            sq = fmaf(v, v, sq);
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
@@ -35,9 +50,21 @@ __global__ void rms_norm_kernel(const __half *__restrict__ x, const __half *__re
     }
     __syncthreads();
     const float inv = inv_s;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float nrm = __fmul_rn(__half2float(xr[i]), inv);
-        yr[i] = __float2half_rn(__fmul_rn(nrm, __half2float(w[i])));
+    if (vec) {
+        for (int i = threadIdx.x; i < (d >> 3); i += blockDim.x) {
+            const uint4 raw = reinterpret_cast<const uint4 *>(xr)[i], wraw = reinterpret_cast<const uint4 *>(w)[i];
+            const __half *xh = reinterpret_cast<const __half *>(&raw), *wh = reinterpret_cast<const __half *>(&wraw);
+            __align__(16) __half o[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                o[j] = __float2half_rn(__fmul_rn(__fmul_rn(__half2float(xh[j]), inv), __half2float(wh[j])));
+            reinterpret_cast<uint4 *>(yr)[i] = *reinterpret_cast<const uint4 *>(o);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float nrm = __fmul_rn(__half2float(xr[i]), inv);
+            yr[i] = __float2half_rn(__fmul_rn(nrm, __half2float(w[i])));
+        }
     }
 }
 

@@ -63,6 +63,52 @@ def split_for(name: str) -> int:
     return _lib.SPLIT_NONE
 
 
+class WeightCache:
+    """GGUFWeightCache (src/model/gguf_weight_cache.rs): tensors of a GGUF file uploaded on first use,
+    at most ``capacity`` of them resident (LRU).  ``load_weight_cache_gguf_f16(path, capacity)`` /
+    ``get_weight(cache, name)`` of the builtin surface; the cached tensors stay quantized."""
+
+    def __init__(self, dev: Device, path, capacity: int):
+        self.dev = dev
+        h = C.c_void_p()
+        check(dev.lib.tlc_weight_cache_open(dev.handle, str(path).encode(), int(capacity), C.byref(h)))
+        self.handle = h
+
+    def close(self) -> None:
+        if self.handle and self.dev.handle:
+            self.dev.lib.tlc_weight_cache_close(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def get_weight(self, name: str) -> QTensor:
+        """The tensor stays owned by the cache: valid until evicted, cleared or closed."""
+        h = C.c_void_p()
+        check(self.dev.lib.tlc_weight_cache_get(self.handle, name.encode(), C.byref(h)))
+        t = QTensor(self.dev, h)
+        t._owner = self
+        t.__class__ = _BorrowedQTensor
+        return t
+
+    def contains(self, name: str) -> bool:
+        return bool(self.dev.lib.tlc_weight_cache_contains(self.handle, name.encode()))
+
+    def clear(self) -> None:
+        check(self.dev.lib.tlc_weight_cache_clear(self.handle))
+
+    def stats(self) -> dict:
+        n, cap = C.c_int64(), C.c_int64()
+        hits, misses, ev = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        check(self.dev.lib.tlc_weight_cache_stats(self.handle, C.byref(n), C.byref(cap), C.byref(hits), C.byref(misses),
+                                                  C.byref(ev)))
+        return {"len": n.value, "capacity": cap.value, "hits": hits.value, "misses": misses.value,
+                "evictions": ev.value}
+
+
 class Model:
     """Model<T> = name -> tensor map (src/model/mod.rs:39-45), tensors resident on the device."""
 

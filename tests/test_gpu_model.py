@@ -239,3 +239,45 @@ def test_runner_temperature_sampling_is_reproducible(dev, ref):
     assert runs[0] != runs[2]
     # greedy again after switching back
     llm.set_sampling(0.0)
+
+
+def test_weight_cache_lru(dev, ref, tmp_path):
+    """GGUFWeightCache: lazy upload, LRU eviction by tensor count, hit / miss accounting, errors."""
+    from tensorlogic_b200 import _lib
+    from tensorlogic_b200.api import TensorError, linear
+    from tensorlogic_b200.model import WeightCache, synthetic_host_weights
+    arch = _small_arch()
+    weights = synthetic_host_weights(arch, seed=15)
+    path = tmp_path / "cache.gguf"
+    write_gguf(path, weights, arch)
+    cache = WeightCache(dev, path, 2)
+    assert cache.contains("blk.0.attn_q.weight") and not cache.contains("nope.weight")
+    names = ["blk.0.attn_q.weight", "blk.0.ffn_down.weight", "blk.1.attn_k.weight"]
+    x = None
+    for name in names[:2]:
+        w = cache.get_weight(name)
+        gtype, raw = weights[name]
+        n, k = raw.shape[0], raw.shape[1] * 32
+        assert w.type == gtype and w.shape == (n, k)
+        assert np.array_equal(w.dequantize().numpy().view(np.uint16), ref.dequant(gtype, raw, n * k).reshape(n, k).view(np.uint16))
+        x = synth_x = np.random.default_rng(1).standard_normal((2, k)).astype(np.float16)
+        assert rel_l2(linear(dev.tensor(synth_x), w).numpy(), ref.linear_q(gtype, raw, n, k, synth_x)) < 2e-3
+    assert cache.stats() == {"len": 2, "capacity": 2, "hits": 0, "misses": 2, "evictions": 0}
+    cache.get_weight(names[0])                                   # hit: q becomes the most recent
+    cache.get_weight(names[2])                                   # miss: evicts ffn_down, the least recent
+    st = cache.stats()
+    assert (st["len"], st["hits"], st["misses"], st["evictions"]) == (2, 1, 3, 1)
+    cache.get_weight(names[0])                                   # still resident
+    assert cache.stats()["hits"] == 2
+    cache.get_weight(names[1])                                   # reloaded
+    assert cache.stats()["misses"] == 4
+    with pytest.raises(TensorError) as e:
+        cache.get_weight("blk.9.attn_q.weight")
+    assert e.value.code == _lib.ERR_LOAD and "Weight not found" in str(e.value)
+    cache.clear()
+    assert cache.stats()["len"] == 0
+    with pytest.raises(TensorError):
+        WeightCache(dev, path, 0)
+    with pytest.raises(TensorError):
+        WeightCache(dev, tmp_path / "missing.gguf", 2)
+    cache.close()
