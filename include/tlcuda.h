@@ -162,8 +162,10 @@ TLC_API int32_t tlc_host_free(void *p);
 /* Replaces the load-time CPU dequantization (GGUFLoader::dequantize_q4_0 /
  * dequantize_q8_0, src/model/formats/gguf.rs:22-112, and the upload at
  * gguf.rs:450): the GGUF blocks of W [n_rows, n_cols] (row-major, n_cols
- * fastest; 18-byte Q4_0 / 34-byte Q8_0 blocks of 32 along a row) are copied to
- * HBM unchanged.  `blocks` is a HOST pointer to the FULL tensor; with
+ * fastest; 18-byte Q4_0 / 34-byte Q8_0 blocks of 32 along a row) are kept in
+ * HBM bit for bit, regrouped on the device into tiles of 16 rows (the order the
+ * matrix kernels fetch them in; tlc_qtensor_blocks gives the file's order
+ * back).  `blocks` is a HOST pointer to the FULL tensor; with
  * tp_size > 1 only this rank's shard is kept (rows [r*N/tp, (r+1)*N/tp) for
  * TLC_SPLIT_ROWS; block columns [r*K/tp, (r+1)*K/tp) of every row for
  * TLC_SPLIT_COLS).  F16 and F32 tensors are accepted too (F32 is converted
@@ -195,11 +197,15 @@ TLC_API int32_t tlc_qtensor_create_normal_f16(tlc_ctx *ctx, int64_t n_rows, int6
                                               uint64_t seed, uint64_t tensor_id, float mean,
                                               float std, tlc_qtensor **out);
 TLC_API int32_t tlc_qtensor_destroy(tlc_qtensor *qt);
-/* Local (per-rank) shape and storage.  row_pitch is the distance in bytes
- * between rows in HBM: the GGUF row size rounded up to 16 (equal to it, i.e.
- * a verbatim copy of the file's bytes, whenever n_cols is a multiple of 256). */
+/* Local (per-rank) shape and storage.  For F16 tensors row_pitch is the
+ * distance in bytes between rows in HBM (the row size rounded up to 16); for
+ * Q4_0 / Q8_0 tensors, whose storage is tiled, it is the GGUF size of one row. */
 TLC_API int32_t tlc_qtensor_info(tlc_qtensor *qt, int32_t *type, int64_t *n_rows,
                                  int64_t *n_cols, size_t *row_pitch, const void **dev_ptr);
+/* Writes the local shard's GGUF blocks in the file's order (row-major,
+ * n_rows * n_cols/32 blocks, no padding) to device memory: the inverse of the
+ * regrouping done at upload, bit for bit.  F16 tensors are copied row by row. */
+TLC_API int32_t tlc_qtensor_blocks(tlc_ctx *ctx, tlc_qtensor *qt, void *out_dev);
 /* Device-side GGUFLoader::dequantize_q4_0 / _q8_0: writes the n_rows*n_cols
  * f16 values of the local shard; bit-exact with the reference. */
 TLC_API int32_t tlc_dequant(tlc_ctx *ctx, tlc_qtensor *qt, void *out_f16_dev);

@@ -84,6 +84,7 @@ PROTOTYPES = {
     "tlc_qtensor_create_normal_f16": (i32, [vp, i64, i64, u64, u64, f32, f32, P(vp)]),
     "tlc_qtensor_destroy": (i32, [vp]),
     "tlc_qtensor_info": (i32, [vp, P(i32), P(i64), P(i64), P(sz), P(vp)]),
+    "tlc_qtensor_blocks": (i32, [vp, vp, vp]),
     "tlc_dequant": (i32, [vp, vp, vp]),
     "tlc_linear": (i32, [vp, vp, vp, i32, i64, vp, vp]),
     "tlc_linear_host": (i32, [vp, vp, vp, i32, i64, vp, vp]),

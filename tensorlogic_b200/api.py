@@ -196,9 +196,13 @@ class QTensor:
         return out
 
     def raw_bytes(self) -> np.ndarray:
-        """The shard's bytes as stored in HBM: uint8 [n_rows, row_pitch]."""
-        out = np.empty((self.shape[0], self.row_pitch), np.uint8)
-        check(self.dev.lib.tlc_download(self.dev.handle, out.ctypes.data, self.ptr, out.nbytes))
+        """The shard's GGUF blocks (or f16 rows) in the file's order: uint8 [n_rows, bytes per row]."""
+        per_row = {_lib.TYPE_Q4_0: 18, _lib.TYPE_Q8_0: 34}.get(self.type)
+        row_bytes = self.shape[1] // 32 * per_row if per_row else self.shape[1] * 2
+        stage = self.dev.empty((self.shape[0] * row_bytes // 2,))
+        check(self.dev.lib.tlc_qtensor_blocks(self.dev.handle, self.handle, stage.ptr))
+        out = np.empty((self.shape[0], row_bytes), np.uint8)
+        check(self.dev.lib.tlc_download(self.dev.handle, out.ctypes.data, stage.ptr, out.nbytes))
         return out
 
 

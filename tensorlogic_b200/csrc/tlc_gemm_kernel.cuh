@@ -22,7 +22,8 @@
 //               swizzled K-major tile, several steps ahead;
 //   warps 4-11  B producers (4*NT of them work): thread r dequantizes row r of
 //               the weight tile (2 blocks = 64 values) into the same layout; the
-//               raw blocks are fetched a group of K steps ahead into registers;
+//               row's quants (64 contiguous bytes per tile of the tiled weight
+//               layout) are fetched a group of K steps ahead into registers;
 //   warp 12     allocates tensor memory and issues the MMAs: four K=16
 //               tcgen05.mma per sub-tile and stage, tcgen05.commit to hand the
 //               stage back.
@@ -42,9 +43,10 @@ constexpr int kBK = 64;  // K elements per stage (one 128-byte swizzle row)
 constexpr int kThreads = 416;
 
 struct GemmParams {
-    const uint8_t *w;   // blocks, row-major [N, K/32]
-    const uint8_t *w2;  // second weight of the SiLU.mul pair (same shape and pitch) or null
-    size_t w_pitch;
+    const uint8_t *w;   // weight tiles [slab of 16 rows][k-tile] (tlc_tile.cuh)
+    const uint8_t *w2;  // second weight of the SiLU.mul pair (same shape) or null
+    size_t w_pitch;     // bytes of one 16-row slab
+    int k_tiles;        // tiles per slab
     const __half *x;         // [M, K]
     __half *y;               // [M, N]
     const __half *residual;  // [M, N] or null: y = f16(acc) + residual

@@ -7,109 +7,104 @@ using namespace tlc_gemm;
 
 namespace {
 
-// Dequantizes the two blocks of one K step of one weight row (`cur`: the 9 / 17
-// 32-bit words that hold them) into the row's eight 16-byte pieces of the
-// swizzled tile at `bt` (`piece`: their byte offsets).
+// Dequantizes one block of a weight row -- `q`: its quant words (4 for Q4_0, 8
+// for Q8_0), `d`: its scale -- into four 16-byte pieces of the swizzled tile at
+// `bt` (`piece`: the byte offsets of the row's pieces, `e`: which half of the K step).
 template <int QT>
-__device__ __forceinline__ void dequant_step(const uint32_t *cur, uint8_t *bt, const uint32_t (&piece)[8]) {
+__device__ __forceinline__ void dequant_block(const uint32_t *q, __half d, uint8_t *bt, const uint32_t (&piece)[8],
+                                              int e) {
+    const __half2 d2 = __half2half2(d);
+    uint4 c[4];
     if (QT == TLC_TYPE_Q4_0) {
-        // 36 bytes: d0 | qs0[16] | d1 | qs1[16]; the even block's qs sit 2 bytes past a word boundary
         const __half2 bias = __float2half2_rn(1032.f);  // 1024 (magic) + 8
-#pragma unroll
-        for (int e = 0; e < 2; e++) {
-            uint32_t q[4];
-            __half d;
-            if (e == 0) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) q[j] = __funnelshift_r(cur[j], cur[j + 1], 16);
-                d = __ushort_as_half((unsigned short)(cur[0] & 0xFFFFu));
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; j++) q[j] = cur[5 + j];
-                d = __ushort_as_half((unsigned short)(cur[4] >> 16));
-            }
-            const __half2 d2 = __half2half2(d);
-            uint4 c[4];
-            c[0] = dequant8(q[0] & 0x0F0F0F0Fu, q[1] & 0x0F0F0F0Fu, bias, d2);                // elems 0..7
-            c[1] = dequant8(q[2] & 0x0F0F0F0Fu, q[3] & 0x0F0F0F0Fu, bias, d2);                // 8..15
-            c[2] = dequant8((q[0] >> 4) & 0x0F0F0F0Fu, (q[1] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 16..23
-            c[3] = dequant8((q[2] >> 4) & 0x0F0F0F0Fu, (q[3] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 24..31
-#pragma unroll
-            for (int j = 0; j < 4; j++) *reinterpret_cast<uint4 *>(bt + piece[4 * e + j]) = c[j];
-        }
+        c[0] = dequant8(q[0] & 0x0F0F0F0Fu, q[1] & 0x0F0F0F0Fu, bias, d2);                // elems 0..7
+        c[1] = dequant8(q[2] & 0x0F0F0F0Fu, q[3] & 0x0F0F0F0Fu, bias, d2);                // 8..15
+        c[2] = dequant8((q[0] >> 4) & 0x0F0F0F0Fu, (q[1] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 16..23
+        c[3] = dequant8((q[2] >> 4) & 0x0F0F0F0Fu, (q[3] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 24..31
     } else {
-        // 68 bytes: d0 | q0[32] | d1 | q1[32]
         const __half2 bias = __float2half2_rn(1152.f);  // 1024 (magic) + 128 (sign flip)
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            uint32_t q[8];
-            __half d;
-            if (e == 0) {
-#pragma unroll
-                for (int j = 0; j < 8; j++) q[j] = __funnelshift_r(cur[j], cur[j + 1], 16) ^ 0x80808080u;
-                d = __ushort_as_half((unsigned short)(cur[0] & 0xFFFFu));
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; j++) q[j] = cur[9 + j] ^ 0x80808080u;
-                d = __ushort_as_half((unsigned short)(cur[8] >> 16));
-            }
-            const __half2 d2 = __half2half2(d);
-#pragma unroll
-            for (int j = 0; j < 4; j++)
-                *reinterpret_cast<uint4 *>(bt + piece[4 * e + j]) = dequant8(q[2 * j], q[2 * j + 1], bias, d2);
-        }
+        for (int j = 0; j < 4; j++) c[j] = dequant8(q[2 * j] ^ 0x80808080u, q[2 * j + 1] ^ 0x80808080u, bias, d2);
     }
+#pragma unroll
+    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4 *>(bt + piece[4 * e + j]) = c[j];
 }
 
-// B producer of one weight row.  The row's raw blocks are fetched in groups of
-// nine 16-byte pieces -- Q4_0: 8 blocks = four K steps (144 bytes); Q8_0: 4
-// blocks = two K steps (136 bytes, which start 0 or 8 bytes into the first
-// piece) -- one group ahead of their use, so the global-memory latency is
-// spread over a group's worth of K steps.
+// B producer of one weight row.  The row's share of a weight tile (64 bytes of
+// quants: four 16-byte pieces, plus its block scales) covers two K steps for
+// Q4_0 and one for Q8_0; shares are fetched in groups of two tiles, one group
+// ahead of their use, so the global-memory latency is spread over a group's
+// worth of K steps.
 template <int QT, int STAGES, int STAGE_BYTES>
 __device__ __forceinline__ void produce_b(const GemmParams &p, uint8_t *btiles, uint64_t *full, uint64_t *empty,
                                           volatile int *abort_flag, const uint8_t *wbase, int wrow, int row, int KT,
                                           int lane) {
-    constexpr int BB = QT == TLC_TYPE_Q4_0 ? 18 : 34;
-    constexpr int RAW_WORDS = 2 * BB / 4;           // 32-bit words of the two blocks of one K step
-    constexpr int SPG = QT == TLC_TYPE_Q4_0 ? 4 : 2;  // K steps per group
-    constexpr int GV4 = 9;                           // 16-byte pieces per group
-    // `row`: row of the tile this thread fills; `wrow`: the weight row it holds (of `wbase`)
-    const bool row_ok = wrow < p.n;
-    const uint4 *wrow4 = reinterpret_cast<const uint4 *>(wbase + (size_t)(row_ok ? wrow : 0) * p.w_pitch);
+    constexpr int TILE = QT == TLC_TYPE_Q4_0 ? 1152 : 1088;
+    constexpr int TS = QT == TLC_TYPE_Q4_0 ? 2 : 1;  // K steps per tile
+    constexpr int GT = 2;                             // tiles per group
+    // `row`: row of the smem tile this thread fills; `wrow`: the weight row it holds (of `wbase`).
     // Rows past N load nothing: a zero scale makes every value of the tile row zero.
-    const int limit_v4 = row_ok ? (int)(p.w_pitch >> 4) : 0;
-    uint4 nxt4[GV4], cur4[GV4];
+    const bool row_ok = wrow < p.n;
+    const int r16 = wrow & 15;
+    const uint8_t *slab = wbase + (size_t)(row_ok ? wrow >> 4 : 0) * p.w_pitch;
+    const uint32_t qoff = (uint32_t)((r16 >> 3) * 512 + (r16 & 7) * 64);
+    const uint32_t soff = 1024u + (uint32_t)r16 * (QT == TLC_TYPE_Q4_0 ? 8u : 4u);
+    uint4 nxt4[GT * 4], cur4[GT * 4];
+    uint32_t nxts[GT * TS], curs[GT * TS];
     auto load_group = [&](int g) {
-        const int start = QT == TLC_TYPE_Q4_0 ? 9 * g : (17 * g) >> 1;
 #pragma unroll
-        for (int i = 0; i < GV4; i++) {
-            const int idx = start + i;  // the last group may end in the row's padding
-            nxt4[i] = idx < limit_v4 ? __ldg(wrow4 + idx) : make_uint4(0, 0, 0, 0);
+        for (int i = 0; i < GT; i++) {
+            const int kt = g * GT + i;
+            const bool ok = row_ok && kt < p.k_tiles;
+            const uint8_t *tile = slab + (size_t)(ok ? kt : 0) * TILE;
+#pragma unroll
+            for (int t = 0; t < 4; t++)
+                nxt4[i * 4 + t] = ok ? __ldg(reinterpret_cast<const uint4 *>(tile + qoff) + t) : make_uint4(0, 0, 0, 0);
+            if (QT == TLC_TYPE_Q4_0) {
+                const uint2 sc = ok ? __ldg(reinterpret_cast<const uint2 *>(tile + soff)) : make_uint2(0, 0);
+                nxts[i * TS] = sc.x;
+                nxts[i * TS + TS - 1] = sc.y;
+            } else {
+                nxts[i * TS] = ok ? __ldg(reinterpret_cast<const uint32_t *>(tile + soff)) : 0u;
+            }
         }
     };
     // byte offsets of the eight 16-byte pieces of this row under the 128-byte swizzle
     uint32_t piece[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) piece[j] = (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4));
+    constexpr int SPG = GT * TS;  // K steps per group
     const int n_groups = (KT + SPG - 1) / SPG;
-    // WOFF: word of the group's first block inside cur4 (odd Q8_0 groups start 8 bytes in)
-    auto process = [&](int g, auto woff_c) {
-        constexpr int WOFF = decltype(woff_c)::value;
+    auto comp = [](const uint4 &v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; };
+    auto process = [&](int g) {
 #pragma unroll
         for (int st = 0; st < SPG; st++) {
             const int kt = g * SPG + st;
             if (kt >= KT) break;
-            uint32_t cur[RAW_WORDS];
-#pragma unroll
-            for (int i = 0; i < RAW_WORDS; i++) {
-                const int wi = WOFF + st * RAW_WORDS + i;
-                const uint4 v = cur4[wi >> 2];
-                cur[i] = (wi & 3) == 0 ? v.x : (wi & 3) == 1 ? v.y : (wi & 3) == 2 ? v.z : v.w;
-            }
+            const int ti = st / TS;        // tile of the group
+            const int half = st % TS;      // Q4_0: which pair of the tile's four blocks
+            const uint32_t scw = curs[ti * TS + half];  // the two scales of this K step
             const int s = kt % STAGES;
             mbar_wait(&empty[s], ((kt / STAGES) & 1u) ^ 1u, abort_flag, p.status, 11, p.wait_ns);
-            dequant_step<QT>(cur, btiles + (size_t)s * STAGE_BYTES, piece);
+            uint8_t *bt = btiles + (size_t)s * STAGE_BYTES;
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const __half d = __ushort_as_half((unsigned short)(e == 0 ? scw & 0xFFFFu : scw >> 16));
+                if (QT == TLC_TYPE_Q4_0) {
+                    uint32_t q[4];
+#pragma unroll
+                    for (int t = 0; t < 4; t++) q[t] = comp(cur4[ti * 4 + t], 2 * half + e);
+                    dequant_block<QT>(q, d, bt, piece, e);
+                } else {
+                    uint32_t q[8];
+#pragma unroll
+                    for (int t = 0; t < 4; t++) {
+                        q[2 * t] = comp(cur4[ti * 4 + t], 2 * e);
+                        q[2 * t + 1] = comp(cur4[ti * 4 + t], 2 * e + 1);
+                    }
+                    dequant_block<QT>(q, d, bt, piece, e);
+                }
+            }
             fence_async_proxy();
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
@@ -117,17 +112,13 @@ __device__ __forceinline__ void produce_b(const GemmParams &p, uint8_t *btiles, 
     };
     load_group(0);
 #pragma unroll 1
-    for (int g = 0; g < n_groups; g += 2) {
+    for (int g = 0; g < n_groups; g++) {
 #pragma unroll
-        for (int i = 0; i < GV4; i++) cur4[i] = nxt4[i];
+        for (int i = 0; i < GT * 4; i++) cur4[i] = nxt4[i];
+#pragma unroll
+        for (int i = 0; i < GT * TS; i++) curs[i] = nxts[i];
         if (g + 1 < n_groups) load_group(g + 1);
-        process(g, std::integral_constant<int, 0>{});
-        if (g + 1 < n_groups) {
-#pragma unroll
-            for (int i = 0; i < GV4; i++) cur4[i] = nxt4[i];
-            if (g + 2 < n_groups) load_group(g + 2);
-            process(g + 1, std::integral_constant<int, QT == TLC_TYPE_Q4_0 ? 0 : 2>{});
-        }
+        process(g);
     }
 }
 
@@ -465,7 +456,8 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
         const tlc_qtensor *w = a.outs[i].w;
         GemmParams p{};
         p.w = static_cast<const uint8_t *>(w->data);
-        p.w_pitch = w->row_pitch;
+        p.w_pitch = w->slab_pitch;
+        p.k_tiles = (int)w->k_tiles;
         p.x = x;
         p.m = a.m;
         p.n = (int)w->n_rows;
@@ -474,7 +466,7 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.wait_ns = ctx->wait_ns;
         p.y = static_cast<__half *>(a.outs[i].y);
         if (swiglu) {
-            TLC_REQUIRE(a.outs[1].w->row_pitch == w->row_pitch, TLC_ERR_SHAPE_MISMATCH,
+            TLC_REQUIRE(a.outs[1].w->slab_pitch == w->slab_pitch, TLC_ERR_SHAPE_MISMATCH,
                         "gate and up projections must have the same layout");
             p.w2 = static_cast<const uint8_t *>(a.outs[1].w->data);
             p.row_stride = p.n;

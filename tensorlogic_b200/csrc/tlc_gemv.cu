@@ -1,5 +1,5 @@
 // Fused dequant-GEMV for decode-sized activations (M <= 16) over weights kept
-// in their native GGUF Q4_0 / Q8_0 block layout.
+// as GGUF Q4_0 / Q8_0 blocks in 16-row tiles (tlc_tile.cuh).
 //
 // Takes the place of the dense f16 kernels the reference runs after
 // dequantizing at load time (matmul_transposed_b_tiled_f16,
@@ -7,17 +7,18 @@
 // and of the separate rms_norm / rope / sigmoid / mul / add launches around
 // them in the TL scripts (debug/chat_demo_with_kvcache.tl:219-290).
 //
-// Design (memory-bound; the weight bytes are read from HBM exactly once):
+// Design (the weight bytes are read from HBM exactly once):
 //   * persistent CTAs, up to two per SM, each walking 16-row slabs of the weight(s);
-//   * a producer warp streams the raw block bytes of a slab into a shared
-//     memory ring with 16-byte-granular bulk async copies (one per row per
-//     stage) that complete on mbarriers -- no thread ever issues a narrow
-//     global load for weight data, and the ring keeps tens of KB per SM in
-//     flight independent of occupancy;
-//   * eight consumer warps unpack nibbles / bytes in registers straight into
-//     f16 tensor-core fragments: a 4-bit (8-bit) integer n placed in the low
-//     mantissa bits of a binary16 is the subnormal n * 2^-24, so one AND per
-//     pair of weights yields an exact A fragment; the -8 (-128) offset is
+//   * a producer warp streams the tiles of a slab into a shared memory ring,
+//     ONE bulk async copy of up to 18 KB per stage (a stage's 16 tiles are
+//     contiguous in HBM), completing on mbarriers -- no thread ever issues a
+//     narrow global load for weight data, and the ring keeps tens of KB per SM
+//     in flight independent of occupancy;
+//   * eight consumer warps read their fragment words with two conflict-free
+//     16-byte shared loads per tile and unpack nibbles / bytes in registers
+//     straight into f16 tensor-core fragments: a 4-bit (8-bit) integer n placed
+//     in the low mantissa bits of a binary16 is the subnormal n * 2^-24, so one
+//     AND per pair of weights yields an exact A fragment; the -8 (-128) offset is
 //     carried by the accumulator's initial value (-8 * sum of the 32
 //     activations of the block) and the block scale d multiplies the 16x8 block
 //     result in f32;  mma.sync m16n8k16 with f32 accumulation does the dot
@@ -31,19 +32,15 @@
 
 #include "tlc_gemv_kernel.cuh"
 #include "tlc_internal.h"
+#include "tlc_tile.cuh"
 
 using namespace tlc_gemv;
 
 namespace {
 
-__device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
-    return __half2float(__ushort_as_half((unsigned short)bits16));
-}
-
 // ---------------------------------------------------------------------------
-// Generic path: any type (F16 included), any M, no alignment assumptions.  One
-// warp per output row; used for f16 weights only (embedding-tied heads, norms
-// never go through linear) -- it is correct but far from the roofline.
+// Generic path for dense f16 weights: any M, no alignment assumptions.  One
+// warp per output row -- correct but far from the roofline.
 // ---------------------------------------------------------------------------
 __global__ void linear_generic_kernel(const uint8_t *__restrict__ w, size_t pitch, int type, int n_rows,
                                       int k, const __half *__restrict__ x, int m, __half *__restrict__ y,
@@ -58,29 +55,6 @@ __global__ void linear_generic_kernel(const uint8_t *__restrict__ w, size_t pitc
         if (type == TLC_TYPE_F16) {
             const __half *wr = reinterpret_cast<const __half *>(row);
             for (int i = lane; i < k; i += 32) acc = fmaf(__half2float(wr[i]), __half2float(xr[i]), acc);
-        } else {
-            const int bb = type == TLC_TYPE_Q4_0 ? 18 : 34;
-            for (int b = lane; b < k / 32; b += 32) {
-                const uint8_t *blk = row + (size_t)b * bb;
-                const float d = half_bits_to_float((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
-                float s = 0.f;
-                if (type == TLC_TYPE_Q4_0) {
-                    for (int j = 0; j < 16; j++) {
-                        const uint8_t q = blk[2 + j];
-                        // dequantized weight rounded to f16 first, as the reference's loader does
-                        const float w0 = __half2float(__float2half_rn(__fmul_rn((float)((int)(q & 15) - 8), d)));
-                        const float w1 = __half2float(__float2half_rn(__fmul_rn((float)((int)(q >> 4) - 8), d)));
-                        s = fmaf(w0, __half2float(xr[b * 32 + j]), s);
-                        s = fmaf(w1, __half2float(xr[b * 32 + j + 16]), s);
-                    }
-                } else {
-                    for (int j = 0; j < 32; j++) {
-                        const float wv = __half2float(__float2half_rn(__fmul_rn((float)(int8_t)blk[2 + j], d)));
-                        s = fmaf(wv, __half2float(xr[b * 32 + j]), s);
-                    }
-                }
-                acc += s;
-            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -181,8 +155,7 @@ int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
 template <int QT, int NT>
 int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     using T = QTraits<QT>;
-    constexpr int PITCH = stage_pitch(T::KCB * T::BB);
-    constexpr size_t STAGE_BYTES = (size_t)kRows * PITCH;
+    constexpr size_t STAGE_BYTES = (size_t)kTilesPerStage * T::TILE_BYTES;
     const size_t budget = (size_t)ctx->prop.sharedMemPerBlockOptin;
     const size_t fixed1 = fixed_smem_bytes(p.nblk_pad, p.m, NT, p.subs);
     TLC_REQUIRE(fixed1 + 2 * STAGE_BYTES <= budget, TLC_ERR_INVALID_OPERATION,
@@ -253,9 +226,9 @@ int32_t tlc_selftest_mbarrier_wait(tlc_ctx *ctx) {
 
 // Largest number of activation rows one launch can take for this K.
 static int gemv_max_m(tlc_ctx *ctx, int type, int k) {
-    const int nblk_pad = ((k / 32) + 1) & ~1;
+    const int nblk_pad = (int)tlc_tile::k_tiles(type, k) * tlc_tile::tile_blocks(type);
     const size_t budget = (size_t)ctx->prop.sharedMemPerBlockOptin;
-    const size_t stage = type == TLC_TYPE_Q4_0 ? (size_t)kRows * stage_pitch(64 * 18) : (size_t)kRows * stage_pitch(32 * 34);
+    const size_t stage = (size_t)kTilesPerStage * tlc_tile::tile_bytes(type);
     for (int m = 16; m >= 1; m--) {
         int nt = m > 8 ? 2 : 1;
         if (gemv_fixed_smem(nblk_pad, m, nt) + 3 * stage <= budget) return m;
@@ -342,7 +315,7 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
         for (int i = 0; i < a.n_out; i++) {
             const tlc_qtensor *w = a.outs[i].w;
             p.t[i].w = static_cast<const uint8_t *>(w->data);
-            p.t[i].pitch = w->row_pitch;
+            p.t[i].slab_pitch = w->slab_pitch;
             p.t[i].n = (int)w->n_rows;
             // Outputs are [m, N] row-major: a pass over rows m0.. writes at y + m0*N.
             const long long rs = a.outs[i].row_stride >= 0 ? a.outs[i].row_stride : (long long)w->n_rows;
@@ -361,9 +334,9 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
         }
         p.k = (int)k;
         p.nblk = (int)(k / 32);
-        p.nblk_pad = (p.nblk + 1) & ~1;
-        const int kcb = type == TLC_TYPE_Q4_0 ? 64 : 32;
-        p.nchunks = (p.nblk + kcb - 1) / kcb;
+        p.ktiles = (int)w0->k_tiles;
+        p.nblk_pad = p.ktiles * tlc_tile::tile_blocks(type);
+        p.nchunks = (p.ktiles + kTilesPerStage - 1) / kTilesPerStage;
         p.m = mc;
         p.x = static_cast<const __half *>(a.x) + (size_t)m0 * k;
         p.norm_w = static_cast<const __half *>(a.norm_w);

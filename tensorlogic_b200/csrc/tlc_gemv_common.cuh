@@ -15,31 +15,24 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 8;
 
+// Weights arrive in the tiled layout of tlc_tile.cuh: a ring stage is 16
+// consecutive tiles of one 16-row slab (Q4_0: 64 blocks, Q8_0: 32 blocks of K).
+constexpr int kTilesPerStage = 16;
 template <int QT> struct QTraits;
 template <> struct QTraits<TLC_TYPE_Q4_0> {
-    static constexpr int BB = 18;         // bytes per block
-    static constexpr int KCB = 64;        // blocks per ring stage and row (1152 B)
-    static constexpr int PAIR_WORDS = 9;  // 32-bit words per (even, odd) block pair
+    static constexpr int TB = 4;             // blocks per tile
+    static constexpr int TILE_BYTES = 1152;  // 1024 quant bytes + 16 rows x 4 f16 scales
     static constexpr float OFFSET = 8.0f;
 };
 template <> struct QTraits<TLC_TYPE_Q8_0> {
-    static constexpr int BB = 34;
-    static constexpr int KCB = 32;  // 1088 B
-    static constexpr int PAIR_WORDS = 17;
+    static constexpr int TB = 2;
+    static constexpr int TILE_BYTES = 1088;  // 1024 quant bytes + 16 rows x 2 f16 scales
     static constexpr float OFFSET = 128.0f;
 };
 
-// Shared-memory distance between the rows of a stage: the smallest odd
-// multiple of 16 bytes that holds a row segment, so that the 8 row groups of a
-// warp-wide 32-bit load fall into 8 different bank quads.
-__host__ __device__ constexpr int stage_pitch(int seg_bytes) {
-    int units = (seg_bytes + 15) / 16;
-    return (units | 1) * 16;
-}
-
 struct GemvTensor {
-    const uint8_t *w;
-    size_t pitch;
+    const uint8_t *w;   // tiles, [slab][k-tile]
+    size_t slab_pitch;  // bytes of one 16-row slab
     int n;  // rows of W (outputs)
     __half *y;
     int rope_heads;
@@ -56,7 +49,8 @@ struct GemvParams {
     int subs;      // slabs per unit (2 for the gate/up pair)
     int k;
     int nblk;      // k / 32
-    int nblk_pad;  // rounded up to even
+    int nblk_pad;  // rounded up to whole tiles
+    int ktiles;    // tiles per slab
     int nchunks;   // ring stages per slab
     int m;
     const __half *x;
@@ -137,10 +131,10 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
     return v;
 }
-__device__ __forceinline__ __half lds_f16(uint32_t a) {
-    unsigned short v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
-    return __ushort_as_half(v);
+__device__ __forceinline__ uint2 lds_u64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
 }
 __device__ __forceinline__ uint4 lds_u128(uint32_t a) {
     uint4 v;

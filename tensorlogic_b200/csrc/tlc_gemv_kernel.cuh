@@ -13,7 +13,7 @@ namespace tlc_gemv {
 //   ...  cinit [nblk_pad][NT][4 quad lanes] float2  accumulator start per block (columns 2t, 2t+1)
 //   ...  xzero one zero uint4 (B fragment of activation rows that do not exist)
 //   ...  xperm [nblk_pad][m][4 quad lanes] uint4    activations in fragment order
-//   ...  ring  [stages][16 rows][PITCH]             raw weight bytes (128-byte aligned)
+//   ...  ring  [stages][16 tiles]                   weight tiles as they lie in HBM (128-byte aligned)
 __host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, int as) {
     size_t s = 768;
     s += (size_t)2 * as * kConsumerWarps * kRows * (8 * nt) * sizeof(float);
@@ -28,9 +28,8 @@ template <int QT, int NT, int AS>
 __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams p) {
     using T = QTraits<QT>;
     constexpr int MP = 8 * NT;  // padded activation rows
-    constexpr int PITCH = stage_pitch(T::KCB * T::BB);
-    constexpr int STAGE_BYTES = kRows * PITCH;
-    constexpr int PW = T::PAIR_WORDS;
+    constexpr int TILE = T::TILE_BYTES;
+    constexpr int STAGE_BYTES = kTilesPerStage * TILE;
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -82,22 +81,20 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                     if (ti == 1 && sl >= p.slabs[1]) { sl -= p.slabs[1]; ti = 2; }
                 }
                 const uint8_t *wbase = ti == 0 ? p.t[0].w : ti == 1 ? p.t[1].w : p.t[2].w;
-                const size_t wpitch = ti == 0 ? p.t[0].pitch : ti == 1 ? p.t[1].pitch : p.t[2].pitch;
-                const int wn = ti == 0 ? p.t[0].n : ti == 1 ? p.t[1].n : p.t[2].n;
-                const int rows_valid = min(kRows, wn - sl * kRows);
+                const size_t spitch = ti == 0 ? p.t[0].slab_pitch : ti == 1 ? p.t[1].slab_pitch : p.t[2].slab_pitch;
                 for (int c = 0; c < p.nchunks; c++, it++) {
                     const int s = it % S;
                     const uint32_t par = ((it / S) & 1u) ^ 1u;
                     // On a timeout the producer stops issuing copies; the consumers'
                     // own bounded waits then end the CTA.
                     if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], par, abort_flag, p.status, 1, p.wait_ns))) return;
-                    const int kcb = min(T::KCB, p.nblk - c * T::KCB);
-                    const uint32_t bytes_row = (uint32_t)((kcb * T::BB + 15) & ~15);
-                    if (lane == 0) mbar_expect_tx(&full[s], bytes_row * (uint32_t)rows_valid);
-                    __syncwarp();
-                    if (lane < rows_valid) {
-                        const uint8_t *src = wbase + (size_t)(sl * kRows + lane) * wpitch + (size_t)c * (T::KCB * T::BB);
-                        bulk_g2s(stages + (size_t)s * STAGE_BYTES + lane * PITCH, src, bytes_row, &full[s]);
+                    // The stage's tiles are contiguous in HBM: one bulk copy.
+                    const int ntiles = min(kTilesPerStage, p.ktiles - c * kTilesPerStage);
+                    const uint32_t bytes = (uint32_t)(ntiles * TILE);
+                    if (lane == 0) {
+                        mbar_expect_tx(&full[s], bytes);
+                        bulk_g2s(stages + (size_t)s * STAGE_BYTES,
+                                 wbase + (size_t)sl * spitch + (size_t)c * (kTilesPerStage * TILE), bytes, &full[s]);
                     }
                 }
             }
@@ -232,7 +229,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
     }
     const uint32_t ci_addr = smem_u32(cinit + t);
     const uint32_t stages_addr = smem_u32(stages);
-    const uint32_t seg_lo = g * PITCH, seg_hi = (g + 8) * PITCH;
 
     // Units of this CTA: with only a few per CTA a balanced contiguous range
     // (1.5 % faster on the TinyLlama decode step), otherwise blockIdx.x,
@@ -265,68 +261,67 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                 // A wait that ran out skips the math but keeps the barrier protocol
                 // going, so every warp still reaches the same bar.sync calls.
                 const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], par, abort_flag, p.status, 2, p.wait_ns));
-                const int kcb = min(T::KCB, p.nblk - c * T::KCB);
-                const int npairs = ready ? (kcb + 1) >> 1 : 0;
-                const uint32_t row_lo = stages_addr + (uint32_t)s * STAGE_BYTES + seg_lo;
-                const uint32_t row_hi = stages_addr + (uint32_t)s * STAGE_BYTES + seg_hi;
+                const int ntiles = ready ? min(kTilesPerStage, p.ktiles - c * kTilesPerStage) : 0;
+                const uint32_t sbase = stages_addr + (uint32_t)s * STAGE_BYTES;
 
-                // One (even, odd) block pair: 2 blocks x 16 rows.  Pair pr starts
-                // 4*PW*pr bytes into the 4-byte aligned row segment; the even block's
-                // qs bytes sit 2 bytes past a word boundary, hence the funnel shifts.
-                auto do_pair = [&](int pr) {
-                    const uint32_t q0 = row_lo + 4 * PW * pr, q1 = row_hi + 4 * PW * pr;
-                    uint32_t we0[2], we1[2], wo0[2], wo1[2];
+                // One tile: TB blocks x 16 rows.  Lane (g, t) reads the words of rows g and
+                // g + 8 with two 16-byte loads, and the rows' block scales.
+                auto do_tile = [&](int ti) {
+                    const uint32_t tb = sbase + (uint32_t)ti * TILE;
+                    const uint4 vlo = lds_u128(tb + lane * 16);
+                    const uint4 vhi = lds_u128(tb + 512 + lane * 16);
+                    const uint32_t lo[4] = {vlo.x, vlo.y, vlo.z, vlo.w}, hi[4] = {vhi.x, vhi.y, vhi.z, vhi.w};
+                    float dlo[T::TB], dhi[T::TB];
                     if (QT == TLC_TYPE_Q4_0) {
-                        we0[0] = __funnelshift_r(lds_u32(q0 + 4 * t), lds_u32(q0 + 4 * t + 4), 16);
-                        we1[0] = __funnelshift_r(lds_u32(q1 + 4 * t), lds_u32(q1 + 4 * t + 4), 16);
-                        wo0[0] = lds_u32(q0 + 20 + 4 * t);
-                        wo1[0] = lds_u32(q1 + 20 + 4 * t);
-                        we0[1] = we1[1] = wo0[1] = wo1[1] = 0;
+                        const uint2 slo = lds_u64(tb + 1024 + g * 8), shi = lds_u64(tb + 1024 + (g + 8) * 8);
+                        const float2 l0 = __half22float2(*reinterpret_cast<const __half2 *>(&slo.x));
+                        const float2 l1 = __half22float2(*reinterpret_cast<const __half2 *>(&slo.y));
+                        const float2 h0 = __half22float2(*reinterpret_cast<const __half2 *>(&shi.x));
+                        const float2 h1 = __half22float2(*reinterpret_cast<const __half2 *>(&shi.y));
+                        dlo[0] = l0.x; dlo[1] = l0.y; dlo[T::TB - 2] = l1.x; dlo[T::TB - 1] = l1.y;
+                        dhi[0] = h0.x; dhi[1] = h0.y; dhi[T::TB - 2] = h1.x; dhi[T::TB - 1] = h1.y;
                     } else {
-                        const uint32_t a0 = lds_u32(q0 + 8 * t), a1 = lds_u32(q0 + 8 * t + 4), a2 = lds_u32(q0 + 8 * t + 8);
-                        const uint32_t b0 = lds_u32(q1 + 8 * t), b1 = lds_u32(q1 + 8 * t + 4), b2 = lds_u32(q1 + 8 * t + 8);
-                        we0[0] = __funnelshift_r(a0, a1, 16);
-                        we0[1] = __funnelshift_r(a1, a2, 16);
-                        we1[0] = __funnelshift_r(b0, b1, 16);
-                        we1[1] = __funnelshift_r(b1, b2, 16);
-                        wo0[0] = lds_u32(q0 + 36 + 8 * t);
-                        wo0[1] = lds_u32(q0 + 40 + 8 * t);
-                        wo1[0] = lds_u32(q1 + 36 + 8 * t);
-                        wo1[1] = lds_u32(q1 + 40 + 8 * t);
+                        const uint32_t slo = lds_u32(tb + 1024 + g * 4), shi = lds_u32(tb + 1024 + (g + 8) * 4);
+                        const float2 l0 = __half22float2(*reinterpret_cast<const __half2 *>(&slo));
+                        const float2 h0 = __half22float2(*reinterpret_cast<const __half2 *>(&shi));
+                        dlo[0] = l0.x; dlo[1] = l0.y;
+                        dhi[0] = h0.x; dhi[1] = h0.y;
                     }
-                    const float de0 = __half2float(lds_f16(q0)), de1 = __half2float(lds_f16(q1));
-                    float do0 = __half2float(lds_f16(q0 + T::BB)), do1 = __half2float(lds_f16(q1 + T::BB));
-                    if (2 * pr + 1 >= kcb) {  // odd tail block does not exist
-                        do0 = 0.f;
-                        do1 = 0.f;
-                    }
-                    const uint32_t b = (uint32_t)(c * T::KCB + 2 * pr);
+                    const uint32_t b0 = (uint32_t)((c * kTilesPerStage + ti) * T::TB);
 #pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        uint32_t a1[4], a2[4];
-                        if (e == 0) unpack<QT>(we0, we1, a1, a2);
-                        else unpack<QT>(wo0, wo1, a1, a2);
-                        const float dlo = e == 0 ? de0 : do0, dhi = e == 0 ? de1 : do1;
+                    for (int j = 0; j < T::TB; j++) {
+                        uint32_t w0[2], w1[2], a1[4], a2[4];
+                        if (QT == TLC_TYPE_Q4_0) {
+                            w0[0] = lo[j];
+                            w1[0] = hi[j];
+                            w0[1] = w1[1] = 0;
+                        } else {
+                            w0[0] = lo[2 * j];
+                            w0[1] = lo[2 * j + 1];
+                            w1[0] = hi[2 * j];
+                            w1[1] = hi[2 * j + 1];
+                        }
+                        unpack<QT>(w0, w1, a1, a2);
 #pragma unroll
                         for (int nt = 0; nt < NT; nt++) {
-                            const uint4 xp = lds_u128(xp_addr[nt] + (b + e) * xp_stride[nt]);
-                            const float2 ci = lds_f32x2(ci_addr + ((b + e) * NT + nt) * 32);
+                            const uint4 xp = lds_u128(xp_addr[nt] + (b0 + j) * xp_stride[nt]);
+                            const float2 ci = lds_f32x2(ci_addr + ((b0 + j) * NT + nt) * 32);
                             const float cc[4] = {ci.x, ci.y, ci.x, ci.y};
                             float d1[4], d2[4];
                             mma16816(d1, a1, xp.x, xp.y, cc);
                             mma16816(d2, a2, xp.z, xp.w, d1);
-                            acc[a][nt * 4 + 0] = fmaf(dlo, d2[0], acc[a][nt * 4 + 0]);
-                            acc[a][nt * 4 + 1] = fmaf(dlo, d2[1], acc[a][nt * 4 + 1]);
-                            acc[a][nt * 4 + 2] = fmaf(dhi, d2[2], acc[a][nt * 4 + 2]);
-                            acc[a][nt * 4 + 3] = fmaf(dhi, d2[3], acc[a][nt * 4 + 3]);
+                            acc[a][nt * 4 + 0] = fmaf(dlo[j], d2[0], acc[a][nt * 4 + 0]);
+                            acc[a][nt * 4 + 1] = fmaf(dlo[j], d2[1], acc[a][nt * 4 + 1]);
+                            acc[a][nt * 4 + 2] = fmaf(dhi[j], d2[2], acc[a][nt * 4 + 2]);
+                            acc[a][nt * 4 + 3] = fmaf(dhi[j], d2[3], acc[a][nt * 4 + 3]);
                         }
                     }
                 };
-                if (npairs == T::KCB / 2) {
+                if (ntiles == kTilesPerStage) {
 #pragma unroll
-                    for (int i = 0; i < T::KCB / 2 / kConsumerWarps; i++) do_pair(warp + i * kConsumerWarps);
+                    for (int i = 0; i < kTilesPerStage / kConsumerWarps; i++) do_tile(warp + i * kConsumerWarps);
                 } else {
-                    for (int pr = warp; pr < npairs; pr += kConsumerWarps) do_pair(pr);
+                    for (int ti = warp; ti < ntiles; ti += kConsumerWarps) do_tile(ti);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);

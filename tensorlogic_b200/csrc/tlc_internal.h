@@ -72,9 +72,11 @@ struct tlc_qtensor {
     int64_t n_cols;      // local cols (K of this rank)
     int64_t full_rows;   // unsharded shape
     int64_t full_cols;
-    size_t row_bytes;    // bytes of one local row (no padding)
-    size_t row_pitch;    // distance between rows in HBM: row_bytes rounded up to 16
-    size_t bytes;        // n_rows * row_pitch
+    size_t row_bytes;    // bytes of one local row as GGUF stores it (no padding)
+    size_t row_pitch;    // F16: distance between rows in HBM (row_bytes rounded up to 16); Q4_0 / Q8_0: 0
+    int64_t k_tiles;     // Q4_0 / Q8_0: tiles along K (tlc_tile.cuh); F16: 0
+    size_t slab_pitch;   // Q4_0 / Q8_0: bytes of one 16-row slab = k_tiles * tile bytes
+    size_t bytes;        // allocation: n_rows * row_pitch, or slabs * slab_pitch
     void *data;          // device
     int32_t tp_rank, tp_size, split;
 };

@@ -1,5 +1,6 @@
-// Quantized weights kept in HBM in their native GGUF block layout, the
-// device-side dequantizer, and the counter-based synthetic weight generator.
+// Quantized weights kept in HBM as their GGUF blocks (regrouped into 16-row
+// tiles, tlc_tile.cuh), the device-side dequantizer, and the counter-based
+// synthetic weight generator.
 //
 // Replaces the load-time CPU dequantization of the TensorLogic loaders
 // (src/model/formats/gguf.rs:22-112, :377-450; mmap_gguf.rs:383-439).
@@ -7,6 +8,7 @@
 
 #include "tlc_internal.h"
 #include "tlc_synth.cuh"
+#include "tlc_tile.cuh"
 
 // ---------------------------------------------------------------------------
 // Dequantization: one thread per block of 32.  Bit-exact with
@@ -14,14 +16,15 @@
 // low nibbles -> elements 0..15, high nibbles -> 16..31.  And with
 // dequantize_q8_0 (gguf.rs:22-53): f16_rne(float(q)*float(d)).
 // ---------------------------------------------------------------------------
-__global__ void dequant_q4_0_kernel(const uint8_t *__restrict__ data, size_t row_pitch,
+__global__ void dequant_q4_0_kernel(const uint8_t *__restrict__ data, int64_t ktiles,
                                     int blocks_per_row, int64_t n_rows, __half *__restrict__ out) {
     int64_t gb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t total = n_rows * blocks_per_row;
     if (gb >= total) return;
     int64_t row = gb / blocks_per_row;
     int bc = (int)(gb % blocks_per_row);
-    const uint8_t *blk = data + row * row_pitch + (size_t)bc * 18;
+    uint8_t blk[18];
+    tlc_tile::load_block(data, TLC_TYPE_Q4_0, ktiles, row, bc, blk);
     uint16_t dbits = (uint16_t)(blk[0] | (blk[1] << 8));
     float d = __half2float(__ushort_as_half(dbits));
     __half *o = out + (row * blocks_per_row + bc) * 32;
@@ -33,14 +36,15 @@ __global__ void dequant_q4_0_kernel(const uint8_t *__restrict__ data, size_t row
     }
 }
 
-__global__ void dequant_q8_0_kernel(const uint8_t *__restrict__ data, size_t row_pitch,
+__global__ void dequant_q8_0_kernel(const uint8_t *__restrict__ data, int64_t ktiles,
                                     int blocks_per_row, int64_t n_rows, __half *__restrict__ out) {
     int64_t gb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t total = n_rows * blocks_per_row;
     if (gb >= total) return;
     int64_t row = gb / blocks_per_row;
     int bc = (int)(gb % blocks_per_row);
-    const uint8_t *blk = data + row * row_pitch + (size_t)bc * 34;
+    uint8_t blk[34];
+    tlc_tile::load_block(data, TLC_TYPE_Q8_0, ktiles, row, bc, blk);
     uint16_t dbits = (uint16_t)(blk[0] | (blk[1] << 8));
     float d = __half2float(__ushort_as_half(dbits));
     __half *o = out + (row * blocks_per_row + bc) * 32;
@@ -49,6 +53,34 @@ __global__ void dequant_q8_0_kernel(const uint8_t *__restrict__ data, size_t row
         int8_t q = (int8_t)blk[2 + j];
         o[j] = __float2half_rn(__fmul_rn((float)q, d));
     }
+}
+
+// Regrouping of row-major GGUF blocks (`src`, rows src_pitch apart) into tiles
+// and back: one thread per block.
+__global__ void tile_blocks_kernel(const uint8_t *__restrict__ src, size_t src_pitch, int type, int blocks_per_row,
+                                   int64_t n_rows, int64_t ktiles, uint8_t *__restrict__ dst) {
+    int64_t gb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gb >= n_rows * blocks_per_row) return;
+    int64_t row = gb / blocks_per_row;
+    int bc = (int)(gb % blocks_per_row);
+    const int bb = tlc_tile::block_bytes(type);
+    const uint16_t *s16 = reinterpret_cast<const uint16_t *>(src + row * src_pitch + (size_t)bc * bb);
+    __align__(4) uint8_t blk[36];
+    for (int i = 0; i < bb / 2; i++) reinterpret_cast<uint16_t *>(blk)[i] = s16[i];
+    tlc_tile::store_block(dst, type, ktiles, row, bc, blk);
+}
+
+__global__ void untile_blocks_kernel(const uint8_t *__restrict__ data, int type, int blocks_per_row, int64_t n_rows,
+                                     int64_t ktiles, uint8_t *__restrict__ out) {
+    int64_t gb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gb >= n_rows * blocks_per_row) return;
+    int64_t row = gb / blocks_per_row;
+    int bc = (int)(gb % blocks_per_row);
+    const int bb = tlc_tile::block_bytes(type);
+    __align__(4) uint8_t blk[36];
+    tlc_tile::load_block(data, type, ktiles, row, bc, blk);
+    uint16_t *o16 = reinterpret_cast<uint16_t *>(out + (size_t)gb * bb);
+    for (int i = 0; i < bb / 2; i++) o16[i] = reinterpret_cast<const uint16_t *>(blk)[i];
 }
 
 // Q6_K (GGUFLoader::dequantize_q6_k, gguf.rs:128-218, the llama.cpp order): one
@@ -97,7 +129,7 @@ __global__ void copy_rows_f16_kernel(const uint8_t *__restrict__ data, size_t ro
 // stream is defined by tlc_synth.cuh and restated in numpy by the Python
 // package so that host- and device-generated weights are identical.
 // ---------------------------------------------------------------------------
-__global__ void synth_blocks_kernel(uint8_t *__restrict__ data, size_t row_pitch, int type,
+__global__ void synth_blocks_kernel(uint8_t *__restrict__ data, int64_t ktiles, int type,
                                     int blocks_per_row, int64_t n_rows, int64_t row0, int64_t bc0,
                                     int64_t full_blocks_per_row, uint64_t key, int scale_log2) {
     int64_t lb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -105,11 +137,12 @@ __global__ void synth_blocks_kernel(uint8_t *__restrict__ data, size_t row_pitch
     int64_t row = lb / blocks_per_row;
     int bc = (int)(lb % blocks_per_row);
     uint64_t gb = (uint64_t)((row0 + row) * full_blocks_per_row + bc0 + bc);
-    // The block is written straight to its (2-byte aligned) place in HBM.
+    __align__(8) uint8_t blk[40];
     if (type == TLC_TYPE_Q4_0)
-        tlc_synth_q4_0_block(key, gb, scale_log2, data + row * row_pitch + (size_t)bc * 18);
+        tlc_synth_q4_0_block(key, gb, scale_log2, blk);
     else
-        tlc_synth_q8_0_block(key, gb, scale_log2, data + row * row_pitch + (size_t)bc * 34);
+        tlc_synth_q8_0_block(key, gb, scale_log2, blk);
+    tlc_tile::store_block(data, type, ktiles, row, bc, blk);
 }
 
 // ---------------------------------------------------------------------------
@@ -166,11 +199,19 @@ static int32_t alloc_qtensor(tlc_ctx *ctx, int32_t type, int64_t rows, int64_t c
     qt->full_rows = full_rows;
     qt->full_cols = full_cols;
     qt->row_bytes = bytes_per_row(qt->type, cols);
-    // Rows start on 16-byte boundaries so that the GEMV can move them with
-    // 16-byte bulk copies; for column counts in multiples of 256 this pitch
-    // equals the GGUF row size and the tensor is a verbatim copy.
-    qt->row_pitch = (qt->row_bytes + 15) & ~(size_t)15;
-    qt->bytes = qt->row_pitch * (size_t)rows;
+    if (qt->type == TLC_TYPE_Q4_0 || qt->type == TLC_TYPE_Q8_0) {
+        // Tiles of 16 rows; rows past N and blocks past K stay zero.
+        qt->row_pitch = 0;
+        qt->k_tiles = tlc_tile::k_tiles(qt->type, cols);
+        qt->slab_pitch = (size_t)qt->k_tiles * tlc_tile::tile_bytes(qt->type);
+        qt->bytes = qt->slab_pitch * (size_t)tlc_tile::slabs(rows);
+    } else {
+        // Dense rows start on 16-byte boundaries.
+        qt->row_pitch = (qt->row_bytes + 15) & ~(size_t)15;
+        qt->k_tiles = 0;
+        qt->slab_pitch = 0;
+        qt->bytes = qt->row_pitch * (size_t)rows;
+    }
     qt->tp_rank = tp_rank;
     qt->tp_size = tp_size;
     qt->split = split;
@@ -260,10 +301,28 @@ extern "C" int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows
         col_off = (size_t)(col0 / 32) * tlc_block_bytes(type);
     }
     cudaError_t e = cudaMemsetAsync(qt->data, 0, qt->bytes + 16, ctx->stream);
-    if (e == cudaSuccess)
+    void *tmp = nullptr;
+    if (qt->slab_pitch) {
+        // The shard's rows go to a staging buffer as the file has them; a kernel regroups them.
+        if (e == cudaSuccess) e = cudaMalloc(&tmp, qt->row_bytes * (size_t)rows);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(tmp, qt->row_bytes, src + (size_t)row0 * src_pitch + col_off, src_pitch,
+                                  qt->row_bytes, (size_t)rows, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) {
+            const int bpr = (int)(cols / 32);
+            const int64_t total = rows * bpr;
+            tile_blocks_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
+                static_cast<const uint8_t *>(tmp), qt->row_bytes, qt->type, bpr, rows, qt->k_tiles,
+                static_cast<uint8_t *>(qt->data));
+            ctx->launches++;
+            e = cudaGetLastError();
+        }
+    } else if (e == cudaSuccess) {
         e = cudaMemcpy2DAsync(qt->data, qt->row_pitch, src + (size_t)row0 * src_pitch + col_off, src_pitch,
                               qt->row_bytes, (size_t)rows, cudaMemcpyHostToDevice, ctx->stream);
+    }
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // `blocks`/`conv` may go away
+    if (tmp) cudaFree(tmp);
     if (e != cudaSuccess) {
         cudaGetLastError();
         cudaFree(qt->data);
@@ -299,7 +358,7 @@ extern "C" int32_t tlc_qtensor_create_synthetic(tlc_ctx *ctx, int32_t type, int6
     int threads = 256;
     int64_t grid = (total + threads - 1) / threads;
     synth_blocks_kernel<<<(unsigned)grid, threads, 0, ctx->stream>>>(
-        static_cast<uint8_t *>(qt->data), qt->row_pitch, type, bpr, rows, row0, col0 / 32, n_cols / 32,
+        static_cast<uint8_t *>(qt->data), qt->k_tiles, type, bpr, rows, row0, col0 / 32, n_cols / 32,
         tlc_synth_key(seed, tensor_id), scale_log2);
     ctx->launches++;
     e = cudaGetLastError();
@@ -388,7 +447,7 @@ extern "C" int32_t tlc_qtensor_info(tlc_qtensor *qt, int32_t *type, int64_t *n_r
     if (type) *type = qt->type;
     if (n_rows) *n_rows = qt->n_rows;
     if (n_cols) *n_cols = qt->n_cols;
-    if (row_pitch) *row_pitch = qt->row_pitch;
+    if (row_pitch) *row_pitch = qt->slab_pitch ? qt->row_bytes : qt->row_pitch;
     if (dev_ptr) *dev_ptr = qt->data;
     return TLC_OK;
 }
@@ -430,10 +489,28 @@ extern "C" int32_t tlc_dequant(tlc_ctx *ctx, tlc_qtensor *qt, void *out_f16_dev)
         int64_t total = qt->n_rows * bpr;
         unsigned grid = (unsigned)((total + threads - 1) / threads);
         if (qt->type == TLC_TYPE_Q4_0)
-            dequant_q4_0_kernel<<<grid, threads, 0, ctx->stream>>>(data, qt->row_pitch, bpr, qt->n_rows, out);
+            dequant_q4_0_kernel<<<grid, threads, 0, ctx->stream>>>(data, qt->k_tiles, bpr, qt->n_rows, out);
         else
-            dequant_q8_0_kernel<<<grid, threads, 0, ctx->stream>>>(data, qt->row_pitch, bpr, qt->n_rows, out);
+            dequant_q8_0_kernel<<<grid, threads, 0, ctx->stream>>>(data, qt->k_tiles, bpr, qt->n_rows, out);
     }
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
+
+extern "C" int32_t tlc_qtensor_blocks(tlc_ctx *ctx, tlc_qtensor *qt, void *out_dev) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(qt && out_dev, TLC_ERR_INVALID_OPERATION, "tlc_qtensor_blocks: null pointer");
+    TLC_REQUIRE(qt->ctx->device == ctx->device, TLC_ERR_DEVICE, "tlc_qtensor_blocks: tensor lives on device %d, context on %d",
+                qt->ctx->device, ctx->device);
+    if (!qt->slab_pitch) {
+        TLC_CUDA(cudaMemcpy2DAsync(out_dev, qt->row_bytes, qt->data, qt->row_pitch, qt->row_bytes, (size_t)qt->n_rows,
+                                   cudaMemcpyDeviceToDevice, ctx->stream));
+        return TLC_OK;
+    }
+    const int bpr = (int)(qt->n_cols / 32);
+    const int64_t total = qt->n_rows * bpr;
+    untile_blocks_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
+        static_cast<const uint8_t *>(qt->data), qt->type, bpr, qt->n_rows, qt->k_tiles, static_cast<uint8_t *>(out_dev));
     TLC_CHECK_LAUNCH(ctx);
     return TLC_OK;
 }
