@@ -65,7 +65,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
         // ------------------------------ producer ------------------------------
         // Weights are never written by a kernel, so the ring starts filling
         // before the previous kernel of the stream has finished.
-        uint32_t it = 0;
+        int rs = 0;
+        uint32_t rpar = 1;
         const int pu_lo = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
         const int pu_hi = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
         const int pcount = p.contig ? pu_hi - pu_lo
@@ -82,12 +83,15 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                 }
                 const uint8_t *wbase = ti == 0 ? p.t[0].w : ti == 1 ? p.t[1].w : p.t[2].w;
                 const size_t spitch = ti == 0 ? p.t[0].slab_pitch : ti == 1 ? p.t[1].slab_pitch : p.t[2].slab_pitch;
-                for (int c = 0; c < p.nchunks; c++, it++) {
-                    const int s = it % S;
-                    const uint32_t par = ((it / S) & 1u) ^ 1u;
+                for (int c = 0; c < p.nchunks; c++) {
+                    const int s = rs;
                     // On a timeout the producer stops issuing copies; the consumers'
                     // own bounded waits then end the CTA.
-                    if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], par, abort_flag, p.status, 1, p.wait_ns))) return;
+                    if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], rpar, abort_flag, p.status, 1, p.wait_ns))) return;
+                    if (++rs == S) {
+                        rs = 0;
+                        rpar ^= 1u;
+                    }
                     // The stage's tiles are contiguous in HBM: one bulk copy.
                     const int ntiles = min(kTilesPerStage, p.ktiles - c * kTilesPerStage);
                     const uint32_t bytes = (uint32_t)(ntiles * TILE);
@@ -241,8 +245,28 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
     const int n_mine = p.contig ? u_hi - u_lo
                                 : ((int)p.total_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int ub = AS / p.subs;  // units per batch
-    uint32_t it = 0;
+    int rs = 0;           // ring position and its parity, carried from stage to stage
+    uint32_t rpar = 0;
     int batch_count = 0;
+
+    // Words and scales of one tile for this lane: rows g (lo) and g + 8 (hi).
+    struct TileRegs {
+        uint4 vlo, vhi;
+        uint32_t slo[2], shi[2];
+    };
+    auto load_tile = [&](TileRegs &r, uint32_t tb) {
+        r.vlo = lds_u128(tb + lane * 16);
+        r.vhi = lds_u128(tb + 512 + lane * 16);
+        if (QT == TLC_TYPE_Q4_0) {
+            const uint2 a = lds_u64(tb + 1024 + g * 8), b = lds_u64(tb + 1024 + (g + 8) * 8);
+            r.slo[0] = a.x; r.slo[1] = a.y;
+            r.shi[0] = b.x; r.shi[1] = b.y;
+        } else {
+            r.slo[0] = lds_u32(tb + 1024 + g * 4);
+            r.shi[0] = lds_u32(tb + 1024 + (g + 8) * 4);
+            r.slo[1] = r.shi[1] = 0;
+        }
+    };
 
     for (int i0 = 0; i0 < n_mine; i0 += ub, batch_count++) {
         const int nsets = min(ub, n_mine - i0) * p.subs;
@@ -255,76 +279,97 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
 #pragma unroll
         for (int a = 0; a < AS; a++) {
             if (a >= nsets) break;
-            for (int c = 0; c < p.nchunks; c++, it++) {
-                const int s = it % S;
-                const uint32_t par = (it / S) & 1u;
+            // The math of one tile, block by block; B fragments and accumulator
+            // start values of block j + 1 are fetched while block j is in the
+            // tensor cores.  b0: first block of the tile.
+            auto do_tile = [&](const TileRegs &r, uint32_t b0) {
+                const uint32_t lo[4] = {r.vlo.x, r.vlo.y, r.vlo.z, r.vlo.w};
+                const uint32_t hi[4] = {r.vhi.x, r.vhi.y, r.vhi.z, r.vhi.w};
+                float dlo[4], dhi[4];
+#pragma unroll
+                for (int h = 0; h < T::TB / 2; h++) {
+                    const float2 l = __half22float2(*reinterpret_cast<const __half2 *>(&r.slo[h]));
+                    const float2 u = __half22float2(*reinterpret_cast<const __half2 *>(&r.shi[h]));
+                    dlo[2 * h] = l.x; dlo[2 * h + 1] = l.y;
+                    dhi[2 * h] = u.x; dhi[2 * h + 1] = u.y;
+                }
+                uint32_t xa[NT], ca = ci_addr + b0 * (NT * 32);
+                uint4 xp[NT];
+                float2 ci[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    xa[nt] = xp_addr[nt] + b0 * xp_stride[nt];
+                    xp[nt] = lds_u128(xa[nt]);
+                    ci[nt] = lds_f32x2(ca + nt * 32);
+                }
+#pragma unroll
+                for (int j = 0; j < T::TB; j++) {
+                    uint32_t w0[2], w1[2], a1[4], a2[4];
+                    if (QT == TLC_TYPE_Q4_0) {
+                        w0[0] = lo[j];
+                        w1[0] = hi[j];
+                        w0[1] = w1[1] = 0;
+                    } else {
+                        w0[0] = lo[2 * j];
+                        w0[1] = lo[2 * j + 1];
+                        w1[0] = hi[2 * j];
+                        w1[1] = hi[2 * j + 1];
+                    }
+                    unpack<QT>(w0, w1, a1, a2);
+                    uint4 xc[NT];
+                    float2 cc2[NT];
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        xc[nt] = xp[nt];
+                        cc2[nt] = ci[nt];
+                        if (j + 1 < T::TB) {
+                            xa[nt] += xp_stride[nt];
+                            xp[nt] = lds_u128(xa[nt]);
+                            ci[nt] = lds_f32x2(ca + ((j + 1) * NT + nt) * 32);
+                        }
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        const float cc[4] = {cc2[nt].x, cc2[nt].y, cc2[nt].x, cc2[nt].y};
+                        float d1[4], d2[4];
+                        mma16816(d1, a1, xc[nt].x, xc[nt].y, cc);
+                        mma16816(d2, a2, xc[nt].z, xc[nt].w, d1);
+                        acc[a][nt * 4 + 0] = fmaf(dlo[j], d2[0], acc[a][nt * 4 + 0]);
+                        acc[a][nt * 4 + 1] = fmaf(dlo[j], d2[1], acc[a][nt * 4 + 1]);
+                        acc[a][nt * 4 + 2] = fmaf(dhi[j], d2[2], acc[a][nt * 4 + 2]);
+                        acc[a][nt * 4 + 3] = fmaf(dhi[j], d2[3], acc[a][nt * 4 + 3]);
+                    }
+                }
+            };
+            for (int c = 0; c < p.nchunks; c++) {
                 // A wait that ran out skips the math but keeps the barrier protocol
                 // going, so every warp still reaches the same bar.sync calls.
-                const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], par, abort_flag, p.status, 2, p.wait_ns));
+                const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[rs], rpar, abort_flag, p.status, 2, p.wait_ns));
                 const int ntiles = ready ? min(kTilesPerStage, p.ktiles - c * kTilesPerStage) : 0;
-                const uint32_t sbase = stages_addr + (uint32_t)s * STAGE_BYTES;
-
-                // One tile: TB blocks x 16 rows.  Lane (g, t) reads the words of rows g and
-                // g + 8 with two 16-byte loads, and the rows' block scales.
-                auto do_tile = [&](int ti) {
-                    const uint32_t tb = sbase + (uint32_t)ti * TILE;
-                    const uint4 vlo = lds_u128(tb + lane * 16);
-                    const uint4 vhi = lds_u128(tb + 512 + lane * 16);
-                    const uint32_t lo[4] = {vlo.x, vlo.y, vlo.z, vlo.w}, hi[4] = {vhi.x, vhi.y, vhi.z, vhi.w};
-                    float dlo[T::TB], dhi[T::TB];
-                    if (QT == TLC_TYPE_Q4_0) {
-                        const uint2 slo = lds_u64(tb + 1024 + g * 8), shi = lds_u64(tb + 1024 + (g + 8) * 8);
-                        const float2 l0 = __half22float2(*reinterpret_cast<const __half2 *>(&slo.x));
-                        const float2 l1 = __half22float2(*reinterpret_cast<const __half2 *>(&slo.y));
-                        const float2 h0 = __half22float2(*reinterpret_cast<const __half2 *>(&shi.x));
-                        const float2 h1 = __half22float2(*reinterpret_cast<const __half2 *>(&shi.y));
-                        dlo[0] = l0.x; dlo[1] = l0.y; dlo[T::TB - 2] = l1.x; dlo[T::TB - 1] = l1.y;
-                        dhi[0] = h0.x; dhi[1] = h0.y; dhi[T::TB - 2] = h1.x; dhi[T::TB - 1] = h1.y;
-                    } else {
-                        const uint32_t slo = lds_u32(tb + 1024 + g * 4), shi = lds_u32(tb + 1024 + (g + 8) * 4);
-                        const float2 l0 = __half22float2(*reinterpret_cast<const __half2 *>(&slo));
-                        const float2 h0 = __half22float2(*reinterpret_cast<const __half2 *>(&shi));
-                        dlo[0] = l0.x; dlo[1] = l0.y;
-                        dhi[0] = h0.x; dhi[1] = h0.y;
-                    }
-                    const uint32_t b0 = (uint32_t)((c * kTilesPerStage + ti) * T::TB);
-#pragma unroll
-                    for (int j = 0; j < T::TB; j++) {
-                        uint32_t w0[2], w1[2], a1[4], a2[4];
-                        if (QT == TLC_TYPE_Q4_0) {
-                            w0[0] = lo[j];
-                            w1[0] = hi[j];
-                            w0[1] = w1[1] = 0;
-                        } else {
-                            w0[0] = lo[2 * j];
-                            w0[1] = lo[2 * j + 1];
-                            w1[0] = hi[2 * j];
-                            w1[1] = hi[2 * j + 1];
-                        }
-                        unpack<QT>(w0, w1, a1, a2);
-#pragma unroll
-                        for (int nt = 0; nt < NT; nt++) {
-                            const uint4 xp = lds_u128(xp_addr[nt] + (b0 + j) * xp_stride[nt]);
-                            const float2 ci = lds_f32x2(ci_addr + ((b0 + j) * NT + nt) * 32);
-                            const float cc[4] = {ci.x, ci.y, ci.x, ci.y};
-                            float d1[4], d2[4];
-                            mma16816(d1, a1, xp.x, xp.y, cc);
-                            mma16816(d2, a2, xp.z, xp.w, d1);
-                            acc[a][nt * 4 + 0] = fmaf(dlo[j], d2[0], acc[a][nt * 4 + 0]);
-                            acc[a][nt * 4 + 1] = fmaf(dlo[j], d2[1], acc[a][nt * 4 + 1]);
-                            acc[a][nt * 4 + 2] = fmaf(dhi[j], d2[2], acc[a][nt * 4 + 2]);
-                            acc[a][nt * 4 + 3] = fmaf(dhi[j], d2[3], acc[a][nt * 4 + 3]);
-                        }
-                    }
-                };
+                const uint32_t sbase = stages_addr + (uint32_t)rs * STAGE_BYTES;
+                const uint32_t cb0 = (uint32_t)(c * kTilesPerStage * T::TB);  // first block of the stage
                 if (ntiles == kTilesPerStage) {
-#pragma unroll
-                    for (int i = 0; i < kTilesPerStage / kConsumerWarps; i++) do_tile(warp + i * kConsumerWarps);
+                    // Lane (g, t) reads the words of rows g and g + 8 of its warp's two tiles
+                    // up front (four 16-byte loads), then runs the blocks.
+                    static_assert(kTilesPerStage == 2 * kConsumerWarps, "two tiles per warp and stage");
+                    TileRegs r0, r1;
+                    load_tile(r0, sbase + (uint32_t)warp * TILE);
+                    load_tile(r1, sbase + (uint32_t)(warp + kConsumerWarps) * TILE);
+                    do_tile(r0, cb0 + (uint32_t)warp * T::TB);
+                    do_tile(r1, cb0 + (uint32_t)(warp + kConsumerWarps) * T::TB);
                 } else {
-                    for (int ti = warp; ti < ntiles; ti += kConsumerWarps) do_tile(ti);
+                    for (int ti = warp; ti < ntiles; ti += kConsumerWarps) {
+                        TileRegs r0;
+                        load_tile(r0, sbase + (uint32_t)ti * TILE);
+                        do_tile(r0, cb0 + (uint32_t)ti * T::TB);
+                    }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[s]);
+                if (lane == 0) mbar_arrive(&empty[rs]);
+                if (++rs == S) {
+                    rs = 0;
+                    rpar ^= 1u;
+                }
             }
         }
 
