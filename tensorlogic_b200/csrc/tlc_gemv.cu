@@ -123,13 +123,13 @@ __global__ void __launch_bounds__(256) linear_f16_kernel(const uint8_t *__restri
     }
 }
 
-template <int QT, int NT, int AS>
+template <int QT, int NT, int AS, bool M1>
 int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)ctx->prop.sharedMemPerBlockOptin));
-        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                       cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 63] = true;
     }
@@ -143,7 +143,7 @@ int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<QT, NT, AS>, p);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<QT, NT, AS, M1>, p);
     if (le != cudaSuccess) {
         cudaGetLastError();
         return tlc_fail(TLC_ERR_CUDA, "gemv launch failed: %s", cudaGetErrorString(le));
@@ -168,8 +168,8 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     // (Measured on the TinyLlama decode step: keeping small launches at one CTA per
     // SM, to leave room for the next kernel's early CTAs, costs 8 % against
     // letting them spread over two CTAs per SM.)
-    const bool two = fits_half;
-    const size_t cap = fits_half ? half : budget;
+    const bool two = fits_half && kCtasPerSm == 2;
+    const size_t cap = two ? half : budget;
     const int max_ctas = two ? 2 * ctx->sm_count : ctx->sm_count;
     const int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
     // Accumulator sets per reduction: enough units for about four ring stages
@@ -192,9 +192,16 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     p.pdl_mode = ctx->pdl_mode;
     p.contig = units_per_cta <= 4 ? 1 : 0;
     const size_t smem = smem_fixed + (size_t)stages * STAGE_BYTES;
-    if (as == 1) return launch_mma_as<QT, NT, 1>(ctx, p, grid, smem);
-    if (as == 2) return launch_mma_as<QT, NT, 2>(ctx, p, grid, smem);
-    return launch_mma_as<QT, NT, 4>(ctx, p, grid, smem);
+    if constexpr (NT == 1) {
+        if (p.m == 1) {  // the decode step of one sequence
+            if (as == 1) return launch_mma_as<QT, 1, 1, true>(ctx, p, grid, smem);
+            if (as == 2) return launch_mma_as<QT, 1, 2, true>(ctx, p, grid, smem);
+            return launch_mma_as<QT, 1, 4, true>(ctx, p, grid, smem);
+        }
+    }
+    if (as == 1) return launch_mma_as<QT, NT, 1, false>(ctx, p, grid, smem);
+    if (as == 2) return launch_mma_as<QT, NT, 2, false>(ctx, p, grid, smem);
+    return launch_mma_as<QT, NT, 4, false>(ctx, p, grid, smem);
 }
 
 size_t gemv_fixed_smem(int nblk_pad, int m, int nt) { return fixed_smem_bytes(nblk_pad, m, nt, 2); }

@@ -6,26 +6,32 @@
 namespace tlc_gemv {
 
 // Shared-memory layout (bytes from the start of dynamic shared memory):
-//   0    full[8], empty[8] mbarriers
-//   128  abort flag
-//   256  sum-of-squares partials [16 activation rows][8 warps]
-//   768  red   [2][AS sets][8 warps][16 rows][MP] f32   cross-warp reduction, double buffered
-//   ...  cinit [nblk_pad][NT][4 quad lanes] float2  accumulator start per block (columns 2t, 2t+1)
+//   0    full[12] mbarriers      128  empty[12] mbarriers      256  abort flag
+//   512  sum-of-squares partials [16 activation rows][consumer warps]
+//   1536 red   [2][AS sets][consumer warps][16 rows][MP] f32   cross-warp reduction, double buffered
+//   ...  cinit [nblk_pad][NT][4 quad lanes] float2  accumulator start per block (columns 2t, 2t+1);
+//              with one activation row: [nblk_pad] float4, the start value four times (a whole
+//              C fragment in one load; columns past the first are never read back)
 //   ...  xzero one zero uint4 (B fragment of activation rows that do not exist)
 //   ...  xperm [nblk_pad][m][4 quad lanes] uint4    activations in fragment order
 //   ...  ring  [stages][16 tiles]                   weight tiles as they lie in HBM (128-byte aligned)
 __host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, int as) {
-    size_t s = 768;
+    size_t s = kHeaderBytes;
     s += (size_t)2 * as * kConsumerWarps * kRows * (8 * nt) * sizeof(float);
-    s += (size_t)nblk_pad * nt * 4 * sizeof(float2);
+    s += m == 1 ? (size_t)nblk_pad * sizeof(float4) : (size_t)nblk_pad * nt * 4 * sizeof(float2);
     s += sizeof(uint4);
     s += (size_t)nblk_pad * m * 4 * sizeof(uint4);
     s += 128;  // ring alignment slack
     return s;
 }
 
-template <int QT, int NT, int AS>
-__global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams p) {
+// M1: exactly one activation row (the decode step of one sequence).  Columns 1-7
+// of the 16x8 tensor-core tile are then never read back, so every lane may load
+// the same B fragments and accumulator start values: their shared-memory
+// addresses become warp-uniform with compile-time strides.
+template <int QT, int NT, int AS, bool M1>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const GemvParams p) {
+    static_assert(!M1 || NT == 1, "one activation row needs one column tile");
     using T = QTraits<QT>;
     constexpr int MP = 8 * NT;  // padded activation rows
     constexpr int TILE = T::TILE_BYTES;
@@ -33,12 +39,14 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-    uint64_t *empty = full + kMaxStages;
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 128);
-    float *sq_part = reinterpret_cast<float *>(smem + 256);
-    float *red = reinterpret_cast<float *>(smem + 768);
+    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + 128);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 256);
+    float *sq_part = reinterpret_cast<float *>(smem + 512);
+    float *red = reinterpret_cast<float *>(smem + kHeaderBytes);
+    static_assert(kMaxStages * 8 <= 128 && 512 + 16 * kConsumerWarps * 4 <= kHeaderBytes, "header layout");
     float2 *cinit = reinterpret_cast<float2 *>(red + 2 * AS * kConsumerWarps * kRows * MP);
-    uint4 *xzero = reinterpret_cast<uint4 *>(cinit + (size_t)p.nblk_pad * NT * 4);
+    uint4 *xzero = M1 ? reinterpret_cast<uint4 *>(reinterpret_cast<float4 *>(cinit) + p.nblk_pad)
+                      : reinterpret_cast<uint4 *>(cinit + (size_t)p.nblk_pad * NT * 4);
     uint4 *xperm = xzero + 1;
     uint8_t *stages = reinterpret_cast<uint8_t *>(xperm + (size_t)p.nblk_pad * p.m * 4);
     stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(stages) + 127) & ~(uintptr_t)127);
@@ -131,7 +139,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
             if (lane == 0) sq_part[m * kConsumerWarps + warp] = sq;
         }
     }
-    for (int i = ctid; i < p.nblk_pad * NT * 4; i += kConsumerThreads) cinit[i] = make_float2(0.f, 0.f);
+    for (int i = ctid; i < (M1 ? p.nblk_pad * 2 : p.nblk_pad * NT * 4); i += kConsumerThreads)
+        cinit[i] = make_float2(0.f, 0.f);
     if (ctid == 0) *xzero = make_uint4(0, 0, 0, 0);
     consumer_bar();
 
@@ -211,8 +220,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                     // Column m of the 16x8 tile sits in the C fragment of quad lane (m%8)/2,
                     // components m%2 (row g) and m%2 + 2 (row g+8).
                     const float cv = -T::OFFSET * 5.9604644775390625e-08f * s;  // * 2^-24
-                    float *cf = reinterpret_cast<float *>(&cinit[(b * NT + (m >> 3)) * 4 + ((m & 7) >> 1)]);
-                    cf[m & 1] = cv;  // rows g and g+8 of the tile start from the same value
+                    if (M1) {
+                        reinterpret_cast<float4 *>(cinit)[b] = make_float4(cv, cv, cv, cv);
+                    } else {
+                        float *cf = reinterpret_cast<float *>(&cinit[(b * NT + (m >> 3)) * 4 + ((m & 7) >> 1)]);
+                        cf[m & 1] = cv;  // rows g and g+8 of the tile start from the same value
+                    }
                 }
             }
         }
@@ -228,10 +241,10 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const bool has = nt * 8 + g < p.m;
-        xp_addr[nt] = has ? smem_u32(xperm + (nt * 8 + g) * 4 + t) : smem_u32(xzero);
-        xp_stride[nt] = has ? (uint32_t)p.m * 64u : 0u;
+        xp_addr[nt] = M1 ? smem_u32(xperm + t) : has ? smem_u32(xperm + (nt * 8 + g) * 4 + t) : smem_u32(xzero);
+        xp_stride[nt] = M1 ? 64u : has ? (uint32_t)p.m * 64u : 0u;
     }
-    const uint32_t ci_addr = smem_u32(cinit + t);
+    const uint32_t ci_addr = M1 ? smem_u32(cinit) : smem_u32(cinit + t);
     const uint32_t stages_addr = smem_u32(stages);
 
     // Units of this CTA: with only a few per CTA a balanced contiguous range
@@ -293,6 +306,42 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                     dlo[2 * h] = l.x; dlo[2 * h + 1] = l.y;
                     dhi[2 * h] = u.x; dhi[2 * h + 1] = u.y;
                 }
+                if (M1) {
+                    // B fragments 64 bytes and start values 16 bytes apart from block to block
+                    const uint32_t xa = xp_addr[0] + b0 * 64u, ca = ci_addr + b0 * 16u;
+                    uint4 xp = lds_u128(xa);
+                    uint4 ci = lds_u128(ca);
+#pragma unroll
+                    for (int j = 0; j < T::TB; j++) {
+                        uint32_t w0[2], w1[2], a1[4], a2[4];
+                        if (QT == TLC_TYPE_Q4_0) {
+                            w0[0] = lo[j];
+                            w1[0] = hi[j];
+                            w0[1] = w1[1] = 0;
+                        } else {
+                            w0[0] = lo[2 * j];
+                            w0[1] = lo[2 * j + 1];
+                            w1[0] = hi[2 * j];
+                            w1[1] = hi[2 * j + 1];
+                        }
+                        unpack<QT>(w0, w1, a1, a2);
+                        const uint4 xc = xp, cq = ci;
+                        if (j + 1 < T::TB) {
+                            xp = lds_u128(xa + (j + 1) * 64);
+                            ci = lds_u128(ca + (j + 1) * 16);
+                        }
+                        const float cc[4] = {__uint_as_float(cq.x), __uint_as_float(cq.y), __uint_as_float(cq.z),
+                                             __uint_as_float(cq.w)};
+                        float d1[4], d2[4];
+                        mma16816(d1, a1, xc.x, xc.y, cc);
+                        mma16816(d2, a2, xc.z, xc.w, d1);
+                        acc[a][0] = fmaf(dlo[j], d2[0], acc[a][0]);
+                        acc[a][1] = fmaf(dlo[j], d2[1], acc[a][1]);
+                        acc[a][2] = fmaf(dhi[j], d2[2], acc[a][2]);
+                        acc[a][3] = fmaf(dhi[j], d2[3], acc[a][3]);
+                    }
+                    return;
+                }
                 uint32_t xa[NT], ca = ci_addr + b0 * (NT * 32);
                 uint4 xp[NT];
                 float2 ci[NT];
@@ -351,12 +400,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_mma_kernel(const GemvParams 
                 if (ntiles == kTilesPerStage) {
                     // Lane (g, t) reads the words of rows g and g + 8 of its warp's two tiles
                     // up front (four 16-byte loads), then runs the blocks.
-                    static_assert(kTilesPerStage == 2 * kConsumerWarps, "two tiles per warp and stage");
-                    TileRegs r0, r1;
-                    load_tile(r0, sbase + (uint32_t)warp * TILE);
-                    load_tile(r1, sbase + (uint32_t)(warp + kConsumerWarps) * TILE);
-                    do_tile(r0, cb0 + (uint32_t)warp * T::TB);
-                    do_tile(r1, cb0 + (uint32_t)(warp + kConsumerWarps) * T::TB);
+                    constexpr int TPW = kTilesPerStage / kConsumerWarps;  // tiles per warp and stage
+                    static_assert(TPW * kConsumerWarps == kTilesPerStage && TPW >= 1, "whole tiles per warp");
+                    TileRegs r[TPW];
+#pragma unroll
+                    for (int i = 0; i < TPW; i++) load_tile(r[i], sbase + (uint32_t)(warp + i * kConsumerWarps) * TILE);
+#pragma unroll
+                    for (int i = 0; i < TPW; i++) do_tile(r[i], cb0 + (uint32_t)(warp + i * kConsumerWarps) * T::TB);
                 } else {
                     for (int ti = warp; ti < ntiles; ti += kConsumerWarps) {
                         TileRegs r0;
