@@ -335,10 +335,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
                         float d1[4], d2[4];
                         mma16816(d1, a1, xc.x, xc.y, cc);
                         mma16816(d2, a2, xc.z, xc.w, d1);
+                        // only column 0 of the tile (d2[0], d2[2] of quad lane 0) is ever read back
                         acc[a][0] = fmaf(dlo[j], d2[0], acc[a][0]);
-                        acc[a][1] = fmaf(dlo[j], d2[1], acc[a][1]);
                         acc[a][2] = fmaf(dhi[j], d2[2], acc[a][2]);
-                        acc[a][3] = fmaf(dhi[j], d2[3], acc[a][3]);
                     }
                     return;
                 }
