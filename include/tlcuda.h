@@ -206,6 +206,18 @@ TLC_API int32_t tlc_qtensor_info(tlc_qtensor *qt, int32_t *type, int64_t *n_rows
  * n_rows * n_cols/32 blocks, no padding) to device memory: the inverse of the
  * regrouping done at upload, bit for bit.  F16 tensors are copied row by row. */
 TLC_API int32_t tlc_qtensor_blocks(tlc_ctx *ctx, tlc_qtensor *qt, void *out_dev);
+/* The regrouping on the host (no GPU needed): bytes a Q4_0 / Q8_0 tensor of this shape
+ * occupies in HBM, and the tiled image of row-major GGUF blocks (what tlc_qtensor_create
+ * stores: dev_ptr of tlc_qtensor_info points at exactly these bytes).  Tiles of 16 rows,
+ * [slab = row / 16][k-tile]; a Q4_0 tile is 16 rows x 4 blocks = 1152 bytes: 16-byte groups
+ * [row / 8 % 2][row % 8][t] holding quant word t (bytes 4t..4t+3 of qs) of the row's four
+ * blocks, then [row][block] f16 scales at byte 1024; a Q8_0 tile is 16 rows x 2 blocks =
+ * 1088 bytes: group [..][..][t] holds words 2t, 2t+1 of block 0, then of block 1; scales at
+ * byte 1024.  Rows past n_rows and blocks past n_cols / 32 are zero.  No counterpart
+ * upstream (the reference keeps dequantized f16 rows). */
+TLC_API size_t tlc_tiled_bytes(int32_t type, int64_t n_rows, int64_t n_cols);
+TLC_API int32_t tlc_tile_blocks_host(int32_t type, int64_t n_rows, int64_t n_cols,
+                                     const void *blocks, void *tiles_out);
 /* Device-side GGUFLoader::dequantize_q4_0 / _q8_0: writes the n_rows*n_cols
  * f16 values of the local shard; bit-exact with the reference. */
 TLC_API int32_t tlc_dequant(tlc_ctx *ctx, tlc_qtensor *qt, void *out_f16_dev);

@@ -85,6 +85,8 @@ PROTOTYPES = {
     "tlc_qtensor_destroy": (i32, [vp]),
     "tlc_qtensor_info": (i32, [vp, P(i32), P(i64), P(i64), P(sz), P(vp)]),
     "tlc_qtensor_blocks": (i32, [vp, vp, vp]),
+    "tlc_tiled_bytes": (sz, [i32, i64, i64]),
+    "tlc_tile_blocks_host": (i32, [i32, i64, i64, vp, vp]),
     "tlc_dequant": (i32, [vp, vp, vp]),
     "tlc_linear": (i32, [vp, vp, vp, i32, i64, vp, vp]),
     "tlc_linear_host": (i32, [vp, vp, vp, i32, i64, vp, vp]),

@@ -514,3 +514,24 @@ extern "C" int32_t tlc_qtensor_blocks(tlc_ctx *ctx, tlc_qtensor *qt, void *out_d
     TLC_CHECK_LAUNCH(ctx);
     return TLC_OK;
 }
+
+extern "C" size_t tlc_tiled_bytes(int32_t type, int64_t n_rows, int64_t n_cols) {
+    if ((type != TLC_TYPE_Q4_0 && type != TLC_TYPE_Q8_0) || n_rows <= 0 || n_cols <= 0) return 0;
+    return (size_t)tlc_tile::slabs(n_rows) * (size_t)tlc_tile::k_tiles(type, n_cols) * tlc_tile::tile_bytes(type);
+}
+
+extern "C" int32_t tlc_tile_blocks_host(int32_t type, int64_t n_rows, int64_t n_cols, const void *blocks,
+                                        void *tiles_out) {
+    TLC_REQUIRE(type == TLC_TYPE_Q4_0 || type == TLC_TYPE_Q8_0, TLC_ERR_INVALID_OPERATION,
+                "tile_blocks_host: type %d is not stored in tiles", type);
+    TLC_REQUIRE(blocks && tiles_out && n_rows > 0 && n_cols > 0 && n_cols % 32 == 0, TLC_ERR_INVALID_OPERATION,
+                "tile_blocks_host: bad arguments");
+    const int64_t bpr = n_cols / 32, ktiles = tlc_tile::k_tiles(type, n_cols);
+    const int bb = tlc_tile::block_bytes(type);
+    uint8_t *dst = static_cast<uint8_t *>(tiles_out);
+    memset(dst, 0, tlc_tiled_bytes(type, n_rows, n_cols));
+    const uint8_t *src = static_cast<const uint8_t *>(blocks);
+    for (int64_t r = 0; r < n_rows; r++)
+        for (int64_t b = 0; b < bpr; b++) tlc_tile::store_block(dst, type, ktiles, r, b, src + (size_t)(r * bpr + b) * bb);
+    return TLC_OK;
+}

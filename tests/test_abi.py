@@ -96,3 +96,45 @@ def test_synthetic_distributions():
     assert abs(x.mean()) < 0.02 and abs(x.std() - 1.0) < 0.02
     ids = synth.token_ids(0, "ids", 4096, 32000)
     assert ids.min() >= 0 and ids.max() < 32000 and len(np.unique(ids)) > 3800
+
+
+def _tile_numpy(qtype, n_rows, n_cols, raw):
+    """The tiled weight layout restated with numpy index arithmetic (the header's description)."""
+    bb, tb, tile = (18, 4, 1152) if qtype == 2 else (34, 2, 1088)
+    bpr = n_cols // 32
+    ktiles = -(-bpr // tb)
+    slabs = -(-n_rows // 16)
+    out = np.zeros(slabs * ktiles * tile, np.uint8)
+    blocks = np.asarray(raw, np.uint8).reshape(n_rows, bpr, bb)
+    for r in range(n_rows):
+        for b in range(bpr):
+            base = ((r // 16) * ktiles + b // tb) * tile
+            rr, j = r % 16, b % tb
+            group = base + (rr // 8) * 512 + (rr % 8) * 64
+            qs = blocks[r, b, 2:]
+            for w in range((bb - 2) // 4):
+                if qtype == 2:
+                    off = group + w * 16 + j * 4
+                else:
+                    off = group + (w // 2) * 16 + (j * 2 + (w & 1)) * 4
+                out[off:off + 4] = qs[4 * w:4 * w + 4]
+            so = base + 1024 + (rr * tb + j) * 2
+            out[so:so + 2] = blocks[r, b, :2]
+    return out
+
+
+@pytest.mark.parametrize("qtype,bb", [(2, 18), (8, 34)])
+@pytest.mark.parametrize("n_rows,n_cols", [(16, 128), (1, 32), (17, 96), (40, 416)])
+def test_tiled_layout_host(lib, qtype, bb, n_rows, n_cols):
+    """The host restatement of the device layout: sizes, positions of every byte, zero padding."""
+    rng = np.random.default_rng(n_rows * 1000 + n_cols + qtype)
+    raw = rng.integers(0, 256, n_rows * (n_cols // 32) * bb, dtype=np.uint8)
+    want = _tile_numpy(qtype, n_rows, n_cols, raw)
+    assert lib.tlc_tiled_bytes(qtype, n_rows, n_cols) == want.size
+    got = np.full(want.size, 0xAA, np.uint8)
+    assert lib.tlc_tile_blocks_host(qtype, n_rows, n_cols, raw.ctypes.data, got.ctypes.data) == 0
+    assert np.array_equal(got, want)
+    # every input byte appears exactly once: the regrouping is a permutation plus zero padding
+    assert np.array_equal(np.sort(got[got != 0]), np.sort(raw[raw != 0]))
+    assert lib.tlc_tiled_bytes(1, n_rows, n_cols) == 0            # f16 tensors are not tiled
+    assert lib.tlc_tile_blocks_host(1, n_rows, n_cols, raw.ctypes.data, got.ctypes.data) != 0

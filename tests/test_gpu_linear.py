@@ -305,3 +305,21 @@ def test_bounded_wait_reports_timeout_and_context_survives(dev, ref, kind):
     x = _x(2, 256, seed=31)
     y = linear(dev.tensor(x), QTensor.from_blocks(dev, Q4, 64, 256, raw)).numpy()
     assert rel_l2(y, ref.linear_q(Q4, raw, 64, 256, x)) < TIGHT
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("qtype", [Q4, Q8])
+@pytest.mark.parametrize("n,k", [(48, 256), (33, 96), (130, 1056)])
+def test_device_storage_is_the_tiled_layout(dev, qtype, n, k):
+    """HBM holds exactly the bytes of the host-side regrouping; tlc_qtensor_blocks undoes it bit for bit."""
+    from tensorlogic_b200.api import QTensor, check
+    raw = _weights(qtype, n, k, seed=11, name=f"t{n}x{k}")
+    w = QTensor.from_blocks(dev, qtype, n, k, raw)
+    size = dev.lib.tlc_tiled_bytes(qtype, n, k)
+    want = np.empty(size, np.uint8)
+    flat = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+    check(dev.lib.tlc_tile_blocks_host(qtype, n, k, flat.ctypes.data, want.ctypes.data))
+    got = np.empty(size, np.uint8)
+    check(dev.lib.tlc_download(dev.handle, got.ctypes.data, w.ptr, size))
+    assert np.array_equal(got, want)
+    assert np.array_equal(w.raw_bytes().reshape(-1), flat)
