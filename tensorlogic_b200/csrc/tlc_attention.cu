@@ -54,6 +54,7 @@ struct AttnParams {
     float *part_ml;  // [rows][nsplit][2]
     float *part_o;   // [rows][nsplit][D]
     int *counters;   // [B][q_tiles][Hkv], zero between launches
+    int push_offset; // cluster mode: byte offset of the merge area in dynamic shared memory
     int cluster;     // 1: the nsplit CTAs of a tile form a thread-block cluster and merge through
                      // distributed shared memory instead of global scratch
 };
@@ -103,10 +104,11 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     __half *vs = ks + 2 * TILE;                         // [2][TILE]
     __shared__ float sm_m[4][16], sm_l[4][16];
     __shared__ int sm_last;
-    __shared__ float cl_m[16], cl_l[16];
-    __shared__ __align__(16) float cl_o[16][D];
 
-    tlc_pdl_prologue();  // q and the cache rows of this step come from the previous kernel
+    // Cluster mode: tell the peers this CTA is running (its shared memory may be written from
+    // now on); the matching wait comes just before the first remote store.
+    if (p.cluster) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int b = blockIdx.z, hk = blockIdx.y;
@@ -128,20 +130,6 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     const int k_end = min(visible_end, k_begin + p.keys_per_split);
     const int ntiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
 
-    // Q fragments (A operand), straight from global memory.
-    uint32_t qa[KSTEPS][4];
-    {
-        const __half *q_lo = p.q + ((size_t)(b * p.I + (valid_lo ? qi_lo : 0)) * p.H + head_lo) * D;
-        const __half *q_hi = p.q + ((size_t)(b * p.I + (valid_hi ? qi_hi : 0)) * p.H + head_hi) * D;
-#pragma unroll
-        for (int kk = 0; kk < KSTEPS; kk++) {
-            qa[kk][0] = valid_lo ? *reinterpret_cast<const uint32_t *>(q_lo + 16 * kk + 2 * t) : 0u;
-            qa[kk][1] = valid_hi ? *reinterpret_cast<const uint32_t *>(q_hi + 16 * kk + 2 * t) : 0u;
-            qa[kk][2] = valid_lo ? *reinterpret_cast<const uint32_t *>(q_lo + 16 * kk + 8 + 2 * t) : 0u;
-            qa[kk][3] = valid_hi ? *reinterpret_cast<const uint32_t *>(q_hi + 16 * kk + 8 + 2 * t) : 0u;
-        }
-    }
-
     const __half *kbase = p.kc + ((size_t)b * p.Tmax * p.Hkv + hk) * D;
     const __half *vbase = p.vc + ((size_t)b * p.Tmax * p.Hkv + hk) * D;
     const size_t key_stride = (size_t)p.Hkv * D;
@@ -160,13 +148,35 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         cp_async_commit();
     };
 
+    // A decode step's query and its newest cache row come from the previous kernel of the
+    // stream; the older rows were written by earlier steps (and the positions before this
+    // step began), so a first tile made of older rows only is fetched before waiting for
+    // that kernel.
+    const bool early = p.I == 1 && ntiles > 0 && k_begin + kTileKeys <= pos0;
+    if (early) load_tile(0, 0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // Q fragments (A operand), straight from global memory.
+    uint32_t qa[KSTEPS][4];
+    {
+        const __half *q_lo = p.q + ((size_t)(b * p.I + (valid_lo ? qi_lo : 0)) * p.H + head_lo) * D;
+        const __half *q_hi = p.q + ((size_t)(b * p.I + (valid_hi ? qi_hi : 0)) * p.H + head_hi) * D;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; kk++) {
+            qa[kk][0] = valid_lo ? *reinterpret_cast<const uint32_t *>(q_lo + 16 * kk + 2 * t) : 0u;
+            qa[kk][1] = valid_hi ? *reinterpret_cast<const uint32_t *>(q_hi + 16 * kk + 2 * t) : 0u;
+            qa[kk][2] = valid_lo ? *reinterpret_cast<const uint32_t *>(q_lo + 16 * kk + 8 + 2 * t) : 0u;
+            qa[kk][3] = valid_hi ? *reinterpret_cast<const uint32_t *>(q_hi + 16 * kk + 8 + 2 * t) : 0u;
+        }
+    }
+
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[NDT][4];
 #pragma unroll
     for (int i = 0; i < NDT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     const __half scale_h = __float2half_rn(p.scale);
 
-    if (ntiles > 0) load_tile(0, 0);
+    if (ntiles > 0 && !early) load_tile(0, 0);
     for (int tile = 0; tile < ntiles; tile++) {
         const int stage = tile & 1;
         if (tile + 1 < ntiles) {
@@ -303,28 +313,38 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     }
 
     if (p.cluster) {
-        // ---- split keys inside a cluster: partials stay in shared memory, rank 0 reads
-        // its peers' through distributed shared memory ----
+        // ---- split keys inside a cluster: every CTA stores its partial (max, sum, O) into
+        // rank 0's shared memory through distributed shared memory, one cluster barrier, and
+        // rank 0 merges from its own memory; the peers are free to leave at once ----
         namespace cg = cooperative_groups;
         cg::cluster_group cl = cg::this_cluster();
+        // [nsplit][16] max, [nsplit][16] sum, [nsplit][16][D] O, behind the K/V tiles
+        float *push = reinterpret_cast<float *>(smem_raw + p.push_offset);
+        float *r0 = cl.map_shared_rank(push, 0);
+        float *pm = r0, *pl = r0 + 8 * 16, *po = r0 + 2 * 8 * 16;
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // every CTA of the cluster has started
         if ((tid & 7) == 0) {
-            cl_m[row] = M;
-            cl_l[row] = L;
+            pm[split * 16 + row] = M;
+            pl[split * 16 + row] = L;
         }
 #pragma unroll
-        for (int j = 0; j < DPT; j++) cl_o[row][d0 + j] = acc[j];
-        cl.sync();
+        for (int j = 0; j < DPT; j += 4)
+            *reinterpret_cast<float4 *>(po + ((size_t)split * 16 + row) * D + d0 + j) =
+                make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         if (cl.block_rank() == 0 && row_valid) {
+            const float *lm = push, *ll = push + 8 * 16, *lo = push + 2 * 8 * 16;
             float Mg = -INFINITY;
-            for (int sp = 0; sp < p.nsplit; sp++) Mg = fmaxf(Mg, cl.map_shared_rank(cl_m, sp)[row]);
+            for (int sp = 0; sp < p.nsplit; sp++) Mg = fmaxf(Mg, lm[sp * 16 + row]);
             float Lg = 0.f;
 #pragma unroll
             for (int j = 0; j < DPT; j++) acc[j] = 0.f;
             for (int sp = 0; sp < p.nsplit; sp++) {
-                const float ms = cl.map_shared_rank(cl_m, sp)[row];
+                const float ms = lm[sp * 16 + row];
                 const float wgt = ms == -INFINITY ? 0.f : expf(ms - Mg);
-                Lg += cl.map_shared_rank(cl_l, sp)[row] * wgt;
-                const float *ro = cl.map_shared_rank(&cl_o[0][0], sp) + row * D + d0;
+                Lg += ll[sp * 16 + row] * wgt;
+                const float *ro = lo + ((size_t)sp * 16 + row) * D + d0;
 #pragma unroll
                 for (int j = 0; j < DPT; j += 4) {
                     const float4 v = *reinterpret_cast<const float4 *>(ro + j);
@@ -338,7 +358,6 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
 #pragma unroll
             for (int j = 0; j < DPT; j++) p.out[out_row * D + d0 + j] = __float2half_rn(acc[j] * inv);
         }
-        cl.sync();  // peers keep their shared memory alive until rank 0 has read it
         return;
     }
 
@@ -562,6 +581,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_prefill_kernel(const A
 
 // cache.append for the unfused surface: rows of K/V [m, Hkv*D] go to position
 // pos(row) of sequence seq(row).
+// Dynamic shared memory an attention_kernel<D> launch may ask for: the K/V tiles plus, in
+// cluster mode, the merge area of rank 0.  Every place that sets the kernel's limit uses this
+// value, so one launcher never lowers the limit another one needs.
+static constexpr size_t attention_smem_limit(int D) {
+    return (size_t)4 * kTileKeys * (D + 8) * sizeof(__half) + 128 + (size_t)8 * 16 * (D + 2) * sizeof(float);
+}
+
 __global__ void kv_append_kernel(const __half *__restrict__ k, const __half *__restrict__ v,
                                  __half *__restrict__ kc, __half *__restrict__ vc, int m, int row_elems,
                                  int tmax, int pos_offset, const int *__restrict__ positions, int batched) {
@@ -683,7 +709,11 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
     dim3 grid(p.q_tiles * nsplit, Hkv, batch);
     const size_t smem = (size_t)4 * kTileKeys * (D + 8) * sizeof(__half);
     const size_t smem_o = (size_t)4 * 16 * D * sizeof(float);
-    const size_t smem_bytes = smem > smem_o ? smem : smem_o;
+    size_t smem_bytes = smem > smem_o ? smem : smem_o;
+    if (cluster) {  // the merge area of rank 0 (every CTA of the launch has the same layout)
+        p.push_offset = (int)((smem_bytes + 127) & ~(size_t)127);
+        smem_bytes = (size_t)p.push_offset + (size_t)8 * 16 * (D + 2) * sizeof(float);
+    }
     // All kernels of a decode step ask for the same (maximal) shared-memory
     // carve-out: switching the L1/shared split between consecutive launches
     // makes the SMs drain first.
@@ -692,12 +722,12 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
     if (!configured[di][ctx->device & 63]) {
         if (D == 64) {
             TLC_CUDA(cudaFuncSetAttribute(attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)smem_bytes));
+                                          (int)attention_smem_limit(64)));
             TLC_CUDA(cudaFuncSetAttribute(attention_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                           cudaSharedmemCarveoutMaxShared));
         } else {
             TLC_CUDA(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)smem_bytes));
+                                          (int)attention_smem_limit(128)));
             TLC_CUDA(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                           cudaSharedmemCarveoutMaxShared));
         }
@@ -877,9 +907,9 @@ extern "C" int32_t tlc_attention_decode_static(void *stream, const void *q_dev, 
         }
         TLC_CUDA(cudaDeviceGetAttribute(&su.sm_count, cudaDevAttrMultiProcessorCount, device));
         TLC_CUDA(cudaFuncSetAttribute(attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)((size_t)4 * kTileKeys * (64 + 8) * sizeof(__half))));
+                                      (int)attention_smem_limit(64)));
         TLC_CUDA(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)((size_t)4 * kTileKeys * (128 + 8) * sizeof(__half))));
+                                      (int)attention_smem_limit(128)));
         su.scratch = static_cast<unsigned char *>(p);
         su.done = true;
     }
