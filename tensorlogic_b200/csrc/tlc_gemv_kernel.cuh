@@ -117,6 +117,28 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
     // -------------------------------- consumers --------------------------------
     const int ctid = tid;  // 0..kConsumerThreads-1
     const bool do_norm = p.norm_w != nullptr;
+    // The norm weights do not come from the previous kernel: the first round's are fetched
+    // (the later rounds' brought into the cache) while that kernel is still running.
+    uint4 nw_first = make_uint4(0, 0, 0, 0);
+    if (do_norm) {
+        const int items = p.nblk_pad * p.m * 4;
+        for (int idx = ctid; idx < items; idx += kConsumerThreads) {
+            const int t = idx & 3, b = (idx >> 2) / p.m;
+            if (b >= p.nblk) continue;
+            const __half *wr = p.norm_w + b * 32;
+            if (idx == ctid) {
+                if (QT == TLC_TYPE_Q4_0) {
+                    const uint2 lo = *reinterpret_cast<const uint2 *>(wr + 4 * t);
+                    const uint2 hi = *reinterpret_cast<const uint2 *>(wr + 16 + 4 * t);
+                    nw_first = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                } else {
+                    nw_first = *reinterpret_cast<const uint4 *>(wr + 8 * t);
+                }
+            } else {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(wr));
+            }
+        }
+    }
     pdl_wait();  // the activations (and residual) come from the previous kernel
 
     // (a) sum of squares per activation row: every thread takes 8-element chunks.
@@ -171,20 +193,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
                     for (int w = 0; w < kConsumerWarps; w++) ss += sq_part[m * kConsumerWarps + w];
                     inv = 1.0f / sqrtf(ss / (float)p.k + p.eps);
                 }
-                __half raw[8], nw[8];
+                __align__(16) __half raw[8], nw[8];
                 if (QT == TLC_TYPE_Q4_0) {
                     *reinterpret_cast<uint2 *>(&raw[0]) = *reinterpret_cast<const uint2 *>(xr + 4 * t);
                     *reinterpret_cast<uint2 *>(&raw[4]) = *reinterpret_cast<const uint2 *>(xr + 16 + 4 * t);
-                    if (do_norm) {
+                    if (do_norm && r > 0) {
                         const __half *wr = p.norm_w + b * 32;
                         *reinterpret_cast<uint2 *>(&nw[0]) = *reinterpret_cast<const uint2 *>(wr + 4 * t);
                         *reinterpret_cast<uint2 *>(&nw[4]) = *reinterpret_cast<const uint2 *>(wr + 16 + 4 * t);
                     }
                 } else {
                     *reinterpret_cast<uint4 *>(&raw[0]) = *reinterpret_cast<const uint4 *>(xr + 8 * t);
-                    if (do_norm)
+                    if (do_norm && r > 0)
                         *reinterpret_cast<uint4 *>(&nw[0]) = *reinterpret_cast<const uint4 *>(p.norm_w + b * 32 + 8 * t);
                 }
+                if (do_norm && r == 0) *reinterpret_cast<uint4 *>(&nw[0]) = nw_first;
                 float f[8];
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
