@@ -93,7 +93,11 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *   "wait_limit_ms" how long a device-side wait (mbarrier, peer flag) may last before the
  *                 kernel gives up and the next tlc_synchronize returns TLC_ERR_TIMEOUT;
  *   "pdl"         programmatic dependent launch on (1) / off (0);
- *   "pdl_mode"    1 = let the successor start at once, 2 = after the last slab.
+ *   "pdl_mode"    1 = let the successor start at once, 2 = after the last slab;
+ *   "host_graph"  tlc_llama_decode_host runs as one graph launch with copy nodes (1, default)
+ *                 or as copy + graph + copy (0);
+ *   "host_poll"   with host_graph: the host watches the pinned result words (1, default)
+ *                 instead of synchronizing the stream (0).
  * Unknown names fail with TLC_ERR_INVALID_OPERATION. */
 TLC_API int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value);
 /* Failure-detection self-test.  Enqueues a kernel whose device-side wait can never be

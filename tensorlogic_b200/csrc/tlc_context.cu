@@ -77,6 +77,8 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (const char *e = getenv("TLC_PDL_MODE")) ctx->pdl_mode = atoi(e);
     if (const char *e = getenv("TLC_PDL_SMALL")) ctx->pdl_small = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMM_MIN_M")) ctx->gemm_min_m = atoi(e);
+    if (const char *e = getenv("TLC_HOST_GRAPH")) ctx->host_graph = atoi(e) != 0;
+    if (const char *e = getenv("TLC_HOST_POLL")) ctx->host_poll = atoi(e) != 0;
     *out = ctx;
     return TLC_OK;
 }
@@ -97,6 +99,10 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         ctx->use_pdl = value != 0;
     else if (n == "pdl_mode")
         ctx->pdl_mode = (int)value;
+    else if (n == "host_graph")
+        ctx->host_graph = value != 0;
+    else if (n == "host_poll")
+        ctx->host_poll = value != 0;
     else
         return tlc_fail(TLC_ERR_INVALID_OPERATION, "set_option: unknown option '%s'", name);
     return TLC_OK;
@@ -152,6 +158,12 @@ extern "C" int32_t tlc_synchronize(tlc_ctx *ctx) {
     TLC_CUDA(cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(tlc_dev_status),
                              cudaMemcpyDeviceToHost, ctx->stream));
     TLC_CUDA(cudaStreamSynchronize(ctx->stream));
+    return tlc_status_after_sync(ctx);
+}
+
+// The status word has just been copied to its pinned mirror and the stream is idle:
+// report (once) a bounded wait that gave up, and clear the word.
+int32_t tlc_status_after_sync(tlc_ctx *ctx) {
     if (ctx->host_status->code != 0) {
         int code = ctx->host_status->code, where = ctx->host_status->where;
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(tlc_dev_status), ctx->stream);

@@ -52,6 +52,8 @@ struct tlc_ctx {
     // TLC_GEMM_MIN_M: activation rows from which quantized linears run as the
     // tensor-core GEMM (0: decide from the shape; a huge value keeps the GEMV).
     int gemm_min_m = 0;
+    bool host_graph = true;  // decode_host: ids up, the step, results down as ONE graph launch
+    bool host_poll = true;   // ... and the host watches the pinned result words instead of a stream sync
     // How long a device-side wait (mbarrier, peer flag) may last before the kernel gives up,
     // sets the status word and drains; option "wait_limit_ms".
     uint64_t wait_ns = 2000000000ull;
@@ -118,6 +120,8 @@ int32_t tlc_selftest_mbarrier_wait(tlc_ctx *ctx);
 int32_t tlc_selftest_peer_wait(tlc_ctx *ctx);
 // Makes the context's device current; every entry point calls it first.
 int32_t tlc_enter(tlc_ctx *ctx);
+// After a stream synchronize that followed a copy of the status word to host_status.
+int32_t tlc_status_after_sync(tlc_ctx *ctx);
 // Ensures ctx->scratch holds at least `bytes`.
 int32_t tlc_scratch_reserve(tlc_ctx *ctx, size_t bytes);
 

@@ -23,6 +23,7 @@
 // residual, and the vocabulary shards of the logits are all-gathered.
 // RoPE takes the true position of every token (the reference's decode branch
 // calls rope() with its default offset 0, chat_demo_with_kvcache.tl:236,:244).
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <memory>
@@ -635,8 +636,65 @@ extern "C" int32_t tlc_llama_decode_host(tlc_llama *L, int32_t batch, const int3
     if (ids_host) {
         if (int32_t rc = check_ids(L, ids_host, batch)) return rc;
         memcpy(L->host_ids, ids_host, (size_t)batch * 4);
-        TLC_CUDA(cudaMemcpyAsync(L->ids, L->host_ids, (size_t)batch * 4, cudaMemcpyHostToDevice, L->ctx->stream));
     }
+    if (ids_host && !logits_host && !L->cfg.no_graph && L->ctx->host_graph) {
+        // The common call: token ids up, one step, sampled ids and the status word down --
+        // all of it one graph (copy nodes around the step's kernels), one launch, one wait.
+        tlc_ctx *ctx = L->ctx;
+        const int key = 1000 + batch;
+        if (!L->graph.count(key)) {
+            if (int32_t rc = decode_enqueue(L, batch, 0, 7)) return rc;  // warms the kernels, captures the plain step
+            TLC_CUDA(cudaStreamSynchronize(ctx->stream));
+            const uint64_t launches_before = ctx->launches;
+            TLC_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+            cudaError_t ce = cudaMemcpyAsync(L->ids, L->host_ids, (size_t)batch * 4, cudaMemcpyHostToDevice, ctx->stream);
+            int32_t rc = ce == cudaSuccess ? forward(L, batch, true, 0, false, true, true, 7) : TLC_OK;
+            // the status word first: once the sampled ids have landed, it has too
+            if (ce == cudaSuccess && !rc)
+                ce = cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(tlc_dev_status), cudaMemcpyDeviceToHost,
+                                     ctx->stream);
+            if (ce == cudaSuccess && !rc)
+                ce = cudaMemcpyAsync(L->host_next, L->next_ids, (size_t)batch * 4, cudaMemcpyDeviceToHost, ctx->stream);
+            cudaGraph_t g = nullptr;
+            cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+            ctx->launches = launches_before;
+            if (rc || ce != cudaSuccess || e != cudaSuccess) {
+                if (g) cudaGraphDestroy(g);
+                cudaGetLastError();
+                if (rc) return rc;
+                return tlc_fail(TLC_ERR_CUDA, "graph capture of the host step failed: %s",
+                                cudaGetErrorString(ce != cudaSuccess ? ce : e));
+            }
+            cudaGraphExec_t ge = nullptr;
+            e = cudaGraphInstantiate(&ge, g, 0);
+            cudaGraphDestroy(g);
+            if (e != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+            L->graph[key] = ge;
+        }
+        volatile int32_t *landed = L->host_next;
+        for (int i = 0; i < batch; i++) landed[i] = -1;  // no token id is negative
+        TLC_CUDA(cudaGraphLaunch(L->graph[key], ctx->stream));
+        ctx->launches += (uint64_t)L->launches_in[7];
+        bool seen = false;
+        if (ctx->host_poll) {
+            // Watch the pinned words the last copy node writes; after 50 ms without them
+            // (an error, a very long step) fall back to the stream synchronize below.
+            const auto t0 = std::chrono::steady_clock::now();
+            for (long spin = 0; !seen; spin++) {
+                seen = true;
+                for (int i = 0; i < batch; i++) seen = seen && landed[i] >= 0;
+                if (!seen && (spin & 1023) == 1023 &&
+                    std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(50))
+                    break;
+            }
+        }
+        if (!seen) TLC_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (int32_t rc = tlc_status_after_sync(ctx)) return rc;
+        memcpy(next_ids_host, L->host_next, (size_t)batch * 4);
+        return TLC_OK;
+    }
+    if (ids_host)
+        TLC_CUDA(cudaMemcpyAsync(L->ids, L->host_ids, (size_t)batch * 4, cudaMemcpyHostToDevice, L->ctx->stream));
     if (int32_t rc = tlc_llama_decode_enqueue(L, batch, 1)) return rc;
     if (logits_host)
         if (int32_t rc = copy_logits(L, logits_host, batch)) return rc;
