@@ -123,19 +123,19 @@ __global__ void __launch_bounds__(256) linear_f16_kernel(const uint8_t *__restri
     }
 }
 
-template <int QT, int NT, int AS, bool M1>
+template <int QT, int NT, int AS, bool M1, int CW>
 int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)ctx->prop.sharedMemPerBlockOptin));
-        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                      cudaSharedmemCarveoutMaxShared));
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1, CW>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 63] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3((CW + 1) * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -143,13 +143,27 @@ int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<QT, NT, AS, M1>, p);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<QT, NT, AS, M1, CW>, p);
     if (le != cudaSuccess) {
         cudaGetLastError();
         return tlc_fail(TLC_ERR_CUDA, "gemv launch failed: %s", cudaGetErrorString(le));
     }
     TLC_CHECK_LAUNCH(ctx);
     return TLC_OK;
+}
+
+template <int QT, int NT, int CW>
+int32_t launch_mma_cw(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem, int as) {
+    if constexpr (NT == 1) {
+        if (p.m == 1) {  // the decode step of one sequence
+            if (as == 1) return launch_mma_as<QT, 1, 1, true, CW>(ctx, p, grid, smem);
+            if (as == 2) return launch_mma_as<QT, 1, 2, true, CW>(ctx, p, grid, smem);
+            return launch_mma_as<QT, 1, 4, true, CW>(ctx, p, grid, smem);
+        }
+    }
+    if (as == 1) return launch_mma_as<QT, NT, 1, false, CW>(ctx, p, grid, smem);
+    if (as == 2) return launch_mma_as<QT, NT, 2, false, CW>(ctx, p, grid, smem);
+    return launch_mma_as<QT, NT, 4, false, CW>(ctx, p, grid, smem);
 }
 
 template <int QT, int NT>
@@ -168,7 +182,10 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     // (Measured on the TinyLlama decode step: keeping small launches at one CTA per
     // SM, to leave room for the next kernel's early CTAs, costs 8 % against
     // letting them spread over two CTAs per SM.)
-    const bool two = fits_half && kCtasPerSm == 2;
+    const bool two = fits_half;
+    // One CTA per SM: sixteen consumer warps instead of eight, if the larger reduction
+    // buffers still leave three ring stages.
+    const int cw = !two && fixed_smem_bytes(p.nblk_pad, p.m, NT, p.subs, 16) + 3 * STAGE_BYTES <= budget ? 16 : 8;
     const size_t cap = two ? half : budget;
     const int max_ctas = two ? 2 * ctx->sm_count : ctx->sm_count;
     const int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
@@ -181,8 +198,8 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     if (ub > units_per_cta) ub = units_per_cta;
     int as = p.subs;
     while (as < ub * p.subs && as < (NT == 2 ? 2 : 4)) as *= 2;
-    while (as > p.subs && fixed_smem_bytes(p.nblk_pad, p.m, NT, as) + 3 * STAGE_BYTES > cap) as /= 2;
-    const size_t smem_fixed = fixed_smem_bytes(p.nblk_pad, p.m, NT, as);
+    while (as > p.subs && fixed_smem_bytes(p.nblk_pad, p.m, NT, as, cw) + 3 * STAGE_BYTES > cap) as /= 2;
+    const size_t smem_fixed = fixed_smem_bytes(p.nblk_pad, p.m, NT, as, cw);
     // No more stages than this CTA will ever fill.
     const long per_cta = (long)units_per_cta * p.subs * p.nchunks;
     int stages = (int)((cap - smem_fixed) / STAGE_BYTES);
@@ -192,16 +209,7 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     p.pdl_mode = ctx->pdl_mode;
     p.contig = units_per_cta <= 4 ? 1 : 0;
     const size_t smem = smem_fixed + (size_t)stages * STAGE_BYTES;
-    if constexpr (NT == 1) {
-        if (p.m == 1) {  // the decode step of one sequence
-            if (as == 1) return launch_mma_as<QT, 1, 1, true>(ctx, p, grid, smem);
-            if (as == 2) return launch_mma_as<QT, 1, 2, true>(ctx, p, grid, smem);
-            return launch_mma_as<QT, 1, 4, true>(ctx, p, grid, smem);
-        }
-    }
-    if (as == 1) return launch_mma_as<QT, NT, 1, false>(ctx, p, grid, smem);
-    if (as == 2) return launch_mma_as<QT, NT, 2, false>(ctx, p, grid, smem);
-    return launch_mma_as<QT, NT, 4, false>(ctx, p, grid, smem);
+    return cw == 16 ? launch_mma_cw<QT, NT, 16>(ctx, p, grid, smem, as) : launch_mma_cw<QT, NT, 8>(ctx, p, grid, smem, as);
 }
 
 size_t gemv_fixed_smem(int nblk_pad, int m, int nt) { return fixed_smem_bytes(nblk_pad, m, nt, 2); }

@@ -10,13 +10,10 @@
 namespace tlc_gemv {
 
 constexpr int kRows = 16;  // rows of W per slab (the M of m16n8k16)
-// Eight consumer warps per CTA and two CTAs per SM; sixteen warps in one CTA
-// per SM measured 14 % slower on a 132 MB weight (one barrier and one
-// reduction over twice the warps) and 0.3 % faster on the TinyLlama step.
-constexpr int kConsumerWarps = 8;
-constexpr int kCtasPerSm = 2;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+// Eight consumer warps per CTA and two CTAs per SM wherever two CTAs fit: sixteen
+// warps in one CTA per SM measured 14 % slower on a 132 MB weight (one barrier and
+// one reduction over twice the warps).  Launches whose activations leave room for
+// one CTA only (several rows of a long K) take the sixteen-warp form.
 constexpr int kMaxStages = 12;
 constexpr int kHeaderBytes = 1536;  // mbarriers, abort flag, sum-of-squares partials
 
@@ -121,8 +118,9 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         "l"(src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
+template <int N>
 __device__ __forceinline__ void consumer_bar() {
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(N) : "memory");
 }
 // Programmatic dependent launch: let the next kernel of the stream be scheduled
 // now (it may start fetching its weights), and wait for the previous kernel's

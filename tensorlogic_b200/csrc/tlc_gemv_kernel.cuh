@@ -15,9 +15,9 @@ namespace tlc_gemv {
 //   ...  xzero one zero uint4 (B fragment of activation rows that do not exist)
 //   ...  xperm [nblk_pad][m][4 quad lanes] uint4    activations in fragment order
 //   ...  ring  [stages][16 tiles]                   weight tiles as they lie in HBM (128-byte aligned)
-__host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, int as) {
+__host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, int as, int cw = 8) {
     size_t s = kHeaderBytes;
-    s += (size_t)2 * as * kConsumerWarps * kRows * (8 * nt) * sizeof(float);
+    s += (size_t)2 * as * cw * kRows * (8 * nt) * sizeof(float);
     s += m == 1 ? (size_t)nblk_pad * sizeof(float4) : (size_t)nblk_pad * nt * 4 * sizeof(float2);
     s += sizeof(uint4);
     s += (size_t)nblk_pad * m * 4 * sizeof(uint4);
@@ -29,9 +29,13 @@ __host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, 
 // of the 16x8 tensor-core tile are then never read back, so every lane may load
 // the same B fragments and accumulator start values: their shared-memory
 // addresses become warp-uniform with compile-time strides.
-template <int QT, int NT, int AS, bool M1>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const GemvParams p) {
+// CW: consumer warps, 8 (two CTAs per SM) or 16 (one CTA per SM, for launches whose
+// activations leave no room for two).
+template <int QT, int NT, int AS, bool M1, int CW>
+__global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kernel(const GemvParams p) {
     static_assert(!M1 || NT == 1, "one activation row needs one column tile");
+    static_assert(CW == 8 || CW == 16, "8 or 16 consumer warps");
+    constexpr int CT = CW * 32;  // consumer threads
     using T = QTraits<QT>;
     constexpr int MP = 8 * NT;  // padded activation rows
     constexpr int TILE = T::TILE_BYTES;
@@ -43,8 +47,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 256);
     float *sq_part = reinterpret_cast<float *>(smem + 512);
     float *red = reinterpret_cast<float *>(smem + kHeaderBytes);
-    static_assert(kMaxStages * 8 <= 128 && 512 + 16 * kConsumerWarps * 4 <= kHeaderBytes, "header layout");
-    float2 *cinit = reinterpret_cast<float2 *>(red + 2 * AS * kConsumerWarps * kRows * MP);
+    static_assert(kMaxStages * 8 <= 128 && 512 + 16 * CW * 4 <= kHeaderBytes, "header layout");
+    float2 *cinit = reinterpret_cast<float2 *>(red + 2 * AS * CW * kRows * MP);
     uint4 *xzero = M1 ? reinterpret_cast<uint4 *>(reinterpret_cast<float4 *>(cinit) + p.nblk_pad)
                       : reinterpret_cast<uint4 *>(cinit + (size_t)p.nblk_pad * NT * 4);
     uint4 *xperm = xzero + 1;
@@ -58,7 +62,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
     if (tid == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kConsumerWarps);
+            mbar_init(&empty[s], CW);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -69,7 +73,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
     // warps only read weights, everything else waits for this grid to finish.
     if (p.pdl_mode == 1) pdl_launch_dependents();
 
-    if (warp == kConsumerWarps) {
+    if (warp == CW) {
         // ------------------------------ producer ------------------------------
         // Weights are never written by a kernel, so the ring starts filling
         // before the previous kernel of the stream has finished.
@@ -115,14 +119,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
     }
 
     // -------------------------------- consumers --------------------------------
-    const int ctid = tid;  // 0..kConsumerThreads-1
+    const int ctid = tid;  // 0..CT-1
     const bool do_norm = p.norm_w != nullptr;
     // The norm weights do not come from the previous kernel: the first round's are fetched
     // (the later rounds' brought into the cache) while that kernel is still running.
     uint4 nw_first = make_uint4(0, 0, 0, 0);
     if (do_norm) {
         const int items = p.nblk_pad * p.m * 4;
-        for (int idx = ctid; idx < items; idx += kConsumerThreads) {
+        for (int idx = ctid; idx < items; idx += CT) {
             const int t = idx & 3, b = (idx >> 2) / p.m;
             if (b >= p.nblk) continue;
             const __half *wr = p.norm_w + b * 32;
@@ -146,7 +150,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
         for (int m = 0; m < p.m; m++) {
             const __half *xr = p.x + (size_t)m * p.k;
             float sq = 0.f;
-            for (int k = ctid * 8; k < p.k; k += kConsumerThreads * 8) {
+            for (int k = ctid * 8; k < p.k; k += CT * 8) {
                 const uint4 raw = *reinterpret_cast<const uint4 *>(xr + k);
                 const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
 #pragma unroll
@@ -158,13 +162,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            if (lane == 0) sq_part[m * kConsumerWarps + warp] = sq;
+            if (lane == 0) sq_part[m * CW + warp] = sq;
         }
     }
-    for (int i = ctid; i < (M1 ? p.nblk_pad * 2 : p.nblk_pad * NT * 4); i += kConsumerThreads)
+    for (int i = ctid; i < (M1 ? p.nblk_pad * 2 : p.nblk_pad * NT * 4); i += CT)
         cinit[i] = make_float2(0.f, 0.f);
     if (ctid == 0) *xzero = make_uint4(0, 0, 0, 0);
-    consumer_bar();
+    consumer_bar<CT>();
 
     // (b) activations into fragment order + accumulator start values.  Item =
     // (block b, activation row m, quad lane t); the 4 t-items of a (b, m) are
@@ -173,9 +177,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
     //   Q8_0 fragment order: {8t .. 8t+7}
     {
         const int items = p.nblk_pad * p.m * 4;
-        const int rounds = (items + kConsumerThreads - 1) / kConsumerThreads;
+        const int rounds = (items + CT - 1) / CT;
         for (int r = 0; r < rounds; r++) {
-            const int idx = ctid + r * kConsumerThreads;
+            const int idx = ctid + r * CT;
             const bool live = idx < items;
             const int t = idx & 3;
             const int bm = idx >> 2;
@@ -190,7 +194,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
                 if (do_norm) {
                     float ss = 0.f;
 #pragma unroll
-                    for (int w = 0; w < kConsumerWarps; w++) ss += sq_part[m * kConsumerWarps + w];
+                    for (int w = 0; w < CW; w++) ss += sq_part[m * CW + w];
                     inv = 1.0f / sqrtf(ss / (float)p.k + p.eps);
                 }
                 __align__(16) __half raw[8], nw[8];
@@ -253,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
             }
         }
     }
-    consumer_bar();
+    consumer_bar<CT>();
 
     // (c) main loop
     const int g = lane >> 2, t = lane & 3;
@@ -422,15 +426,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
                 if (ntiles == kTilesPerStage) {
                     // Lane (g, t) reads the words of rows g and g + 8 of its warp's two tiles
                     // up front (four 16-byte loads), then runs the blocks.
-                    constexpr int TPW = kTilesPerStage / kConsumerWarps;  // tiles per warp and stage
-                    static_assert(TPW * kConsumerWarps == kTilesPerStage && TPW >= 1, "whole tiles per warp");
+                    constexpr int TPW = kTilesPerStage / CW;  // tiles per warp and stage
+                    static_assert(TPW * CW == kTilesPerStage && TPW >= 1, "whole tiles per warp");
                     TileRegs r[TPW];
 #pragma unroll
-                    for (int i = 0; i < TPW; i++) load_tile(r[i], sbase + (uint32_t)(warp + i * kConsumerWarps) * TILE);
+                    for (int i = 0; i < TPW; i++) load_tile(r[i], sbase + (uint32_t)(warp + i * CW) * TILE);
 #pragma unroll
-                    for (int i = 0; i < TPW; i++) do_tile(r[i], cb0 + (uint32_t)(warp + i * kConsumerWarps) * T::TB);
+                    for (int i = 0; i < TPW; i++) do_tile(r[i], cb0 + (uint32_t)(warp + i * CW) * T::TB);
                 } else {
-                    for (int ti = warp; ti < ntiles; ti += kConsumerWarps) {
+                    for (int ti = warp; ti < ntiles; ti += CW) {
                         TileRegs r0;
                         load_tile(r0, sbase + (uint32_t)ti * TILE);
                         do_tile(r0, cb0 + (uint32_t)ti * T::TB);
@@ -447,11 +451,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
 
         // (d) cross-warp reduction and epilogue of the batch
         if (p.pdl_mode == 2 && i0 + ub >= n_mine) pdl_launch_dependents();
-        float *rbuf = red + (size_t)(batch_count & 1) * (AS * kConsumerWarps * kRows * MP);
+        float *rbuf = red + (size_t)(batch_count & 1) * (AS * CW * kRows * MP);
 #pragma unroll
         for (int a = 0; a < AS; a++) {
             if (a >= nsets) break;
-            float *mine = rbuf + (a * kConsumerWarps + warp) * (kRows * MP);
+            float *mine = rbuf + (a * CW + warp) * (kRows * MP);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
                 *reinterpret_cast<float2 *>(&mine[g * MP + nt * 8 + 2 * t]) = make_float2(acc[a][nt * 4 + 0], acc[a][nt * 4 + 1]);
@@ -459,10 +463,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
                     make_float2(acc[a][nt * 4 + 2], acc[a][nt * 4 + 3]);
             }
         }
-        consumer_bar();
+        consumer_bar<CT>();
         // Outputs of the batch: (unit, row, activation row) items over the consumer threads.
         const int per_unit = kRows * p.m;
-        for (int item = ctid; item < (nsets / p.subs) * per_unit; item += kConsumerThreads) {
+        for (int item = ctid; item < (nsets / p.subs) * per_unit; item += CT) {
             const int ui = item / per_unit, rc = item % per_unit;
             const int col = rc >> 4, row = rc & 15;
             const int a0 = ui * p.subs;
@@ -475,10 +479,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) gemv_mma_kernel(const Ge
             const int wn = ti == 0 ? p.t[0].n : ti == 1 ? p.t[1].n : p.t[2].n;
             if (n >= wn) continue;
             auto total = [&](int set, int r_) {
-                const float *base = rbuf + (size_t)set * kConsumerWarps * (kRows * MP) + r_ * MP + col;
+                const float *base = rbuf + (size_t)set * CW * (kRows * MP) + r_ * MP + col;
                 float v = 0.f;
 #pragma unroll
-                for (int w = 0; w < kConsumerWarps; w++) v += base[w * (kRows * MP)];
+                for (int w = 0; w < CW; w++) v += base[w * (kRows * MP)];
                 return v * 16777216.0f;  // undo the 2^-24 of the integer fragments
             };
             __half *yout = ti == 0 ? p.t[0].y : ti == 1 ? p.t[1].y : p.t[2].y;
