@@ -94,6 +94,7 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *                 kernel gives up and the next tlc_synchronize returns TLC_ERR_TIMEOUT;
  *   "pdl"         programmatic dependent launch on (1) / off (0);
  *   "pdl_mode"    1 = let the successor start at once, 2 = after the last slab;
+ *   "l2_hint"     the GEMV's weight copies carry the evict-first L2 hint (1, default) or none (0);
  *   "host_graph"  tlc_llama_decode_host runs as one graph launch with copy nodes (1, default)
  *                 or as copy + graph + copy (0);
  *   "host_poll"   with host_graph: the host watches the pinned result words (1, default)

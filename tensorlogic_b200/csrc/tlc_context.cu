@@ -77,6 +77,7 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (const char *e = getenv("TLC_PDL_MODE")) ctx->pdl_mode = atoi(e);
     if (const char *e = getenv("TLC_PDL_SMALL")) ctx->pdl_small = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMM_MIN_M")) ctx->gemm_min_m = atoi(e);
+    if (const char *e = getenv("TLC_L2_HINT")) ctx->l2_hint = atoi(e);
     if (const char *e = getenv("TLC_HOST_GRAPH")) ctx->host_graph = atoi(e) != 0;
     if (const char *e = getenv("TLC_HOST_POLL")) ctx->host_poll = atoi(e) != 0;
     *out = ctx;
@@ -99,6 +100,8 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         ctx->use_pdl = value != 0;
     else if (n == "pdl_mode")
         ctx->pdl_mode = (int)value;
+    else if (n == "l2_hint")
+        ctx->l2_hint = value != 0;
     else if (n == "host_graph")
         ctx->host_graph = value != 0;
     else if (n == "host_poll")

@@ -207,6 +207,7 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     if (stages > per_cta) stages = per_cta < 2 ? 2 : (int)per_cta;
     p.nstages = stages;
     p.pdl_mode = ctx->pdl_mode;
+    p.l2_hint = ctx->l2_hint;
     p.contig = units_per_cta <= 4 ? 1 : 0;
     const size_t smem = smem_fixed + (size_t)stages * STAGE_BYTES;
     return cw == 16 ? launch_mma_cw<QT, NT, 16>(ctx, p, grid, smem, as) : launch_mma_cw<QT, NT, 8>(ctx, p, grid, smem, as);

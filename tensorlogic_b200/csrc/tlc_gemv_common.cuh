@@ -66,6 +66,7 @@ struct GemvParams {
     const int *positions;
     int nstages;
     int contig;    // 1: each CTA takes a contiguous range of units, 0: units blockIdx.x, + gridDim.x, ...
+    int l2_hint;   // 1: weight copies carry the evict-first L2 hint
     int pdl_mode;  // 1: let the next kernel be scheduled at once, 2: only when this CTA's last slab is done
     tlc_dev_status *status;
     uint64_t wait_ns;  // how long a wait may last before the kernel gives up
@@ -116,6 +117,21 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
             smem_u32(dst)),
         "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+// The same copy with an L2 eviction hint: weight tiles are read once per launch, so they
+// are marked evict-first and leave the L2 to activations, norm weights and the KV cache.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void *dst, const void *src, uint32_t bytes, uint64_t *bar,
+                                              uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
+            "r"(smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
 template <int N>

@@ -79,6 +79,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
         // before the previous kernel of the stream has finished.
         int rs = 0;
         uint32_t rpar = 1;
+        const uint64_t policy = l2_evict_first_policy();
         const int pu_lo = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
         const int pu_hi = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
         const int pcount = p.contig ? pu_hi - pu_lo
@@ -109,8 +110,13 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                     const uint32_t bytes = (uint32_t)(ntiles * TILE);
                     if (lane == 0) {
                         mbar_expect_tx(&full[s], bytes);
-                        bulk_g2s(stages + (size_t)s * STAGE_BYTES,
-                                 wbase + (size_t)sl * spitch + (size_t)c * (kTilesPerStage * TILE), bytes, &full[s]);
+                        if (p.l2_hint)
+                            bulk_g2s_hint(stages + (size_t)s * STAGE_BYTES,
+                                          wbase + (size_t)sl * spitch + (size_t)c * (kTilesPerStage * TILE), bytes,
+                                          &full[s], policy);
+                        else
+                            bulk_g2s(stages + (size_t)s * STAGE_BYTES,
+                                     wbase + (size_t)sl * spitch + (size_t)c * (kTilesPerStage * TILE), bytes, &full[s]);
                     }
                 }
             }

@@ -52,6 +52,7 @@ struct tlc_ctx {
     // TLC_GEMM_MIN_M: activation rows from which quantized linears run as the
     // tensor-core GEMM (0: decide from the shape; a huge value keeps the GEMV).
     int gemm_min_m = 0;
+    int l2_hint = 1;         // GEMV weight copies marked evict-first in the L2 (measured: +3 % on the decode step)
     bool host_graph = true;  // decode_host: ids up, the step, results down as ONE graph launch
     bool host_poll = true;   // ... and the host watches the pinned result words instead of a stream sync
     // How long a device-side wait (mbarrier, peer flag) may last before the kernel gives up,
