@@ -138,3 +138,10 @@ def test_tiled_layout_host(lib, qtype, bb, n_rows, n_cols):
     assert np.array_equal(np.sort(got[got != 0]), np.sort(raw[raw != 0]))
     assert lib.tlc_tiled_bytes(1, n_rows, n_cols) == 0            # f16 tensors are not tiled
     assert lib.tlc_tile_blocks_host(1, n_rows, n_cols, raw.ctypes.data, got.ctypes.data) != 0
+
+
+def test_integration_doc_binds_every_symbol():
+    """The Rust extern block a TensorLogic maintainer would add lists every entry point of the header."""
+    doc = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    missing = [s for s in _declared_symbols() if f"fn {s}(" not in doc]
+    assert not missing, missing
