@@ -47,6 +47,14 @@ struct LayerWeights {
     tlc_qtensor *attn_norm, *wq, *wk, *wv, *wo, *ffn_norm, *w_gate, *w_up, *w_down;
 };
 
+// Where a decode step that runs as one graph reports to the host without copy nodes:
+// pinned host words the sampling kernel writes directly (status first, then the token).
+struct HostReport {
+    int *host_next;                      // [batch] pinned, or null
+    tlc_dev_status *host_status;         // pinned mirror of the status word
+    const tlc_dev_status *dev_status;
+};
+
 struct tlc_llama {
     tlc_ctx *ctx;
     tlc_llama_config cfg;
@@ -62,7 +70,9 @@ struct tlc_llama {
     int32_t *ids, *positions, *next_ids;
     int32_t *host_ids;  // pinned staging
     int32_t *host_next;
-    std::map<int, cudaGraphExec_t> graph;  // decode graphs keyed by batch * 8 + parts
+    std::map<int, cudaGraphExec_t> graph;  // decode graphs keyed by batch * 8 + parts (1000 + batch: the host step)
+    const int *ids_src = nullptr;          // set while the host step is captured: token ids read from pinned memory
+    HostReport report{};                   //   and results reported straight to pinned memory
     int launches_in[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // kernels per step, by parts mask
     int heads_local, kv_heads_local, ffn_local, vocab_local;
     float temperature = 0.f;   // <= 1e-4: greedy
@@ -70,6 +80,16 @@ struct tlc_llama {
 };
 
 namespace {
+
+__device__ __forceinline__ void report_to_host(const HostReport &hr, int b, int tok) {
+    if (!hr.host_next) return;
+    if (b == 0 && hr.host_status) {
+        hr.host_status->code = hr.dev_status->code;
+        hr.host_status->where = hr.dev_status->where;
+    }
+    __threadfence_system();
+    *reinterpret_cast<volatile int *>(hr.host_next + b) = tok;
+}
 
 __global__ void embed_kernel(const uint8_t *__restrict__ table, size_t pitch, int vocab, int d,
                              const int *__restrict__ ids, int m, __half *__restrict__ y) {
@@ -91,7 +111,7 @@ __global__ void embed_kernel(const uint8_t *__restrict__ table, size_t pitch, in
 // [shard][row][vocab_per_shard]; token index = shard * vocab_per_shard + i.
 __global__ void argmax_advance_kernel(const __half *__restrict__ logits, int vocab, int shards, int rows,
                                       int *__restrict__ next_ids, int *__restrict__ ids,
-                                      int *__restrict__ positions, int advance) {
+                                      int *__restrict__ positions, int advance, HostReport hr) {
     __shared__ float sv[32];
     __shared__ int si[32];
     tlc_pdl_prologue();  // the logits come from the previous kernel
@@ -148,6 +168,7 @@ __global__ void argmax_advance_kernel(const __half *__restrict__ logits, int voc
                 ids[b] = bi;
                 positions[b] += 1;
             }
+            report_to_host(hr, b, bi);
         }
     }
 }
@@ -174,7 +195,7 @@ __global__ void __launch_bounds__(1024) sample_advance_kernel(const __half *__re
                                                               int rows, float temperature, uint64_t seed,
                                                               const float *__restrict__ uniforms, int fixed_pos,
                                                               int *__restrict__ next_ids, int *__restrict__ ids,
-                                                              int *__restrict__ positions, int advance) {
+                                                              int *__restrict__ positions, int advance, HostReport hr) {
     __shared__ float red[32];
     __shared__ float warp_sum[32];
     __shared__ int found_min;
@@ -240,6 +261,7 @@ __global__ void __launch_bounds__(1024) sample_advance_kernel(const __half *__re
             ids[b] = tok;
             positions[b] += 1;
         }
+        report_to_host(hr, b, tok);
     }
 }
 
@@ -376,7 +398,7 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         const size_t total = (size_t)m * (d / 8);
         cudaError_t le = tlc_launch_pdl(ctx, embed_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
                                         static_cast<const uint8_t *>(L->tok_embd->data), L->tok_embd->row_pitch,
-                                        (int)L->tok_embd->n_rows, d, (const int *)L->ids, m, L->x);
+                                        (int)L->tok_embd->n_rows, d, L->ids_src ? L->ids_src : (const int *)L->ids, m, L->x);
         if (le != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "embedding launch failed: %s", cudaGetErrorString(le));
         TLC_CHECK_LAUNCH(ctx);
     }
@@ -479,10 +501,11 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
                 L->temperature > 0.0001f
                     ? tlc_launch_pdl(ctx, sample_advance_kernel, dim3(srows), dim3(1024), 0, lg, L->vocab_local,
                                      c.tp_size, rows, L->temperature, L->sample_seed, (const float *)nullptr,
-                                     decode ? -1 : pos0 + m - 1, (int *)L->next_ids, (int *)L->ids, (int *)L->positions, advance ? 1 : 0)
+                                     decode ? -1 : pos0 + m - 1, (int *)L->next_ids, (int *)L->ids, (int *)L->positions, advance ? 1 : 0,
+                                     L->report)
                     : tlc_launch_pdl(ctx, argmax_advance_kernel, dim3(srows), dim3(1024), 0, lg, L->vocab_local,
                                      c.tp_size, rows, (int *)L->next_ids, (int *)L->ids, (int *)L->positions,
-                                     advance ? 1 : 0);
+                                     advance ? 1 : 0, L->report);
             if (le != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "sampling launch failed: %s", cudaGetErrorString(le));
             TLC_CHECK_LAUNCH(ctx);
         }
@@ -647,14 +670,14 @@ extern "C" int32_t tlc_llama_decode_host(tlc_llama *L, int32_t batch, const int3
             TLC_CUDA(cudaStreamSynchronize(ctx->stream));
             const uint64_t launches_before = ctx->launches;
             TLC_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-            cudaError_t ce = cudaMemcpyAsync(L->ids, L->host_ids, (size_t)batch * 4, cudaMemcpyHostToDevice, ctx->stream);
-            int32_t rc = ce == cudaSuccess ? forward(L, batch, true, 0, false, true, true, 7) : TLC_OK;
-            // the status word first: once the sampled ids have landed, it has too
-            if (ce == cudaSuccess && !rc)
-                ce = cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(tlc_dev_status), cudaMemcpyDeviceToHost,
-                                     ctx->stream);
-            if (ce == cudaSuccess && !rc)
-                ce = cudaMemcpyAsync(L->host_next, L->next_ids, (size_t)batch * 4, cudaMemcpyDeviceToHost, ctx->stream);
+            // No copy nodes: the embedding gather reads the ids from pinned host memory and the
+            // sampling kernel writes the status word, then the sampled ids, to pinned host memory.
+            cudaError_t ce = cudaSuccess;
+            L->ids_src = L->host_ids;
+            L->report = HostReport{L->host_next, ctx->host_status, ctx->dev_status};
+            int32_t rc = forward(L, batch, true, 0, false, true, true, 7);
+            L->ids_src = nullptr;
+            L->report = HostReport{};
             cudaGraph_t g = nullptr;
             cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
             ctx->launches = launches_before;
@@ -758,10 +781,10 @@ extern "C" int32_t tlc_temperature_sample(tlc_ctx *ctx, const void *logits_dev, 
         if (temperature > 0.0001f)
             sample_advance_kernel<<<rows, 1024, 0, ctx->stream>>>(
                 static_cast<const __half *>(logits_dev), vocab, 1, rows, temperature, 0, (const float *)tlc_buf_ptr(ub),
-                -1, (int *)tlc_buf_ptr(ib), nullptr, nullptr, 0);
+                -1, (int *)tlc_buf_ptr(ib), nullptr, nullptr, 0, HostReport{});
         else
             argmax_advance_kernel<<<rows, 1024, 0, ctx->stream>>>(static_cast<const __half *>(logits_dev), vocab, 1, rows,
-                                                                   (int *)tlc_buf_ptr(ib), nullptr, nullptr, 0);
+                                                                   (int *)tlc_buf_ptr(ib), nullptr, nullptr, 0, HostReport{});
         ctx->launches++;
         if (cudaGetLastError() != cudaSuccess) rc = tlc_fail(TLC_ERR_CUDA, "sampling launch failed");
     }
