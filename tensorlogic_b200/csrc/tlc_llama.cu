@@ -120,6 +120,22 @@ __global__ void argmax_advance_kernel(const __half *__restrict__ logits, int voc
     int bi = -1;
     for (int sh = 0; sh < shards; sh++) {
         const __half *row = logits + ((size_t)sh * rows + b) * vocab;
+        if (vocab % 8 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+            // 16-byte loads; a thread still meets its elements in increasing index order
+            for (int c = threadIdx.x; c < vocab / 8; c += blockDim.x) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(row + 8 * c);
+                const __half *h = reinterpret_cast<const __half *>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float v = __half2float(h[j]);
+                    if (bi < 0 || !(v < best)) {
+                        best = v;
+                        bi = sh * vocab + 8 * c + j;
+                    }
+                }
+            }
+            continue;
+        }
         for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
             const float v = __half2float(row[i]);
             if (bi < 0 || !(v < best)) {  // v >= best (or unordered): later index wins
