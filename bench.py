@@ -47,7 +47,7 @@ METRIC = "q4_0_decode_tokens_per_s"
 L2_BYTES = 126 * 1000 * 1000
 # DRAM bytes per GEMV launch of the N=1 workload, from one ncu capture of this command
 # (profiles/tinyllama_decode_launches.md): 586.92 MB read + ~0 written over the 89 launches of a step.
-NCU_GEMV_TRAFFIC_PER_LAUNCH = 587.11e6 / 89
+NCU_GEMV_TRAFFIC_PER_LAUNCH = 587.14e6 / 89
 
 
 def load_peaks() -> dict:
