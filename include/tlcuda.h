@@ -333,22 +333,32 @@ TLC_API int32_t tlc_attention(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer, c
  * positions_dev (one query per sequence), on caller-owned buffers:
  *   q, out        [batch, n_heads, head_dim] f16
  *   k/v_cache_dev [batch, max_seq, n_kv_heads, head_dim] f16 (one layer)
- * launched on `stream` (a cudaStream_t) of the CURRENT device.  The split-key
- * partial results and ticket counters live in a 2 MiB + 4 KiB array inside the
- * library image, per GPU, for the life of the process; a call is rejected
+ * launched on `stream` (a cudaStream_t) of the CURRENT device (a stream of
+ * another device is refused with TLC_ERR_DEVICE).  The split-key partial
+ * results, ticket counters and one status word live in a 2 MiB + 4.25 KiB array
+ * inside the library image, per GPU, for the life of the process; a call is rejected
  * (TLC_ERR_BUFFER_EXHAUSTED) when batch * n_heads * splits * (head_dim + 2) * 4
  * bytes exceed 2 MiB (splits = key splits the launch uses, about 2 * SMs /
  * (batch * n_kv_heads), at most max_keys / 64) or batch * n_kv_heads exceeds 1024.  The first call on a
  * device looks the array's address up (cudaGetSymbolAddress) and sets kernel
  * attributes; make that first call before any stream capture.  All calls on a
  * device share the array: two calls that overlap on the GPU (different
- * streams) race; calls on one stream are safe.  Never calls cudaMalloc /
- * cudaFree or any allocating routine. */
+ * streams) race; calls on one stream are safe.  The first-call set-up is
+ * guarded by a mutex, so host threads may race to make it.  positions_dev[b] + 1
+ * keys are read per sequence, never more than max_keys: a larger position is cut
+ * there and tlc_attention_decode_static_status reports it.  Never calls
+ * cudaMalloc / cudaFree or any allocating routine. */
 TLC_API int32_t tlc_attention_decode_static(void *stream, const void *q_dev, const void *k_cache_dev,
                                             const void *v_cache_dev, void *out_dev, int32_t batch,
                                             int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
                                             int32_t max_seq, const int32_t *positions_dev,
                                             int32_t max_keys, float scale);
+
+/* Companion of tlc_attention_decode_static (no counterpart in the reference):
+ * waits for `stream`, then sets *clamped_out to 1 if, since the last query on the
+ * current device, a call met a position at or beyond its max_keys and cut the
+ * keys there, else 0; the note is cleared.  Allocates nothing. */
+TLC_API int32_t tlc_attention_decode_static_status(void *stream, int32_t *clamped_out);
 
 /* ---- GGUF models ----------------------------------------------------------- */
 

@@ -328,6 +328,12 @@ TLREF_API int tlref_linear_q_f32acc(int qtype, const uint8_t *wq, const uint16_t
     if (!row_bytes) return -2;
     float *xf = (float *)malloc((size_t)m * k * sizeof(float));
     for (size_t i = 0; i < (size_t)m * k; i++) xf[i] = h2f(x[i]);
+    /* rows in groups of eight, transposed to [group][p][8] for the blocked loop below */
+    float *xt = m >= 8 ? (float *)malloc((size_t)(m / 8) * k * 8 * sizeof(float)) : NULL;
+    if (xt)
+        for (int gI = 0; gI < m / 8; gI++)
+            for (int p = 0; p < k; p++)
+                for (int v = 0; v < 8; v++) xt[((size_t)gI * k + p) * 8 + v] = xf[(size_t)(gI * 8 + v) * k + p];
 #ifdef _OPENMP
     if (threads <= 0) threads = omp_get_max_threads();
 #pragma omp parallel num_threads(threads)
@@ -345,7 +351,22 @@ TLREF_API int tlref_linear_q_f32acc(int qtype, const uint8_t *wq, const uint16_t
             else if (qtype == 14) tlref_dequant_q6_k(row, row_bytes, (size_t)k, wh);
             else memcpy(wh, row, row_bytes);
             for (int p = 0; p < k; p++) wf[p] = h2f(wh[p]);
-            for (int i = 0; i < m; i++) {
+            int i = 0;
+            /* Eight activation rows at a time, one SIMD lane each: every output is still
+             * its own f32 sum over p in index order (separate multiply and add, no
+             * contraction), so the bits are those of the plain loop below -- only the
+             * eight sums advance together instead of one after the other. */
+            for (; xt && i + 8 <= m; i += 8) {
+                const float *xb = xt + (size_t)(i / 8) * k * 8;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (int p = 0; p < k; p++) {
+                    const float wv = wf[p];
+#pragma omp simd
+                    for (int v = 0; v < 8; v++) acc[v] += xb[(size_t)p * 8 + v] * wv;
+                }
+                for (int v = 0; v < 8; v++) y[(size_t)(i + v) * n + j] = f2h(acc[v]);
+            }
+            for (; i < m; i++) {
                 const float *xr = xf + (size_t)i * k;
                 float sum = 0.0f;
                 for (int p = 0; p < k; p++) sum += xr[p] * wf[p];
@@ -356,6 +377,7 @@ TLREF_API int tlref_linear_q_f32acc(int qtype, const uint8_t *wq, const uint16_t
         free(wf);
     }
     free(xf);
+    free(xt);
     return 0;
 }
 

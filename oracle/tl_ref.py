@@ -345,3 +345,42 @@ class RefLlama:
             x = add(x1, dn)
         xf = rms_norm(x, self.w["output_norm.weight"], self.eps)
         return self._lin(xf, "output.weight")
+
+    def forward_batch(self, ids, caches) -> np.ndarray:
+        """One decode step for len(ids) independent sequences: row b is the next token of
+        sequence b, whose keys and values live in caches[b] = (k_list, v_list) (one array per
+        layer, as k_cache / v_cache above; updated in place).  The row-wise operations run
+        on all rows at once, attention runs sequence by sequence -- the same arithmetic as
+        len(ids) separate forward() calls.  Returns logits [len(ids), vocab]."""
+        ids = np.asarray(ids, dtype=np.int32).reshape(-1)
+        B = ids.size
+        assert len(caches) == B
+        pos = np.array([caches[b][0][0].shape[0] for b in range(B)], np.int32)
+        x = embedding(self._f16w("token_embd.weight"), ids)
+        scale = 1.0 / float(np.sqrt(self.D))
+        for l in range(self.n_layers):
+            p = f"blk.{l}."
+            xn = rms_norm(x, self.w[p + "attn_norm.weight"], self.eps)
+            q = self._lin(xn, p + "attn_q.weight").reshape(B, self.H, self.D)
+            k = self._lin(xn, p + "attn_k.weight").reshape(B, self.Hkv, self.D)
+            v = self._lin(xn, p + "attn_v.weight").reshape(B, self.Hkv, self.D)
+            q = rope(q, 0, self.rope_base, positions=pos)
+            k = rope(k, 0, self.rope_base, positions=pos)
+            a = np.empty_like(q)
+            for b in range(B):
+                kl, vl = caches[b]
+                kl[l] = np.concatenate([kl[l], k[b:b + 1]], axis=0)
+                vl[l] = np.concatenate([vl[l], v[b:b + 1]], axis=0)
+                a[b] = attention(q[b:b + 1], kl[l], vl[l], scale, int(pos[b]), self.round_exp, self.f16_pv)[0]
+            o = self._lin(a.reshape(B, self.H * self.D), p + "attn_output.weight")
+            x1 = add(x, o)
+            xn2 = rms_norm(x1, self.w[p + "ffn_norm.weight"], self.eps)
+            act = swiglu(self._lin(xn2, p + "ffn_gate.weight"), self._lin(xn2, p + "ffn_up.weight"))
+            x = add(x1, self._lin(act, p + "ffn_down.weight"))
+        xf = rms_norm(x, self.w["output_norm.weight"], self.eps)
+        return self._lin(xf, "output.weight")
+
+    def empty_caches(self, batch: int):
+        """Caches for forward_batch: `batch` sequences with no tokens yet."""
+        return [([np.zeros((0, self.Hkv, self.D), np.float16) for _ in range(self.n_layers)],
+                 [np.zeros((0, self.Hkv, self.D), np.float16) for _ in range(self.n_layers)]) for _ in range(batch)]

@@ -107,6 +107,7 @@ PROTOTYPES = {
     "tlc_kvcache_append": (i32, [vp, vp, i32, vp, vp, i32, i32, vp]),
     "tlc_attention": (i32, [vp, vp, i32, vp, vp, i32, i32, i32, i32, vp, i32, f32]),
     "tlc_attention_decode_static": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, f32]),
+    "tlc_attention_decode_static_status": (i32, [vp, vp]),
     "tlc_model_load_gguf": (i32, [vp, C.c_char_p, i32, i32, P(vp)]),
     "tlc_gguf_open": (i32, [C.c_char_p, P(vp)]),
     "tlc_gguf_close": (i32, [vp]),

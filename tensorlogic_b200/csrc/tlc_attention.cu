@@ -24,6 +24,8 @@
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "tlc_internal.h"
 
 struct tlc_kvcache {
@@ -57,6 +59,9 @@ struct AttnParams {
     int push_offset; // cluster mode: byte offset of the merge area in dynamic shared memory
     int cluster;     // 1: the nsplit CTAs of a tile form a thread-block cluster and merge through
                      // distributed shared memory instead of global scratch
+    int key_limit;   // keys the launch was sized for (<= Tmax): a sequence whose position says it
+                     // holds more is cut there and the status word (when given) says so
+    tlc_dev_status *status;  // device word or null
 };
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool valid) {
@@ -115,25 +120,18 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     const int qt = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
     const int G = p.G, RQ = 16 / G;
 
-    const int pos0 = p.positions ? p.positions[b] : p.q_pos0;  // position of this sequence's query 0
-    const int T = pos0 + p.I;                                    // keys in the cache (incl. the new ones)
-    // Rows of the tile: r -> (query qt*RQ + r/G, head hk*G + r%G).
-    const int qi_lo = qt * RQ + g / G, qi_hi = qt * RQ + (g + 8) / G;
-    const int head_lo = hk * G + g % G, head_hi = hk * G + (g + 8) % G;
-    const bool valid_lo = qi_lo < p.I, valid_hi = qi_hi < p.I;
-    const int rpos_lo = pos0 + qi_lo, rpos_hi = pos0 + qi_hi;  // last visible key of the row
-
-    // Keys this CTA covers: its split, cut at the last key any row of the tile may see.
-    const int last_q = min(p.I, (qt + 1) * RQ) - 1;
-    const int visible_end = min(T, pos0 + last_q + 1);
+    // A decode step's query, its newest cache row AND its position come from earlier kernels
+    // of the stream.  Before griddepcontrol.wait the position word may still hold the previous
+    // step's value; positions only grow while kernels are in flight (the host resets them
+    // after a stream synchronize), so that value is a lower bound of the true one.  It is used
+    // for one thing only: a first K/V tile that lies entirely below it holds rows of earlier
+    // steps, whatever the true position turns out to be, and is fetched while the previous
+    // kernel is still running.  k_begin does not depend on the position at all.
     const int k_begin = split * p.keys_per_split;
-    const int k_end = min(visible_end, k_begin + p.keys_per_split);
-    const int ntiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
-
     const __half *kbase = p.kc + ((size_t)b * p.Tmax * p.Hkv + hk) * D;
     const __half *vbase = p.vc + ((size_t)b * p.Tmax * p.Hkv + hk) * D;
     const size_t key_stride = (size_t)p.Hkv * D;
-
+    int k_end = 0;  // set below; the early tile is whole, so every key of it passes `< k_end`
     auto load_tile = [&](int tile, int stage) {
         const int j0 = k_begin + tile * kTileKeys;
         constexpr int CHUNKS = kTileKeys * (D / 8);
@@ -147,14 +145,35 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         }
         cp_async_commit();
     };
-
-    // A decode step's query and its newest cache row come from the previous kernel of the
-    // stream; the older rows were written by earlier steps (and the positions before this
-    // step began), so a first tile made of older rows only is fetched before waiting for
-    // that kernel.
-    const bool early = p.I == 1 && ntiles > 0 && k_begin + kTileKeys <= pos0;
-    if (early) load_tile(0, 0);
+    bool early = false;
+    if (p.positions && p.I == 1) {
+        const int hint = min(*reinterpret_cast<const volatile int *>(p.positions + b), p.key_limit - 1);
+        early = k_begin + kTileKeys <= hint && k_begin + kTileKeys <= p.keys_per_split * (split + 1);
+        if (early) {
+            k_end = k_begin + kTileKeys;
+            load_tile(0, 0);
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    int pos0 = p.positions ? *reinterpret_cast<const volatile int *>(p.positions + b) : p.q_pos0;  // position of query 0
+    if (pos0 < 0) pos0 = 0;
+    if (pos0 + p.I > p.key_limit) {  // more keys than the launch (or the cache) holds: cut, and say so
+        pos0 = p.key_limit - p.I;
+        if (p.status && tid == 0 && atomicCAS(&p.status->code, 0, TLC_DEV_INDEX) == 0) p.status->where = 200 + b;
+    }
+    const int T = pos0 + p.I;  // keys in the cache (incl. the new ones)
+    // Rows of the tile: r -> (query qt*RQ + r/G, head hk*G + r%G).
+    const int qi_lo = qt * RQ + g / G, qi_hi = qt * RQ + (g + 8) / G;
+    const int head_lo = hk * G + g % G, head_hi = hk * G + (g + 8) % G;
+    const bool valid_lo = qi_lo < p.I, valid_hi = qi_hi < p.I;
+    const int rpos_lo = pos0 + qi_lo, rpos_hi = pos0 + qi_hi;  // last visible key of the row
+
+    // Keys this CTA covers: its split, cut at the last key any row of the tile may see.
+    const int last_q = min(p.I, (qt + 1) * RQ) - 1;
+    const int visible_end = min(T, pos0 + last_q + 1);
+    k_end = min(visible_end, k_begin + p.keys_per_split);
+    const int ntiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
 
     // Q fragments (A operand), straight from global memory.
     uint32_t qa[KSTEPS][4];
@@ -426,7 +445,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_prefill_kernel(const A
     const int b = blockIdx.z, hk = blockIdx.y, qt = blockIdx.x;
     const int G = p.G, RQ = 64 / G;
     const int pos0 = p.q_pos0;
-    const int T = pos0 + p.I;
+    const int T = min(pos0 + p.I, p.key_limit);  // the host checks pos0 + I <= Tmax; never read past the cache
     // rows of this warp: r_lo = 16*warp + g, r_hi = r_lo + 8; r -> (query qt*RQ + r/G, head hk*G + r%G)
     const int r_lo = 16 * warp + g, r_hi = r_lo + 8;
     const int qi_lo = qt * RQ + r_lo / G, qi_hi = qt * RQ + r_hi / G;
@@ -641,6 +660,8 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
     p.q_pos0 = q_pos0;
     p.positions = positions_dev;
     p.scale = scale;
+    p.key_limit = T;  // <= max_seq (checked above); a position beyond it is cut on the device
+    p.status = ctx->dev_status;
     if (I > 1) {
         // Prefill: 64-row tiles, the warps split the rows (attention_prefill_kernel).
         p.nsplit = 1;
@@ -860,7 +881,8 @@ namespace {
 
 constexpr size_t kStaticPartialBytes = (size_t)2 << 20;  // split-key partials (max, sum, O)
 constexpr size_t kStaticTicketBytes = 4096;              // one int per (sequence, KV head)
-constexpr size_t kStaticScratchBytes = kStaticPartialBytes + kStaticTicketBytes;
+constexpr size_t kStaticStatusBytes = 256;               // a tlc_dev_status: "a position was cut at max_keys"
+constexpr size_t kStaticScratchBytes = kStaticPartialBytes + kStaticTicketBytes + kStaticStatusBytes;
 
 static __device__ __align__(256) unsigned char g_static_attention_scratch[kStaticScratchBytes];
 
@@ -870,6 +892,7 @@ struct StaticSetup {
     int sm_count = 0;
 };
 StaticSetup g_static_setup[64];
+std::mutex g_static_setup_mutex;  // two host threads may make the first call on a device at once
 
 }  // namespace
 
@@ -891,10 +914,20 @@ extern "C" int32_t tlc_attention_decode_static(void *stream, const void *q_dev, 
     int device = 0;
     TLC_CUDA(cudaGetDevice(&device));
     TLC_REQUIRE(device >= 0 && device < 64, TLC_ERR_DEVICE, "device ordinal %d out of range", device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (st != nullptr && st != cudaStreamLegacy && st != cudaStreamPerThread) {
+        // the scratch address below belongs to the current device; a stream of another one would
+        // run the kernel there with this device's pointers
+        int sdev = -1;
+        TLC_CUDA(cudaStreamGetDevice(st, &sdev));
+        TLC_REQUIRE(sdev == device, TLC_ERR_DEVICE,
+                    "attention_decode_static: the stream belongs to device %d, the current device is %d", sdev, device);
+    }
     StaticSetup &su = g_static_setup[device];
     const size_t smem = (size_t)4 * kTileKeys * (D + 8) * sizeof(__half);
     const size_t smem_o = (size_t)4 * 16 * D * sizeof(float);
     const size_t smem_bytes = smem > smem_o ? smem : smem_o;
+    std::lock_guard<std::mutex> setup_lock(g_static_setup_mutex);
     if (!su.done) {
         // First call on this device (which is the current one): in host code the
         // array's name is only a stand-in, the kernel needs its device address.
@@ -911,6 +944,7 @@ extern "C" int32_t tlc_attention_decode_static(void *stream, const void *q_dev, 
         TLC_CUDA(cudaFuncSetAttribute(attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)attention_smem_limit(128)));
         su.scratch = static_cast<unsigned char *>(p);
+        // the status word starts at zero like every __device__ array; later calls leave it alone
         su.done = true;
     }
 
@@ -927,6 +961,10 @@ extern "C" int32_t tlc_attention_decode_static(void *stream, const void *q_dev, 
     p.q_pos0 = 0;
     p.positions = positions_dev;
     p.scale = scale;
+    // positions_dev[b] + 1 keys are read, but never more than max_keys: a larger position is cut
+    // there (the newest keys are dropped) and the status word below records it.
+    p.key_limit = max_keys;
+    p.status = reinterpret_cast<tlc_dev_status *>(su.scratch + kStaticPartialBytes + kStaticTicketBytes);
     p.q_tiles = 1;
     const int tiles = (max_keys + kTileKeys - 1) / kTileKeys;
     const int want = (2 * su.sm_count + batch * n_kv_heads - 1) / (batch * n_kv_heads);
@@ -947,7 +985,6 @@ extern "C" int32_t tlc_attention_decode_static(void *stream, const void *q_dev, 
     p.part_ml = reinterpret_cast<float *>(su.scratch);
     p.part_o = reinterpret_cast<float *>(su.scratch + ml);
     p.counters = reinterpret_cast<int *>(su.scratch + kStaticPartialBytes);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     // The array keeps whatever the previous call left; only the tickets must start at zero.
     TLC_CUDA(cudaMemsetAsync(p.counters, 0, (size_t)batch * n_kv_heads * sizeof(int), st));
     dim3 grid(nsplit, n_kv_heads, batch);
@@ -957,5 +994,33 @@ extern "C" int32_t tlc_attention_decode_static(void *stream, const void *q_dev, 
         attention_kernel<128><<<grid, kAttnThreads, smem_bytes, st>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return tlc_fail(TLC_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    return TLC_OK;
+}
+
+// Reads (and clears) the note tlc_attention_decode_static leaves when a sequence's position
+// was at or beyond max_keys and its keys were cut there: *clamped_out = 1 if that happened
+// since the last query on the current device, else 0.  Waits for `stream`; allocates nothing.
+extern "C" int32_t tlc_attention_decode_static_status(void *stream, int32_t *clamped_out) {
+    TLC_REQUIRE(clamped_out, TLC_ERR_INVALID_OPERATION, "attention_decode_static_status: null pointer");
+    *clamped_out = 0;
+    int device = 0;
+    TLC_CUDA(cudaGetDevice(&device));
+    TLC_REQUIRE(device >= 0 && device < 64, TLC_ERR_DEVICE, "device ordinal %d out of range", device);
+    unsigned char *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> setup_lock(g_static_setup_mutex);
+        if (!g_static_setup[device].done) return TLC_OK;  // never called here: nothing was cut
+        scratch = g_static_setup[device].scratch;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    tlc_dev_status h{};
+    void *word = scratch + kStaticPartialBytes + kStaticTicketBytes;
+    TLC_CUDA(cudaMemcpyAsync(&h, word, sizeof(h), cudaMemcpyDeviceToHost, st));
+    TLC_CUDA(cudaStreamSynchronize(st));
+    if (h.code != 0) {
+        TLC_CUDA(cudaMemsetAsync(word, 0, sizeof(h), st));
+        TLC_CUDA(cudaStreamSynchronize(st));
+        *clamped_out = 1;
+    }
     return TLC_OK;
 }

@@ -171,6 +171,9 @@ int32_t tlc_status_after_sync(tlc_ctx *ctx) {
         int code = ctx->host_status->code, where = ctx->host_status->where;
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(tlc_dev_status), ctx->stream);
         cudaStreamSynchronize(ctx->stream);
+        if (code == TLC_DEV_INDEX)
+            return tlc_fail(TLC_ERR_INDEX, "Index out of bounds: a sequence position lies outside the KV cache "
+                            "(site %d); the access was skipped", where);
         return tlc_fail(TLC_ERR_TIMEOUT, "a device-side bounded wait gave up (code %d at site %d)", code,
                         where);
     }

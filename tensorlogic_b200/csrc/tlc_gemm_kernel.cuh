@@ -58,6 +58,7 @@ struct GemmParams {
     int head_dim;  // > 0: interleaved RoPE over heads of this width
     int pos_offset;
     const int *positions;
+    int max_pos;  // > 0: rows addressed by position are dropped from this position on (status TLC_DEV_INDEX)
     float rope_base;
     int vec_ok;  // strides, N and pointers allow 16-byte stores
     tlc_dev_status *status;

@@ -301,8 +301,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
         for (int pc = warp >> 2; pc < PIECES; pc += 3) {
             const int i = pc / (OUT_COLS / 32), c0 = (pc % (OUT_COLS / 32)) * 32;
             const int row = m0 + 128 * i + 32 * wq + lane;
-            const bool row_ok = row < p.m;
+            bool row_ok = row < p.m;
             const int pos = !row_ok ? 0 : p.positions ? p.positions[row] : p.pos_offset + row;
+            if (row_ok && p.pos_stride != 0 && p.max_pos > 0 && (pos < 0 || pos >= p.max_pos)) {
+                // a cache row that does not exist: nothing is written, the host hears about it
+                if (atomicCAS(&p.status->code, 0, TLC_DEV_INDEX) == 0) p.status->where = 301;
+                row_ok = false;
+            }
             // Dense rows by default; a KV-cache destination addresses rows by (sequence, position).
             __half *ybase = p.y + (size_t)((long long)row * p.row_stride + (long long)pos * p.pos_stride);
             uint32_t r[32];
@@ -479,6 +484,7 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
         }
         p.pos_offset = a.pos_offset;
         p.positions = a.positions;
+        p.max_pos = a.max_pos;
         p.rope_base = (float)a.rope_base;
         p.vec_ok = ((p.row_stride | p.pos_stride | (long long)p.n) & 7) == 0 && ((uintptr_t)p.y & 15) == 0 &&
                    ((uintptr_t)p.residual & 15) == 0;

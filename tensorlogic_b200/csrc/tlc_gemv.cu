@@ -363,6 +363,7 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.pos_offset = a.pos_offset + m0;
         p.rope_base = (float)a.rope_base;
         p.positions = a.positions ? a.positions + m0 : nullptr;
+        p.max_pos = a.max_pos;
         p.status = ctx->dev_status;
         p.wait_ns = ctx->wait_ns;
         const int nt = mc > 8 ? 2 : 1;

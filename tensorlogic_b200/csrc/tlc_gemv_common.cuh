@@ -64,6 +64,7 @@ struct GemvParams {
     int pos_offset;
     float rope_base;
     const int *positions;
+    int max_pos;   // > 0: outputs addressed by position are dropped from this position on (status TLC_DEV_INDEX)
     int nstages;
     int contig;    // 1: each CTA takes a contiguous range of units, 0: units blockIdx.x, + gridDim.x, ...
     int l2_hint;   // 1: weight copies carry the evict-first L2 hint

@@ -502,6 +502,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
             // Where this output goes: dense rows by default; a KV-cache destination
             // addresses rows by (sequence, position) instead.
             const size_t yidx = (size_t)((long long)col * rstride + (long long)pos * pstride) + n;
+            if (pstride != 0 && p.max_pos > 0 && (pos < 0 || pos >= p.max_pos)) {
+                // a cache row that does not exist: nothing is written, the host hears about it
+                if (atomicCAS(&p.status->code, 0, TLC_DEV_INDEX) == 0) p.status->where = 300;
+                continue;
+            }
             if (rheads > 0) {
                 // Interleaved RoPE on the f16-rounded projection
                 // (rope_f16, shaders/unified.metal:2355-2417).

@@ -11,6 +11,8 @@
 // the data alignment honours the general.alignment key (the reference always
 // uses 32).  Quantized tensors are uploaded verbatim; nothing is dequantized.
 #include <cerrno>
+#include <climits>
+#include <cstdint>
 #include <cstring>
 #include <fstream>
 #include <memory>
@@ -61,7 +63,7 @@ struct Reader {
     }
     std::string str() {
         uint64_t n = get<uint64_t>();
-        if (!ok || n > size) {
+        if (!ok || n > left()) {
             ok = false;
             return {};
         }
@@ -70,11 +72,23 @@ struct Reader {
         if (!f) ok = false;
         return s;
     }
+    // Bytes left in the file; a length field larger than this is corrupt, whatever it multiplies to.
+    uint64_t left() {
+        const uint64_t p = pos();
+        return p <= size ? size - p : 0;
+    }
     void skip(uint64_t n) {
+        if (!ok || n > left()) {
+            ok = false;
+            return;
+        }
         f.seekg((std::streamoff)n, std::ios::cur);
         if (!f) ok = false;
     }
-    uint64_t pos() { return (uint64_t)f.tellg(); }
+    uint64_t pos() {
+        const std::streamoff p = f.tellg();
+        return p < 0 ? UINT64_MAX : (uint64_t)p;
+    }
 };
 
 // GGUF metadata value types.
@@ -119,9 +133,12 @@ bool skip_value(Reader &r, uint32_t t, int depth = 0) {
         uint64_t n = r.get<uint64_t>();
         if (!r.ok) return false;
         if (size_t s = scalar_size(et)) {
-            r.skip(n * s);
+            uint64_t total = 0;
+            if (__builtin_mul_overflow(n, (uint64_t)s, &total)) return false;
+            r.skip(total);
             return r.ok;
         }
+        if (n > r.left()) return false;  // every element takes at least one byte
         for (uint64_t i = 0; i < n && r.ok; i++)
             if (!skip_value(r, et, depth + 1)) return false;
         return r.ok;
@@ -280,24 +297,36 @@ static int32_t parse_gguf(const char *path, tlc_gguf *g) {
         t.type = (int32_t)ti.type;
         t.n_dims = (int32_t)ti.dims.size();
         // Reversed dims: file order is fastest-first; [rows, cols] = [prod(dims[1..]), dims[0]].
+        // The header comes from an untrusted file: every product is checked for overflow, so
+        // that a wrapped size can never pass the end-of-file test below.
+        uint64_t rows = 1, elems = 0;
+        bool ok = ti.dims[0] >= 1 && ti.dims[0] <= (uint64_t)INT64_MAX;
+        for (size_t i = 1; ok && i < ti.dims.size(); i++)
+            ok = ti.dims[i] >= 1 && !__builtin_mul_overflow(rows, ti.dims[i], &rows);
+        ok = ok && rows <= (uint64_t)INT64_MAX && !__builtin_mul_overflow(rows, ti.dims[0], &elems);
+        TLC_REQUIRE(ok, TLC_ERR_LOAD, "tensor '%s' has a zero or overflowing shape", ti.name.c_str());
         t.cols = (int64_t)ti.dims[0];
-        t.rows = 1;
-        for (size_t i = 1; i < ti.dims.size(); i++) t.rows *= (int64_t)ti.dims[i];
-        if (t.type == TLC_TYPE_F32) t.nbytes = (uint64_t)t.rows * t.cols * 4;
-        else if (t.type == TLC_TYPE_F16) t.nbytes = (uint64_t)t.rows * t.cols * 2;
+        t.rows = (int64_t)rows;
+        uint64_t units = 0, unit_bytes = 0;  // nbytes = units * unit_bytes
+        if (t.type == TLC_TYPE_F32) { units = elems; unit_bytes = 4; }
+        else if (t.type == TLC_TYPE_F16) { units = elems; unit_bytes = 2; }
         else if (t.type == TLC_TYPE_Q4_0 || t.type == TLC_TYPE_Q8_0) {
             TLC_REQUIRE(t.cols % 32 == 0, TLC_ERR_LOAD, "tensor '%s': %lld columns are not a multiple of 32",
                         t.name.c_str(), (long long)t.cols);
-            t.nbytes = (uint64_t)t.rows * (t.cols / 32) * tlc_block_bytes(t.type);
+            units = elems / 32;
+            unit_bytes = tlc_block_bytes(t.type);
         } else if (t.type == TLC_TYPE_Q6_K) {
             TLC_REQUIRE(t.cols % 256 == 0, TLC_ERR_LOAD, "tensor '%s': %lld columns are not a multiple of 256",
                         t.name.c_str(), (long long)t.cols);
-            t.nbytes = (uint64_t)t.rows * (t.cols / 256) * 210;
-        } else {
-            t.nbytes = 0;  // unsupported type: listed, but cannot be uploaded
-        }
-        t.offset = g->data_start + ti.offset;
-        TLC_REQUIRE(t.offset + t.nbytes <= g->file_size, TLC_ERR_LOAD,
+            units = elems / 256;
+            unit_bytes = 210;
+        }  // else unsupported type: listed with 0 bytes, cannot be uploaded
+        TLC_REQUIRE(!__builtin_mul_overflow(units, unit_bytes, &t.nbytes), TLC_ERR_LOAD,
+                    "tensor '%s' has an overflowing byte size", ti.name.c_str());
+        TLC_REQUIRE(!__builtin_add_overflow(g->data_start, ti.offset, &t.offset) && t.offset <= g->file_size,
+                    TLC_ERR_LOAD, "tensor '%s' starts past the end of the file (offset %llu, file has %llu)",
+                    ti.name.c_str(), (unsigned long long)ti.offset, (unsigned long long)g->file_size);
+        TLC_REQUIRE(t.nbytes <= g->file_size - t.offset, TLC_ERR_LOAD,
                     "tensor '%s' runs past the end of the file (%llu bytes at offset %llu, file has %llu)",
                     t.name.c_str(), (unsigned long long)t.nbytes, (unsigned long long)t.offset,
                     (unsigned long long)g->file_size);

@@ -19,6 +19,10 @@ struct tlc_dev_status {
     int code;   // 0 = fine
     int where;  // kernel-specific location id of the wait that gave up
 };
+// Status codes below TLC_DEV_INDEX mean a bounded wait that ran out (TLC_ERR_TIMEOUT);
+// TLC_DEV_INDEX means a kernel met a sequence position outside its cache and skipped the
+// access (TLC_ERR_INDEX).
+#define TLC_DEV_INDEX 16
 
 struct tlc_pool {
     // idle buffers by class size
@@ -193,6 +197,9 @@ struct tlc_gemv_args {
     int32_t pos_offset = 0;
     uint32_t rope_base = 10000;
     const int32_t *positions = nullptr;  // device int32 [m] or null
+    // Outputs addressed by position (pos_stride != 0, a KV cache): positions >= max_pos are
+    // not stored and the device status word reports TLC_DEV_INDEX.  0: no limit.
+    int32_t max_pos = 0;
 };
 
 int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a);

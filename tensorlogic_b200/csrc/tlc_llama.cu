@@ -75,6 +75,9 @@ struct tlc_llama {
     HostReport report{};                   //   and results reported straight to pinned memory
     int launches_in[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // kernels per step, by parts mask
     int heads_local, kv_heads_local, ffn_local, vocab_local;
+    // Host-side upper bound of every sequence's position (the device copy advances by itself
+    // during graph replays): no step is enqueued that would write cache row max_seq.
+    std::vector<int> pos_hi;
     float temperature = 0.f;   // <= 1e-4: greedy
     uint64_t sample_seed = 0;  // uniform draws: counter-based, keyed by (seed, position, sequence)
 };
@@ -307,6 +310,7 @@ extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_ll
     L->kv_heads_local = c.n_kv_heads / tp;
     L->ffn_local = c.ffn_dim / tp;
     L->layers.resize(c.n_layers);
+    L->pos_hi.assign(64, 0);
     auto expect = [&](tlc_qtensor *t, int64_t rows, int64_t cols, const std::string &name) -> int32_t {
         TLC_REQUIRE(t->n_rows == rows && t->n_cols == cols, TLC_ERR_SHAPE_MISMATCH,
                     "tensor '%s' is [%lld, %lld], expected [%lld, %lld]", name.c_str(), (long long)t->n_rows,
@@ -441,6 +445,7 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
             a.pos_offset = pos0;
             a.rope_base = c.rope_base;
             a.positions = positions;
+            a.max_pos = c.max_seq;  // second line of defence behind the host-side bound (pos_hi)
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
         }
         if (parts & 2)
@@ -579,6 +584,7 @@ extern "C" int32_t tlc_llama_prefill(tlc_llama *L, const int32_t *ids_host, int3
     if (int32_t rc = forward(L, n, false, pos0, all_rows != 0, true, false)) return rc;
     // Sequence 0 continues after the prompt with the sampled token.
     const int32_t next_pos = pos0 + n;
+    L->pos_hi[0] = next_pos;
     L->host_next[32] = next_pos;
     TLC_CUDA(cudaMemcpyAsync(L->positions, &L->host_next[32], 4, cudaMemcpyHostToDevice, L->ctx->stream));
     TLC_CUDA(cudaMemcpyAsync(L->ids, L->next_ids, 4, cudaMemcpyDeviceToDevice, L->ctx->stream));
@@ -604,6 +610,19 @@ extern "C" int32_t tlc_llama_set_state(tlc_llama *L, int32_t batch, const int32_
     TLC_CUDA(cudaStreamSynchronize(L->ctx->stream));  // earlier steps may still read ids/positions
     TLC_CUDA(cudaMemcpy(L->ids, ids_host, (size_t)batch * 4, cudaMemcpyHostToDevice));
     TLC_CUDA(cudaMemcpy(L->positions, positions_host, (size_t)batch * 4, cudaMemcpyHostToDevice));
+    for (int i = 0; i < batch; i++) L->pos_hi[i] = positions_host[i];
+    return TLC_OK;
+}
+
+// A decode step at position p writes cache row p: `steps` more steps need
+// p + steps <= max_seq for every sequence of the batch.  The reference's cache.append
+// concatenates and cannot overflow; a pre-allocated cache has to refuse instead.
+static int32_t reserve_positions(tlc_llama *L, int batch, int steps) {
+    int hi = 0;
+    for (int i = 0; i < batch; i++) hi = L->pos_hi[i] > hi ? L->pos_hi[i] : hi;
+    TLC_REQUIRE((int64_t)hi + steps <= L->cfg.max_seq, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d",
+                hi + steps, L->cfg.max_seq);
+    for (int i = 0; i < batch; i++) L->pos_hi[i] += steps;
     return TLC_OK;
 }
 
@@ -616,8 +635,11 @@ static int32_t decode_enqueue(tlc_llama *L, int32_t batch, int32_t steps, int pa
     TLC_REQUIRE(batch >= 1 && batch <= L->cfg.max_batch, TLC_ERR_SHAPE_MISMATCH, "batch %d (max %d)", batch,
                 L->cfg.max_batch);
     TLC_REQUIRE(parts >= 1 && parts <= 7, TLC_ERR_INVALID_OPERATION, "decode parts mask %d", parts);
+    TLC_REQUIRE(steps >= 0, TLC_ERR_INVALID_OPERATION, "decode of %d steps", steps);
     tlc_ctx *ctx = L->ctx;
     const bool advance = parts == 7;
+    if (advance)
+        if (int32_t rc = reserve_positions(L, batch, steps)) return rc;
     const int key = batch * 8 + parts;
     if (!L->graph.count(key) && !L->cfg.no_graph) {
         // Warm every kernel configuration (function attributes, scratch growth)
@@ -680,6 +702,7 @@ extern "C" int32_t tlc_llama_decode_host(tlc_llama *L, int32_t batch, const int3
         // The common call: token ids up, one step, sampled ids and the status word down --
         // all of it one graph (copy nodes around the step's kernels), one launch, one wait.
         tlc_ctx *ctx = L->ctx;
+        if (int32_t rc = reserve_positions(L, batch, 1)) return rc;  // before anything is launched
         const int key = 1000 + batch;
         if (!L->graph.count(key)) {
             if (int32_t rc = decode_enqueue(L, batch, 0, 7)) return rc;  // warms the kernels, captures the plain step

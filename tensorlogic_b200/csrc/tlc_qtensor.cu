@@ -237,6 +237,11 @@ extern "C" int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows
     if (int32_t rc = shard_shape(type, n_rows, n_cols, tp_rank, tp_size, split, &rows, &cols, &row0, &col0))
         return rc;
     size_t src_row_bytes = type == TLC_TYPE_F32 ? (size_t)n_cols * 4 : bytes_per_row(type, n_cols);
+    {
+        size_t need = 0;
+        TLC_REQUIRE(!__builtin_mul_overflow(src_row_bytes, (size_t)n_rows, &need), TLC_ERR_INVALID_DIMENSION,
+                    "qtensor_create: [%lld, %lld] overflows the byte count", (long long)n_rows, (long long)n_cols);
+    }
     TLC_REQUIRE(type == TLC_TYPE_Q6_K || bytes >= src_row_bytes * (size_t)n_rows, TLC_ERR_LOAD,
                 "tensor data too short: %zu bytes for shape [%lld, %lld] (need %zu)", bytes, (long long)n_rows,
                 (long long)n_cols, src_row_bytes * (size_t)n_rows);

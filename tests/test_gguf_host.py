@@ -98,3 +98,44 @@ def test_unsupported_type_is_listed_not_fatal_at_parse(lib, tmp_path):
     t = _tensors(lib, h)["output.weight"]
     assert t[0] == 14 and (t[1], t[2]) == (4, 256)
     lib.tlc_gguf_close(h)
+
+
+def _handmade_gguf(dims, ggml_type, offset=0, kv=b"", n_kv=0, payload=b"\0" * 64):
+    """A minimal GGUF v3 file with one tensor whose header fields are taken as given."""
+    import struct
+    name = b"t"
+    head = struct.pack("<IIQQ", 0x46554747, 3, 1, n_kv) + kv
+    head += struct.pack("<Q", len(name)) + name + struct.pack("<I", len(dims))
+    head += b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", ggml_type, offset)
+    pad = (-len(head)) % 32
+    return head + b"\0" * pad + payload
+
+
+def test_header_sizes_that_wrap_are_rejected(lib, tmp_path):
+    """Shapes, offsets and lengths whose products or sums wrap around 2^64 must not pass the end-of-file test."""
+    import struct
+    from tensorlogic_b200 import _lib
+    big = 1 << 62
+    arr_kv = struct.pack("<Q", 1) + b"a" + struct.pack("<IIQ", 9, 10, (1 << 61) + 1)  # array of u64, n*8 wraps to 8
+    str_kv = struct.pack("<Q", 1) + b"s" + struct.pack("<IQ", 8, 1 << 63)              # string longer than the file
+    cases = {
+        "rows_x_cols": _handmade_gguf([1 << 33, 1 << 33], 1),             # 2^66 elements
+        "elems_x_4": _handmade_gguf([big, 1], 0),                         # 2^62 * 4 wraps to 0
+        "three_dims": _handmade_gguf([32, 1 << 32, 1 << 32], 2),          # rows wrap to 0
+        "zero_dim": _handmade_gguf([0, 4], 1),
+        "offset_wraps": _handmade_gguf([32], 1, offset=(1 << 64) - 32),   # data_start + offset wraps
+        "offset_past_end": _handmade_gguf([32], 1, offset=1 << 40),
+        "array_len": _handmade_gguf([32], 1, kv=arr_kv, n_kv=1),
+        "string_len": _handmade_gguf([32], 1, kv=str_kv, n_kv=1),
+    }
+    for name, data in cases.items():
+        p = tmp_path / f"{name}.gguf"
+        open(p, "wb").write(data)
+        rc, h = _open(lib, p)
+        assert rc == _lib.ERR_LOAD and not h.value, (name, lib.tlc_last_error())
+    # the same file with an honest shape parses
+    p = tmp_path / "ok.gguf"
+    open(p, "wb").write(_handmade_gguf([32], 1))
+    rc, h = _open(lib, p)
+    assert rc == 0, lib.tlc_last_error()
+    lib.tlc_gguf_close(h)

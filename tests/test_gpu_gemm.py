@@ -78,7 +78,7 @@ def test_edge_scales_through_gemm(dev, ref, golden, qtype):
 @pytest.mark.parametrize("qtype", [Q4, Q8])
 @pytest.mark.parametrize("n,k,m", [(128, 64, 128), (130, 128, 37), (2048, 2048, 128), (256, 5632, 100),
                                    (4000, 2048, 17), (5632, 2048, 700), (96, 4096, 513),
-                                   (200, 96, 130), (64, 1376, 40)])
+                                   (200, 96, 130), (64, 1376, 40), (512, 64, 21), (512, 128, 21)])
 def test_gemm_matches_oracle(dev, ref, qtype, n, k, m):
     from tensorlogic_b200.api import QTensor, linear
     raw = _weights(qtype, n, k, seed=12, name=f"g{n}x{k}")

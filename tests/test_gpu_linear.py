@@ -123,7 +123,8 @@ def test_lm_head_full(dev, ref, qtype):
 
 @pytest.mark.parametrize("qtype", [Q4, Q8])
 @pytest.mark.parametrize("n,k,m", [(16, 32, 1), (1, 32, 1), (17, 64, 3), (33, 96, 5), (50, 288, 7), (130, 1056, 9),
-                                   (48, 2080, 16), (31, 4128, 2), (20, 6144, 13)])
+                                   (48, 2080, 16), (31, 4128, 2), (20, 6144, 13),
+                                   (512, 64, 1), (512, 64, 5), (512, 128, 1), (2048, 64, 16)])
 def test_ragged_shapes(dev, ref, qtype, n, k, m):
     """N not a multiple of the 16-row slab, K not a multiple of 256 (padded row pitch), odd block counts."""
     from tensorlogic_b200.api import QTensor, linear

@@ -81,12 +81,17 @@ def test_shard_ranges_and_split_rules():
 
 
 @pytest.mark.gpu
-def test_tp2_runner_against_oracle():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_runner_against_oracle(world):
+    """tests/tp_parity.py under torchrun at every world size the box has GPUs for: the fused
+    all-reduce against a host sum, then prefill + decode logits against the oracle's unsharded
+    forward.  At 8 ranks every rank holds one query/KV head and two Q4_0 blocks of attn_output."""
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(ROOT, "tests", "tp_parity.py")],
-                       capture_output=True, text=True, timeout=600, env=env)
-    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+                        "--master-addr", "127.0.0.1", "--master-port", str(29517 + world),
+                        os.path.join(ROOT, "tests", "tp_parity.py")],
+                       capture_output=True, text=True, timeout=900, env=env)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
