@@ -80,6 +80,7 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (const char *e = getenv("TLC_L2_HINT")) ctx->l2_hint = atoi(e);
     if (const char *e = getenv("TLC_HOST_GRAPH")) ctx->host_graph = atoi(e) != 0;
     if (const char *e = getenv("TLC_HOST_POLL")) ctx->host_poll = atoi(e) != 0;
+    if (const char *e = getenv("TLC_STEP_KERNEL")) ctx->step_kernel = atoi(e) != 0;
     *out = ctx;
     return TLC_OK;
 }
@@ -106,6 +107,8 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         ctx->host_graph = value != 0;
     else if (n == "host_poll")
         ctx->host_poll = value != 0;
+    else if (n == "step_kernel")
+        ctx->step_kernel = value != 0;
     else
         return tlc_fail(TLC_ERR_INVALID_OPERATION, "set_option: unknown option '%s'", name);
     return TLC_OK;
@@ -170,6 +173,7 @@ int32_t tlc_status_after_sync(tlc_ctx *ctx) {
     if (ctx->host_status->code != 0) {
         int code = ctx->host_status->code, where = ctx->host_status->where;
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(tlc_dev_status), ctx->stream);
+        for (uint32_t *w : ctx->step_syncs) cudaMemsetAsync(w, 0, 2 * sizeof(uint32_t), ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         if (code == TLC_DEV_INDEX)
             return tlc_fail(TLC_ERR_INDEX, "Index out of bounds: a sequence position lies outside the KV cache "

@@ -29,6 +29,7 @@
 #include <memory>
 
 #include "tlc_internal.h"
+#include "tlc_step.h"
 #include "tlc_synth.cuh"
 
 struct tlc_kvcache;
@@ -78,6 +79,12 @@ struct tlc_llama {
     // Host-side upper bound of every sequence's position (the device copy advances by itself
     // during graph replays): no step is enqueued that would write cache row max_seq.
     std::vector<int> pos_hi;
+    // The persistent decode-step kernel (tlc_step.cu): one sequence, greedy, no tensor parallelism.
+    bool step_ok = false;
+    int step_grid = 0, step_qtype = 0, step_kmax = 0, step_splits = 1;
+    uint8_t *step_ws = nullptr;                 // global workspace (partials, tickets, candidates, barrier words)
+    tlc_step::StepWorkspace step_wsl{};
+    tlc_step::StepLayer *step_layers = nullptr;  // device copy of the per-layer pointers
     float temperature = 0.f;   // <= 1e-4: greedy
     uint64_t sample_seed = 0;  // uniform draws: counter-based, keyed by (seed, position, sequence)
 };
@@ -290,6 +297,111 @@ int32_t get(tlc_model *m, const std::string &name, tlc_qtensor **out) { return t
 
 }  // namespace
 
+// Decides whether single-sequence greedy decode steps of this model can run as the
+// persistent step kernel, and if so builds its device-side tables.
+static int32_t step_setup(tlc_llama *L) {
+    const tlc_llama_config &c = L->cfg;
+    L->step_ok = false;
+    if (c.tp_size != 1) return TLC_OK;
+    const int qt = L->out_w->type;
+    if (qt != TLC_TYPE_Q4_0 && qt != TLC_TYPE_Q8_0) return TLC_OK;
+    for (const LayerWeights &w : L->layers)
+        for (const tlc_qtensor *t : {w.wq, w.wk, w.wv, w.wo, w.w_gate, w.w_up, w.w_down})
+            if (t->type != qt) return TLC_OK;
+    const int gq = c.n_heads / c.n_kv_heads;
+    if (gq != 1 && gq != 2 && gq != 4 && gq != 8 && gq != 16) return TLC_OK;
+    const int qd = c.n_heads * c.head_dim;
+    int kmax = c.d_model > qd ? c.d_model : qd;
+    kmax = kmax > c.ffn_dim ? kmax : c.ffn_dim;
+    if (qd % 32 != 0 || c.ffn_dim % 32 != 0 || (c.n_kv_heads * c.head_dim) % 16 != 0) return TLC_OK;
+    int grid = 0;
+    if (!tlc_step::step_supported(L->ctx, qt, c.d_model, kmax, c.head_dim, &grid)) return TLC_OK;
+    if (grid < c.n_kv_heads) return TLC_OK;
+    int splits = grid / c.n_kv_heads;
+    splits = splits > 64 ? 64 : splits;
+    L->step_wsl = tlc_step::step_workspace(c.n_heads, c.head_dim, c.n_kv_heads, splits, grid);
+    cudaError_t e = cudaMalloc(&L->step_ws, L->step_wsl.total);
+    if (e == cudaSuccess) e = cudaMemset(L->step_ws, 0, L->step_wsl.total);
+    if (e == cudaSuccess) e = cudaMalloc(&L->step_layers, sizeof(tlc_step::StepLayer) * (size_t)c.n_layers);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return tlc_fail(TLC_ERR_ALLOCATION, "decode step workspace failed: %s", cudaGetErrorString(e));
+    }
+    std::vector<tlc_step::StepLayer> host((size_t)c.n_layers);
+    for (int l = 0; l < c.n_layers; l++) {
+        const LayerWeights &w = L->layers[(size_t)l];
+        void *kc = nullptr, *vc = nullptr;
+        tlc_kvcache_layer_ptrs(L->cache, l, &kc, &vc);
+        auto u8 = [](const tlc_qtensor *t) { return static_cast<const uint8_t *>(t->data); };
+        host[(size_t)l] = {u8(w.wq), u8(w.wk), u8(w.wv), u8(w.wo), u8(w.w_gate), u8(w.w_up), u8(w.w_down),
+                           static_cast<const __half *>(w.attn_norm->data), static_cast<const __half *>(w.ffn_norm->data),
+                           static_cast<__half *>(kc), static_cast<__half *>(vc)};
+    }
+    TLC_CUDA(cudaMemcpy(L->step_layers, host.data(), sizeof(tlc_step::StepLayer) * host.size(), cudaMemcpyHostToDevice));
+    L->ctx->step_syncs.push_back(reinterpret_cast<uint32_t *>(L->step_ws + L->step_wsl.bar));
+    L->step_ok = true;
+    L->step_grid = grid;
+    L->step_qtype = qt;
+    L->step_kmax = kmax;
+    L->step_splits = splits;
+    return TLC_OK;
+}
+
+static bool step_usable(const tlc_llama *L, int batch) {
+    return L->step_ok && L->ctx->step_kernel && batch == 1 && !(L->temperature > 0.0001f);
+}
+
+// Launches `steps` decode steps of sequence 0 as one persistent kernel.  ids_src: where the
+// first step reads its token (pinned host memory) or null for L->ids; host_next /
+// host_status: pinned words the last step reports to, or null.
+static int32_t step_launch(tlc_llama *L, int steps, const int *ids_src, int *host_next, tlc_dev_status *host_status) {
+    const tlc_llama_config &c = L->cfg;
+    tlc_step::StepParams p{};
+    p.layers = L->step_layers;
+    p.n_layers = c.n_layers;
+    p.d = c.d_model;
+    p.qd = c.n_heads * c.head_dim;
+    p.kvd = c.n_kv_heads * c.head_dim;
+    p.ffn = c.ffn_dim;
+    p.vocab = c.vocab;
+    p.H = c.n_heads;
+    p.Hkv = c.n_kv_heads;
+    p.D = c.head_dim;
+    p.Tmax = c.max_seq;
+    p.eps = c.rms_eps;
+    p.rope_base = (float)c.rope_base;
+    p.attn_scale = 1.0f / sqrtf((float)c.head_dim);
+    p.w_out = static_cast<const uint8_t *>(L->out_w->data);
+    p.out_norm = static_cast<const __half *>(L->out_norm->data);
+    p.embd = static_cast<const uint8_t *>(L->tok_embd->data);
+    p.embd_pitch = L->tok_embd->row_pitch;
+    p.x = L->x;
+    p.x1 = L->x1;
+    p.q = L->q;
+    p.attn = L->attn;
+    p.act = L->act;
+    p.logits = L->logits;
+    const tlc_step::StepWorkspace &w = L->step_wsl;
+    p.part_ml = reinterpret_cast<float *>(L->step_ws + w.part_ml);
+    p.part_o = reinterpret_cast<float *>(L->step_ws + w.part_o);
+    p.tickets = reinterpret_cast<int *>(L->step_ws + w.tickets);
+    p.max_splits = L->step_splits;
+    p.cand_val = reinterpret_cast<float *>(L->step_ws + w.cand_val);
+    p.cand_idx = reinterpret_cast<int *>(L->step_ws + w.cand_idx);
+    p.bar_counter = reinterpret_cast<uint32_t *>(L->step_ws + w.bar);
+    p.bar_base = p.bar_counter + 1;
+    p.ids = L->ids;
+    p.positions = L->positions;
+    p.next_ids = L->next_ids;
+    p.ids_src = ids_src;
+    p.host_next = host_next;
+    p.host_status = host_status;
+    p.steps = steps;
+    p.advance = 1;
+    L->last_logit_rows = 1;
+    return tlc_step::step_launch(L->ctx, L->step_qtype, L->step_grid, L->step_kmax, p);
+}
+
 extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_llama_config *cfg, tlc_llama **out) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
     TLC_REQUIRE(model && cfg && out, TLC_ERR_INVALID_OPERATION, "llama_create: null pointer");
@@ -377,6 +489,7 @@ extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_ll
     TLC_CUDA(cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                   cudaSharedmemCarveoutMaxShared));
     TLC_CUDA(cudaMemsetAsync(L->positions, 0, 64 * 4, ctx->stream));
+    if (int32_t rc = step_setup(L.get())) return rc;
     TLC_CUDA(cudaMallocHost(&L->host_ids, R * 4));
     TLC_CUDA(cudaMallocHost(&L->host_next, 64 * 4));
     *out = L.release();
@@ -390,8 +503,17 @@ extern "C" int32_t tlc_llama_destroy(tlc_llama *L) {
     for (auto &g : L->graph)
         if (g.second) cudaGraphExecDestroy(g.second);
     tlc_kvcache_destroy(L->cache);
+    if (L->step_ws) {
+        auto &v = L->ctx->step_syncs;
+        uint32_t *w = reinterpret_cast<uint32_t *>(L->step_ws + L->step_wsl.bar);
+        for (size_t i = 0; i < v.size(); i++)
+            if (v[i] == w) {
+                v.erase(v.begin() + (long)i);
+                break;
+            }
+    }
     void *bufs[] = {L->x, L->x1, L->q, L->attn, L->act, L->logits, L->ids, L->positions, L->next_ids,
-                    L->part, L->logits_full};
+                    L->part, L->logits_full, L->step_ws, L->step_layers};
     for (void *b : bufs) cudaFree(b);
     cudaFreeHost(L->host_ids);
     cudaFreeHost(L->host_next);
@@ -640,6 +762,12 @@ static int32_t decode_enqueue(tlc_llama *L, int32_t batch, int32_t steps, int pa
     const bool advance = parts == 7;
     if (advance)
         if (int32_t rc = reserve_positions(L, batch, steps)) return rc;
+    if (advance && step_usable(L, batch)) {
+        // the whole run of steps is one launch of the persistent kernel
+        L->launches_in[7] = 1;
+        if (steps == 0) return TLC_OK;
+        return step_launch(L, steps, nullptr, nullptr, nullptr);
+    }
     const int key = batch * 8 + parts;
     if (!L->graph.count(key) && !L->cfg.no_graph) {
         // Warm every kernel configuration (function attributes, scratch growth)
@@ -697,6 +825,35 @@ extern "C" int32_t tlc_llama_decode_host(tlc_llama *L, int32_t batch, const int3
     if (ids_host) {
         if (int32_t rc = check_ids(L, ids_host, batch)) return rc;
         memcpy(L->host_ids, ids_host, (size_t)batch * 4);
+    }
+    if (step_usable(L, batch)) {
+        // One launch: the kernel reads the token id from pinned memory and writes the status
+        // word, then the sampled id, to pinned memory; the host watches that word.
+        tlc_ctx *ctx = L->ctx;
+        if (int32_t rc = reserve_positions(L, batch, 1)) return rc;  // before anything is launched
+        volatile int32_t *landed = L->host_next;
+        landed[0] = -1;  // no token id is negative
+        L->launches_in[7] = 1;
+        if (int32_t rc = step_launch(L, 1, ids_host ? L->host_ids : nullptr, L->host_next, ctx->host_status)) return rc;
+        if (logits_host)
+            if (int32_t rc = copy_logits(L, logits_host, batch)) return rc;
+        bool seen = false;
+        if (ctx->host_poll && !logits_host) {
+            const auto t0 = std::chrono::steady_clock::now();
+            for (long spin = 0; !seen; spin++) {
+                seen = landed[0] >= 0;
+                if (!seen && (spin & 1023) == 1023 &&
+                    std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(50))
+                    break;
+            }
+        }
+        if (!seen) {
+            if (int32_t rc = tlc_synchronize(ctx)) return rc;  // also copies and checks the status word
+        } else if (int32_t rc = tlc_status_after_sync(ctx)) {
+            return rc;
+        }
+        next_ids_host[0] = L->host_next[0];
+        return TLC_OK;
     }
     if (ids_host && !logits_host && !L->cfg.no_graph && L->ctx->host_graph) {
         // The common call: token ids up, one step, sampled ids and the status word down --

@@ -135,7 +135,50 @@ def test_graph_replay_matches_eager_and_free_running_decode(dev):
     llm.decode_enqueue(1, 5)
     nxt, pos = llm.read_state(1)
     assert int(nxt[0]) == outs[0][0][5] and int(pos[0]) == 16 + 5
-    assert llm.launches_per_step == 5 * arch.n_layers + 3
+    assert llm.launches_per_step == 1                      # the whole run of steps is one persistent kernel
+
+
+def test_step_kernel_against_the_kernel_by_kernel_path(dev, ref):
+    """Single-sequence greedy decode runs as one persistent kernel per step; option step_kernel=0
+    keeps the five-launches-per-layer path.  Same tokens, logits within the forward tolerance of
+    each other and of the oracle (the attention's key splits differ, so not bit for bit), for
+    Q4_0 and Q8_0, head_dim 64 and 128, in-kernel multi-step runs included."""
+    from tensorlogic_b200 import _lib, synth
+    from tensorlogic_b200.model import Llama, LlamaArch, model_from_host, synthetic_host_weights
+    cases = [(_small_arch(), _lib.TYPE_Q4_0), (_small_arch(), _lib.TYPE_Q8_0),
+             (LlamaArch(n_layers=3, d_model=512, n_heads=4, n_kv_heads=1, head_dim=128, ffn_dim=1376, vocab=515), _lib.TYPE_Q4_0)]
+    dev.set_option("wait_limit_ms", 300)       # a lost barrier arrival shows up as TIMEOUT at once
+    for arch, qtype in cases:
+        weights = synthetic_host_weights(arch, seed=31, qtype=qtype)
+        model = model_from_host(dev, weights)
+        ids = synth.token_ids(31, "prompt", 70, arch.vocab)     # more than one 64-key tile
+        runs = {}
+        for mode in (1, 0):
+            dev.set_option("step_kernel", mode)
+            try:
+                llm = Llama(dev, model, arch, max_seq=128, max_prefill=80)
+                first, _ = llm.prefill(ids)
+                toks, rows = [int(first)], []
+                for _ in range(6):
+                    nxt, lg = llm.decode([toks[-1]], return_logits=True)
+                    toks.append(int(nxt[0]))
+                    rows.append(lg[0].copy())
+                nxt, _ = llm.decode(None, batch=1)              # continue with the device's own token
+                toks.append(int(nxt[0]))
+                llm.decode_enqueue(1, 9)                        # nine steps inside one launch
+                last, pos = llm.read_state(1)
+                runs[mode] = (toks, np.stack(rows), int(last[0]), int(pos[0]), llm.launches_per_step)
+            finally:
+                dev.set_option("step_kernel", 1)
+        (t1, r1, last1, pos1, n1), (t0, r0, last0, pos0, n0) = runs[1], runs[0]
+        assert n1 == 1 and n0 == 5 * arch.n_layers + 3
+        assert t1 == t0 and last1 == last0 and pos1 == pos0 == 70 + 7 + 9
+        assert rel_l2(r1, r0) < 2e-3
+        oracle = _ref_model(ref, weights, arch)
+        oracle.forward(ids)
+        want = oracle.forward(np.array(t1[:6], np.int32))
+        assert rel_l2(r1, want) < TOL
+    dev.set_option("wait_limit_ms", 2000)
 
 
 def test_batched_decode_matches_single(dev):
