@@ -99,6 +99,8 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *                 or as copy + graph + copy (0);
  *   "host_poll"   with host_graph: the host watches the pinned result words (1, default)
  *                 instead of synchronizing the stream (0).
+ *   "step_kernel" single-sequence greedy decode steps run as ONE persistent kernel (1)
+ *                 or kernel by kernel, five launches per layer (0, default: faster on a B200).
  * Unknown names fail with TLC_ERR_INVALID_OPERATION. */
 TLC_API int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value);
 /* Failure-detection self-test.  Enqueues a kernel whose device-side wait can never be
@@ -455,6 +457,19 @@ TLC_API int32_t tlc_llama_decode_host(tlc_llama *l, int32_t batch, const int32_t
 TLC_API int32_t tlc_llama_decode_enqueue(tlc_llama *l, int32_t batch, int32_t steps);
 TLC_API int32_t tlc_llama_read_state(tlc_llama *l, int32_t batch, int32_t *next_ids_host,
                                      int32_t *positions_host);
+/* Per-phase device timing of `steps` decode steps of sequence 0 (the counterpart of the
+ * per-op times the reference prints under TL_PERF, src/interpreter/builtin_math.rs:190-197,
+ * src/device/kernel_executor.rs:33-41).  With option "step_kernel" = 1 single-sequence greedy
+ * decode runs as one persistent kernel; with this call its first CTA records the device clock (ns) at the
+ * end of each phase: per layer A norm + q/k/v + rope, B attention, C o + residual,
+ * D norm + gate/up + SiLU.mul, E down + residual, then F norm + lm_head, G sample.
+ * out_ns receives [steps][n_layers * 5 + 2][3] values (capacity in elements): per phase the
+ * time its input was complete, its dot products were done and its outputs were stored
+ * (0 where a phase has no such point).  The steps
+ * advance the sequence like tlc_llama_decode_enqueue.  TLC_ERR_INVALID_OPERATION when the
+ * model does not run on that kernel (tensor parallel, temperature sampling, mixed or dense
+ * weight types, option "step_kernel" = 0). */
+TLC_API int32_t tlc_llama_step_trace(tlc_llama *l, int32_t steps, uint64_t *out_ns, size_t capacity);
 /* Sampling of the runner (src/interpreter/builtin_sampling.rs:66-250).  temperature
  * <= 1e-4 is greedy, the default.  Otherwise every step draws the next token as
  * temperature_sample does -- f32 logits / temperature, softmax, first index whose

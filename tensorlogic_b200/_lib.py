@@ -131,6 +131,7 @@ PROTOTYPES = {
     "tlc_llama_decode_host": (i32, [vp, i32, P(i32), P(i32), vp]),
     "tlc_llama_decode_enqueue": (i32, [vp, i32, i32]),
     "tlc_llama_read_state": (i32, [vp, i32, P(i32), P(i32)]),
+    "tlc_llama_step_trace": (i32, [vp, i32, P(u64), sz]),
     "tlc_llama_decode_enqueue_parts": (i32, [vp, i32, i32, i32]),
     "tlc_llama_launches_per_step": (i32, [vp, i32]),
     "tlc_llama_cache": (vp, [vp]),

@@ -173,7 +173,6 @@ int32_t tlc_status_after_sync(tlc_ctx *ctx) {
     if (ctx->host_status->code != 0) {
         int code = ctx->host_status->code, where = ctx->host_status->where;
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(tlc_dev_status), ctx->stream);
-        for (uint32_t *w : ctx->step_syncs) cudaMemsetAsync(w, 0, 2 * sizeof(uint32_t), ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         if (code == TLC_DEV_INDEX)
             return tlc_fail(TLC_ERR_INDEX, "Index out of bounds: a sequence position lies outside the KV cache "

@@ -82,8 +82,11 @@ struct tlc_llama {
     // The persistent decode-step kernel (tlc_step.cu): one sequence, greedy, no tensor parallelism.
     bool step_ok = false;
     int step_grid = 0, step_qtype = 0, step_kmax = 0, step_splits = 1;
-    uint8_t *step_ws = nullptr;                 // global workspace (partials, tickets, candidates, barrier words)
+    uint8_t *step_ws = nullptr;                 // global workspace: the flagged-word buffers
     tlc_step::StepWorkspace step_wsl{};
+    uint32_t step_epoch = 1;                    // first epoch of the next launch (0 is never used)
+    uint64_t *step_trace = nullptr;             // device buffer of the last traced launch
+    size_t step_trace_words = 0;
     tlc_step::StepLayer *step_layers = nullptr;  // device copy of the per-layer pointers
     float temperature = 0.f;   // <= 1e-4: greedy
     uint64_t sample_seed = 0;  // uniform draws: counter-based, keyed by (seed, position, sequence)
@@ -317,9 +320,9 @@ static int32_t step_setup(tlc_llama *L) {
     int grid = 0;
     if (!tlc_step::step_supported(L->ctx, qt, c.d_model, kmax, c.head_dim, &grid)) return TLC_OK;
     if (grid < c.n_kv_heads) return TLC_OK;
-    int splits = grid / c.n_kv_heads;
-    splits = splits > 64 ? 64 : splits;
-    L->step_wsl = tlc_step::step_workspace(c.n_heads, c.head_dim, c.n_kv_heads, splits, grid);
+    const int splits = tlc_step::step_max_splits(grid, c.n_heads, c.n_kv_heads);
+    L->step_wsl = tlc_step::step_workspace(c.d_model, qd, c.n_kv_heads * c.head_dim, c.ffn_dim, c.n_heads, c.head_dim,
+                                           splits, grid);
     cudaError_t e = cudaMalloc(&L->step_ws, L->step_wsl.total);
     if (e == cudaSuccess) e = cudaMemset(L->step_ws, 0, L->step_wsl.total);
     if (e == cudaSuccess) e = cudaMalloc(&L->step_layers, sizeof(tlc_step::StepLayer) * (size_t)c.n_layers);
@@ -338,7 +341,6 @@ static int32_t step_setup(tlc_llama *L) {
                            static_cast<__half *>(kc), static_cast<__half *>(vc)};
     }
     TLC_CUDA(cudaMemcpy(L->step_layers, host.data(), sizeof(tlc_step::StepLayer) * host.size(), cudaMemcpyHostToDevice));
-    L->ctx->step_syncs.push_back(reinterpret_cast<uint32_t *>(L->step_ws + L->step_wsl.bar));
     L->step_ok = true;
     L->step_grid = grid;
     L->step_qtype = qt;
@@ -354,7 +356,8 @@ static bool step_usable(const tlc_llama *L, int batch) {
 // Launches `steps` decode steps of sequence 0 as one persistent kernel.  ids_src: where the
 // first step reads its token (pinned host memory) or null for L->ids; host_next /
 // host_status: pinned words the last step reports to, or null.
-static int32_t step_launch(tlc_llama *L, int steps, const int *ids_src, int *host_next, tlc_dev_status *host_status) {
+static int32_t step_launch(tlc_llama *L, int steps, const int *ids_src, int *host_next, tlc_dev_status *host_status,
+                           uint64_t *trace = nullptr) {
     const tlc_llama_config &c = L->cfg;
     tlc_step::StepParams p{};
     p.layers = L->step_layers;
@@ -375,21 +378,28 @@ static int32_t step_launch(tlc_llama *L, int steps, const int *ids_src, int *hos
     p.out_norm = static_cast<const __half *>(L->out_norm->data);
     p.embd = static_cast<const uint8_t *>(L->tok_embd->data);
     p.embd_pitch = L->tok_embd->row_pitch;
-    p.x = L->x;
-    p.x1 = L->x1;
-    p.q = L->q;
-    p.attn = L->attn;
-    p.act = L->act;
     p.logits = L->logits;
     const tlc_step::StepWorkspace &w = L->step_wsl;
-    p.part_ml = reinterpret_cast<float *>(L->step_ws + w.part_ml);
-    p.part_o = reinterpret_cast<float *>(L->step_ws + w.part_o);
-    p.tickets = reinterpret_cast<int *>(L->step_ws + w.tickets);
+    p.x_w = reinterpret_cast<uint2 *>(L->step_ws + w.x);
+    p.x1_w = reinterpret_cast<uint2 *>(L->step_ws + w.x1);
+    p.q_w = reinterpret_cast<uint2 *>(L->step_ws + w.q);
+    p.kv_w = reinterpret_cast<uint2 *>(L->step_ws + w.kv);
+    p.attn_w = reinterpret_cast<uint2 *>(L->step_ws + w.attn);
+    p.act_w = reinterpret_cast<uint2 *>(L->step_ws + w.act);
+    p.part_w = reinterpret_cast<uint2 *>(L->step_ws + w.part);
+    p.cand_w = reinterpret_cast<uint4 *>(L->step_ws + w.cand);
+    p.tok_w = reinterpret_cast<uint2 *>(L->step_ws + w.tok);
     p.max_splits = L->step_splits;
-    p.cand_val = reinterpret_cast<float *>(L->step_ws + w.cand_val);
-    p.cand_idx = reinterpret_cast<int *>(L->step_ws + w.cand_idx);
-    p.bar_counter = reinterpret_cast<uint32_t *>(L->step_ws + w.bar);
-    p.bar_base = p.bar_counter + 1;
+    p.trace = trace;
+    // Epochs grow from launch to launch; before the 32-bit counter wraps the flagged words
+    // are cleared and counting starts again.
+    const uint64_t need = (uint64_t)steps * tlc_step::epochs_per_step(c.n_layers);
+    if ((uint64_t)L->step_epoch + need >= 0xfffffff0ull) {
+        TLC_CUDA(cudaMemsetAsync(L->step_ws, 0, L->step_wsl.total, L->ctx->stream));
+        L->step_epoch = 1;
+    }
+    p.epoch_base = L->step_epoch;
+    L->step_epoch += (uint32_t)need;
     p.ids = L->ids;
     p.positions = L->positions;
     p.next_ids = L->next_ids;
@@ -397,7 +407,6 @@ static int32_t step_launch(tlc_llama *L, int steps, const int *ids_src, int *hos
     p.host_next = host_next;
     p.host_status = host_status;
     p.steps = steps;
-    p.advance = 1;
     L->last_logit_rows = 1;
     return tlc_step::step_launch(L->ctx, L->step_qtype, L->step_grid, L->step_kmax, p);
 }
@@ -503,17 +512,8 @@ extern "C" int32_t tlc_llama_destroy(tlc_llama *L) {
     for (auto &g : L->graph)
         if (g.second) cudaGraphExecDestroy(g.second);
     tlc_kvcache_destroy(L->cache);
-    if (L->step_ws) {
-        auto &v = L->ctx->step_syncs;
-        uint32_t *w = reinterpret_cast<uint32_t *>(L->step_ws + L->step_wsl.bar);
-        for (size_t i = 0; i < v.size(); i++)
-            if (v[i] == w) {
-                v.erase(v.begin() + (long)i);
-                break;
-            }
-    }
     void *bufs[] = {L->x, L->x1, L->q, L->attn, L->act, L->logits, L->ids, L->positions, L->next_ids,
-                    L->part, L->logits_full, L->step_ws, L->step_layers};
+                    L->part, L->logits_full, L->step_ws, L->step_layers, L->step_trace};
     for (void *b : bufs) cudaFree(b);
     cudaFreeHost(L->host_ids);
     cudaFreeHost(L->host_next);
@@ -994,3 +994,35 @@ extern "C" int32_t tlc_llama_launches_per_step(tlc_llama *L, int32_t parts) {
     return L && parts >= 1 && parts <= 7 ? L->launches_in[parts] : 0;
 }
 extern "C" tlc_kvcache *tlc_llama_cache(tlc_llama *L) { return L ? L->cache : nullptr; }
+
+// Per-phase timing of the persistent decode step (the counterpart of the per-op timing the
+// reference prints under TL_PERF, src/interpreter/builtin_math.rs:190-197): runs `steps`
+// decode steps of sequence 0 with CTA 0 recording the device time (ns) at the end of each of
+// its phases -- per layer A (norm + q/k/v + rope), B (attention), C (o + residual), D (norm +
+// gate/up + SiLU.mul), E (down + residual), then F (norm + lm_head) and G (sample) -- and
+// copies the stamps to out_ns as [steps][n_layers * 5 + 2][3]: for each phase the time its input
+// was complete in shared memory, the time its dot products were done and the time its outputs
+// were stored (phases B and G record only the last).  TLC_ERR_INVALID_OPERATION when the
+// model does not run on the persistent kernel.
+extern "C" int32_t tlc_llama_step_trace(tlc_llama *L, int32_t steps, uint64_t *out_ns, size_t capacity) {
+    TLC_REQUIRE(L && out_ns, TLC_ERR_INVALID_OPERATION, "llama_step_trace: null pointer");
+    if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    TLC_REQUIRE(step_usable(L, 1), TLC_ERR_INVALID_OPERATION,
+                "llama_step_trace: this model / configuration does not run as the persistent step kernel");
+    const size_t per_step = ((size_t)L->cfg.n_layers * 5 + 2) * 3, words = per_step * (size_t)steps;
+    TLC_REQUIRE(steps >= 1 && capacity >= words, TLC_ERR_SHAPE_MISMATCH, "llama_step_trace: %d steps need %zu words (got %zu)",
+                steps, words, capacity);
+    if (int32_t rc = reserve_positions(L, 1, steps)) return rc;
+    if (L->step_trace_words < words) {
+        TLC_CUDA(cudaStreamSynchronize(L->ctx->stream));
+        if (L->step_trace) cudaFree(L->step_trace);
+        L->step_trace = nullptr;
+        L->step_trace_words = 0;
+        TLC_CUDA(cudaMalloc(&L->step_trace, words * sizeof(uint64_t)));
+        L->step_trace_words = words;
+    }
+    TLC_CUDA(cudaMemsetAsync(L->step_trace, 0, words * sizeof(uint64_t), L->ctx->stream));
+    if (int32_t rc = step_launch(L, steps, nullptr, nullptr, nullptr, L->step_trace)) return rc;
+    TLC_CUDA(cudaMemcpyAsync(out_ns, L->step_trace, words * sizeof(uint64_t), cudaMemcpyDeviceToHost, L->ctx->stream));
+    return tlc_synchronize(L->ctx);
+}

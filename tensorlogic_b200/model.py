@@ -337,6 +337,16 @@ class Llama:
                                                 pos.ctypes.data_as(C.POINTER(C.c_int32))))
         return nxt, pos
 
+    def step_trace(self, steps: int = 1) -> np.ndarray:
+        """Device times (ns) of `steps` decode steps of sequence 0 as [steps, n_layers * 5 + 2, 3]:
+        for every phase (input ready, dot products done, outputs stored); phases per layer A (norm + q/k/v + rope), B (attention), C (o +
+        residual), D (norm + gate/up + SiLU.mul), E (down + residual), then F (norm + lm_head)
+        and G (sample).  Only for models that run on the persistent step kernel."""
+        per = self.arch.n_layers * 5 + 2
+        out = np.zeros(steps * per * 3, np.uint64)
+        check(self.dev.lib.tlc_llama_step_trace(self.handle, steps, out.ctypes.data_as(C.POINTER(C.c_uint64)), out.size))
+        return out.reshape(steps, per, 3)
+
     def launches(self, parts: int = 7) -> int:
         return int(self.dev.lib.tlc_llama_launches_per_step(self.handle, parts))
 

@@ -135,12 +135,12 @@ def test_graph_replay_matches_eager_and_free_running_decode(dev):
     llm.decode_enqueue(1, 5)
     nxt, pos = llm.read_state(1)
     assert int(nxt[0]) == outs[0][0][5] and int(pos[0]) == 16 + 5
-    assert llm.launches_per_step == 1                      # the whole run of steps is one persistent kernel
+    assert llm.launches_per_step == 5 * arch.n_layers + 3
 
 
 def test_step_kernel_against_the_kernel_by_kernel_path(dev, ref):
-    """Single-sequence greedy decode runs as one persistent kernel per step; option step_kernel=0
-    keeps the five-launches-per-layer path.  Same tokens, logits within the forward tolerance of
+    """Option step_kernel=1 runs single-sequence greedy decode as one persistent kernel per step;
+    the default is the five-launches-per-layer path.  Same tokens, logits within the forward tolerance of
     each other and of the oracle (the attention's key splits differ, so not bit for bit), for
     Q4_0 and Q8_0, head_dim 64 and 128, in-kernel multi-step runs included."""
     from tensorlogic_b200 import _lib, synth
@@ -169,7 +169,7 @@ def test_step_kernel_against_the_kernel_by_kernel_path(dev, ref):
                 last, pos = llm.read_state(1)
                 runs[mode] = (toks, np.stack(rows), int(last[0]), int(pos[0]), llm.launches_per_step)
             finally:
-                dev.set_option("step_kernel", 1)
+                dev.set_option("step_kernel", 0)
         (t1, r1, last1, pos1, n1), (t0, r0, last0, pos0, n0) = runs[1], runs[0]
         assert n1 == 1 and n0 == 5 * arch.n_layers + 3
         assert t1 == t0 and last1 == last0 and pos1 == pos0 == 70 + 7 + 9
@@ -178,6 +178,20 @@ def test_step_kernel_against_the_kernel_by_kernel_path(dev, ref):
         oracle.forward(ids)
         want = oracle.forward(np.array(t1[:6], np.int32))
         assert rel_l2(r1, want) < TOL
+    # per-phase device timing of the persistent step: stamps grow along the step and across steps
+    dev.set_option("step_kernel", 1)
+    try:
+        llm = Llama(dev, model, arch, max_seq=128, max_prefill=80)
+        llm.prefill(ids)
+        tr = llm.step_trace(2).astype(np.int64)
+        assert tr.shape == (2, arch.n_layers * 5 + 2, 3)
+        ends = tr[:, :, 2].reshape(-1)
+        assert np.all(ends > 0) and np.all(np.diff(ends) >= 0)
+        assert int(llm.read_state(1)[1][0]) == 70 + 2
+    finally:
+        dev.set_option("step_kernel", 0)
+    with pytest.raises(Exception):
+        llm.step_trace(1)                                   # not on the persistent kernel: refused
     dev.set_option("wait_limit_ms", 2000)
 
 
