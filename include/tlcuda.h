@@ -231,6 +231,14 @@ TLC_API int32_t tlc_dequant(tlc_ctx *ctx, tlc_qtensor *qt, void *out_f16_dev);
 
 /* ---- ops ---------------------------------------------------------------- */
 
+/* matmul(a, b) builtin (src/interpreter/builtin_math.rs:39-66, Tensor::matmul
+ * src/ops/matmul.rs:13-75; kernels shaders/unified.metal:33-478): dense
+ * y[m, n] = a[m, k] . b[k2, n], f16 in, f32 accumulate, one rounding to f16.
+ * k != k2 fails with TLC_ERR_INVALID_OPERATION "matmul shape mismatch: [m, k] @ [k2, n]"
+ * (matmul.rs:41-46).  A general-purpose builtin; quantized weights go through tlc_linear. */
+TLC_API int32_t tlc_matmul(tlc_ctx *ctx, const void *a_dev, const void *b_dev, void *y_dev, int32_t m,
+                           int32_t k, int32_t k2, int32_t n);
+
 /* linear(x, W[, bias]) = Tensor::matmul_transposed_b (src/ops/matmul.rs:241-311,
  * builtin src/interpreter/builtin_math.rs:76-199): y[M,N] = x[M,K] . W[N,K]^T,
  * f16 in/out, f32 accumulation, one rounding; optional bias [N] added as a
@@ -253,6 +261,19 @@ TLC_API int32_t tlc_rms_norm(tlc_ctx *ctx, const void *x_dev, const void *w_dev,
 TLC_API int32_t tlc_rope(tlc_ctx *ctx, const void *x_dev, void *y_dev, int32_t seq,
                          int32_t heads, int32_t d, int32_t pos_offset, uint32_t base,
                          const int32_t *positions_dev);
+
+/* rope(x, cos, sin): the arm of the rope builtin with precomputed f16 tables
+ * (src/interpreter/builtin_tensor.rs:634-722, Tensor::rope_candle src/ops/rope.rs:18-65,
+ * kernel rope_candle_f16 shaders/unified.metal:5122-5184).  x, y [seq, heads, head_dim];
+ * cos/sin tables of table_rows (>= seq) rows whose rows lie `pitch` elements apart; the
+ * rotary pair p of position s uses cos[s * pitch + p], sin[s * pitch + p].  A table with one
+ * column per pair ([max_seq, head_dim / 2], pitch = head_dim / 2) rotates like tlc_rope.  The
+ * reference's builtin stores each frequency twice in rows of head_dim values while its kernel
+ * indexes by pair: passing such a table with pitch = head_dim reproduces what the reference
+ * computes (pair p gets frequency p / 2). */
+TLC_API int32_t tlc_rope_table(tlc_ctx *ctx, const void *x_dev, const void *cos_dev, const void *sin_dev,
+                               void *y_dev, int32_t seq, int32_t heads, int32_t head_dim,
+                               int32_t table_rows, int32_t pitch);
 /* sigmoid / mul / add (src/ops/activations.rs:239-266, elementwise.rs:232-330,
  * :48-140). */
 TLC_API int32_t tlc_sigmoid(tlc_ctx *ctx, const void *x_dev, void *y_dev, size_t n);

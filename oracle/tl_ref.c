@@ -434,6 +434,26 @@ TLREF_API void tlref_rope(const uint16_t *x, uint16_t *y, int seq, int heads, in
     }
 }
 
+/* RoPE from precomputed tables: restates kernel rope_candle_f16,
+ * shaders/unified.metal:5122-5184 (dispatched by Tensor::rope_candle,
+ * src/ops/rope.rs:18-65, :121-212).  Pair p of position s reads
+ * table[s * pitch + p]; the shader's own arithmetic is pitch = head_dim
+ * (`seq_idx * head_dim + dim_pair_idx`), a table with one column per pair is
+ * pitch = head_dim / 2.  f32 products, f32 difference / sum, RNE to f16. */
+TLREF_API void tlref_rope_table(const uint16_t *x, const uint16_t *cos_t, const uint16_t *sin_t, uint16_t *y,
+                                int seq, int heads, int d, int pitch) {
+    for (int s = 0; s < seq; s++)
+        for (int h = 0; h < heads; h++) {
+            size_t o = ((size_t)s * heads + h) * d;
+            for (int p = 0; p < d / 2; p++) {
+                float c = h2f(cos_t[(size_t)s * pitch + p]), sn = h2f(sin_t[(size_t)s * pitch + p]);
+                float x0 = h2f(x[o + 2 * p]), x1 = h2f(x[o + 2 * p + 1]);
+                y[o + 2 * p] = f2h(x0 * c - x1 * sn);
+                y[o + 2 * p + 1] = f2h(x0 * sn + x1 * c);
+            }
+        }
+}
+
 /* sigmoid: follows Tensor::sigmoid_cpu, src/ops/activations.rs:252-266:
  * 1/(1+exp(-x)) in f32, RNE to f16. */
 TLREF_API void tlref_sigmoid(const uint16_t *x, uint16_t *y, size_t n) {

@@ -46,6 +46,7 @@ def _load() -> C.CDLL:
         "tlref_linear_q_f32acc": (C.c_int, [C.c_int, u8p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]),
         "tlref_rms_norm": (None, [u16p, u16p, u16p, C.c_int, C.c_int, C.c_float]),
         "tlref_rope": (None, [u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint, i32p]),
+        "tlref_rope_table": (None, [u16p, u16p, u16p, u16p, C.c_int, C.c_int, C.c_int, C.c_int]),
         "tlref_sigmoid": (None, [u16p, u16p, sz]),
         "tlref_mul": (None, [u16p, u16p, u16p, sz]),
         "tlref_add": (None, [u16p, u16p, u16p, sz]),
@@ -189,6 +190,32 @@ def rope(x: np.ndarray, pos_offset: int = 0, base: int = 10000, positions=None) 
         pp = positions.ctypes.data_as(C.POINTER(C.c_int32))
     lib().tlref_rope(_h(x), _h(y), seq, heads, d, pos_offset, base, pp)
     return y
+
+
+def rope_table(x: np.ndarray, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """x [seq, heads, d]; cos/sin f16 tables [rows >= seq, cols]: pair p of position s reads
+    table[s, p] (cols = d reproduces the reference's call, cols = d/2 is one column per pair)."""
+    x, cos, sin = _f16(x), _f16(cos), _f16(sin)
+    seq, heads, d = x.shape
+    assert cos.shape == sin.shape and cos.shape[0] >= seq and cos.shape[1] >= d // 2
+    y = np.empty_like(x)
+    lib().tlref_rope_table(_h(x), _h(cos), _h(sin), _h(y), seq, heads, d, cos.shape[1])
+    return y
+
+
+def precompute_rope_tables(head_dim: int, max_seq: int, base: float = 10000.0, paired: bool = False):
+    """(cos, sin) f16 tables as the reference's builtin makes them
+    (eval_precompute_rope_impl, src/interpreter/builtin_tensor.rs:640-722): f32 frequencies
+    1 / base^(i / head_dim) for even i, f32 angle = pos * freq, f32 cos / sin, each value stored
+    TWICE in rows of head_dim, then rounded to f16.  paired=True stores each value once
+    ([max_seq, head_dim / 2]), the layout the kernel's index arithmetic expects."""
+    i = np.arange(0, head_dim, 2, dtype=np.float32)
+    theta = (np.float32(1.0) / np.power(np.float32(base), i / np.float32(head_dim))).astype(np.float32)
+    ang = (np.arange(max_seq, dtype=np.float32)[:, None] * theta[None, :]).astype(np.float32)
+    c, s_ = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    if not paired:
+        c, s_ = np.repeat(c, 2, axis=1), np.repeat(s_, 2, axis=1)
+    return c.astype(np.float16), s_.astype(np.float16)
 
 
 def sigmoid(x: np.ndarray) -> np.ndarray:

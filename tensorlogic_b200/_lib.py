@@ -92,6 +92,8 @@ PROTOTYPES = {
     "tlc_linear_host": (i32, [vp, vp, vp, i32, i64, vp, vp]),
     "tlc_rms_norm": (i32, [vp, vp, vp, vp, i32, i32, f32]),
     "tlc_rope": (i32, [vp, vp, vp, i32, i32, i32, i32, u32, vp]),
+    "tlc_rope_table": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
+    "tlc_matmul": (i32, [vp, vp, vp, vp, i32, i32, i32, i32]),
     "tlc_sigmoid": (i32, [vp, vp, vp, sz]),
     "tlc_mul": (i32, [vp, vp, vp, vp, sz]),
     "tlc_add": (i32, [vp, vp, vp, vp, sz]),

@@ -256,6 +256,41 @@ def rope(x: Tensor, position_offset: int = 0, positions: Optional[np.ndarray] = 
     return y
 
 
+def rope_table(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    """rope(x, cos, sin): the rope builtin's arm with precomputed f16 tables
+    (src/interpreter/builtin_tensor.rs:634-722 -> Tensor::rope_candle, src/ops/rope.rs:18-65).
+
+    x is [seq, heads, head_dim]; cos / sin are [rows >= seq, cols].  cols = head_dim / 2 is one
+    column per rotary pair (the layout the kernel indexes) and equals rope(x); cols = head_dim
+    is the reference builtin's table (every frequency stored twice), whose result -- pair p gets
+    frequency p // 2 -- is reproduced as the reference computes it.  (Upstream, rope() with three
+    arguments never reaches this op: eval_rope_candle_style returns a sine table instead.)"""
+    if x.ndim != 3:
+        raise TensorError(_lib.ERR_INVALID_OPERATION,
+                          f"rope_candle requires 3D tensor [seq_len, n_heads, head_dim], got {x.ndim}D")
+    if cos.ndim != 2 or sin.ndim != 2:
+        raise TensorError(_lib.ERR_INVALID_OPERATION,
+                          f"cos/sin must be 2D [max_seq_len, head_dim], got cos: {cos.ndim}D, sin: {sin.ndim}D")
+    seq, heads, d = x.shape
+    if cos.shape != sin.shape or cos.shape[1] not in (d, d // 2):
+        raise TensorError(_lib.ERR_INVALID_OPERATION,
+                          f"cos/sin last dim must be head_dim = {d}, got cos: {cos.shape[1]}, sin: {sin.shape[1]}")
+    y = x.dev.empty(x.shape)
+    check(x.dev.lib.tlc_rope_table(x.dev.handle, x.ptr, cos.ptr, sin.ptr, y.ptr, seq, heads, d, cos.shape[0],
+                                   cos.shape[1]))
+    return y
+
+
+def matmul(a: Tensor, b: Tensor) -> Tensor:
+    """matmul(a, b) -> a @ b for 2-D f16 tensors (src/interpreter/builtin_math.rs:39-66,
+    Tensor::matmul src/ops/matmul.rs:13-75): f32 accumulation, one rounding to f16."""
+    if a.ndim != 2 or b.ndim != 2:
+        raise TensorError(_lib.ERR_INVALID_OPERATION, "matmul requires 2D tensors")
+    y = a.dev.empty((a.shape[0], b.shape[1]))
+    check(a.dev.lib.tlc_matmul(a.dev.handle, a.ptr, b.ptr, y.ptr, a.shape[0], a.shape[1], b.shape[0], b.shape[1]))
+    return y
+
+
 def sigmoid(x: Tensor) -> Tensor:
     y = x.dev.empty(x.shape)
     check(x.dev.lib.tlc_sigmoid(x.dev.handle, x.ptr, y.ptr, x.size))

@@ -123,13 +123,13 @@ __global__ void __launch_bounds__(256) linear_f16_kernel(const uint8_t *__restri
     }
 }
 
-template <int QT, int NT, int AS, bool M1, int CW>
+template <int QT, int NT, int AS, bool M1, int CW, bool F8 = false>
 int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1, CW, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)ctx->prop.sharedMemPerBlockOptin));
-        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1, CW>,
+        TLC_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<QT, NT, AS, M1, CW, F8>,
                                       cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 63] = true;
     }
@@ -143,7 +143,7 @@ int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->use_pdl ? 1 : 0;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<QT, NT, AS, M1, CW>, p);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<QT, NT, AS, M1, CW, F8>, p);
     if (le != cudaSuccess) {
         cudaGetLastError();
         return tlc_fail(TLC_ERR_CUDA, "gemv launch failed: %s", cudaGetErrorString(le));
@@ -153,7 +153,14 @@ int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
 }
 
 template <int QT, int NT, int CW>
-int32_t launch_mma_cw(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem, int as) {
+int32_t launch_mma_cw(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem, int as, bool f8) {
+    if constexpr (NT == 1 && QT == TLC_TYPE_Q4_0) {
+        if (p.m == 1 && f8) {  // one sequence, Q4_0: the FP8-limb form of the dot products
+            if (as == 1) return launch_mma_as<QT, 1, 1, true, CW, true>(ctx, p, grid, smem);
+            if (as == 2) return launch_mma_as<QT, 1, 2, true, CW, true>(ctx, p, grid, smem);
+            return launch_mma_as<QT, 1, 4, true, CW, true>(ctx, p, grid, smem);
+        }
+    }
     if constexpr (NT == 1) {
         if (p.m == 1) {  // the decode step of one sequence
             if (as == 1) return launch_mma_as<QT, 1, 1, true, CW>(ctx, p, grid, smem);
@@ -171,6 +178,13 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     using T = QTraits<QT>;
     constexpr size_t STAGE_BYTES = (size_t)kTilesPerStage * T::TILE_BYTES;
     const size_t budget = (size_t)ctx->prop.sharedMemPerBlockOptin;
+    // One activation row of a Q4_0 weight runs on the FP8 form (option "gemv_f8"), as long as its
+    // limbs (128 bytes per block) leave room for the ring.
+    bool f8 = QT == TLC_TYPE_Q4_0 && NT == 1 && p.m == 1 && ctx->gemv_f8;
+    if (f8 && fixed_smem_bytes(p.nblk_pad, p.m, NT, p.subs, 8, true) + 3 * STAGE_BYTES > budget) f8 = false;
+    auto fixed_smem_bytes = [f8](int nblk_pad, int m, int nt, int as, int cw = 8) {
+        return tlc_gemv::fixed_smem_bytes(nblk_pad, m, nt, as, cw, f8);
+    };
     const size_t fixed1 = fixed_smem_bytes(p.nblk_pad, p.m, NT, p.subs);
     TLC_REQUIRE(fixed1 + 2 * STAGE_BYTES <= budget, TLC_ERR_INVALID_OPERATION,
                 "gemv: activations of %d x %d do not fit in shared memory", p.m, p.k);
@@ -210,7 +224,7 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     p.l2_hint = ctx->l2_hint;
     p.contig = units_per_cta <= 4 ? 1 : 0;
     const size_t smem = smem_fixed + (size_t)stages * STAGE_BYTES;
-    return cw == 16 ? launch_mma_cw<QT, NT, 16>(ctx, p, grid, smem, as) : launch_mma_cw<QT, NT, 8>(ctx, p, grid, smem, as);
+    return cw == 16 ? launch_mma_cw<QT, NT, 16>(ctx, p, grid, smem, as, f8) : launch_mma_cw<QT, NT, 8>(ctx, p, grid, smem, as, f8);
 }
 
 size_t gemv_fixed_smem(int nblk_pad, int m, int nt) { return fixed_smem_bytes(nblk_pad, m, nt, 2); }

@@ -177,6 +177,15 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
           "f"(c[3]));
 }
 
+// FP8 (e4m3) tensor-core step: 16 rows x 32 k of A, 32 k x 8 columns of B, f32 accumulate in place.
+__device__ __forceinline__ void mma16832_e4m3(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 // Integer fragments of one block for rows g (w0*) and g+8 (w1*).
 //   Q4_0: one 32-bit word of nibbles per row; every nibble ends up in the
 //   lowest mantissa bits, so all fragments carry the same 2^-24 and the

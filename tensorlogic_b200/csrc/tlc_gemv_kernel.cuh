@@ -15,12 +15,13 @@ namespace tlc_gemv {
 //   ...  xzero one zero uint4 (B fragment of activation rows that do not exist)
 //   ...  xperm [nblk_pad][m][4 quad lanes] uint4    activations in fragment order
 //   ...  ring  [stages][16 tiles]                   weight tiles as they lie in HBM (128-byte aligned)
-__host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, int as, int cw = 8) {
+//              F8 (below): [nblk_pad][4 limbs][32] bytes, the activations as FP8 limbs
+__host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, int as, int cw = 8, bool f8 = false) {
     size_t s = kHeaderBytes;
     s += (size_t)2 * as * cw * kRows * (8 * nt) * sizeof(float);
     s += m == 1 ? (size_t)nblk_pad * sizeof(float4) : (size_t)nblk_pad * nt * 4 * sizeof(float2);
     s += sizeof(uint4);
-    s += (size_t)nblk_pad * m * 4 * sizeof(uint4);
+    s += f8 ? (size_t)nblk_pad * 128 : (size_t)nblk_pad * m * 4 * sizeof(uint4);
     s += 128;  // ring alignment slack
     return s;
 }
@@ -31,9 +32,20 @@ __host__ __device__ inline size_t fixed_smem_bytes(int nblk_pad, int m, int nt, 
 // addresses become warp-uniform with compile-time strides.
 // CW: consumer warps, 8 (two CTAs per SM) or 16 (one CTA per SM, for launches whose
 // activations leave no room for two).
-template <int QT, int NT, int AS, bool M1, int CW>
+// F8 (one activation row, Q4_0): the dot products run on the FP8 tensor-core path.  A nibble n in
+// a byte of its own IS the e4m3 number n * 2^-9 (exponent fields 0 and 1 share one scale, as
+// with the f16 subnormals above), so `w & 0x0F0F0F0F` and `(w >> 4) & 0x0F0F0F0F` are finished A
+// fragments of m16n8k32: three integer operations per eight weights instead of seven, one MMA
+// per block instead of two.  The activation row, scaled by a power of two so that its largest
+// value lies in [64, 256), is split into four e4m3 limbs x' = l0 + l1 + l2 + l3 (each the e4m3
+// rounding of what the earlier ones left: 16 significant bits, absolute error <= 2^-10, i.e.
+// <= 2^-16 of the row's largest value); the limbs are four columns of the B operand, every
+// product and every 32-term sum is exact in the f32 accumulator, and the four columns are added
+// once per slab.  A row with a non-finite value yields NaN outputs.
+template <int QT, int NT, int AS, bool M1, int CW, bool F8 = false>
 __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kernel(const GemvParams p) {
     static_assert(!M1 || NT == 1, "one activation row needs one column tile");
+    static_assert(!F8 || (M1 && QT == TLC_TYPE_Q4_0), "the FP8 path is for one activation row of Q4_0");
     static_assert(CW == 8 || CW == 16, "8 or 16 consumer warps");
     constexpr int CT = CW * 32;  // consumer threads
     using T = QTraits<QT>;
@@ -52,7 +64,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     uint4 *xzero = M1 ? reinterpret_cast<uint4 *>(reinterpret_cast<float4 *>(cinit) + p.nblk_pad)
                       : reinterpret_cast<uint4 *>(cinit + (size_t)p.nblk_pad * NT * 4);
     uint4 *xperm = xzero + 1;
-    uint8_t *stages = reinterpret_cast<uint8_t *>(xperm + (size_t)p.nblk_pad * p.m * 4);
+    uint8_t *stages = F8 ? reinterpret_cast<uint8_t *>(xperm) + (size_t)p.nblk_pad * 128
+                         : reinterpret_cast<uint8_t *>(xperm + (size_t)p.nblk_pad * p.m * 4);
+    float *f8_scale = reinterpret_cast<float *>(smem + 260);  // F8: 2^9 / (the row's power-of-two scale), NaN for a non-finite row
+    float *mx_part = sq_part + CW;                            // F8: per-warp maxima of |x| and |norm weight| (rows 1, 2 of sq_part: one activation row uses row 0 only)
     stages = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(stages) + 127) & ~(uintptr_t)127);
 
     const int tid = threadIdx.x;
@@ -152,7 +167,46 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     pdl_wait();  // the activations (and residual) come from the previous kernel
 
     // (a) sum of squares per activation row: every thread takes 8-element chunks.
-    if (do_norm) {
+    if (F8) {
+        // also the largest |x| and |norm weight|: their product (times the normalisation factor)
+        // bounds the normalised row, which fixes its power-of-two scale without another pass
+        float sq = 0.f, mx = 0.f, mw = do_norm ? 0.f : 1.f;
+        bool bad = false;
+        for (int k = ctid * 8; k < p.k; k += CT * 8) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(p.x + k);
+            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 v = __half22float2(h[j]);
+                sq = fmaf(v.x, v.x, sq);
+                sq = fmaf(v.y, v.y, sq);
+                mx = fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y)));
+                bad = bad || !(fabsf(v.x) <= 65504.f) || !(fabsf(v.y) <= 65504.f);
+            }
+            if (do_norm) {
+                const uint4 wraw = *reinterpret_cast<const uint4 *>(p.norm_w + k);
+                const __half2 *wh = reinterpret_cast<const __half2 *>(&wraw);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 v = __half22float2(wh[j]);
+                    mw = fmaxf(mw, fmaxf(fabsf(v.x), fabsf(v.y)));
+                    bad = bad || !(fabsf(v.x) <= 65504.f) || !(fabsf(v.y) <= 65504.f);
+                }
+            }
+        }
+        if (bad) mx = INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, o));
+        }
+        if (lane == 0) {
+            sq_part[warp] = sq;
+            mx_part[warp] = mx;
+            mx_part[CW + warp] = mw;
+        }
+    } else if (do_norm) {
         for (int m = 0; m < p.m; m++) {
             const __half *xr = p.x + (size_t)m * p.k;
             float sq = 0.f;
@@ -184,6 +238,23 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     {
         const int items = p.nblk_pad * p.m * 4;
         const int rounds = (items + CT - 1) / CT;
+        float f8_s = 1.f;  // F8: the row's power-of-two scale
+        if (F8) {
+            float ss = 0.f, mxv = 0.f, mwv = 0.f;
+#pragma unroll
+            for (int w = 0; w < CW; w++) {
+                ss += sq_part[w];
+                mxv = fmaxf(mxv, mx_part[w]);
+                mwv = fmaxf(mwv, mx_part[CW + w]);
+            }
+            // |f16((x * inv) * w)| <= bound * (1 + 2^-10): the scaled row stays below 256
+            const float bound = do_norm ? mxv * (1.0f / sqrtf(ss / (float)p.k + p.eps)) * mwv * 1.001f : mxv;
+            const bool bad = !(bound <= 3.0e38f);
+            int e = bound > 0.f && !bad ? 7 - ilogbf(bound) : 0;
+            e = e < -100 ? -100 : e > 100 ? 100 : e;
+            f8_s = exp2f((float)e);
+            if (ctid == 0) *f8_scale = bad ? __int_as_float(0x7fc00000) : 512.0f / f8_s;  // 2^9 undoes the e4m3 nibbles
+        }
         for (int r = 0; r < rounds; r++) {
             const int idx = ctid + r * CT;
             const bool live = idx < items;
@@ -227,13 +298,53 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                     if (do_norm)
                         f[j] = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(f[j], inv), __half2float(nw[j]))));
                 }
-                if (QT == TLC_TYPE_Q4_0) {
+                if (F8) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = f[j] * f8_s;  // natural order: 4t .. 4t+3, 16+4t .. 19+4t
+                } else if (QT == TLC_TYPE_Q4_0) {
                     v[0] = f[0]; v[1] = f[2]; v[2] = f[4]; v[3] = f[6];
                     v[4] = f[1]; v[5] = f[3]; v[6] = f[5]; v[7] = f[7];
                 } else {
 #pragma unroll
                     for (int j = 0; j < 8; j++) v[j] = f[j];
                 }
+            }
+            if (F8) {
+                // Four e4m3 limbs per value, each the rounding of what the earlier ones left; limb c
+                // of the item's eight values is eight bytes of column c of the B operand, and the
+                // column's sum over the block (exact in f32) gives the accumulator its start
+                // value -8 * 2^-9 * sum: the -8 of (q - 8) for that column.
+                float cs[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t wd[2];
+                    float sum = 0.f;
+#pragma unroll
+                    for (int hw = 0; hw < 2; hw++) {
+                        uint16_t p01, p23;
+                        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(p01) : "f"(v[4 * hw + 1]), "f"(v[4 * hw + 0]));
+                        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(p23) : "f"(v[4 * hw + 3]), "f"(v[4 * hw + 2]));
+                        uint32_t h01, h23;
+                        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(p01));
+                        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"(p23));
+                        const float2 q01 = __half22float2(*reinterpret_cast<const __half2 *>(&h01));
+                        const float2 q23 = __half22float2(*reinterpret_cast<const __half2 *>(&h23));
+                        v[4 * hw + 0] -= q01.x;
+                        v[4 * hw + 1] -= q01.y;
+                        v[4 * hw + 2] -= q23.x;
+                        v[4 * hw + 3] -= q23.y;
+                        sum += (q01.x + q01.y) + (q23.x + q23.y);
+                        wd[hw] = (uint32_t)p01 | ((uint32_t)p23 << 16);
+                    }
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    cs[c] = -8.0f * 0.001953125f * sum;
+                    if (live)
+                        *reinterpret_cast<uint2 *>(reinterpret_cast<uint8_t *>(xperm) + ((size_t)(b * 4 + c) * 32 + t * 8)) =
+                            make_uint2(wd[0], wd[1]);
+                }
+                if (live && t == 0) reinterpret_cast<float4 *>(cinit)[b] = make_float4(cs[0], cs[1], cs[2], cs[3]);
+                continue;
             }
             float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
             s += __shfl_xor_sync(0xffffffffu, s, 1);
@@ -338,6 +449,30 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                     const float2 u = __half22float2(*reinterpret_cast<const __half2 *>(&r.shi[h]));
                     dlo[2 * h] = l.x; dlo[2 * h + 1] = l.y;
                     dhi[2 * h] = u.x; dhi[2 * h + 1] = u.y;
+                }
+                if (F8) {
+                    // B fragment: limb column g & 3 (columns 4-7 repeat 0-3 and are never read back),
+                    // 128 bytes per block; start values of columns 2(t&1), 2(t&1)+1, 16 bytes per block
+                    const uint32_t xa = smem_u32(xperm) + (uint32_t)((g & 3) * 32 + t * 8) + b0 * 128u;
+                    const uint32_t ca = smem_u32(cinit) + (uint32_t)((t & 1) * 8) + b0 * 16u;
+                    uint2 bf = lds_u64(xa);
+                    float2 ci = lds_f32x2(ca);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint32_t fa[4] = {lo[j] & 0x0F0F0F0Fu, hi[j] & 0x0F0F0F0Fu, (lo[j] >> 4) & 0x0F0F0F0Fu,
+                                                (hi[j] >> 4) & 0x0F0F0F0Fu};
+                        const uint2 bc = bf;
+                        const float2 cc = ci;
+                        if (j + 1 < 4) {
+                            bf = lds_u64(xa + (j + 1) * 128);
+                            ci = lds_f32x2(ca + (j + 1) * 16);
+                        }
+                        float d[4] = {cc.x, cc.y, cc.x, cc.y};
+                        mma16832_e4m3(d, fa, bc.x, bc.y);
+                        acc[a][0] = fmaf(dlo[j], d[0] + d[1], acc[a][0]);
+                        acc[a][2] = fmaf(dhi[j], d[2] + d[3], acc[a][2]);
+                    }
+                    return;
                 }
                 if (M1) {
                     // B fragments 64 bytes and start values 16 bytes apart from block to block
@@ -456,6 +591,13 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
         }
 
         // (d) cross-warp reduction and epilogue of the batch
+        if (F8) {  // quad lanes 0 and 1 hold limb columns 0-1 and 2-3: lane 0 gets their sum
+#pragma unroll
+            for (int a = 0; a < AS; a++) {
+                acc[a][0] += __shfl_xor_sync(0xffffffffu, acc[a][0], 1);
+                acc[a][2] += __shfl_xor_sync(0xffffffffu, acc[a][2], 1);
+            }
+        }
         if (p.pdl_mode == 2 && i0 + ub >= n_mine) pdl_launch_dependents();
         float *rbuf = red + (size_t)(batch_count & 1) * (AS * CW * kRows * MP);
 #pragma unroll
@@ -489,6 +631,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < CW; w++) v += base[w * (kRows * MP)];
+                if (F8) return v * *f8_scale;  // undo the row's scale and the 2^-9 of the e4m3 nibbles
                 return v * 16777216.0f;  // undo the 2^-24 of the integer fragments
             };
             __half *yout = ti == 0 ? p.t[0].y : ti == 1 ? p.t[1].y : p.t[2].y;

@@ -89,6 +89,70 @@ __global__ void rope_kernel(const __half *__restrict__ x, __half *__restrict__ y
     y[o + 1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs)));
 }
 
+// rope_candle_f16 (shaders/unified.metal:5122-5184): the same interleaved rotation with the
+// cosines and sines read from f16 tables instead of being worked out.  Pair p of position s
+// reads table[s * pitch + p] -- exactly the shader's index arithmetic (`seq_idx * head_dim +
+// dim_pair_idx`, i.e. pitch = head_dim there).  One thread per pair.
+__global__ void rope_table_kernel(const __half *__restrict__ x, const __half *__restrict__ cos_t,
+                                  const __half *__restrict__ sin_t, __half *__restrict__ y, int seq, int heads, int d,
+                                  int pitch) {
+    const int half_d = d >> 1;
+    const size_t total = (size_t)seq * heads * half_d;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int pair = (int)(i % half_d);
+    const size_t sh = i / half_d;
+    const int s = (int)(sh / heads);
+    const float cs = __half2float(cos_t[(size_t)s * pitch + pair]), sn = __half2float(sin_t[(size_t)s * pitch + pair]);
+    const size_t o = sh * d + 2 * pair;
+    const float x0 = __half2float(x[o]), x1 = __half2float(x[o + 1]);
+    y[o] = __float2half_rn(__fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn)));
+    y[o + 1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs)));
+}
+
+// Dense C[M, N] = A[M, K] . B[K, N], f16 in, f32 accumulate, one rounding to f16 (the matmul
+// builtin: Tensor::matmul, src/ops/matmul.rs:13-75; kernels matmul_f16 / matmul_tiled_f16,
+// shaders/unified.metal:33-478).  64 x 64 output tile per CTA of 256 threads, 4 x 4 outputs per
+// thread, K in steps of 16 through shared memory.  A general-purpose builtin, not a tuned path:
+// the model's linears never come here (they are quantized or go through tlc_linear).
+__global__ void __launch_bounds__(256) matmul_f16_kernel(const __half *__restrict__ a, const __half *__restrict__ b,
+                                                         __half *__restrict__ c, int m, int k, int n) {
+    __shared__ float as[16][64 + 1], bs[16][64 + 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < k; k0 += 16) {
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            const int r = i >> 4, kk = i & 15;  // A tile: 64 rows x 16 k
+            as[kk][r] = row0 + r < m && k0 + kk < k ? __half2float(a[(size_t)(row0 + r) * k + k0 + kk]) : 0.f;
+            const int kb = i >> 6, cc = i & 63;  // B tile: 16 k x 64 columns
+            bs[kb][cc] = k0 + kb < k && col0 + cc < n ? __half2float(b[(size_t)(k0 + kb) * n + col0 + cc]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; kk++) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                av[i] = as[kk][ty * 4 + i];
+                bv[i] = bs[kk][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int r = row0 + ty * 4 + i, cc = col0 + tx * 4 + j;
+            if (r < m && cc < n) c[(size_t)r * n + cc] = __float2half_rn(acc[i][j]);
+        }
+}
+
 // sigmoid: f32 math, RNE to f16 (Tensor::sigmoid_cpu, src/ops/activations.rs:252-266).
 __global__ void sigmoid_kernel(const __half *__restrict__ x, __half *__restrict__ y, size_t n) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -213,6 +277,52 @@ extern "C" int32_t tlc_rope(tlc_ctx *ctx, const void *x_dev, void *y_dev, int32_
     rope_kernel<<<blocks_for(total, 256), 256, 0, ctx->stream>>>(
         static_cast<const __half *>(x_dev), static_cast<__half *>(y_dev), seq, heads, d, pos_offset, (float)base,
         positions_dev);
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
+
+// rope(x, cos, sin): the arm of the rope builtin that takes precomputed tables
+// (src/interpreter/builtin_tensor.rs:634-722 -> Tensor::rope_candle, src/ops/rope.rs:18-65).
+// x, y: [seq, heads, d] f16; cos/sin: f16 tables of table_rows rows, `pitch` elements apart;
+// pair p of position s uses cos[s * pitch + p], sin[s * pitch + p].
+//   * A table of head_dim / 2 columns (pitch = head_dim / 2, one column per rotary pair) is what
+//     the kernel's index arithmetic is written for, and gives the same rotation as tlc_rope.
+//   * The reference's own builtin stores every frequency twice in rows of head_dim values and
+//     passes pitch = head_dim in effect: pair p then reads column p of a row laid out
+//     c0 c0 c1 c1 ..., i.e. frequency p / 2 -- its result, quirk included, is reproduced by
+//     passing that table with pitch = head_dim.
+extern "C" int32_t tlc_rope_table(tlc_ctx *ctx, const void *x_dev, const void *cos_dev, const void *sin_dev,
+                                  void *y_dev, int32_t seq, int32_t heads, int32_t d, int32_t table_rows,
+                                  int32_t pitch) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(x_dev && cos_dev && sin_dev && y_dev, TLC_ERR_INVALID_OPERATION, "rope: null pointer");
+    TLC_REQUIRE(d > 0 && d % 2 == 0, TLC_ERR_INVALID_OPERATION, "RoPE requires even head_dim, got %d", d);
+    TLC_REQUIRE(seq >= 0 && heads > 0, TLC_ERR_INVALID_DIMENSION, "rope: bad shape [%d, %d, %d]", seq, heads, d);
+    TLC_REQUIRE(pitch >= d / 2, TLC_ERR_INVALID_OPERATION,
+                "cos/sin last dim must hold head_dim / 2 = %d pairs, got %d", d / 2, pitch);
+    TLC_REQUIRE(table_rows >= seq, TLC_ERR_INVALID_OPERATION,
+                "cos/sin first dim must be >= seq_len = %d, got cos: %d, sin: %d", seq, table_rows, table_rows);
+    if (seq == 0) return TLC_OK;
+    const size_t total = (size_t)seq * heads * (d / 2);
+    rope_table_kernel<<<blocks_for(total, 256), 256, 0, ctx->stream>>>(
+        static_cast<const __half *>(x_dev), static_cast<const __half *>(cos_dev), static_cast<const __half *>(sin_dev),
+        static_cast<__half *>(y_dev), seq, heads, d, pitch);
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
+}
+
+// matmul(a, b): a [m, k] . b [k2, n] -> y [m, n], all f16 on the device.  Shape rule and message
+// of Tensor::matmul (src/ops/matmul.rs:36-46).
+extern "C" int32_t tlc_matmul(tlc_ctx *ctx, const void *a_dev, const void *b_dev, void *y_dev, int32_t m, int32_t k,
+                              int32_t k2, int32_t n) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    TLC_REQUIRE(a_dev && b_dev && y_dev, TLC_ERR_INVALID_OPERATION, "matmul: null pointer");
+    TLC_REQUIRE(m >= 0 && k >= 0 && k2 >= 0 && n >= 0, TLC_ERR_INVALID_DIMENSION, "matmul: bad shape");
+    TLC_REQUIRE(k == k2, TLC_ERR_INVALID_OPERATION, "matmul shape mismatch: [%d, %d] @ [%d, %d]", m, k, k2, n);
+    if (m == 0 || n == 0) return TLC_OK;
+    const dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64));
+    matmul_f16_kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const __half *>(a_dev), static_cast<const __half *>(b_dev),
+                                                     static_cast<__half *>(y_dev), m, k, n);
     TLC_CHECK_LAUNCH(ctx);
     return TLC_OK;
 }

@@ -145,3 +145,26 @@ def test_integration_doc_binds_every_symbol():
     doc = open(os.path.join(ROOT, "INTEGRATION.md")).read()
     missing = [s for s in _declared_symbols() if f"fn {s}(" not in doc]
     assert not missing, missing
+
+
+def test_rust_shim_matches_header():
+    """rust/src/device/cuda_ffi.rs is generated from the header and must not be stale; the hand-
+    written Rust files may only call entry points the header declares (they cannot be compiled
+    here, so this is what keeps them honest)."""
+    import re
+    import subprocess
+    import sys
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "rust", "gen_ffi.py"), "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    header = open(os.path.join(ROOT, "include", "tlcuda.h")).read()
+    declared = set(re.findall(r"\b(tlc_\w+)\s*\(", header))
+    ffi = open(os.path.join(ROOT, "rust", "src", "device", "cuda_ffi.rs")).read()
+    assert set(re.findall(r"pub fn (tlc_\w+)\(", ffi)) == {n for n in declared if re.search(r"TLC_API[^;]*\b%s\s*\(" % n, header)}
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "rust", "src")):
+        for f in files:
+            if f.endswith(".rs") and f != "cuda_ffi.rs":
+                text = open(os.path.join(dirpath, f)).read()
+                for name in set(re.findall(r"ffi::(tlc_\w+)\s*\(", text)):
+                    assert name in declared, (f, name)
+                for const in set(re.findall(r"ffi::(TLC_\w+)", text)):
+                    assert re.search(r"pub const %s:" % const, ffi), (f, const)

@@ -324,3 +324,48 @@ def test_device_storage_is_the_tiled_layout(dev, qtype, n, k):
     check(dev.lib.tlc_download(dev.handle, got.ctypes.data, w.ptr, size))
     assert np.array_equal(got, want)
     assert np.array_equal(w.raw_bytes().reshape(-1), flat)
+
+
+@pytest.mark.parametrize("n,k", [(2048, 2048), (512, 5632), (130, 1056), (48, 8192)])
+def test_fp8_limb_form_of_one_row(dev, ref, n, k):
+    """One activation row against a Q4_0 weight runs on the FP8 tensor-core form (nibbles as e4m3
+    values, the row as four e4m3 limbs under a power-of-two scale).  Same answers as the f16
+    fragments (option gemv_f8 = 0) and as the oracle, also for a row with a huge outlier, a tiny
+    row, a zero row, with a fused RMSNorm, and non-finite in, non-finite out."""
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.api import QTensor, linear, norm_linear_multi
+    raw = synth.blocks(Q4, 21, synth.tensor_id(f"f8_{n}x{k}"), n, k)
+    w = QTensor.from_blocks(dev, Q4, n, k, raw)
+    base = synth.activations(21, f"f8x{k}", (1, k))
+    outlier = base.copy()
+    outlier[0, 3] = np.float16(900.0)
+    outlier[0, 40:200] *= np.float16(1e-3)
+    cases = {"normal": base, "outlier": outlier, "tiny": (base.astype(np.float32) * 3e-5).astype(np.float16),
+             "zero": np.zeros_like(base)}
+
+    def both(fn):
+        out = {}
+        for mode in (1, 0):
+            dev.set_option("gemv_f8", mode)
+            try:
+                out[mode] = fn()
+            finally:
+                dev.set_option("gemv_f8", 1)
+        return out[1], out[0]
+
+    for name, x in cases.items():
+        y8, y16 = both(lambda: linear(dev.tensor(x), w).numpy())
+        want = ref.linear_q(Q4, raw, n, k, x)
+        if name == "zero":
+            assert not np.any(y8.astype(np.float32)) and not np.any(y16.astype(np.float32))
+            continue
+        assert rel_l2(y8, want) < TIGHT and rel_l2(y16, want) < TIGHT, name
+        assert rel_l2(y8, y16) < 5e-4, name
+    nw = synth.norm_weight(21, "f8norm", k)
+    (y8,), (y16,) = both(lambda: [t.numpy() for t in norm_linear_multi(dev.tensor(outlier), [w], dev.tensor(nw), 1e-5)])
+    want = ref.linear_q(Q4, raw, n, k, ref.rms_norm(outlier, nw, 1e-5))
+    assert rel_l2(y8, want) < TIGHT and rel_l2(y8, y16) < 5e-4
+    bad = base.copy()
+    bad[0, 5] = np.float16(np.inf)
+    y8, y16 = both(lambda: linear(dev.tensor(bad), w).numpy())
+    assert not np.any(np.isfinite(y8.astype(np.float32))) and not np.any(np.isfinite(y16.astype(np.float32)))

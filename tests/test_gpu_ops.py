@@ -192,3 +192,54 @@ def test_fused_small_and_ragged(dev, ref):
     res = synth.activations(23, "res", (3, 40))
     y = linear_residual(dev.tensor(x), wa, dev.tensor(res)).numpy()
     assert rel_l2(y, ref.add(res, ref.linear_q(Q4, ra, 40, d, x))) < TIGHT
+
+
+def test_rope_with_tables(dev, ref):
+    """rope(x, cos, sin) on the device is bit for bit the oracle's restatement of rope_candle_f16,
+    for the pair-indexed table and for the reference builtin's duplicated one; shape errors as upstream."""
+    from tensorlogic_b200 import _lib
+    from tensorlogic_b200._lib import TensorError
+    from tensorlogic_b200.api import rope, rope_table
+    rng = np.random.default_rng(41)
+    for seq, heads, d in [(7, 4, 64), (33, 2, 128), (1, 32, 64)]:
+        x = rng.standard_normal((seq, heads, d)).astype(np.float16)
+        for paired in (True, False):
+            cos, sin = ref.precompute_rope_tables(d, seq + 5, 10000.0, paired=paired)
+            got = rope_table(dev.tensor(x), dev.tensor(cos), dev.tensor(sin)).numpy()
+            assert np.array_equal(got.view(np.uint16), ref.rope_table(x, cos, sin).view(np.uint16))
+        cos, sin = ref.precompute_rope_tables(d, seq, 10000.0, paired=True)
+        close = rope_table(dev.tensor(x), dev.tensor(cos), dev.tensor(sin)).numpy().astype(np.float32)
+        assert np.max(np.abs(close - rope(dev.tensor(x)).numpy().astype(np.float32))) < 2e-2
+    x = dev.tensor(rng.standard_normal((4, 2, 64)).astype(np.float16))
+    cos, sin = ref.precompute_rope_tables(64, 3, 10000.0)
+    with pytest.raises(TensorError) as e:                     # fewer table rows than positions
+        rope_table(x, dev.tensor(cos), dev.tensor(sin))
+    assert e.value.code == _lib.ERR_INVALID_OPERATION and "first dim must be >= seq_len" in str(e.value)
+    cos, sin = ref.precompute_rope_tables(32, 8, 10000.0)
+    with pytest.raises(TensorError) as e:                     # tables made for another head_dim
+        rope_table(x, dev.tensor(cos[:, :24]), dev.tensor(sin[:, :24]))
+    assert "last dim must be head_dim" in str(e.value)
+    with pytest.raises(TensorError):
+        rope_table(dev.tensor(np.zeros((4, 64), np.float16)), dev.tensor(cos), dev.tensor(sin))
+
+
+def test_matmul_builtin(dev, ref):
+    """matmul(a, b): the reference's KAT ([[1,2,3],[4,5,6]] @ [[1,2],[3,4],[5,6]] = [[22,28],[49,64]],
+    src/ops/matmul.rs:466-504), ragged shapes against the oracle's f32-accumulating product, the
+    shape-mismatch message."""
+    from tensorlogic_b200 import _lib
+    from tensorlogic_b200._lib import TensorError
+    from tensorlogic_b200.api import matmul
+    a = np.array([[1, 2, 3], [4, 5, 6]], np.float16)
+    b = np.array([[1, 2], [3, 4], [5, 6]], np.float16)
+    assert np.array_equal(matmul(dev.tensor(a), dev.tensor(b)).numpy(), np.array([[22, 28], [49, 64]], np.float16))
+    rng = np.random.default_rng(42)
+    for m, k, n in [(1, 2048, 2048), (10, 2048, 300), (65, 17, 129), (128, 100, 64), (3, 1, 5)]:
+        a = rng.standard_normal((m, k)).astype(np.float16)
+        b = (rng.standard_normal((k, n)) * 0.05).astype(np.float16)
+        got = matmul(dev.tensor(a), dev.tensor(b)).numpy()
+        want = ref.linear_f32acc(a, np.ascontiguousarray(b.T))          # a @ b, f32 sums in k order
+        assert got.shape == (m, n) and rel_l2(got, want) < 1e-3
+    with pytest.raises(TensorError) as e:
+        matmul(dev.tensor(np.zeros((2, 3), np.float16)), dev.tensor(np.zeros((4, 2), np.float16)))
+    assert e.value.code == _lib.ERR_INVALID_OPERATION and "matmul shape mismatch: [2, 3] @ [4, 2]" in str(e.value)

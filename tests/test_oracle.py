@@ -316,3 +316,27 @@ def test_temperature_sample_kats(ref):
     p = np.exp(lg.astype(np.float64) / 0.7)
     p /= p.sum()
     assert np.abs(cnt / 20000 - p).max() < 0.015
+
+
+def test_rope_table_layouts(ref):
+    """rope(x, cos, sin): with one table column per rotary pair the table form equals the
+    computed form up to the f16 rounding of the tables; with the reference builtin's own table
+    (every frequency stored twice, rows of head_dim) the kernel's pair-indexed read gives pair p
+    the frequency p // 2 -- restated as the reference computes it, not corrected."""
+    rng = np.random.default_rng(40)
+    seq, heads, d = 9, 3, 64
+    x = rng.standard_normal((seq, heads, d)).astype(np.float16)
+    cos_p, sin_p = ref.precompute_rope_tables(d, 16, 10000.0, paired=True)
+    assert cos_p.shape == (16, d // 2)
+    y_tab = ref.rope_table(x, cos_p, sin_p)
+    y_cmp = ref.rope(x, 0, 10000)
+    assert np.max(np.abs(y_tab.astype(np.float32) - y_cmp.astype(np.float32))) < 8e-3   # tables are f16
+    cos_r, sin_r = ref.precompute_rope_tables(d, 16, 10000.0)
+    assert cos_r.shape == (16, d) and np.array_equal(cos_r[:, 0::2], cos_r[:, 1::2])
+    y_ref_layout = ref.rope_table(x, cos_r, sin_r)
+    # pair p reads column p of c0 c0 c1 c1 ...: the frequency of pair p // 2
+    want = ref.rope_table(x, np.ascontiguousarray(cos_p[:, np.arange(d // 2) // 2]), np.ascontiguousarray(sin_p[:, np.arange(d // 2) // 2]))
+    assert np.array_equal(y_ref_layout.view(np.uint16), want.view(np.uint16))
+    # position 0 rotates nothing in either layout
+    assert np.array_equal(y_tab[0].view(np.uint16), x[0].view(np.uint16))
+    assert np.array_equal(y_ref_layout[0].view(np.uint16), x[0].view(np.uint16))
