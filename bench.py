@@ -47,6 +47,26 @@ METRIC = "q4_0_decode_tokens_per_s"
 L2_BYTES = 126 * 1000 * 1000
 
 
+def workload_name(n_gpus: int, batch: int = 1, big: bool = False) -> str:
+    """The `config.workload` string, the same in both arms (`--impl ours` / `--impl reference`)."""
+    if n_gpus > 1 or big:
+        return (f"llama-2-70b-shape q4_0 decode, TP{n_gpus}, batch {batch}, 2048-token context (BASELINE configs[4]); "
+                f"NOT the N=1 workload (tinyllama, configs[2])")
+    return "tinyllama-1.1b q4_0 decode, batch 1, 512-token prompt (BASELINE configs[2])"
+
+
+def profiled_traffic(key: str):
+    """DRAM bytes per launch of a kernel from the ncu summaries under profiles/ (traffic.json):
+    (bytes or None, where it comes from).  Taken from a capture, never measured in the run."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(path):
+        return None, None
+    entry = json.load(open(path)).get(key)
+    if not entry:
+        return None, None
+    return float(entry["dram_bytes_per_launch"]), f"from profiles/{entry['summary']} (one ncu capture), not measured in this run"
+
+
 def load_peaks() -> dict:
     """Measured roofline denominators (MEASURED_PEAKS.json beside this file), else the pool's fallback figures."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -89,6 +109,14 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc, self.thread = index, [], None, None
+        self.t0, self.t1 = None, None
+
+    def mark_start(self):
+        """The timed region starts now (samples outside it are kept apart)."""
+        self.t0 = time.perf_counter()
+
+    def mark_end(self):
+        self.t1 = time.perf_counter()
 
     def __enter__(self):
         try:
@@ -103,7 +131,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
     def __exit__(self, *exc):
         if self.proc:
@@ -117,7 +145,15 @@ class ClockSampler:
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        rows, window = [r for _, r in self.rows], "sampler lifetime"
+        if self.t0 is not None and self.t1 is not None:
+            # nvidia-smi reports about 0.1 s late: a sample belongs to the region it was taken in
+            inside = [r for t, r in self.rows if self.t0 <= t - 0.05 <= self.t1 + 0.15]
+            if inside:
+                rows, window = inside, "timed region"
+            else:
+                window = "warm-up + timed region (the timed region is shorter than the sampling period)"
+        for r in rows:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -127,7 +163,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def dist_setup(n_gpus: int):
@@ -143,85 +179,129 @@ def dist_setup(n_gpus: int):
     return rank, world, local
 
 
-def cpu_baseline(arch, seed: int, budget_s: float = 12.0, row_div: int = 1) -> dict:
-    """The reference's CPU path on a bounded sample, scaled to tokens/s.
+class CpuSample:
+    """A bounded sample of the reference's CPU path for one decode token.
 
     Restated by oracle/tl_ref.c: GGUF dequantization (src/model/formats/gguf.rs:68-112) happens
     once at load upstream and is not timed; per token the linears run as transpose + matmul_cpu with
-    an f16 running sum on one thread (src/ops/matmul.rs:201-228, :293-297).  The sample is the seven
-    linears of one layer plus a slice of lm_head rows; a token costs n_layers * layer + lm_head.
+    an f16 running sum on one thread (src/ops/matmul.rs:201-228, :293-297).  One `step()` runs the
+    seven linears of one layer plus `head_rows` lm_head rows; a token costs n_layers * layer +
+    lm_head, so tokens/s = 1 / (n_layers * row_div * t_layer + vocab / head_rows * t_head).
     row_div > 1 takes only every row_div-th part of each linear's rows (the cost is linear in the
-    rows) so that the 70B shape stays a bounded sample too.
+    rows) so that the 70B shape stays a bounded sample too.  Attention, norms and sampling are not
+    charged to the CPU (that favours the CPU).
     """
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import tl_ref as ref
-    from tensorlogic_b200 import synth
-    d, qd, kvd, f = arch.d_model, arch.n_heads * arch.head_dim, arch.n_kv_heads * arch.head_dim, arch.ffn_dim
-    shapes = [("attn_q", qd, d), ("attn_k", kvd, d), ("attn_v", kvd, d), ("attn_output", d, qd), ("ffn_gate", f, d),
-              ("ffn_up", f, d), ("ffn_down", d, f)]
-    ws = []
-    for name, n, k in shapes:
-        n = max(16, n // row_div)
-        raw = synth.blocks(2, seed, synth.tensor_id(f"blk.0.{name}.weight"), n, k)
-        ws.append((ref.dequant(2, raw, n * k).reshape(n, k), synth.activations(seed, f"cpu.{name}", (1, k))))
-    head_rows = 4000
-    raw = synth.blocks(2, seed, synth.tensor_id("output.weight"), head_rows, d)
-    head = ref.dequant(2, raw, head_rows * d).reshape(head_rows, d)
-    xh = synth.activations(seed, "cpu.head", (1, d))
-    t_layer, t_head, reps = 0.0, 0.0, 0
-    t_start = time.perf_counter()
-    while reps < 1 or (time.perf_counter() - t_start) < budget_s:
+
+    def __init__(self, arch, seed: int, row_div: int = 1, head_rows: int = 4000):
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import tl_ref as ref
+        from tensorlogic_b200 import synth
+        self.ref, self.arch, self.row_div, self.head_rows = ref, arch, row_div, head_rows
+        d, qd, kvd, f = arch.d_model, arch.n_heads * arch.head_dim, arch.n_kv_heads * arch.head_dim, arch.ffn_dim
+        shapes = [("attn_q", qd, d), ("attn_k", kvd, d), ("attn_v", kvd, d), ("attn_output", d, qd), ("ffn_gate", f, d),
+                  ("ffn_up", f, d), ("ffn_down", d, f)]
+        self.ws = []
+        for name, n, k in shapes:
+            n = max(16, n // row_div)
+            raw = synth.blocks(2, seed, synth.tensor_id(f"blk.0.{name}.weight"), n, k)
+            self.ws.append((ref.dequant(2, raw, n * k).reshape(n, k), synth.activations(seed, f"cpu.{name}", (1, k))))
+        raw = synth.blocks(2, seed, synth.tensor_id("output.weight"), head_rows, d)
+        self.head = ref.dequant(2, raw, head_rows * d).reshape(head_rows, d)
+        self.xh = synth.activations(seed, "cpu.head", (1, d))
+        self.t_layer, self.t_head, self.reps = 0.0, 0.0, 0
+
+    def step(self, count: bool = True) -> float:
+        """One sample; returns its wall time in seconds."""
         t0 = time.perf_counter()
-        for w, x in ws:
-            ref.linear_literal(x, w)
+        for w, x in self.ws:
+            self.ref.linear_literal(x, w)
         t1 = time.perf_counter()
-        ref.linear_literal(xh, head)
+        self.ref.linear_literal(self.xh, self.head)
         t2 = time.perf_counter()
-        t_layer += t1 - t0
-        t_head += t2 - t1
-        reps += 1
-    t_token = arch.n_layers * (t_layer / reps) * row_div + (t_head / reps) * (arch.vocab / head_rows)
-    # the multi-threaded f32-accumulating variant (no counterpart upstream), for context
-    t0 = time.perf_counter()
-    for w, x in ws:
-        ref.linear_f32acc(x, w)
-    ref.linear_f32acc(xh, head)
-    t_mt_layer = time.perf_counter() - t0
-    macs_sample = sum(w.size for w, _ in ws) + head.size
-    macs_token = arch.n_layers * sum(w.size for w, _ in ws) * row_div + arch.vocab * d
-    return {"value": 1.0 / t_token, "unit": "tokens/s", "cores": 1, "kind": "port",
-            "sample": (f"{reps}x (7 linears of one layer{f', 1/{row_div} of their rows' if row_div > 1 else ''} + {head_rows} "
-                       f"lm_head rows), literal f16-accumulate matmul on "
-                       f"pre-dequantized f16 weights, scaled to {arch.n_layers} layers + {arch.vocab} lm_head rows; "
-                       f"attention, norms and sampling not counted (favours the CPU)"),
-            "f16c": bool(ref.uses_f16c()), "host_cores_available": os.cpu_count(),
-            "mt_f32acc_tokens_per_s": (macs_sample / macs_token) / t_mt_layer, "mt_threads": ref.num_threads()}
+        if count:
+            self.t_layer += t1 - t0
+            self.t_head += t2 - t1
+            self.reps += 1
+        return t2 - t0
+
+    def token_seconds(self) -> float:
+        a = self.arch
+        return a.n_layers * (self.t_layer / self.reps) * self.row_div + (self.t_head / self.reps) * (a.vocab / self.head_rows)
+
+    def sample_fraction(self) -> float:
+        """Multiply-adds of one sample / multiply-adds of one token."""
+        a = self.arch
+        sample = sum(w.size for w, _ in self.ws) + self.head.size
+        token = a.n_layers * sum(w.size for w, _ in self.ws) * self.row_div + a.vocab * a.d_model
+        return sample / token
+
+    def summary(self) -> dict:
+        ref, a = self.ref, self.arch
+        # the multi-threaded f32-accumulating variant (no counterpart upstream), for context
+        t0 = time.perf_counter()
+        for w, x in self.ws:
+            ref.linear_f32acc(x, w)
+        ref.linear_f32acc(self.xh, self.head)
+        t_mt = time.perf_counter() - t0
+        div = f", 1/{self.row_div} of their rows" if self.row_div > 1 else ""
+        return {"value": 1.0 / self.token_seconds(), "unit": "tokens/s", "cores": 1, "kind": "port",
+                "sample": (f"{self.reps}x (7 linears of one layer{div} + {self.head_rows} "
+                           f"lm_head rows), literal f16-accumulate matmul on "
+                           f"pre-dequantized f16 weights, scaled to {a.n_layers} layers + {a.vocab} lm_head rows; "
+                           f"attention, norms and sampling not counted (favours the CPU)"),
+                "sample_fraction_of_a_token": self.sample_fraction(),
+                "f16c": bool(ref.uses_f16c()), "host_cores_available": os.cpu_count(),
+                "mt_f32acc_tokens_per_s": self.sample_fraction() / t_mt, "mt_threads": ref.num_threads()}
+
+
+def cpu_baseline(arch, seed: int, budget_s: float = 12.0, row_div: int = 1) -> dict:
+    """The reference's CPU path on a bounded sample (CpuSample), repeated for about budget_s seconds."""
+    sample = CpuSample(arch, seed, row_div)
+    t_start = time.perf_counter()
+    while sample.reps < 1 or (time.perf_counter() - t_start) < budget_s:
+        sample.step()
+    return sample.summary()
 
 
 def run_reference(args, rank: int, world: int) -> None:
-    """--impl reference: the reference's own CPU implementation of the path (no GPU work)."""
+    """--impl reference: the reference's own CPU implementation of the path (no GPU work).
+
+    A "step" of this arm is one bounded sample of a token's work (CpuSample.step); W samples warm
+    up, K are timed.  `ms_per_step` is the measured time of a sample; `value` (tokens/s) is that
+    time scaled to a whole token, and `extrapolation` says by how much."""
     if rank != 0:
         return
     from tensorlogic_b200.model import LLAMA2_70B, TINYLLAMA
     # the same workload as this repo's arm at that N: TinyLlama at N = 1, the 70B shape beyond
-    big = args.gpus > 1
+    big = args.gpus > 1 or args.workload == "decode70b"
     arch = LLAMA2_70B if big else TINYLLAMA
-    # each "step" is a bounded sample of one token's work; the whole run stays within minutes
-    steps = max(1, args.steps)
-    budget = min(150.0, 1.2 * (args.warmup + steps)) if steps > 1 else 12.0
+    t_wall = time.perf_counter()
+    sample = CpuSample(arch, SEED, row_div=16 if big else 1)
+    # a sample takes ~0.5 s: bound the run to a few minutes whatever K is asked for
+    K = max(1, min(args.steps, 256))
+    for _ in range(max(0, min(args.warmup, 8))):
+        sample.step(count=False)
     t0 = time.perf_counter()
-    base = cpu_baseline(arch, SEED, budget_s=max(6.0, budget), row_div=16 if big else 1)
-    elapsed = time.perf_counter() - t0
+    for _ in range(K):
+        sample.step()
+        if time.perf_counter() - t0 > 150.0:
+            break
+    timed = time.perf_counter() - t0
+    base = sample.summary()
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / base["value"],
+        "steps": sample.reps, "warmup": args.warmup, "ms_per_step": 1e3 * timed / sample.reps,
         "higher_is_better": True, "scaling": "strong" if big else "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": "llama-2-70b-shape q4_0 decode, batch 1 (BASELINE configs[4]); the reference has no "
-                               "multi-GPU path: one host process" if big else
-                               "tinyllama-1.1b q4_0 decode, batch 1 (BASELINE configs[2])",
-                   "note": "reference CPU path (transpose + f16-accumulating matmul_cpu, 1 thread), "
-                           "bounded sample per step extrapolated to a token", "wall_s": round(elapsed, 1)},
+        "config": {"workload": workload_name(args.gpus, args.batch, big),
+                   "note": "reference CPU path (transpose + f16-accumulating matmul_cpu, 1 thread; the reference has no "
+                           "multi-GPU path: one host process); a step is a bounded sample of one token's linears",
+                   "wall_s": round(time.perf_counter() - t_wall, 1)},
+        "extrapolation": {"step_is": "one sample = 7 linears of one layer + 4000 lm_head rows" +
+                                     (" (1/16 of the rows of each)" if big else ""),
+                          "sample_fraction_of_a_token": base["sample_fraction_of_a_token"],
+                          "seconds_per_token_extrapolated": 1.0 / base["value"],
+                          "value_is": "1 / seconds_per_token_extrapolated"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -238,7 +318,7 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
     K, W = args.steps, max(args.warmup, 3)
     dev = Device(local)
     model = synthetic_model(dev, arch, SEED)
-    max_seq = PROMPT_TOKENS + 2 * (K + W) + 64
+    max_seq = PROMPT_TOKENS + 2 * K + 3 * W + 64
     llm = Llama(dev, model, arch, max_seq=max_seq, max_batch=1, max_prefill=PROMPT_TOKENS)
     stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local))
     ids = synth.token_ids(SEED, f"prompt.{rank}", PROMPT_TOKENS, arch.vocab)
@@ -266,10 +346,15 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = dev.launch_count
     with ClockSampler(local) as clocks:
+        llm.decode_enqueue(1, W)       # nvidia-smi needs a moment to start: keep the GPU in the same state meanwhile
+        barrier()
+        launches0 = dev.launch_count
+        clocks.mark_start()
         e0.record(stream)
         llm.decode_enqueue(1, K)
         e1.record(stream)
         barrier()
+        clocks.mark_end()
     ms = max_over_ranks(e0.elapsed_time(e1))
     gpu_launches = dev.launch_count - launches0
     tok_s = world * K / (ms / 1e3)
@@ -325,7 +410,7 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         bytes_per_launch = gemv_bytes / gemv_launches
         kernel_name = "gemv_mma_kernel<Q4_0> (fused dequant-GEMV, M=1)"
         kernel_launches_per_step = gemv_launches
-        traffic, traffic_src = None, None
+        traffic, traffic_src = profiled_traffic("tinyllama_decode_gemv")
     achieved = bytes_per_launch / (kernel_us * 1e-6) / 1e9
     step_bytes = tinyllama_bytes_per_token(arch, context_mid)
 
@@ -336,7 +421,7 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "tinyllama-1.1b q4_0 decode, batch 1, 512-token prompt (BASELINE configs[2])",
+        "config": {"workload": workload_name(1),
                    "context_tokens_mid_run": context_mid, "parallelism": "single" if world == 1 else f"replicas x{world}",
                    "l2": "weights of one step (582 MB) exceed the 126 MB L2: every step re-reads them from HBM",
                    "step_hbm_bytes": step_bytes, "step_hbm_gbs": step_bytes / (ms / K * 1e-3) / 1e9,
@@ -369,58 +454,81 @@ def llama_bytes_per_step(arch, tp: int, batch: int, context: int) -> int:
     return weights + kv
 
 
-def run_tp(args, rank: int, world: int, local: int) -> None:
-    """N > 1: Llama-2-70B-shape Q4_0 decode, tensor-parallel over the N GPUs (BASELINE configs[4]):
-    column-parallel q/k/v/gate/up/lm_head, row-parallel o/down with an all-reduce after each (one peer-memory
-    kernel fused with the residual add; NCCL with --nccl-allreduce),
-    2048 positions already in the KV cache (filled with random f16 on the device)."""
+def time_decode(dev, llm, stream, batch, K, W, barrier, clocks=None):
+    """W warm-up steps, then K steps between two CUDA events on the library's stream: ms, launches."""
     import torch
-    import torch.distributed as dist
-    from tensorlogic_b200.api import Device
-    from tensorlogic_b200.comm import Comm, unique_id
-    from tensorlogic_b200.model import LLAMA2_70B, Llama, synthetic_model
-    arch, batch, context = LLAMA2_70B, args.batch, 2048
-    K, W = args.steps, max(args.warmup, 3)
-    dev = Device(local)
-    box = [unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(box, src=0, device=torch.device("cuda", local))
-    comm = Comm(dev, box[0], rank, world)
-    if not args.nccl_allreduce:
-        # peer-memory exchange: the [batch, d_model] all-reduces run as one kernel over NVLink
-        def gather(blob):
-            out = [None] * world
-            dist.all_gather_object(out, blob)
-            return out
-        comm.enable_p2p(max(16, batch) * arch.d_model, gather)
-    model = synthetic_model(dev, arch, SEED, tp_rank=rank, tp_size=world, device_embeddings=True)
-    max_seq = context + 2 * (K + W) + 64
-    llm = Llama(dev, model, arch, max_seq=max_seq, max_batch=batch, max_prefill=16, tp_rank=rank, tp_size=world)
-    llm.set_comm(comm)
-    llm.fill_cache_random(SEED)
-    llm.set_state([(7 + 13 * b) % arch.vocab for b in range(batch)], [context] * batch)
-    stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local))
-
-    def barrier():
-        dev.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(ms: float) -> float:
-        t = torch.tensor([ms], device=f"cuda:{local}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
     llm.decode_enqueue(batch, W)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = dev.launch_count
+    if clocks:
+        clocks.mark_start()
+    e0.record(stream)
+    llm.decode_enqueue(batch, K)
+    e1.record(stream)
+    barrier()
+    if clocks:
+        clocks.mark_end()
+    return e0.elapsed_time(e1), dev.launch_count - launches0
+
+
+def run_tp(args, rank: int, world: int, local: int) -> None:
+    """Llama-2-70B-shape Q4_0 decode (BASELINE configs[4]), tensor-parallel over the N GPUs of the
+    launch (N = 1 with --workload decode70b: the whole 38.65 GB model on one GPU):
+    column-parallel q/k/v/gate/up/lm_head, row-parallel o/down with an all-reduce after each (one
+    peer-memory kernel fused with the residual add; NCCL with --nccl-allreduce), 2048 positions
+    already in the KV cache (filled with random f16 on the device).  With N > 1, rank 0 also times
+    the unsharded model on its own GPU afterwards, so that the line carries `speedup_vs_tp1`."""
+    import torch
+    from tensorlogic_b200.api import Device
+    from tensorlogic_b200.model import LLAMA2_70B, Llama, synthetic_model
+    arch, batch, context = LLAMA2_70B, args.batch, 2048
+    K, W = args.steps, max(args.warmup, 3)
+    dev = Device(local)
+    comm = None
+    if world > 1:
+        import torch.distributed as dist
+        from tensorlogic_b200.comm import Comm, unique_id
+        box = [unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, device=torch.device("cuda", local))
+        comm = Comm(dev, box[0], rank, world)
+        if not args.nccl_allreduce:
+            # peer-memory exchange: the [batch, d_model] all-reduces run as one kernel over NVLink
+            def gather(blob):
+                out = [None] * world
+                dist.all_gather_object(out, blob)
+                return out
+            comm.enable_p2p(max(16, batch) * arch.d_model, gather)
+    max_seq = context + 2 * K + 3 * W + 64
+    stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local))
+
+    def barrier():
+        dev.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def build(tp_rank, tp_size):
+        model = synthetic_model(dev, arch, SEED, tp_rank=tp_rank, tp_size=tp_size, device_embeddings=True)
+        llm = Llama(dev, model, arch, max_seq=max_seq, max_batch=batch, max_prefill=16, tp_rank=tp_rank, tp_size=tp_size)
+        if tp_size > 1:
+            llm.set_comm(comm)
+        llm.fill_cache_random(SEED)
+        llm.set_state([(7 + 13 * b) % arch.vocab for b in range(batch)], [context] * batch)
+        return model, llm
+
+    model, llm = build(rank, world)
     with ClockSampler(local) as clocks:
-        e0.record(stream)
-        llm.decode_enqueue(batch, K)
-        e1.record(stream)
-        barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1))
-    gpu_launches = dev.launch_count - launches0
+        llm.decode_enqueue(batch, W)   # nvidia-smi needs a moment to start
+        ms, gpu_launches = time_decode(dev, llm, stream, batch, K, W, barrier, clocks)
+    ms = max_over_ranks(ms)
     tok_s = batch * K / (ms / 1e3)
 
     # end to end: token ids up from the host, sampled tokens back, every step, on every rank
@@ -434,7 +542,8 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
     dev.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
 
-    # dominant kernel: the GEMV launches of a step, replayed alone (no collectives in that graph)
+    # dominant kernel: the GEMV launches of a step, replayed alone (in a sharded model that
+    # graph also holds the collectives that follow o/down and lm_head)
     llm.decode_enqueue(batch, W, parts=1)
     dev.synchronize()
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -443,6 +552,22 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
     g1.record(stream)
     dev.synchronize()
     gemv_ms = max_over_ranks(g0.elapsed_time(g1))
+    launches_per_step = llm.launches(7)
+
+    # the one-GPU point of the scaling curve: the unsharded model on rank 0's GPU
+    tp1 = None
+    if world > 1:
+        barrier()
+        if rank == 0:
+            del llm, model
+            dev.pool_trim(0)
+            K1 = min(K, 16)
+            _m1, llm1 = build(0, 1)
+            ms1, _ = time_decode(dev, llm1, stream, batch, K1, 3, lambda: dev.synchronize())
+            tp1 = {"ms_per_step": ms1 / K1, "value": batch * K1 / (ms1 / 1e3), "steps": K1,
+                   "note": "the whole model on rank 0's GPU, same batch and context, timed after the sharded run"}
+            del llm1, _m1
+        barrier()
     if rank != 0:
         return
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -452,33 +577,37 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
     q4 = lambda n, k: n * (k // 32) * 18
     wbytes = (arch.n_layers * (q4(qd, d) + 2 * q4(kvd, d) + q4(d, qd) + 2 * q4(f, d) + q4(d, f)) + q4(arch.vocab, d)) // world
     gemv_launches = 4 * arch.n_layers + 1
-    # parts=1 in a sharded model also issues the collectives that follow o/down and lm_head
     us = gemv_ms * 1e3 / (K * gemv_launches)
     achieved = wbytes / gemv_launches / (us * 1e-6) / 1e9
-    step_bytes = llama_bytes_per_step(arch, world, batch, context + W + K // 2)
+    step_bytes = llama_bytes_per_step(arch, world, batch, context + 2 * W + K // 2)
+    traffic, traffic_src = profiled_traffic(f"llama70b_tp{world}_gemv")
     line = {
         "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"llama-2-70b-shape q4_0 decode, TP{world}, batch {batch}, 2048-token context "
-                               f"(BASELINE configs[4]); NOT the N=1 workload (tinyllama, configs[2])",
-                   "parallelism": f"tp{world}", "batch": batch, "collectives_per_step": 2 * arch.n_layers + 1,
-                   "allreduce_bytes": batch * d * 2,
-                   "allreduce": "one-shot peer-memory kernel fused with the residual add" if comm.p2p_ready
-                   else "nccl all-reduce + add kernel",
+        "config": {"workload": workload_name(world, batch, True),
+                   "parallelism": f"tp{world}", "batch": batch,
+                   "collectives_per_step": 2 * arch.n_layers + 1 if world > 1 else 0,
+                   "allreduce_bytes": batch * d * 2 if world > 1 else 0,
+                   "allreduce": ("one-shot peer-memory kernel fused with the residual add" if comm.p2p_ready
+                                 else "nccl all-reduce + add kernel") if comm else "none (one GPU)",
                    "step_hbm_bytes_per_gpu": step_bytes,
                    "step_hbm_gbs_per_gpu": step_bytes / (ms / K * 1e-3) / 1e9,
-                   "l2": "per-GPU weights (GBs) exceed the 126 MB L2", "launches_per_step": llm.launches(7), "seed": SEED},
+                   "l2": "per-GPU weights (GBs) exceed the 126 MB L2", "launches_per_step": launches_per_step, "seed": SEED},
         "e2e": {"value": batch * K / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
                 "d2h_bytes_per_step": 4 * batch, "ms_per_step": e2e_ms / K},
         "gpu_launches": int(gpu_launches),
         "clocks": clocks.summary(),
-        "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q4_0> (per-rank shard; time includes the NCCL "
-                     "collectives interleaved with the GEMV launches)", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q4_0> (per-rank shard" +
+                     ("; the time includes the collectives interleaved with the GEMV launches)" if world > 1 else ")"),
+                     "achieved": achieved, "peak": peak,
                      "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                      "bytes_per_launch": wbytes / gemv_launches, "us_per_launch": us,
-                     "launches_per_step": gemv_launches, "traffic": None},
+                     "launches_per_step": gemv_launches, "traffic": traffic, "traffic_source": traffic_src},
     }
+    if tp1 is not None:
+        line["tp1"] = tp1
+        line["speedup_vs_tp1"] = tp1["ms_per_step"] / (ms / K)
     print(json.dumps(line), flush=True)
 
 
@@ -617,8 +746,9 @@ def run_prefill(args, rank: int, world: int, local: int) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode: the headline workload (default); prefill: Llama-2-7B-shape 2048-token prefill")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b"],
+                    help="decode: the headline workload (default); prefill: Llama-2-7B-shape 2048-token prefill; "
+                         "decode70b: the Llama-2-70B-shape decode of the N > 1 runs on ONE GPU (the TP1 point)")
     ap.add_argument("--kernel", default=None, choices=["linear"],
                     help="micro-benchmark one kernel instead of the decode workload (see run_kernel)")
     ap.add_argument("--qtype", default="q4_0", choices=["q4_0", "q8_0"])
@@ -647,7 +777,7 @@ def main() -> None:
     try:
         if args.workload == "prefill":
             run_prefill(args, rank, world, local)
-        elif world > 1:
+        elif world > 1 or args.workload == "decode70b":
             run_tp(args, rank, world, local)
         else:
             run_ours(args, rank, world, local)

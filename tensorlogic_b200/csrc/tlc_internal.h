@@ -63,9 +63,10 @@ struct tlc_ctx {
     // sets the status word and drains; option "wait_limit_ms".
     uint64_t wait_ns = 2000000000ull;
     int gemm_tile = 0;  // 0: pick the GEMM tile from the shape; 11, 12, 22: force 128x128, 128x256, 256x256
-    // Option "gemv_f8" / TLC_GEMV_F8: one activation row against a Q4_0 weight takes the FP8-limb
-    // form of the fused GEMV (tlc_gemv_kernel.cuh); 0 keeps the f16 fragments.
-    bool gemv_f8 = true;
+    // Option "gemv_f8" / TLC_GEMV_F8=1: one activation row against a Q4_0 weight takes the FP8-limb
+    // form of the fused GEMV (tlc_gemv_kernel.cuh).  Off by default: fewer instructions per block,
+    // but measured slower on a B200 (35.3 vs 30.5 us on a 132 MB weight, 7.1 vs 5.5 us on 6.5 MB).
+    bool gemv_f8 = false;
     // Option "step_kernel" / TLC_STEP_KERNEL=1: single-sequence greedy decode steps run as one
     // persistent kernel (tlc_step.cu) when the model allows it.  Off by default: on a B200 the
     // TinyLlama step takes 0.79 ms that way against 0.61 ms kernel by kernel (its hand-overs

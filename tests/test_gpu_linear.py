@@ -328,8 +328,8 @@ def test_device_storage_is_the_tiled_layout(dev, qtype, n, k):
 
 @pytest.mark.parametrize("n,k", [(2048, 2048), (512, 5632), (130, 1056), (48, 8192)])
 def test_fp8_limb_form_of_one_row(dev, ref, n, k):
-    """One activation row against a Q4_0 weight runs on the FP8 tensor-core form (nibbles as e4m3
-    values, the row as four e4m3 limbs under a power-of-two scale).  Same answers as the f16
+    """With option gemv_f8 = 1 one activation row against a Q4_0 weight runs on the FP8 tensor-core
+    form (nibbles as e4m3 values, the row as four e4m3 limbs under a power-of-two scale).  Same answers as the f16
     fragments (option gemv_f8 = 0) and as the oracle, also for a row with a huge outlier, a tiny
     row, a zero row, with a fused RMSNorm, and non-finite in, non-finite out."""
     from tensorlogic_b200 import synth
@@ -350,7 +350,7 @@ def test_fp8_limb_form_of_one_row(dev, ref, n, k):
             try:
                 out[mode] = fn()
             finally:
-                dev.set_option("gemv_f8", 1)
+                dev.set_option("gemv_f8", 0)
         return out[1], out[0]
 
     for name, x in cases.items():
