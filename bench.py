@@ -483,6 +483,15 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
     from tensorlogic_b200.api import Device
     from tensorlogic_b200.model import LLAMA2_70B, Llama, synthetic_model
     arch, batch, context = LLAMA2_70B, args.batch, 2048
+    shard_of = args.as_shard if world == 1 else 1
+    if shard_of > 1:
+        # One rank's share of the tensor-parallel model as a model of its own on one GPU: the same
+        # kernels on the same shapes as a rank of TP<shard_of> runs, without the collectives
+        # (the partial sums of o / down are simply used as they are).  Gives the compute floor of
+        # a rank and a launch list that ncu can take (it must not wrap a multi-rank command).
+        from tensorlogic_b200.model import LlamaArch
+        arch = LlamaArch(arch.n_layers, arch.d_model, arch.n_heads // shard_of, arch.n_kv_heads // shard_of, arch.head_dim,
+                         arch.ffn_dim // shard_of, arch.vocab // shard_of)
     K, W = args.steps, max(args.warmup, 3)
     dev = Device(local)
     comm = None
@@ -585,8 +594,10 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
         "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": workload_name(world, batch, True),
-                   "parallelism": f"tp{world}", "batch": batch,
+        "config": {"workload": workload_name(world, batch, True) if shard_of == 1 else
+                   f"ONE rank's share of llama-2-70b-shape q4_0 decode at TP{shard_of} (batch {batch}, 2048-token context) as "
+                   f"a model of its own on one GPU, no collectives: the compute floor of a TP{shard_of} rank",
+                   "parallelism": f"tp{world}" if shard_of == 1 else f"one shard of tp{shard_of}", "batch": batch,
                    "collectives_per_step": 2 * arch.n_layers + 1 if world > 1 else 0,
                    "allreduce_bytes": batch * d * 2 if world > 1 else 0,
                    "allreduce": ("one-shot peer-memory kernel fused with the residual add" if comm.p2p_ready
@@ -760,6 +771,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="decode batch of the tensor-parallel (N > 1) workload")
+    ap.add_argument("--as-shard", type=int, default=1,
+                    help="with --workload decode70b on one GPU: run ONE rank's share of TP<N> (no collectives)")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="N > 1: keep the all-reduces on NCCL instead of the peer-memory kernel (for comparison)")
     args = ap.parse_args()

@@ -199,6 +199,8 @@ class QTensor:
         """The shard's GGUF blocks (or f16 rows) in the file's order: uint8 [n_rows, bytes per row]."""
         per_row = {_lib.TYPE_Q4_0: 18, _lib.TYPE_Q8_0: 34}.get(self.type)
         row_bytes = self.shape[1] // 32 * per_row if per_row else self.shape[1] * 2
+        if self.type == 14:                                   # Q6_K: 210-byte super-blocks of 256 values
+            row_bytes = self.shape[1] // 256 * 210
         stage = self.dev.empty((self.shape[0] * row_bytes // 2,))
         check(self.dev.lib.tlc_qtensor_blocks(self.dev.handle, self.handle, stage.ptr))
         out = np.empty((self.shape[0], row_bytes), np.uint8)

@@ -123,6 +123,88 @@ __global__ void __launch_bounds__(256) linear_f16_kernel(const uint8_t *__restri
     }
 }
 
+// ---------------------------------------------------------------------------
+// Q6_K weights kept quantized (stock Q4_0 GGUF files store output.weight, the largest
+// linear of a decode step, as Q6_K: GGUFLoader::dequantize_q6_k, src/model/formats/gguf.rs:
+// 128-218).  One warp per output row over rows of 224-byte padded super-blocks (tlc_qtensor.cu);
+// sixteen lanes share a super-block: lane (half h, quarter q) takes l = 4q .. 4q+3 of half h,
+// i.e. one 32-bit word each of ql[l], ql[l+32], qh[l] and from them the sixteen weights
+// l, l+32, l+64, l+96.  The four 6-bit values of a word are put together with byte-wise integer
+// operations, turned into exact f16 (1024 + q, minus 1056) and accumulated in f32 against up to
+// MR activation rows held in shared memory; the group's scale d * sc multiplies the group's sum.
+// HBM-bound on 0.875 bytes per weight (the f16 copy the reference keeps costs 2).
+// ---------------------------------------------------------------------------
+template <int MR>
+__global__ void __launch_bounds__(256) linear_q6k_kernel(const uint8_t *__restrict__ w, size_t pitch, int n_rows, int k,
+                                                         const __half *__restrict__ x, int m, __half *__restrict__ y,
+                                                         const __half *__restrict__ bias,
+                                                         const __half *__restrict__ residual) {
+    extern __shared__ __align__(16) uint8_t q6_smem[];
+    __half *xs = reinterpret_cast<__half *>(q6_smem);  // [m][k]
+    tlc_pdl_prologue();
+    for (int i = threadIdx.x * 8; i < m * k; i += blockDim.x * 8)
+        *reinterpret_cast<uint4 *>(xs + i) = *reinterpret_cast<const uint4 *>(x + i);
+    __syncthreads();
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    const int sub = lane & 15, h = sub >> 3, q = sub & 7, is = q >> 2;
+    const int n_sb = k >> 8;
+    float acc[MR];
+#pragma unroll
+    for (int i = 0; i < MR; i++) acc[i] = 0.f;
+    const __half2 bias1056 = __float2half2_rn(1056.0f);  // 1024 (the magic exponent) + 32 (the offset of q)
+    for (int sb = lane >> 4; sb < n_sb; sb += 2) {
+        const uint8_t *blk = w + (size_t)row * pitch + (size_t)sb * 224;
+        const uint32_t qa = *reinterpret_cast<const uint32_t *>(blk + 64 * h + 4 * q);
+        const uint32_t qb = *reinterpret_cast<const uint32_t *>(blk + 64 * h + 32 + 4 * q);
+        const uint32_t qh = *reinterpret_cast<const uint32_t *>(blk + 128 + 32 * h + 4 * q);
+        const uint2 scw = *reinterpret_cast<const uint2 *>(blk + 192 + 8 * h);
+        const float d = __half2float(*reinterpret_cast<const __half *>(blk + 208));
+        // group j (elements l + 32 j): four 6-bit values in the four bytes of a word
+        uint32_t qv[4];
+        qv[0] = (qa & 0x0F0F0F0Fu) | ((qh & 0x03030303u) << 4);
+        qv[1] = (qb & 0x0F0F0F0Fu) | (((qh >> 2) & 0x03030303u) << 4);
+        qv[2] = ((qa >> 4) & 0x0F0F0F0Fu) | (((qh >> 4) & 0x03030303u) << 4);
+        qv[3] = ((qb >> 4) & 0x0F0F0F0Fu) | (((qh >> 6) & 0x03030303u) << 4);
+        const uint32_t scs[2] = {scw.x, scw.y};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // bytes (b0, b1 | b2, b3) -> f16 pairs 1024 + b, then - 1056: exactly q - 32
+            const uint32_t p01 = __byte_perm(qv[j], 0x64646464u, 0x4140), p23 = __byte_perm(qv[j], 0x64646464u, 0x4342);
+            const float2 w01 = __half22float2(__hsub2(*reinterpret_cast<const __half2 *>(&p01), bias1056));
+            const float2 w23 = __half22float2(__hsub2(*reinterpret_cast<const __half2 *>(&p23), bias1056));
+            const int sidx = is + 2 * j;  // scale of this group: byte sidx of the half's eight
+            const float scale = d * (float)(int8_t)((scs[sidx >> 2] >> (8 * (sidx & 3))) & 0xFF);
+            const int e0 = sb * 256 + 128 * h + 4 * q + 32 * j;
+#pragma unroll
+            for (int i = 0; i < MR; i++) {
+                if (i < m) {
+                    const uint2 xr = *reinterpret_cast<const uint2 *>(xs + (size_t)i * k + e0);
+                    const float2 x01 = __half22float2(*reinterpret_cast<const __half2 *>(&xr.x));
+                    const float2 x23 = __half22float2(*reinterpret_cast<const __half2 *>(&xr.y));
+                    const float s = fmaf(w01.x, x01.x, fmaf(w01.y, x01.y, fmaf(w23.x, x23.x, w23.y * x23.y)));
+                    acc[i] = fmaf(scale, s, acc[i]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MR; i++) {
+        if (i < m) {
+            float v = acc[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) {
+                __half hv = __float2half_rn(v);
+                if (bias) hv = __hadd(hv, bias[row]);
+                if (residual) hv = __hadd(hv, residual[(size_t)i * n_rows + row]);
+                y[(size_t)i * n_rows + row] = hv;
+            }
+        }
+    }
+}
+
 template <int QT, int NT, int AS, bool M1, int CW, bool F8 = false>
 int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     static bool configured[64] = {};
@@ -324,6 +406,52 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
             if (le != cudaSuccess) {
                 cudaGetLastError();
                 return tlc_fail(TLC_ERR_CUDA, "f16 linear launch failed: %s", cudaGetErrorString(le));
+            }
+            TLC_CHECK_LAUNCH(ctx);
+        }
+        return TLC_OK;
+    }
+
+    if (type == TLC_TYPE_Q6_K) {
+        // Resident Q6_K (one weight per launch; RMSNorm, if asked for, as its own kernel; bias
+        // and residual in the store).  More than eight activation rows take further passes.
+        TLC_REQUIRE(a.epilogue != TLC_EPI_SWIGLU && a.n_out == 1 && a.outs[0].rope_heads == 0 &&
+                        a.outs[0].row_stride < 0 && a.outs[0].pos_stride == 0,
+                    TLC_ERR_INVALID_OPERATION, "fused RoPE / SiLU.mul / cache epilogues need a Q4_0 or Q8_0 weight");
+        const __half *x = static_cast<const __half *>(a.x);
+        if (a.norm_w) {
+            if (int32_t rc = tlc_scratch_reserve(ctx, (size_t)a.m * k * 2)) return rc;
+            if (int32_t rc = tlc_rms_norm(ctx, a.x, a.norm_w, ctx->scratch, a.m, (int32_t)k, a.eps)) return rc;
+            x = static_cast<const __half *>(ctx->scratch);
+        }
+        TLC_REQUIRE(((uintptr_t)x & 15) == 0, TLC_ERR_INVALID_OPERATION, "linear: activations must be 16-byte aligned");
+        const __half *residual = a.epilogue == TLC_EPI_RESIDUAL ? static_cast<const __half *>(a.residual) : nullptr;
+        // rows per pass: up to eight, fewer if the activation rows would not fit in shared memory
+        int per = 8;
+        while (per > 1 && (size_t)per * k * 2 > (size_t)ctx->prop.sharedMemPerBlockOptin - 1024) per >>= 1;
+        TLC_REQUIRE((size_t)per * k * 2 <= (size_t)ctx->prop.sharedMemPerBlockOptin - 1024, TLC_ERR_INVALID_OPERATION,
+                    "linear: K = %lld too large for the shared-memory staging", (long long)k);
+        static bool configured[64] = {};
+        if (!configured[ctx->device & 63]) {
+            TLC_CUDA(cudaFuncSetAttribute(linear_q6k_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)ctx->prop.sharedMemPerBlockOptin));
+            TLC_CUDA(cudaFuncSetAttribute(linear_q6k_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)ctx->prop.sharedMemPerBlockOptin));
+            TLC_CUDA(cudaFuncSetAttribute(linear_q6k_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)ctx->prop.sharedMemPerBlockOptin));
+            configured[ctx->device & 63] = true;
+        }
+        const unsigned grid = (unsigned)((w0->n_rows * 32 + 255) / 256);
+        for (int m0 = 0; m0 < a.m; m0 += per) {
+            const int mc = a.m - m0 < per ? a.m - m0 : per;
+            auto kern = mc == 1 ? linear_q6k_kernel<1> : mc <= 4 ? linear_q6k_kernel<4> : linear_q6k_kernel<8>;
+            cudaError_t le = tlc_launch_pdl(
+                ctx, kern, dim3(grid), dim3(256), (size_t)mc * k * 2, static_cast<const uint8_t *>(w0->data), w0->row_pitch,
+                (int)w0->n_rows, (int)k, x + (size_t)m0 * k, mc, static_cast<__half *>(a.outs[0].y) + (size_t)m0 * w0->n_rows,
+                static_cast<const __half *>(a.bias), residual ? residual + (size_t)m0 * w0->n_rows : nullptr);
+            if (le != cudaSuccess) {
+                cudaGetLastError();
+                return tlc_fail(TLC_ERR_CUDA, "Q6_K linear launch failed: %s", cudaGetErrorString(le));
             }
             TLC_CHECK_LAUNCH(ctx);
         }

@@ -417,7 +417,7 @@ extern "C" int32_t tlc_model_load_gguf(tlc_ctx *ctx, const char *path, int32_t t
             return rc;
         // The embedding gather reads f16 rows: a quantized table is dequantized once, here
         // (the reference dequantizes every tensor at load time).
-        if (t.name == "token_embd.weight" && (qt->type == TLC_TYPE_Q4_0 || qt->type == TLC_TYPE_Q8_0)) {
+        if (t.name == "token_embd.weight" && qt->type != TLC_TYPE_F16) {
             tlc_qtensor *dense = nullptr;
             if (int32_t rc = tlc_qtensor_to_f16(ctx, qt, &dense)) {
                 tlc_qtensor_destroy(qt);

@@ -67,6 +67,9 @@ struct tlc_ctx {
     // form of the fused GEMV (tlc_gemv_kernel.cuh).  Off by default: fewer instructions per block,
     // but measured slower on a B200 (35.3 vs 30.5 us on a 132 MB weight, 7.1 vs 5.5 us on 6.5 MB).
     bool gemv_f8 = false;
+    // Option "q6k_resident" / TLC_Q6K_RESIDENT=0: Q6_K tensors are expanded to f16 at upload (what
+    // the reference's loader keeps) instead of staying quantized in HBM.
+    bool q6k_resident = true;
     // Option "step_kernel" / TLC_STEP_KERNEL=1: single-sequence greedy decode steps run as one
     // persistent kernel (tlc_step.cu) when the model allows it.  Off by default: on a B200 the
     // TinyLlama step takes 0.79 ms that way against 0.61 ms kernel by kernel (its hand-overs

@@ -87,7 +87,7 @@ __global__ void untile_blocks_kernel(const uint8_t *__restrict__ data, int type,
 // thread per (row, super-block, half, l) produces the four values l, l+32, l+64,
 // l+96 of its half: q = 4 bits of ql | 2 bits of qh, value = f16_rne((d*sc)*(q-32)).
 // Writes columns [col0, col0 + out_cols) of the row into a dense-pitch f16 tensor.
-__global__ void dequant_q6_k_kernel(const uint8_t *__restrict__ data, int sb_per_row, int64_t n_rows,
+__global__ void dequant_q6_k_kernel(const uint8_t *__restrict__ data, int sb_per_row, int sb_bytes, int64_t n_rows,
                                     int64_t col0, int64_t out_cols, __half *__restrict__ out, size_t out_pitch) {
     const int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t total = n_rows * sb_per_row * 64;
@@ -96,7 +96,7 @@ __global__ void dequant_q6_k_kernel(const uint8_t *__restrict__ data, int sb_per
     const int64_t sbi = gi >> 6;
     const int64_t row = sbi / sb_per_row;
     const int sb = (int)(sbi % sb_per_row);
-    const uint8_t *blk = data + (size_t)sbi * 210;
+    const uint8_t *blk = data + (size_t)sbi * sb_bytes;  // 210 as in the file, 224 in the resident (padded) form
     const uint8_t *ql = blk + 64 * half, *qh = blk + 128 + 32 * half;
     const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * half);
     const float d = __half2float(__ushort_as_half((unsigned short)(blk[208] | (blk[209] << 8))));
@@ -113,6 +113,22 @@ __global__ void dequant_q6_k_kernel(const uint8_t *__restrict__ data, int sb_per
         const int64_t col = (int64_t)sb * 256 + 128 * half + l + 32 * j - col0;
         if (col >= 0 && col < out_cols)
             orow[col] = __float2half_rn(__fmul_rn(__fmul_rn(d, (float)sc[is + 2 * j]), (float)q[j]));
+    }
+}
+
+// Resident Q6_K: the file's 210-byte super-blocks, each padded to 224 bytes (ql 128 | qh 64 |
+// scales 16 | d 2 | 14 zero bytes) so that every piece starts on a 16-byte boundary.  No byte
+// of a super-block is changed.  pad = true: 210 -> 224; false: back to the file's form.
+__global__ void q6k_repad_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int64_t n_sb, bool pad) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per 2 bytes
+    if (i >= n_sb * 112) return;
+    const int64_t sb = i / 112;
+    const int w = (int)(i % 112);
+    if (pad) {
+        const uint16_t v = w < 105 ? *reinterpret_cast<const uint16_t *>(src + sb * 210 + 2 * w) : (uint16_t)0;
+        *reinterpret_cast<uint16_t *>(dst + sb * 224 + 2 * w) = v;
+    } else if (w < 105) {
+        *reinterpret_cast<uint16_t *>(dst + sb * 210 + 2 * w) = *reinterpret_cast<const uint16_t *>(src + sb * 224 + 2 * w);
     }
 }
 
@@ -185,6 +201,7 @@ static int32_t shard_shape(int32_t type, int64_t n_rows, int64_t n_cols, int32_t
 static size_t bytes_per_row(int32_t type, int64_t cols) {
     if (type == TLC_TYPE_Q4_0) return (size_t)(cols / 32) * 18;
     if (type == TLC_TYPE_Q8_0) return (size_t)(cols / 32) * 34;
+    if (type == TLC_TYPE_Q6_K) return (size_t)(cols / 256) * 210;
     return (size_t)cols * 2;  // F16 (F32 is converted on the host first)
 }
 
@@ -205,6 +222,12 @@ static int32_t alloc_qtensor(tlc_ctx *ctx, int32_t type, int64_t rows, int64_t c
         qt->k_tiles = tlc_tile::k_tiles(qt->type, cols);
         qt->slab_pitch = (size_t)qt->k_tiles * tlc_tile::tile_bytes(qt->type);
         qt->bytes = qt->slab_pitch * (size_t)tlc_tile::slabs(rows);
+    } else if (qt->type == TLC_TYPE_Q6_K) {
+        // Resident Q6_K: rows of 224-byte padded super-blocks (q6k_repad_kernel).
+        qt->row_pitch = (size_t)(cols / 256) * 224;
+        qt->k_tiles = 0;
+        qt->slab_pitch = 0;
+        qt->bytes = qt->row_pitch * (size_t)rows;
     } else {
         // Dense rows start on 16-byte boundaries.
         qt->row_pitch = (qt->row_bytes + 15) & ~(size_t)15;
@@ -246,7 +269,6 @@ extern "C" int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows
                 "tensor data too short: %zu bytes for shape [%lld, %lld] (need %zu)", bytes, (long long)n_rows,
                 (long long)n_cols, src_row_bytes * (size_t)n_rows);
     if (type == TLC_TYPE_Q6_K) {
-        // Dequantized on the device into an F16 tensor (what the reference's loader keeps in memory).
         TLC_REQUIRE(n_cols % 256 == 0, TLC_ERR_LOAD, "Q6_K tensor needs columns in multiples of 256 (got %lld)",
                     (long long)n_cols);
         const int sb_per_row = (int)(n_cols / 256);
@@ -254,6 +276,37 @@ extern "C" int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows
         TLC_REQUIRE(bytes >= q_row_bytes * (size_t)n_rows, TLC_ERR_LOAD,
                     "tensor data too short: %zu bytes for Q6_K shape [%lld, %lld] (need %zu)", bytes, (long long)n_rows,
                     (long long)n_cols, q_row_bytes * (size_t)n_rows);
+        if (ctx->q6k_resident && cols == n_cols) {
+            // Whole rows (no column shard): the super-blocks stay quantized in HBM, 0.875 bytes per
+            // weight instead of the 2 of an f16 copy; linear() runs on them directly.
+            tlc_qtensor *qt = nullptr;
+            if (int32_t rc = alloc_qtensor(ctx, TLC_TYPE_Q6_K, rows, cols, n_rows, n_cols, tp_rank, tp_size, split, &qt))
+                return rc;
+            void *tmp = nullptr;
+            const int64_t n_sb = rows * sb_per_row;
+            cudaError_t e = cudaMalloc(&tmp, q_row_bytes * (size_t)rows);
+            if (e == cudaSuccess)
+                e = cudaMemcpyAsync(tmp, static_cast<const uint8_t *>(blocks) + (size_t)row0 * q_row_bytes,
+                                    q_row_bytes * (size_t)rows, cudaMemcpyHostToDevice, ctx->stream);
+            if (e == cudaSuccess) {
+                q6k_repad_kernel<<<(unsigned)((n_sb * 112 + 255) / 256), 256, 0, ctx->stream>>>(
+                    static_cast<const uint8_t *>(tmp), static_cast<uint8_t *>(qt->data), n_sb, true);
+                ctx->launches++;
+                e = cudaGetLastError();
+            }
+            if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+            cudaFree(tmp);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                cudaFree(qt->data);
+                delete qt;
+                return tlc_fail(TLC_ERR_CUDA, "Q6_K upload failed: %s", cudaGetErrorString(e));
+            }
+            *out = qt;
+            return TLC_OK;
+        }
+        // A column shard (or option "q6k_resident" = 0): dequantized on the device into an F16
+        // tensor, which is what the reference's loader keeps in memory.
         tlc_qtensor *qt = nullptr;
         if (int32_t rc = alloc_qtensor(ctx, TLC_TYPE_F16, rows, cols, n_rows, n_cols, tp_rank, tp_size, split, &qt))
             return rc;
@@ -266,7 +319,7 @@ extern "C" int32_t tlc_qtensor_create(tlc_ctx *ctx, int32_t type, int64_t n_rows
         if (e == cudaSuccess) {
             const int64_t total = rows * sb_per_row * 64;
             dequant_q6_k_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
-                static_cast<const uint8_t *>(tmp), sb_per_row, rows, col0, cols, static_cast<__half *>(qt->data),
+                static_cast<const uint8_t *>(tmp), sb_per_row, 210, rows, col0, cols, static_cast<__half *>(qt->data),
                 qt->row_pitch);
             ctx->launches++;
             e = cudaGetLastError();
@@ -489,6 +542,11 @@ extern "C" int32_t tlc_dequant(tlc_ctx *ctx, tlc_qtensor *qt, void *out_f16_dev)
         int64_t total = qt->n_rows * qt->n_cols;
         copy_rows_f16_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, ctx->stream>>>(
             data, qt->row_pitch, qt->n_cols, qt->n_rows, out);
+    } else if (qt->type == TLC_TYPE_Q6_K) {
+        const int sb_per_row = (int)(qt->n_cols / 256);
+        const int64_t total = qt->n_rows * sb_per_row * 64;
+        dequant_q6_k_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, ctx->stream>>>(
+            data, sb_per_row, 224, qt->n_rows, 0, qt->n_cols, out, (size_t)qt->n_cols * 2);
     } else {
         int bpr = (int)(qt->n_cols / 32);
         int64_t total = qt->n_rows * bpr;
@@ -507,6 +565,13 @@ extern "C" int32_t tlc_qtensor_blocks(tlc_ctx *ctx, tlc_qtensor *qt, void *out_d
     TLC_REQUIRE(qt && out_dev, TLC_ERR_INVALID_OPERATION, "tlc_qtensor_blocks: null pointer");
     TLC_REQUIRE(qt->ctx->device == ctx->device, TLC_ERR_DEVICE, "tlc_qtensor_blocks: tensor lives on device %d, context on %d",
                 qt->ctx->device, ctx->device);
+    if (qt->type == TLC_TYPE_Q6_K) {
+        const int64_t n_sb = qt->n_rows * (qt->n_cols / 256);
+        q6k_repad_kernel<<<(unsigned)((n_sb * 112 + 255) / 256), 256, 0, ctx->stream>>>(
+            static_cast<const uint8_t *>(qt->data), static_cast<uint8_t *>(out_dev), n_sb, false);
+        TLC_CHECK_LAUNCH(ctx);
+        return TLC_OK;
+    }
     if (!qt->slab_pitch) {
         TLC_CUDA(cudaMemcpy2DAsync(out_dev, qt->row_bytes, qt->data, qt->row_pitch, qt->row_bytes, (size_t)qt->n_rows,
                                    cudaMemcpyDeviceToDevice, ctx->stream));

@@ -1,5 +1,6 @@
-"""GPU tests of Q6_K tensors: accepted on upload, dequantized on the device into F16 tensors
-(what the reference's loader keeps in memory), used by linear() and the runner."""
+"""GPU tests of Q6_K tensors: kept quantized in HBM (210-byte super-blocks padded to 224), dequantized
+bit-exactly on demand, used by linear() through a fused kernel and by the runner; column shards
+and option q6k_resident = 0 take the f16 expansion the reference's loader keeps in memory."""
 import os
 
 import numpy as np
@@ -28,7 +29,8 @@ def test_q6_k_upload_is_bit_exact(dev, ref):
     g = np.load(os.path.join(HERE, "golden", "q6_k.npz"))
     raw = g["q6_k_bytes"]                                      # 12 super-blocks -> W [3, 1024]
     w = QTensor.from_blocks(dev, Q6K, 3, 1024, raw)
-    assert w.type == 1 and w.shape == (3, 1024)                # an F16 tensor from here on
+    assert w.type == Q6K and w.shape == (3, 1024)              # stays quantized in HBM
+    assert np.array_equal(w.raw_bytes().reshape(-1), np.ascontiguousarray(raw).view(np.uint8).reshape(-1))
     got = w.dequantize().numpy()
     want = ref.dequant(Q6K, raw, 3072).reshape(3, 1024)
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
@@ -88,3 +90,40 @@ def test_real_file_layout_q6_k_head_and_q4_0_embeddings(dev, ref, tmp_path):
     ow["token_embd.weight"] = (1, emb)
     want = _ref_model(ref, ow, arch).forward(ids)
     assert rel_l2(logits, want) < 1e-2
+
+
+@pytest.mark.parametrize("n,k", [(96, 768), (1000, 2048), (33, 256), (257, 4096)])
+def test_q6_k_fused_linear(dev, ref, n, k):
+    """linear() on resident Q6_K against the oracle (dequantize as the loader does, f32 sums) for
+    1 .. 19 activation rows, with bias, with the fused residual and RMSNorm entry points, and
+    against the f16 expansion (option q6k_resident = 0)."""
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.api import QTensor, linear, linear_residual, norm_linear_multi
+    rng = np.random.default_rng(n + k)
+    raw = _q6k_blocks(rng, n, k)
+    w = QTensor.from_blocks(dev, Q6K, n, k, raw)
+    assert w.type == Q6K
+    dev.set_option("q6k_resident", 0)
+    try:
+        w16 = QTensor.from_blocks(dev, Q6K, n, k, raw)
+    finally:
+        dev.set_option("q6k_resident", 1)
+    assert w16.type == 1
+    for m in (1, 2, 5, 8, 19):
+        x = rng.standard_normal((m, k)).astype(np.float16)
+        want = ref.linear_q(Q6K, raw, n, k, x)
+        l0 = dev.launch_count
+        y = linear(dev.tensor(x), w).numpy()
+        assert dev.launch_count - l0 == (m + 7) // 8
+        assert y.shape == (m, n) and rel_l2(y, want) < 2e-3, m
+        assert rel_l2(y, linear(dev.tensor(x), w16).numpy()) < 1e-3
+    x = rng.standard_normal((3, k)).astype(np.float16)
+    bias = rng.standard_normal(n).astype(np.float16)
+    want = ref.add(ref.linear_q(Q6K, raw, n, k, x), np.broadcast_to(bias, (3, n)))
+    assert rel_l2(linear(dev.tensor(x), w, dev.tensor(bias)).numpy(), want) < 2e-3
+    res = rng.standard_normal((3, n)).astype(np.float16)
+    want = ref.add(res, ref.linear_q(Q6K, raw, n, k, x))
+    assert rel_l2(linear_residual(dev.tensor(x), w, dev.tensor(res)).numpy(), want) < 2e-3
+    nw = synth.norm_weight(3, "q6norm", k)
+    (got,) = norm_linear_multi(dev.tensor(x), [w], dev.tensor(nw), 1e-5)
+    assert rel_l2(got.numpy(), ref.linear_q(Q6K, raw, n, k, ref.rms_norm(x, nw, 1e-5))) < 2e-3
