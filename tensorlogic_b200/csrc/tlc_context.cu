@@ -82,6 +82,7 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (const char *e = getenv("TLC_HOST_POLL")) ctx->host_poll = atoi(e) != 0;
     if (const char *e = getenv("TLC_STEP_KERNEL")) ctx->step_kernel = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMV_F8")) ctx->gemv_f8 = atoi(e) != 0;
+    if (const char *e = getenv("TLC_GEMV_SPLITK")) ctx->gemv_splitk = atoi(e) != 0;
     if (const char *e = getenv("TLC_Q6K_RESIDENT")) ctx->q6k_resident = atoi(e) != 0;
     *out = ctx;
     return TLC_OK;
@@ -113,6 +114,8 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         ctx->step_kernel = value != 0;
     else if (n == "gemv_f8")
         ctx->gemv_f8 = value != 0;
+    else if (n == "gemv_splitk")
+        ctx->gemv_splitk = value != 0;
     else if (n == "q6k_resident")
         ctx->q6k_resident = value != 0;
     else

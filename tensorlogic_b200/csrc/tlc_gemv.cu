@@ -205,6 +205,66 @@ __global__ void __launch_bounds__(256) linear_q6k_kernel(const uint8_t *__restri
     }
 }
 
+// Second half of a split-K launch (GemvParams::ksplit > 1): one thread per output adds the K
+// windows' f32 shares in window order (so the result does not depend on scheduling) and applies
+// the epilogue of gemv_mma_kernel -- f16 rounding, then bias / residual / SiLU(gate)*up /
+// interleaved RoPE, dense or (sequence, position) addressing.
+__global__ void __launch_bounds__(256) gemv_splitk_finish_kernel(const GemvParams p) {
+    tlc_pdl_prologue();
+    const int nout = p.subs == 2 ? p.t[0].n : p.ntot;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)p.m * nout) return;
+    const int col = (int)(i / nout), nn = (int)(i % nout);
+    int ti = 0, n = nn;
+    if (p.subs == 1) {
+        if (n >= p.t[0].n) { n -= p.t[0].n; ti = 1; }
+        if (ti == 1 && n >= p.t[1].n) { n -= p.t[1].n; ti = 2; }
+    }
+    const int noff = nn - n;
+    auto sum = [&](int off) {
+        float v = 0.f;
+        for (int w = 0; w < p.ksplit; w++) v += p.partial[((size_t)w * p.m + col) * p.ntot + off];
+        return v;
+    };
+    const int wn = ti == 0 ? p.t[0].n : ti == 1 ? p.t[1].n : p.t[2].n;
+    __half *yout = ti == 0 ? p.t[0].y : ti == 1 ? p.t[1].y : p.t[2].y;
+    const long long rstride = ti == 0 ? p.t[0].row_stride : ti == 1 ? p.t[1].row_stride : p.t[2].row_stride;
+    const long long pstride = ti == 0 ? p.t[0].pos_stride : ti == 1 ? p.t[1].pos_stride : p.t[2].pos_stride;
+    const int rheads = ti == 0 ? p.t[0].rope_heads : ti == 1 ? p.t[1].rope_heads : p.t[2].rope_heads;
+    const int hdim = ti == 0 ? p.t[0].head_dim : ti == 1 ? p.t[1].head_dim : p.t[2].head_dim;
+    __half h = __float2half_rn(sum(noff + n));
+    const size_t oidx = (size_t)col * wn + n;
+    const int pos = p.positions ? p.positions[col] : p.pos_offset + col;
+    const size_t yidx = (size_t)((long long)col * rstride + (long long)pos * pstride) + n;
+    if (pstride != 0 && p.max_pos > 0 && (pos < 0 || pos >= p.max_pos)) {
+        if (atomicCAS(&p.status->code, 0, TLC_DEV_INDEX) == 0) p.status->where = 302;
+        return;
+    }
+    if (rheads > 0) {
+        const __half hp = __float2half_rn(sum(noff + (n ^ 1)));
+        const int dim = n % hdim;
+        const int pair = dim >> 1;
+        const float x0 = __half2float((dim & 1) ? hp : h);
+        const float x1 = __half2float((dim & 1) ? h : hp);
+        const float exponent = (float)(2 * pair) / (float)hdim;
+        const float freq = 1.0f / powf(p.rope_base, exponent);
+        const float theta = (float)(unsigned)pos * freq;
+        const float cs = cosf(theta), sn = sinf(theta);
+        const float r = (dim & 1) ? __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs))
+                                  : __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+        yout[yidx] = __float2half_rn(r);
+    } else if (p.epilogue == TLC_EPI_RESIDUAL) {
+        yout[yidx] = __hadd(h, p.residual[oidx]);
+    } else if (p.epilogue == TLC_EPI_SWIGLU) {
+        const __half up = __float2half_rn(sum(p.t[0].n + n));
+        const __half sg = __float2half_rn(1.0f / (1.0f + expf(-__half2float(h))));
+        p.t[0].y[oidx] = __hmul(__hmul(h, sg), up);
+    } else {
+        if (p.bias) h = __hadd(h, p.bias[n]);
+        yout[yidx] = h;
+    }
+}
+
 template <int QT, int NT, int AS, bool M1, int CW, bool F8 = false>
 int32_t launch_mma_as(tlc_ctx *ctx, GemvParams &p, int grid, size_t smem) {
     static bool configured[64] = {};
@@ -284,11 +344,15 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     const int cw = !two && fixed_smem_bytes(p.nblk_pad, p.m, NT, p.subs, 16) + 3 * STAGE_BYTES <= budget ? 16 : 8;
     const size_t cap = two ? half : budget;
     const int max_ctas = two ? 2 * ctx->sm_count : ctx->sm_count;
-    const int grid = p.total_units < max_ctas ? p.total_units : max_ctas;
+    const int ks = p.ksplit > 1 ? p.ksplit : 1;
+    // Split K: the CTAs come in groups of ks (one per window); a group shares the slabs.
+    int grid = p.total_units * ks < max_ctas ? p.total_units * ks : max_ctas;
+    grid -= grid % ks;
+    if (grid < ks) grid = ks;
     // Accumulator sets per reduction: enough units for about four ring stages
     // between two cross-warp reductions, as far as this CTA has units and the
     // shared memory (reduction buffers grow with the sets) allows.
-    const int units_per_cta = (p.total_units + grid - 1) / grid;
+    const int units_per_cta = (p.total_units + grid / ks - 1) / (grid / ks);
     const int iters_per_unit = p.subs * p.nchunks;
     int ub = (4 + iters_per_unit - 1) / iters_per_unit;
     if (ub > units_per_cta) ub = units_per_cta;
@@ -346,6 +410,35 @@ static int gemv_max_m(tlc_ctx *ctx, int type, int k) {
         if (gemv_fixed_smem(nblk_pad, m, nt) + 3 * stage <= budget) return m;
     }
     return 0;
+}
+
+// Split K for several activation rows.  The rows sit in shared memory in fragment order, 64 bytes
+// per block and row: 8 rows of K = 8192 already take half an SM's shared memory, 16 rows of
+// K = 28672 eight times an SM's.  Instead of passing over the weights once per group of rows that
+// fits, the K range is cut into windows: every CTA keeps only its window of the rows, the windows'
+// f32 partial sums meet in gemv_splitk_finish_kernel.  The weights are read once.
+// Returns the number of windows (1: no split) for m rows; the window must hold at least one ring
+// stage of tiles and leave room for two CTAs per SM.
+static int gemv_choose_ksplit(tlc_ctx *ctx, int type, int64_t ktiles, int m, int n_sub) {
+    const int tb = tlc_tile::tile_blocks(type);
+    const size_t stage = (size_t)kTilesPerStage * tlc_tile::tile_bytes(type);
+    const size_t half = (size_t)ctx->prop.sharedMemPerMultiprocessor / 2 - 1024;
+    const int nt = m > 8 ? 2 : 1;
+    static const int cand[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32};
+    for (int ks : cand) {
+        const int64_t win = (ktiles + ks - 1) / ks;
+        if (ks > 1 && win < kTilesPerStage) break;
+        if (fixed_smem_bytes((int)win * tb, m, nt, n_sub) + 3 * stage <= half) return ks;
+    }
+    return 1;
+}
+
+// Bytes of context scratch a fused linear over m rows of width k with n_total outputs may need
+// (the split-K partial sums); callers that capture graphs reserve it up front.
+size_t tlc_gemv_scratch_bytes(tlc_ctx *ctx, int type, int64_t k, int m, int64_t n_total) {
+    if ((type != TLC_TYPE_Q4_0 && type != TLC_TYPE_Q8_0) || m < 2 || m > 16) return 0;
+    const int ks = gemv_choose_ksplit(ctx, type, tlc_tile::k_tiles(type, k), m, 2);
+    return ks > 1 ? (size_t)ks * m * (size_t)n_total * sizeof(float) : 0;
 }
 
 int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
@@ -460,10 +553,16 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
 
     if (tlc_gemm_eligible(ctx, a)) return tlc_launch_gemm(ctx, a);
 
-    const int max_m = gemv_max_m(ctx, type, (int)k);
+    int max_m = gemv_max_m(ctx, type, (int)k);
     TLC_REQUIRE(max_m >= 1, TLC_ERR_INVALID_OPERATION, "gemv: K = %lld too large for the shared-memory staging",
                 (long long)k);
-    // Activation rows beyond what one launch can hold are processed in
+    // Up to 16 rows whose fragments do not leave two CTAs per SM room: one pass with K cut into windows.
+    int ksplit = 1;
+    if (a.m >= 2 && a.m <= 16 && ctx->gemv_splitk) {
+        ksplit = gemv_choose_ksplit(ctx, type, w0->k_tiles, a.m, a.epilogue == TLC_EPI_SWIGLU ? 2 : 1);
+        if (ksplit > 1) max_m = a.m;
+    }
+    // Otherwise activation rows beyond what one launch can hold are processed in
     // further passes over the weights.
     for (int m0 = 0; m0 < a.m; m0 += max_m) {
         const int mc = a.m - m0 < max_m ? a.m - m0 : max_m;
@@ -508,6 +607,21 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.max_pos = a.max_pos;
         p.status = ctx->dev_status;
         p.wait_ns = ctx->wait_ns;
+        if (ksplit > 1) {
+            p.ksplit = ksplit;
+            p.ktiles_full = p.ktiles;
+            p.ktiles_win = (p.ktiles + ksplit - 1) / ksplit;
+            p.ntot = 0;
+            for (int i = 0; i < a.n_out; i++) p.ntot += p.t[i].n;
+            // what the launcher sizes shared memory, stages and batches by: one window
+            p.ktiles = p.ktiles_win;
+            p.nblk_pad = p.ktiles_win * tlc_tile::tile_blocks(type);
+            p.nblk = p.nblk_pad;
+            p.nchunks = (p.ktiles_win + kTilesPerStage - 1) / kTilesPerStage;
+            const size_t need = (size_t)ksplit * mc * (size_t)p.ntot * sizeof(float);
+            if (int32_t rc = tlc_scratch_reserve(ctx, need)) return rc;
+            p.partial = static_cast<float *>(ctx->scratch);
+        }
         const int nt = mc > 8 ? 2 : 1;
         int32_t rc;
         if (type == TLC_TYPE_Q4_0)
@@ -515,6 +629,16 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
         else
             rc = nt == 1 ? launch_mma<TLC_TYPE_Q8_0, 1>(ctx, p) : launch_mma<TLC_TYPE_Q8_0, 2>(ctx, p);
         if (rc) return rc;
+        if (ksplit > 1) {
+            const int nout = p.subs == 2 ? p.t[0].n : p.ntot;
+            const size_t total = (size_t)mc * nout;
+            cudaError_t le = tlc_launch_pdl(ctx, gemv_splitk_finish_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, p);
+            if (le != cudaSuccess) {
+                cudaGetLastError();
+                return tlc_fail(TLC_ERR_CUDA, "split-K finish launch failed: %s", cudaGetErrorString(le));
+            }
+            TLC_CHECK_LAUNCH(ctx);
+        }
     }
     return TLC_OK;
 }

@@ -71,6 +71,11 @@ struct GemvParams {
     int pdl_mode;  // 1: let the next kernel be scheduled at once, 2: only when this CTA's last slab is done
     tlc_dev_status *status;
     uint64_t wait_ns;  // how long a wait may last before the kernel gives up
+    // Split K (ksplit > 1): the K range is cut into ksplit windows of ktiles_win tiles (nblk_pad is
+    // then a window's padded block count); CTA b takes window b % ksplit and writes its f32 share of
+    // every output to partial[window][activation row][ntot outputs] instead of running the epilogue.
+    int ksplit, ktiles_win, ktiles_full, ntot;
+    float *partial;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -73,6 +73,17 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     const int S = p.nstages;
+    // Split K (p.ksplit > 1): CTA b works on K window b % ksplit -- tiles [kt0, kt0 + p.ktiles) of
+    // every slab it owns, p.nblk blocks of the activation rows starting at block kb0 -- and shares
+    // the slabs with the other CTAs of the same window.
+    const int ks = p.ksplit > 1 ? (int)blockIdx.x % p.ksplit : 0;
+    const int cta_i = p.ksplit > 1 ? (int)blockIdx.x / p.ksplit : (int)blockIdx.x;
+    const int cta_n = p.ksplit > 1 ? (int)gridDim.x / p.ksplit : (int)gridDim.x;
+    const int kt0 = ks * p.ktiles_win;
+    const int kb0 = kt0 * T::TB;
+    const int my_ktiles = p.ksplit > 1 ? max(0, min(p.ktiles_win, p.ktiles_full - kt0)) : p.ktiles;
+    const int my_nchunks = p.ksplit > 1 ? (my_ktiles + kTilesPerStage - 1) / kTilesPerStage : p.nchunks;
+    const int my_nblk = p.ksplit > 1 ? max(0, min(p.ktiles_win * T::TB, p.k / 32 - kb0)) : p.nblk;
 
     if (tid == 0) {
         for (int s = 0; s < S; s++) {
@@ -95,12 +106,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
         int rs = 0;
         uint32_t rpar = 1;
         const uint64_t policy = l2_evict_first_policy();
-        const int pu_lo = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
-        const int pu_hi = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
-        const int pcount = p.contig ? pu_hi - pu_lo
-                                    : ((int)p.total_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+        const int pu_lo = (int)((long long)cta_i * p.total_units / cta_n);
+        const int pu_hi = (int)((long long)(cta_i + 1) * p.total_units / cta_n);
+        const int pcount = p.contig ? pu_hi - pu_lo : ((int)p.total_units - cta_i + cta_n - 1) / cta_n;
         for (int ui = 0; ui < pcount; ui++) {
-            const int unit = p.contig ? pu_lo + ui : (int)blockIdx.x + ui * (int)gridDim.x;
+            const int unit = p.contig ? pu_lo + ui : cta_i + ui * cta_n;
             for (int sub = 0; sub < p.subs; sub++) {
                 int ti = 0, sl = unit;
                 if (p.subs == 2) {
@@ -111,7 +121,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                 }
                 const uint8_t *wbase = ti == 0 ? p.t[0].w : ti == 1 ? p.t[1].w : p.t[2].w;
                 const size_t spitch = ti == 0 ? p.t[0].slab_pitch : ti == 1 ? p.t[1].slab_pitch : p.t[2].slab_pitch;
-                for (int c = 0; c < p.nchunks; c++) {
+                for (int c = 0; c < my_nchunks; c++) {
                     const int s = rs;
                     // On a timeout the producer stops issuing copies; the consumers'
                     // own bounded waits then end the CTA.
@@ -121,17 +131,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                         rpar ^= 1u;
                     }
                     // The stage's tiles are contiguous in HBM: one bulk copy.
-                    const int ntiles = min(kTilesPerStage, p.ktiles - c * kTilesPerStage);
+                    const int ntiles = min(kTilesPerStage, my_ktiles - c * kTilesPerStage);
                     const uint32_t bytes = (uint32_t)(ntiles * TILE);
                     if (lane == 0) {
+                        const uint8_t *src = wbase + (size_t)sl * spitch + (size_t)(kt0 + c * kTilesPerStage) * TILE;
                         mbar_expect_tx(&full[s], bytes);
                         if (p.l2_hint)
-                            bulk_g2s_hint(stages + (size_t)s * STAGE_BYTES,
-                                          wbase + (size_t)sl * spitch + (size_t)c * (kTilesPerStage * TILE), bytes,
-                                          &full[s], policy);
+                            bulk_g2s_hint(stages + (size_t)s * STAGE_BYTES, src, bytes, &full[s], policy);
                         else
-                            bulk_g2s(stages + (size_t)s * STAGE_BYTES,
-                                     wbase + (size_t)sl * spitch + (size_t)c * (kTilesPerStage * TILE), bytes, &full[s]);
+                            bulk_g2s(stages + (size_t)s * STAGE_BYTES, src, bytes, &full[s]);
                     }
                 }
             }
@@ -149,8 +157,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
         const int items = p.nblk_pad * p.m * 4;
         for (int idx = ctid; idx < items; idx += CT) {
             const int t = idx & 3, b = (idx >> 2) / p.m;
-            if (b >= p.nblk) continue;
-            const __half *wr = p.norm_w + b * 32;
+            if (b >= my_nblk) continue;
+            const __half *wr = p.norm_w + (kb0 + b) * 32;
             if (idx == ctid) {
                 if (QT == TLC_TYPE_Q4_0) {
                     const uint2 lo = *reinterpret_cast<const uint2 *>(wr + 4 * t);
@@ -265,8 +273,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
             float v[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) v[j] = 0.f;
-            if (live && b < p.nblk) {
-                const __half *xr = p.x + (size_t)m * p.k + b * 32;
+            if (live && b < my_nblk) {
+                const __half *xr = p.x + (size_t)m * p.k + (kb0 + b) * 32;
                 float inv = 1.f;
                 if (do_norm) {
                     float ss = 0.f;
@@ -279,14 +287,14 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                     *reinterpret_cast<uint2 *>(&raw[0]) = *reinterpret_cast<const uint2 *>(xr + 4 * t);
                     *reinterpret_cast<uint2 *>(&raw[4]) = *reinterpret_cast<const uint2 *>(xr + 16 + 4 * t);
                     if (do_norm && r > 0) {
-                        const __half *wr = p.norm_w + b * 32;
+                        const __half *wr = p.norm_w + (kb0 + b) * 32;
                         *reinterpret_cast<uint2 *>(&nw[0]) = *reinterpret_cast<const uint2 *>(wr + 4 * t);
                         *reinterpret_cast<uint2 *>(&nw[4]) = *reinterpret_cast<const uint2 *>(wr + 16 + 4 * t);
                     }
                 } else {
                     *reinterpret_cast<uint4 *>(&raw[0]) = *reinterpret_cast<const uint4 *>(xr + 8 * t);
                     if (do_norm && r > 0)
-                        *reinterpret_cast<uint4 *>(&nw[0]) = *reinterpret_cast<const uint4 *>(p.norm_w + b * 32 + 8 * t);
+                        *reinterpret_cast<uint4 *>(&nw[0]) = *reinterpret_cast<const uint4 *>(p.norm_w + (kb0 + b) * 32 + 8 * t);
                 }
                 if (do_norm && r == 0) *reinterpret_cast<uint4 *>(&nw[0]) = nw_first;
                 float f[8];
@@ -397,10 +405,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     // rows (9 % faster on a 132 MB weight).  They are processed in batches of AS
     // accumulator sets (one set = one 16-row slab; a gate/up unit takes two) with
     // ONE cross-warp reduction per batch.
-    const int u_lo = (int)((long long)blockIdx.x * p.total_units / gridDim.x);
-    const int u_hi = (int)((long long)(blockIdx.x + 1) * p.total_units / gridDim.x);
-    const int n_mine = p.contig ? u_hi - u_lo
-                                : ((int)p.total_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int u_lo = (int)((long long)cta_i * p.total_units / cta_n);
+    const int u_hi = (int)((long long)(cta_i + 1) * p.total_units / cta_n);
+    const int n_mine = p.contig ? u_hi - u_lo : ((int)p.total_units - cta_i + cta_n - 1) / cta_n;
     const int ub = AS / p.subs;  // units per batch
     int rs = 0;           // ring position and its parity, carried from stage to stage
     uint32_t rpar = 0;
@@ -557,11 +564,11 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                     }
                 }
             };
-            for (int c = 0; c < p.nchunks; c++) {
+            for (int c = 0; c < my_nchunks; c++) {
                 // A wait that ran out skips the math but keeps the barrier protocol
                 // going, so every warp still reaches the same bar.sync calls.
                 const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[rs], rpar, abort_flag, p.status, 2, p.wait_ns));
-                const int ntiles = ready ? min(kTilesPerStage, p.ktiles - c * kTilesPerStage) : 0;
+                const int ntiles = ready ? min(kTilesPerStage, my_ktiles - c * kTilesPerStage) : 0;
                 const uint32_t sbase = stages_addr + (uint32_t)rs * STAGE_BYTES;
                 const uint32_t cb0 = (uint32_t)(c * kTilesPerStage * T::TB);  // first block of the stage
                 if (ntiles == kTilesPerStage) {
@@ -618,7 +625,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
             const int ui = item / per_unit, rc = item % per_unit;
             const int col = rc >> 4, row = rc & 15;
             const int a0 = ui * p.subs;
-            int ti = 0, sl = p.contig ? u_lo + i0 + ui : (int)blockIdx.x + (i0 + ui) * (int)gridDim.x;
+            int ti = 0, sl = p.contig ? u_lo + i0 + ui : cta_i + (i0 + ui) * cta_n;
             if (p.subs == 1) {
                 if (sl >= p.slabs[0]) { sl -= p.slabs[0]; ti = 1; }
                 if (ti == 1 && sl >= p.slabs[1]) { sl -= p.slabs[1]; ti = 2; }
@@ -634,6 +641,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                 if (F8) return v * *f8_scale;  // undo the row's scale and the 2^-9 of the e4m3 nibbles
                 return v * 16777216.0f;  // undo the 2^-24 of the integer fragments
             };
+            if (p.ksplit > 1) {
+                // Split K: this window's f32 share of the dot product; gemv_splitk_finish_kernel adds
+                // the windows and applies the epilogue.  Outputs of the fused weights lie side by side.
+                const int noff = ti == 0 ? 0 : ti == 1 ? p.t[0].n : p.t[0].n + p.t[1].n;
+                float *dst = p.partial + ((size_t)ks * p.m + col) * p.ntot + noff + n;
+                *dst = total(a0, row);
+                if (p.subs == 2) dst[p.t[0].n] = total(a0 + 1, row);
+                continue;
+            }
             __half *yout = ti == 0 ? p.t[0].y : ti == 1 ? p.t[1].y : p.t[2].y;
             const long long rstride = ti == 0 ? p.t[0].row_stride : ti == 1 ? p.t[1].row_stride : p.t[2].row_stride;
             const long long pstride = ti == 0 ? p.t[0].pos_stride : ti == 1 ? p.t[1].pos_stride : p.t[2].pos_stride;

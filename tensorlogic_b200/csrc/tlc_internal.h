@@ -67,6 +67,9 @@ struct tlc_ctx {
     // form of the fused GEMV (tlc_gemv_kernel.cuh).  Off by default: fewer instructions per block,
     // but measured slower on a B200 (35.3 vs 30.5 us on a 132 MB weight, 7.1 vs 5.5 us on 6.5 MB).
     bool gemv_f8 = false;
+    // Option "gemv_splitk" / TLC_GEMV_SPLITK=0: 2..16 activation rows whose fragments crowd the
+    // shared memory take further passes over the weights instead of one pass with K cut into windows.
+    bool gemv_splitk = true;
     // Option "q6k_resident" / TLC_Q6K_RESIDENT=0: Q6_K tensors are expanded to f16 at upload (what
     // the reference's loader keeps) instead of staying quantized in HBM.
     bool q6k_resident = true;
@@ -223,6 +226,8 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a);
 // Scratch the GEMM path needs for m rows of width k with a fused RMSNorm and a
 // SiLU.mul pair of n_swiglu outputs (reserve it before capturing a graph).
 size_t tlc_gemm_scratch_bytes(int m, int64_t k, int64_t n_swiglu);
+// Scratch the fused GEMV may need for m rows (split-K partial sums; 0 when it does not split).
+size_t tlc_gemv_scratch_bytes(tlc_ctx *ctx, int type, int64_t k, int m, int64_t n_total);
 
 struct tlc_kvcache;
 int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const void *q_dev, void *out_dev,

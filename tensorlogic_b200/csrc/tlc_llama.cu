@@ -491,6 +491,17 @@ extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_ll
     {
         const int64_t kmax = d > qd ? d : qd;
         if (int32_t rc = tlc_scratch_reserve(ctx, tlc_gemm_scratch_bytes(L->max_rows, kmax, L->ffn_local))) return rc;
+        // ... and the split-K partial sums of the batched decode GEMVs
+        const int qt0 = L->layers[0].wq->type;
+        size_t need = 0;
+        for (int m = 2; m <= c.max_batch && m <= 16; m++) {
+            const size_t cand[] = {tlc_gemv_scratch_bytes(ctx, qt0, d, m, qd + 2 * kvd), tlc_gemv_scratch_bytes(ctx, qt0, qd, m, d),
+                                   tlc_gemv_scratch_bytes(ctx, qt0, d, m, 2 * (int64_t)L->ffn_local),
+                                   tlc_gemv_scratch_bytes(ctx, qt0, L->ffn_local, m, d),
+                                   tlc_gemv_scratch_bytes(ctx, L->out_w->type, d, m, L->vocab_local)};
+            for (size_t b : cand) need = b > need ? b : need;
+        }
+        if (int32_t rc = tlc_scratch_reserve(ctx, need)) return rc;
     }
     // Same shared-memory carve-out as the GEMV and attention kernels they run between.
     TLC_CUDA(cudaFuncSetAttribute(embed_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,

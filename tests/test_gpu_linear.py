@@ -369,3 +369,47 @@ def test_fp8_limb_form_of_one_row(dev, ref, n, k):
     bad[0, 5] = np.float16(np.inf)
     y8, y16 = both(lambda: linear(dev.tensor(bad), w).numpy())
     assert not np.any(np.isfinite(y8.astype(np.float32))) and not np.any(np.isfinite(y16.astype(np.float32)))
+
+
+@pytest.mark.parametrize("qtype", [Q4, Q8])
+@pytest.mark.parametrize("n,k", [(256, 8192), (100, 28672), (512, 14336)])
+def test_split_k_for_many_rows_of_a_wide_input(dev, ref, qtype, n, k):
+    """2 to 16 activation rows of a wide K do not fit the shared memory in fragment order: the K
+    range is cut into windows (one pass over the weights, f32 partial sums, a finishing kernel with
+    the epilogue) instead of several passes.  Same answers as the oracle and as the multi-pass form
+    (option gemv_splitk = 0), for the plain, the residual, the SiLU.mul and the RoPE epilogues."""
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.api import QTensor, linear, linear_residual, norm_linear_multi, swiglu_gate_up
+    raw = synth.blocks(qtype, 23, synth.tensor_id(f"sk{n}x{k}"), n, k, scale_log2=-3)
+    raw2 = synth.blocks(qtype, 23, synth.tensor_id(f"sk2{n}x{k}"), n, k, scale_log2=-3)
+    w, w2 = QTensor.from_blocks(dev, qtype, n, k, raw), QTensor.from_blocks(dev, qtype, n, k, raw2)
+    nw = synth.norm_weight(23, "sknorm", k)
+    for m in (2, 8, 13, 16):
+        x = synth.activations(23, f"skx{m}", (m, k))
+        want = ref.linear_q(qtype, raw, n, k, x)
+        l0 = dev.launch_count
+        y = linear(dev.tensor(x), w).numpy()
+        launches = dev.launch_count - l0
+        assert rel_l2(y, want) < TIGHT, m
+        dev.set_option("gemv_splitk", 0)
+        try:
+            l0 = dev.launch_count
+            y_passes = linear(dev.tensor(x), w).numpy()
+            passes = dev.launch_count - l0
+        finally:
+            dev.set_option("gemv_splitk", 1)
+        assert rel_l2(y, y_passes) < 5e-4
+        if passes > 1:
+            assert launches == 2, (m, launches, passes)       # one pass over the weights + the finish
+        res = synth.activations(23, f"skr{m}", (m, n))
+        assert rel_l2(linear_residual(dev.tensor(x), w, dev.tensor(res)).numpy(), ref.add(res, want)) < TIGHT
+        xn = ref.rms_norm(x, nw, 1e-5)
+        act = swiglu_gate_up(dev.tensor(x), w, w2, dev.tensor(nw), 1e-5).numpy()
+        want_act = ref.swiglu(ref.linear_q(qtype, raw, n, k, xn), ref.linear_q(qtype, raw2, n, k, xn))
+        assert rel_l2(act, want_act) < 2 * TIGHT
+        if n % 64 == 0:
+            pos = (np.arange(m, dtype=np.int32) * 11) % 500
+            q, v = norm_linear_multi(dev.tensor(x), [w, w2], dev.tensor(nw), 1e-5, rope_heads=[n // 64, 0], positions=pos)
+            want_q = ref.rope(ref.linear_q(qtype, raw, n, k, xn).reshape(m, n // 64, 64), 0, 10000, positions=pos).reshape(m, n)
+            assert rel_l2(q.numpy(), want_q) < 2 * TIGHT
+            assert rel_l2(v.numpy(), ref.linear_q(qtype, raw2, n, k, xn)) < 2 * TIGHT
