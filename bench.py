@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload at N=1 (BASELINE.json configs[2]): TinyLlama-1.1B architecture with
+Workload at N=1: TinyLlama-1.1B architecture with
 seeded random Q4_0 weights (f16 embeddings and norms), batch 1, 512-token
 prompt, then greedy decode with an f16 KV cache.  A "step" is one decode step
 (one token).  Prints ONE JSON line.
@@ -21,8 +21,7 @@ prompt, then greedy decode with an f16 KV cache.  A "step" is one decode step
                path (single thread, f16 running sum), on a bounded sample.
 
 With --gpus N > 1 (launched under torchrun, one process per GPU) the workload is
-BASELINE.json configs[4]: Llama-2-70B-shape Q4_0 decode, tensor-parallel over
-the N GPUs with an NCCL all-reduce after the row-parallel projections (TinyLlama
+Llama-2-70B-shape Q4_0 decode, tensor-parallel over the N GPUs with an NCCL all-reduce after the row-parallel projections (TinyLlama
 has 4 KV heads and cannot be split 8 ways).  The line names that workload and
 says scaling "strong"; it is a different workload from the N=1 line.
 """
@@ -50,9 +49,9 @@ L2_BYTES = 126 * 1000 * 1000
 def workload_name(n_gpus: int, batch: int = 1, big: bool = False) -> str:
     """The `config.workload` string, the same in both arms (`--impl ours` / `--impl reference`)."""
     if n_gpus > 1 or big:
-        return (f"llama-2-70b-shape q4_0 decode, TP{n_gpus}, batch {batch}, 2048-token context (BASELINE configs[4]); "
-                f"NOT the N=1 workload (tinyllama, configs[2])")
-    return "tinyllama-1.1b q4_0 decode, batch 1, 512-token prompt (BASELINE configs[2])"
+        return (f"llama-2-70b-shape q4_0 decode, TP{n_gpus}, batch {batch}, 2048-token context; "
+                f"NOT the N=1 workload (tinyllama)")
+    return "tinyllama-1.1b q4_0 decode, batch 1, 512-token prompt"
 
 
 def profiled_traffic(key: str):
@@ -473,7 +472,7 @@ def time_decode(dev, llm, stream, batch, K, W, barrier, clocks=None):
 
 
 def run_tp(args, rank: int, world: int, local: int) -> None:
-    """Llama-2-70B-shape Q4_0 decode (BASELINE configs[4]), tensor-parallel over the N GPUs of the
+    """Llama-2-70B-shape Q4_0 decode, tensor-parallel over the N GPUs of the
     launch (N = 1 with --workload decode70b: the whole 38.65 GB model on one GPU):
     column-parallel q/k/v/gate/up/lm_head, row-parallel o/down with an all-reduce after each (one
     peer-memory kernel fused with the residual add; NCCL with --nccl-allreduce), 2048 positions
@@ -675,7 +674,7 @@ def run_kernel(args) -> None:
 
 
 def run_prefill(args, rank: int, world: int, local: int) -> None:
-    """--workload prefill: BASELINE configs[3], Llama-2-7B-shape Q4_0 prefill of 2048 tokens.  The
+    """--workload prefill: Llama-2-7B-shape Q4_0 prefill of 2048 tokens.  The
     per-layer linears run as the tcgen05 dequant-GEMM; with N > 1 GPUs (torchrun) the weights are
     sharded column/row-parallel and the o / down partial sums are all-reduced (NCCL: 16 MB vectors).
     A step is one whole prefill; value = prompt tokens per second, roofline = tensor FLOP/s of the
@@ -739,7 +738,7 @@ def run_prefill(args, rank: int, world: int, local: int) -> None:
         "metric": "q4_0_prefill_tokens_per_s", "value": tokens * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "llama-2-7b-shape q4_0 prefill, 2048 tokens, batch 1 (BASELINE configs[3])",
+        "config": {"workload": "llama-2-7b-shape q4_0 prefill, 2048 tokens, batch 1",
                    "parallelism": "single" if world == 1 else f"tp{world}",
                    "l2": "3.6 GB of weights per pass exceed the 126 MB L2", "seed": SEED},
         "e2e": {"value": tokens * K / (wall_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": tokens * 4,

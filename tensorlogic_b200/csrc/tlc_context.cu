@@ -77,12 +77,14 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (const char *e = getenv("TLC_PDL_MODE")) ctx->pdl_mode = atoi(e);
     if (const char *e = getenv("TLC_PDL_SMALL")) ctx->pdl_small = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMM_MIN_M")) ctx->gemm_min_m = atoi(e);
+    if (const char *e = getenv("TLC_GEMM_PAIR")) ctx->gemm_pair = atoi(e) != 0;
+    if (const char *e = getenv("TLC_GEMM_TMA")) ctx->gemm_tma = atoi(e) != 0;
     if (const char *e = getenv("TLC_L2_HINT")) ctx->l2_hint = atoi(e);
     if (const char *e = getenv("TLC_HOST_GRAPH")) ctx->host_graph = atoi(e) != 0;
     if (const char *e = getenv("TLC_HOST_POLL")) ctx->host_poll = atoi(e) != 0;
     if (const char *e = getenv("TLC_STEP_KERNEL")) ctx->step_kernel = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMV_F8")) ctx->gemv_f8 = atoi(e) != 0;
-    if (const char *e = getenv("TLC_GEMV_SPLITK")) ctx->gemv_splitk = atoi(e) != 0;
+    if (const char *e = getenv("TLC_GEMV_SPLITK")) ctx->gemv_splitk = atoi(e);
     if (const char *e = getenv("TLC_Q6K_RESIDENT")) ctx->q6k_resident = atoi(e) != 0;
     *out = ctx;
     return TLC_OK;
@@ -100,7 +102,11 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         TLC_REQUIRE(value == 0 || value == 11 || value == 12 || value == 22, TLC_ERR_INVALID_OPERATION,
                     "set_option: gemm_tile must be 0, 11, 12 or 22");
         ctx->gemm_tile = (int)value;
-    } else if (n == "pdl")
+    } else if (n == "gemm_pair")
+        ctx->gemm_pair = value != 0;
+    else if (n == "gemm_tma")
+        ctx->gemm_tma = value != 0;
+    else if (n == "pdl")
         ctx->use_pdl = value != 0;
     else if (n == "pdl_mode")
         ctx->pdl_mode = (int)value;
@@ -115,7 +121,7 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
     else if (n == "gemv_f8")
         ctx->gemv_f8 = value != 0;
     else if (n == "gemv_splitk")
-        ctx->gemv_splitk = value != 0;
+        ctx->gemv_splitk = (int)value;
     else if (n == "q6k_resident")
         ctx->q6k_resident = value != 0;
     else

@@ -33,6 +33,7 @@
 // CTA drain, free its tensor memory and return.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "tlc_internal.h"
@@ -61,6 +62,7 @@ struct GemmParams {
     int max_pos;  // > 0: rows addressed by position are dropped from this position on (status TLC_DEV_INDEX)
     float rope_base;
     int vec_ok;  // strides, N and pointers allow 16-byte stores
+    int a_tma;   // the activation tile arrives by TMA (tensor map in the second kernel argument)
     tlc_dev_status *status;
     uint64_t wait_ns;  // how long a wait may last before the kernel gives up
 };
@@ -77,6 +79,18 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One box of a 2-D tensor map into shared memory; its bytes count on `bar`.  x is the inner
+// (contiguous) coordinate and must be a multiple of 16 bytes' worth of elements.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
@@ -167,5 +181,119 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w0, uint32_t w1, __half2 bias
     h[3] = __hmul2(__hsub2(bytes_to_half2(w1, 0x4342), bias), d2);
     return *reinterpret_cast<const uint4 *>(h);
 }
+
+// Dequantizes one block of a weight row -- `q`: its quant words (4 for Q4_0, 8
+// for Q8_0), `d`: its scale -- into four 16-byte pieces of the swizzled tile at
+// `bt` (`piece`: the byte offsets of the row's pieces, `e`: which half of the K step).
+template <int QT>
+__device__ __forceinline__ void dequant_block(const uint32_t *q, __half d, uint8_t *bt, const uint32_t (&piece)[8],
+                                              int e) {
+    const __half2 d2 = __half2half2(d);
+    uint4 c[4];
+    if (QT == TLC_TYPE_Q4_0) {
+        const __half2 bias = __float2half2_rn(1032.f);  // 1024 (magic) + 8
+        c[0] = dequant8(q[0] & 0x0F0F0F0Fu, q[1] & 0x0F0F0F0Fu, bias, d2);                // elems 0..7
+        c[1] = dequant8(q[2] & 0x0F0F0F0Fu, q[3] & 0x0F0F0F0Fu, bias, d2);                // 8..15
+        c[2] = dequant8((q[0] >> 4) & 0x0F0F0F0Fu, (q[1] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 16..23
+        c[3] = dequant8((q[2] >> 4) & 0x0F0F0F0Fu, (q[3] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 24..31
+    } else {
+        const __half2 bias = __float2half2_rn(1152.f);  // 1024 (magic) + 128 (sign flip)
+#pragma unroll
+        for (int j = 0; j < 4; j++) c[j] = dequant8(q[2 * j] ^ 0x80808080u, q[2 * j + 1] ^ 0x80808080u, bias, d2);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4 *>(bt + piece[4 * e + j]) = c[j];
+}
+
+// One 32-column piece of the epilogue for one activation row: f16 rounding of
+// the accumulators `r`, then RoPE / bias / residual as the launch asks, store.
+__device__ __forceinline__ void epilogue_piece(const GemmParams &p, const uint32_t (&r)[32], int row, int pos, int nb,
+                                               __half *ybase) {
+    __align__(16) __half h[32];
+#pragma unroll
+    for (int e = 0; e < 32; e++) h[e] = __float2half_rn(__uint_as_float(r[e]));
+    if (p.head_dim > 0) {
+        // Interleaved RoPE on the f16-rounded projection (rope_f16,
+        // shaders/unified.metal:2355-2417); a pair never straddles this
+        // thread's 32 columns because heads start at even columns.
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+            const int pair = ((nb + e) % p.head_dim) >> 1;
+            const float exponent = (float)(2 * pair) / (float)p.head_dim;
+            const float freq = 1.0f / powf(p.rope_base, exponent);
+            const float theta = (float)(unsigned)pos * freq;
+            const float cs = cosf(theta), sn = sinf(theta);
+            const float x0 = __half2float(h[e]), x1 = __half2float(h[e + 1]);
+            h[e] = __float2half_rn(__fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn)));
+            h[e + 1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs)));
+        }
+    }
+    const bool whole = nb + 32 <= p.n;
+    const bool vec_ok = p.vec_ok != 0;
+    if (p.bias) {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            if (whole || nb + e < p.n) h[e] = __hadd(h[e], p.bias[nb + e]);
+    }
+    if (p.residual) {
+        const __half *rrow = p.residual + (size_t)row * p.n + nb;
+        if (whole && vec_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                const uint4 rv = *reinterpret_cast<const uint4 *>(rrow + 8 * v);
+                const __half *rh = reinterpret_cast<const __half *>(&rv);
+#pragma unroll
+                for (int e = 0; e < 8; e++) h[8 * v + e] = __hadd(h[8 * v + e], rh[e]);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 32; e++)
+                if (nb + e < p.n) h[e] = __hadd(h[e], rrow[e]);
+        }
+    }
+    if (whole && vec_ok) {
+#pragma unroll
+        for (int v = 0; v < 4; v++)
+            *reinterpret_cast<uint4 *>(ybase + nb + 8 * v) = *reinterpret_cast<const uint4 *>(h + 8 * v);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            if (nb + e < p.n) ybase[nb + e] = h[e];
+    }
+}
+
+// The SiLU.mul epilogue of one 32-column piece: `r` the gate accumulators, `ru` the up
+// accumulators.  s = sigmoid(g) (f32, RNE); a = g*s; act = a*u: three f16 roundings as in
+// debug/chat_demo_with_kvcache.tl:26-41 (the GEMV's SiLU.mul epilogue does the same).
+__device__ __forceinline__ void epilogue_piece_swiglu(const GemmParams &p, const uint32_t (&r)[32],
+                                                      const uint32_t (&ru)[32], int nb, __half *ybase) {
+    __align__(16) __half h[32];
+#pragma unroll
+    for (int e = 0; e < 32; e++) {
+        const __half gate = __float2half_rn(__uint_as_float(r[e]));
+        const __half up = __float2half_rn(__uint_as_float(ru[e]));
+        const __half sg = __float2half_rn(1.0f / (1.0f + expf(-__half2float(gate))));
+        h[e] = __hmul(__hmul(gate, sg), up);
+    }
+    if (nb + 32 <= p.n && p.vec_ok) {
+#pragma unroll
+        for (int v = 0; v < 4; v++)
+            *reinterpret_cast<uint4 *>(ybase + nb + 8 * v) = *reinterpret_cast<const uint4 *>(h + 8 * v);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            if (nb + e < p.n) ybase[nb + e] = h[e];
+    }
+}
+
+// Tensor map of activations for the TMA-fed A tile (defined in tlc_gemm_sm100.cu).
+bool encode_x_map(CUtensorMap *map, const GemmParams &p);
+
+// The CTA-pair form of the GEMM (tlc_gemm_pair.cu): persistent clusters of two CTAs, one
+// tcgen05.mma.cta_group::2 tile of 256 activation rows x 256 weight rows per cluster.
+// `sw`: the SiLU.mul pair (w = gate, w2 = up).  TLC_ERR_INVALID_OPERATION when the shape
+// cannot take this form; the caller then uses the single-CTA kernel.
+bool cta_pair_eligible(const tlc_ctx *ctx, const GemmParams &p);
+int32_t launch_cta_pair(tlc_ctx *ctx, const GemmParams &p, int type, bool sw);
 
 }  // namespace tlc_gemm

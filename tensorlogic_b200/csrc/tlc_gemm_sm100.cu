@@ -1,34 +1,37 @@
 // Kernel body and launcher of the tcgen05 dequant-GEMM (see tlc_gemm_kernel.cuh).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
 #include <type_traits>
 
 #include "tlc_gemm_kernel.cuh"
 
 using namespace tlc_gemm;
 
-namespace {
-
-// Dequantizes one block of a weight row -- `q`: its quant words (4 for Q4_0, 8
-// for Q8_0), `d`: its scale -- into four 16-byte pieces of the swizzled tile at
-// `bt` (`piece`: the byte offsets of the row's pieces, `e`: which half of the K step).
-template <int QT>
-__device__ __forceinline__ void dequant_block(const uint32_t *q, __half d, uint8_t *bt, const uint32_t (&piece)[8],
-                                              int e) {
-    const __half2 d2 = __half2half2(d);
-    uint4 c[4];
-    if (QT == TLC_TYPE_Q4_0) {
-        const __half2 bias = __float2half2_rn(1032.f);  // 1024 (magic) + 8
-        c[0] = dequant8(q[0] & 0x0F0F0F0Fu, q[1] & 0x0F0F0F0Fu, bias, d2);                // elems 0..7
-        c[1] = dequant8(q[2] & 0x0F0F0F0Fu, q[3] & 0x0F0F0F0Fu, bias, d2);                // 8..15
-        c[2] = dequant8((q[0] >> 4) & 0x0F0F0F0Fu, (q[1] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 16..23
-        c[3] = dequant8((q[2] >> 4) & 0x0F0F0F0Fu, (q[3] >> 4) & 0x0F0F0F0Fu, bias, d2);  // 24..31
-    } else {
-        const __half2 bias = __float2half2_rn(1152.f);  // 1024 (magic) + 128 (sign flip)
-#pragma unroll
-        for (int j = 0; j < 4; j++) c[j] = dequant8(q[2 * j] ^ 0x80808080u, q[2 * j + 1] ^ 0x80808080u, bias, d2);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4 *>(bt + piece[4 * e + j]) = c[j];
+// Tensor map of the activations [M, K] (f16, rows K elements apart): boxes of 128 rows
+// x 64 columns, 128-byte swizzle, zero fill outside.  False when the driver entry point
+// is missing or refuses the shape; the cp.async loaders take over then.
+bool tlc_gemm::encode_x_map(CUtensorMap *map, const GemmParams &p) {
+    static PFN_cuTensorMapEncodeTiled_v12000 encode = [] {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        cudaGetLastError();
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }();
+    if (!encode || ((uintptr_t)p.x & 15) != 0 || (p.k & 7) != 0) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.k, (cuuint64_t)p.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(p.x), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+namespace {
 
 // B producer of one weight row.  The row's share of a weight tile (64 bytes of
 // quants: four 16-byte pieces, plus its block scales) covers two K steps for
@@ -122,68 +125,12 @@ __device__ __forceinline__ void produce_b(const GemmParams &p, uint8_t *btiles, 
     }
 }
 
-// One 32-column piece of the epilogue for one activation row: f16 rounding of
-// the accumulators `r`, then RoPE / bias / residual as the launch asks, store.
-__device__ __forceinline__ void epilogue_piece(const GemmParams &p, const uint32_t (&r)[32], int row, int pos, int nb,
-                                               __half *ybase) {
-    __align__(16) __half h[32];
-#pragma unroll
-    for (int e = 0; e < 32; e++) h[e] = __float2half_rn(__uint_as_float(r[e]));
-    if (p.head_dim > 0) {
-        // Interleaved RoPE on the f16-rounded projection (rope_f16,
-        // shaders/unified.metal:2355-2417); a pair never straddles this
-        // thread's 32 columns because heads start at even columns.
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-            const int pair = ((nb + e) % p.head_dim) >> 1;
-            const float exponent = (float)(2 * pair) / (float)p.head_dim;
-            const float freq = 1.0f / powf(p.rope_base, exponent);
-            const float theta = (float)(unsigned)pos * freq;
-            const float cs = cosf(theta), sn = sinf(theta);
-            const float x0 = __half2float(h[e]), x1 = __half2float(h[e + 1]);
-            h[e] = __float2half_rn(__fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn)));
-            h[e + 1] = __float2half_rn(__fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs)));
-        }
-    }
-    const bool whole = nb + 32 <= p.n;
-    const bool vec_ok = p.vec_ok != 0;
-    if (p.bias) {
-#pragma unroll
-        for (int e = 0; e < 32; e++)
-            if (whole || nb + e < p.n) h[e] = __hadd(h[e], p.bias[nb + e]);
-    }
-    if (p.residual) {
-        const __half *rrow = p.residual + (size_t)row * p.n + nb;
-        if (whole && vec_ok) {
-#pragma unroll
-            for (int v = 0; v < 4; v++) {
-                const uint4 rv = *reinterpret_cast<const uint4 *>(rrow + 8 * v);
-                const __half *rh = reinterpret_cast<const __half *>(&rv);
-#pragma unroll
-                for (int e = 0; e < 8; e++) h[8 * v + e] = __hadd(h[8 * v + e], rh[e]);
-            }
-        } else {
-#pragma unroll
-            for (int e = 0; e < 32; e++)
-                if (nb + e < p.n) h[e] = __hadd(h[e], rrow[e]);
-        }
-    }
-    if (whole && vec_ok) {
-#pragma unroll
-        for (int v = 0; v < 4; v++)
-            *reinterpret_cast<uint4 *>(ybase + nb + 8 * v) = *reinterpret_cast<const uint4 *>(h + 8 * v);
-    } else {
-#pragma unroll
-        for (int e = 0; e < 32; e++)
-            if (nb + e < p.n) ybase[nb + e] = h[e];
-    }
-}
-
 // SW: the SiLU.mul pair.  The weight tile holds 128 rows of the gate weight (tile rows
 // 0-127) and the same 128 rows of the up weight (tile rows 128-255); the epilogue reads
 // both accumulators and stores silu(gate) * up for the 128 output columns of the CTA.
 template <int QT, int MT, int NT, bool SW>
-__global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
     static_assert(!SW || NT == 2, "the gate/up pair fills a 256-row weight tile");
     constexpr int BN = 128 * NT;
     constexpr int A_BYTES = 128 * MT * 128, B_BYTES = BN * 128;
@@ -207,7 +154,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
-            mbar_init(&full[s], 4 + 4 * NT);  // A-loader warps + working B-producer warps
+            // the activation tile arrives by TMA (one arrive.expect_tx) or from the four
+            // cp.async loader warps; the working B-producer warps arrive once each
+            mbar_init(&full[s], (p.a_tma ? 1 : 4) + 4 * NT);
             mbar_init(&empty[s], 1);          // tcgen05.commit
         }
         mbar_init(accum_bar, 1);
@@ -231,8 +180,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
         const uint8_t *wbase = SW && trow >= 128 ? p.w2 : p.w;
         const int wrow = SW ? n0 + (trow & 127) : n0 + trow;
         produce_b<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, wbase, wrow, trow, KT, lane);
+    } else if (warp < 4 && p.a_tma) {
+        // ------------------------------ A tile by TMA ------------------------------
+        // One thread issues, per K step, MT boxes of 128 rows x 64 columns with the 128-byte
+        // swizzle of the tile; rows past M and columns past K read the zero fill.  The
+        // inner coordinate is a multiple of 64 elements (128 bytes).
+        if (tid == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&x_map)) : "memory");
+            for (int j = 0; j < KT; j++) {
+                const int s = j % kStages;
+                if (!mbar_wait(&empty[s], ((j / kStages) & 1u) ^ 1u, abort_flag, p.status, 12, p.wait_ns)) break;
+                const uint32_t bar = smem_u32(&full[s]);
+                const uint32_t abase = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                mbar_arrive_expect_tx(&full[s], A_BYTES);
+#pragma unroll
+                for (int i = 0; i < MT; i++)
+                    tma_load_2d(abase + i * (128 * 128), &x_map, j * kBK, m0 + 128 * i, bar);
+            }
+        }
+        __syncwarp();  // the other lanes of warp 0 sleep here instead of polling beside the issuer
     } else if (warp < 4) {
-        // ------------------------------ A loaders ------------------------------
+        // ------------------------------ A loaders (cp.async) ------------------------------
         auto issue = [&](int j) {
             const int s = j % kStages;
             mbar_wait(&empty[s], ((j / kStages) & 1u) ^ 1u, abort_flag, p.status, 12, p.wait_ns);
@@ -317,26 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const GemmPar
                 // debug/chat_demo_with_kvcache.tl:26-41 (the GEMV's SiLU.mul epilogue does the same)
                 uint32_t ru[32];
                 tmem_ld32(tmem_base + ((uint32_t)(32 * wq) << 16) + (uint32_t)(BN * i + 128 + c0), ru);
-                if (row_ok && n0 + c0 < p.n) {
-                    __align__(16) __half h[32];
-#pragma unroll
-                    for (int e = 0; e < 32; e++) {
-                        const __half gate = __float2half_rn(__uint_as_float(r[e]));
-                        const __half up = __float2half_rn(__uint_as_float(ru[e]));
-                        const __half sg = __float2half_rn(1.0f / (1.0f + expf(-__half2float(gate))));
-                        h[e] = __hmul(__hmul(gate, sg), up);
-                    }
-                    const int nb = n0 + c0;
-                    if (nb + 32 <= p.n && p.vec_ok) {
-#pragma unroll
-                        for (int v = 0; v < 4; v++)
-                            *reinterpret_cast<uint4 *>(ybase + nb + 8 * v) = *reinterpret_cast<const uint4 *>(h + 8 * v);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 32; e++)
-                            if (nb + e < p.n) ybase[nb + e] = h[e];
-                    }
-                }
+                if (row_ok && n0 + c0 < p.n) epilogue_piece_swiglu(p, r, ru, n0 + c0, ybase);
             } else if (row_ok && n0 + c0 < p.n) {
                 epilogue_piece(p, r, row, pos, n0 + c0, ybase);
             }
@@ -364,7 +313,11 @@ int32_t launch_tile(tlc_ctx *ctx, const GemmParams &p) {
     }
     const int out_cols = SW ? 128 : 128 * NT;  // output columns per CTA
     const dim3 grid((unsigned)((p.n + out_cols - 1) / out_cols), (unsigned)((p.m + 128 * MT - 1) / (128 * MT)));
-    cudaError_t le = tlc_launch_pdl(ctx, gemm_tcgen05_kernel<QT, MT, NT, SW>, grid, dim3(kThreads), smem, p);
+    GemmParams q = p;
+    CUtensorMap x_map;
+    memset(&x_map, 0, sizeof x_map);
+    q.a_tma = ctx->gemm_tma && encode_x_map(&x_map, p) ? 1 : 0;
+    cudaError_t le = tlc_launch_pdl(ctx, gemm_tcgen05_kernel<QT, MT, NT, SW>, grid, dim3(kThreads), smem, q, x_map);
     if (le != cudaSuccess) {
         cudaGetLastError();
         return tlc_fail(TLC_ERR_CUDA, "gemm launch failed: %s", cudaGetErrorString(le));
@@ -409,6 +362,8 @@ int32_t launch_pair_t(tlc_ctx *ctx, const GemmParams &p) {
 }
 
 int32_t launch_one(tlc_ctx *ctx, const GemmParams &p, int type) {
+    // From 129 activation rows on, two SMs share a 256 x 256 tile (tlc_gemm_pair.cu).
+    if (cta_pair_eligible(ctx, p)) return launch_cta_pair(ctx, p, type, p.w2 != nullptr);
     if (p.w2) return type == TLC_TYPE_Q4_0 ? launch_pair_t<TLC_TYPE_Q4_0>(ctx, p) : launch_pair_t<TLC_TYPE_Q8_0>(ctx, p);
     return type == TLC_TYPE_Q4_0 ? launch_one_t<TLC_TYPE_Q4_0>(ctx, p) : launch_one_t<TLC_TYPE_Q8_0>(ctx, p);
 }

@@ -417,18 +417,33 @@ static int gemv_max_m(tlc_ctx *ctx, int type, int k) {
 // K = 28672 eight times an SM's.  Instead of passing over the weights once per group of rows that
 // fits, the K range is cut into windows: every CTA keeps only its window of the rows, the windows'
 // f32 partial sums meet in gemv_splitk_finish_kernel.  The weights are read once.
-// Returns the number of windows (1: no split) for m rows; the window must hold at least one ring
-// stage of tiles and leave room for two CTAs per SM.
-static int gemv_choose_ksplit(tlc_ctx *ctx, int type, int64_t ktiles, int m, int n_sub) {
+// Returns the number of windows (1: no split) for m rows, of which max_m fit in one unsplit launch.
+//  - A launch that runs two CTAs per SM without a split is left alone.
+//  - More than four rows that fit one launch at one CTA per SM stay unsplit (sixteen consumer
+//    warps; 8 rows of K = 8192: 44 us against 50 us split).
+//  - Otherwise the windows are sized for two CTAs per SM, or (option gemv_splitk = 2: first
+//    choice) for one CTA per SM with sixteen consumer warps; a window holds at least eight tiles.
+static int gemv_choose_ksplit(tlc_ctx *ctx, int type, int64_t ktiles, int m, int n_sub, int max_m, int mode) {
     const int tb = tlc_tile::tile_blocks(type);
     const size_t stage = (size_t)kTilesPerStage * tlc_tile::tile_bytes(type);
     const size_t half = (size_t)ctx->prop.sharedMemPerMultiprocessor / 2 - 1024;
+    const size_t budget = (size_t)ctx->prop.sharedMemPerBlockOptin;
     const int nt = m > 8 ? 2 : 1;
-    static const int cand[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32};
-    for (int ks : cand) {
-        const int64_t win = (ktiles + ks - 1) / ks;
-        if (ks > 1 && win < kTilesPerStage) break;
-        if (fixed_smem_bytes((int)win * tb, m, nt, n_sub) + 3 * stage <= half) return ks;
+    auto fits = [&](int64_t win, bool two) {
+        return fixed_smem_bytes((int)win * tb, m, nt, n_sub, two ? 8 : 16) + 3 * stage <= (two ? half : budget);
+    };
+    if (fits(ktiles, true)) return 1;
+    const bool multi_pass = m > max_m;
+    if (!multi_pass && m > 4) return 1;
+    static const int cand[] = {2, 3, 4, 6, 8, 12, 16, 24, 32};
+    for (int round = 0; round < 2; round++) {
+        const bool two = (round == 0) != (mode == 2);
+        if (!two && !multi_pass) continue;  // one CTA per SM is what the unsplit launch already does
+        for (int ks : cand) {
+            const int64_t win = (ktiles + ks - 1) / ks;
+            if (win < 8) break;
+            if (fits(win, two)) return ks;
+        }
     }
     return 1;
 }
@@ -437,7 +452,13 @@ static int gemv_choose_ksplit(tlc_ctx *ctx, int type, int64_t ktiles, int m, int
 // (the split-K partial sums); callers that capture graphs reserve it up front.
 size_t tlc_gemv_scratch_bytes(tlc_ctx *ctx, int type, int64_t k, int m, int64_t n_total) {
     if ((type != TLC_TYPE_Q4_0 && type != TLC_TYPE_Q8_0) || m < 2 || m > 16) return 0;
-    const int ks = gemv_choose_ksplit(ctx, type, tlc_tile::k_tiles(type, k), m, 2);
+    const int max_m = gemv_max_m(ctx, type, (int)k);
+    int ks = 1;
+    for (int mode = 1; mode <= 2; mode++)  // whatever the option says at launch time
+        for (int n_sub = 1; n_sub <= 2; n_sub++) {
+            const int c = gemv_choose_ksplit(ctx, type, tlc_tile::k_tiles(type, k), m, n_sub, max_m, mode);
+            ks = c > ks ? c : ks;
+        }
     return ks > 1 ? (size_t)ks * m * (size_t)n_total * sizeof(float) : 0;
 }
 
@@ -559,7 +580,8 @@ int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {
     // Up to 16 rows whose fragments do not leave two CTAs per SM room: one pass with K cut into windows.
     int ksplit = 1;
     if (a.m >= 2 && a.m <= 16 && ctx->gemv_splitk) {
-        ksplit = gemv_choose_ksplit(ctx, type, w0->k_tiles, a.m, a.epilogue == TLC_EPI_SWIGLU ? 2 : 1);
+        ksplit = gemv_choose_ksplit(ctx, type, w0->k_tiles, a.m, a.epilogue == TLC_EPI_SWIGLU ? 2 : 1, max_m,
+                                    ctx->gemv_splitk);
         if (ksplit > 1) max_m = a.m;
     }
     // Otherwise activation rows beyond what one launch can hold are processed in

@@ -62,6 +62,8 @@ struct tlc_ctx {
     // How long a device-side wait (mbarrier, peer flag) may last before the kernel gives up,
     // sets the status word and drains; option "wait_limit_ms".
     uint64_t wait_ns = 2000000000ull;
+    bool gemm_pair = true;  // GEMM tiles of 256 x 256 on CTA pairs (tcgen05 cta_group::2) from 129 rows on
+    bool gemm_tma = true;  // activation tiles of the GEMM by TMA (false: cp.async loader warps)
     int gemm_tile = 0;  // 0: pick the GEMM tile from the shape; 11, 12, 22: force 128x128, 128x256, 256x256
     // Option "gemv_f8" / TLC_GEMV_F8=1: one activation row against a Q4_0 weight takes the FP8-limb
     // form of the fused GEMV (tlc_gemv_kernel.cuh).  Off by default: fewer instructions per block,
@@ -69,7 +71,7 @@ struct tlc_ctx {
     bool gemv_f8 = false;
     // Option "gemv_splitk" / TLC_GEMV_SPLITK=0: 2..16 activation rows whose fragments crowd the
     // shared memory take further passes over the weights instead of one pass with K cut into windows.
-    bool gemv_splitk = true;
+    int gemv_splitk = 1;  // 0: off; 1: windows sized for two CTAs per SM first; 2: for one CTA per SM first
     // Option "q6k_resident" / TLC_Q6K_RESIDENT=0: Q6_K tensors are expanded to f16 at upload (what
     // the reference's loader keeps) instead of staying quantized in HBM.
     bool q6k_resident = true;

@@ -313,7 +313,7 @@ class Llama:
 
     def fill_cache_random(self, seed: int, std: float = 1.0) -> None:
         """Fill the whole KV cache with f16 N(0, std) on the device: stands in for a context that is
-        'already in the cache' (BASELINE config 4) without running a 2048-token prefill."""
+        'already in the cache' (the 70B-shape decode workload) without running a 2048-token prefill."""
         cache = self.dev.lib.tlc_llama_cache(self.handle)
         kv_local = self.arch.n_kv_heads // max(self._tp_size, 1)
         n = self.max_batch * self._max_seq * kv_local * self.arch.head_dim

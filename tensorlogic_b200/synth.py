@@ -4,7 +4,7 @@ The Q4_0 / Q8_0 byte streams restate csrc/tlc_synth.cuh so that weights
 generated on the host and on the device are identical; activations, norm
 weights and embeddings are only ever generated here.
 
-Distributions (those BASELINE.json's configs name):
+Distributions:
   Q4_0 block: d = f16(U[0.002, 0.02]), 16 bytes of packed nibbles ~ U{0..15}
   Q8_0 block: same d, 32 int8 ~ U{-127..127}
   activations: f16(N(0,1)); norm weights f16(1 + N(0, 0.02));

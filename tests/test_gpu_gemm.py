@@ -114,6 +114,34 @@ def test_every_tile_shape(dev, ref, qtype, tile, n, k, m):
     assert np.array_equal(_bits(yt), _bits(ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]))
 
 
+@pytest.mark.parametrize("qtype", [Q4, Q8])
+@pytest.mark.parametrize("n,k,m", [(300, 640, 300), (512, 1088, 130), (40, 4096, 257), (1000, 64, 129),
+                                   (2100, 96, 2500), (256, 8192, 256)])
+def test_cta_pair_tiles(dev, ref, qtype, n, k, m):
+    """The CTA-pair kernel (two SMs per 256 x 256 tile, persistent): ragged shapes, a walk of
+    several tiles per cluster (2100 x 2500: 90 tiles), both accumulators, ring wrap-around; and
+    the same shapes with the pair form switched off give the single-CTA kernel's result."""
+    from tensorlogic_b200.api import QTensor, linear
+    raw = _weights(qtype, n, k, seed=19, name=f"p{n}x{k}")
+    x = _x(m, k, seed=19, name=f"px{m}x{k}")
+    w = QTensor.from_blocks(dev, qtype, n, k, raw)
+    want = ref.linear_q(qtype, raw, n, k, x)
+    eye = np.eye(k, dtype=np.float16)[:m] if m <= k else None
+    with gemm_from(dev, 1):
+        y = linear(dev.tensor(x), w).numpy()
+        yt = linear(dev.tensor(eye), w).numpy() if eye is not None else None
+        dev.set_option("gemm_pair", 0)
+        try:
+            y1 = linear(dev.tensor(x), w).numpy()
+        finally:
+            dev.set_option("gemm_pair", 1)
+    assert rel_l2(y, want) < TIGHT
+    assert rel_l2(y1, want) < TIGHT
+    assert rel_l2(y, y1) < 1e-4
+    if yt is not None:
+        assert np.array_equal(_bits(yt), _bits(ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]))
+
+
 def test_automatic_tile_choice_large(dev, ref):
     """Shapes large enough that the launcher picks the wide tiles by itself."""
     from tensorlogic_b200.api import QTensor, linear
@@ -160,9 +188,19 @@ def test_default_dispatch(dev, ref):
 @pytest.mark.parametrize("qtype", [Q4, Q8])
 def test_fused_contract_on_gemm(dev, ref, qtype):
     """RMSNorm prologue, RoPE / residual / bias / SiLU.mul epilogues give what the GEMV path gives."""
+    _fused_contract(dev, qtype, 45)
+
+
+@pytest.mark.parametrize("qtype", [Q4, Q8])
+def test_fused_contract_on_cta_pairs(dev, ref, qtype):
+    """The same contract from 129 rows on, where the CTA-pair kernel runs."""
+    _fused_contract(dev, qtype, 300)
+
+
+def _fused_contract(dev, qtype, m):
     from tensorlogic_b200 import synth
     from tensorlogic_b200.api import QTensor, linear, linear_residual, norm_linear_multi, swiglu_gate_up
-    d, heads, kvh, hd, ffn, m = 256, 4, 2, 64, 384, 45
+    d, heads, kvh, hd, ffn = 256, 4, 2, 64, 384
     wq = QTensor.from_blocks(dev, qtype, heads * hd, d, _weights(qtype, heads * hd, d, 16, "q"))
     wk = QTensor.from_blocks(dev, qtype, kvh * hd, d, _weights(qtype, kvh * hd, d, 16, "k"))
     wv = QTensor.from_blocks(dev, qtype, kvh * hd, d, _weights(qtype, kvh * hd, d, 16, "v"))

@@ -2,7 +2,7 @@
 
 Dequantization must be bit-exact with the oracle; linear outputs must be
 within rel-L2 1e-2 of the oracle's dequant + f32-accumulate linear (the
-tolerance BASELINE.json's north_star states).  In practice they are ~1e-4.
+tolerance stated for this path).  In practice they are ~1e-4.
 """
 import numpy as np
 import pytest
@@ -387,6 +387,14 @@ def test_split_k_for_many_rows_of_a_wide_input(dev, ref, qtype, n, k):
     for m in (2, 8, 13, 16):
         x = synth.activations(23, f"skx{m}", (m, k))
         want = ref.linear_q(qtype, raw, n, k, x)
+        dev.set_option("gemv_splitk", 2)                      # windows sized for one CTA per SM first
+        try:
+            l0 = dev.launch_count
+            y = linear(dev.tensor(x), w).numpy()
+            launches2 = dev.launch_count - l0
+        finally:
+            dev.set_option("gemv_splitk", 1)
+        assert rel_l2(y, want) < TIGHT, m
         l0 = dev.launch_count
         y = linear(dev.tensor(x), w).numpy()
         launches = dev.launch_count - l0
@@ -400,7 +408,7 @@ def test_split_k_for_many_rows_of_a_wide_input(dev, ref, qtype, n, k):
             dev.set_option("gemv_splitk", 1)
         assert rel_l2(y, y_passes) < 5e-4
         if passes > 1:
-            assert launches == 2, (m, launches, passes)       # one pass over the weights + the finish
+            assert launches == 2 and launches2 == 2, (m, launches, launches2, passes)  # one pass + the finish
         res = synth.activations(23, f"skr{m}", (m, n))
         assert rel_l2(linear_residual(dev.tensor(x), w, dev.tensor(res)).numpy(), ref.add(res, want)) < TIGHT
         xn = ref.rms_norm(x, nw, 1e-5)
