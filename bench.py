@@ -673,6 +673,65 @@ def run_kernel(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_allreduce(args, rank: int, world: int, local: int) -> None:
+    """--kernel allreduce under torchrun: the exchange step of the tensor-parallel decode on its
+    own.  K x 100 back-to-back all-reduce + residual calls over --n f16 values (default 8192, the
+    70B model's width) on every rank, CUDA events, max over ranks; the peer-memory kernel and the
+    NCCL + add form side by side.  Says what one all-reduce costs when nothing else runs, i.e. how
+    much of a tensor-parallel step is the exchange itself and how much is waiting for the slowest rank."""
+    import torch
+    import torch.distributed as dist
+    from tensorlogic_b200.api import Device
+    from tensorlogic_b200.comm import Comm, unique_id
+    dev = Device(local)
+    box = [unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0, device=torch.device("cuda", local))
+    comm = Comm(dev, box[0], rank, world)
+    n = args.n if args.n != 28672 else 8192
+    rng = np.random.default_rng(rank)
+    part = dev.tensor(rng.standard_normal(n).astype(np.float16))
+    res = dev.tensor(np.zeros(n, np.float16))
+    out = dev.empty((n,))
+    stream = torch.cuda.ExternalStream(dev.stream, device=torch.device("cuda", local))
+    lib = dev.lib
+
+    def burst(count):
+        for _ in range(count):
+            rc = lib.tlc_allreduce_residual_f16(dev.handle, comm.handle, part.ptr, res.ptr, out.ptr, n)
+            if rc:
+                raise RuntimeError(lib.tlc_last_error().decode())
+
+    def timed():
+        burst(100 * max(args.warmup, 3))
+        dev.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            burst(100 * args.steps)
+            e1.record(stream)
+        dev.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (100 * args.steps)], device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    us_nccl = timed()
+
+    def gather(blob):
+        o = [None] * world
+        dist.all_gather_object(o, blob)
+        return o
+    comm.enable_p2p(max(n, 16 * 8192), gather)
+    us_p2p = timed()
+    if rank == 0:
+        print(json.dumps({"kernel": "allreduce_residual", "n": n, "n_gpus": world, "calls": 100 * args.steps,
+                          "us_per_call_peer_memory_kernel": us_p2p, "us_per_call_nccl_plus_add": us_nccl,
+                          "note": "back-to-back calls from the host, nothing else on the stream; max over ranks"}),
+              flush=True)
+    dev.synchronize()
+    comm.close()
+
+
 def run_prefill(args, rank: int, world: int, local: int) -> None:
     """--workload prefill: Llama-2-7B-shape Q4_0 prefill of 2048 tokens.  The
     per-layer linears run as the tcgen05 dequant-GEMM; with N > 1 GPUs (torchrun) the weights are
@@ -759,7 +818,7 @@ def main() -> None:
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b"],
                     help="decode: the headline workload (default); prefill: Llama-2-7B-shape 2048-token prefill; "
                          "decode70b: the Llama-2-70B-shape decode of the N > 1 runs on ONE GPU (the TP1 point)")
-    ap.add_argument("--kernel", default=None, choices=["linear"],
+    ap.add_argument("--kernel", default=None, choices=["linear", "allreduce"],
                     help="micro-benchmark one kernel instead of the decode workload (see run_kernel)")
     ap.add_argument("--qtype", default="q4_0", choices=["q4_0", "q8_0"])
     ap.add_argument("--n", type=int, default=28672)
@@ -781,13 +840,17 @@ def main() -> None:
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
-    if args.kernel:
+    if args.kernel == "linear":
         run_kernel(args)
         return
     if world > 1:
         dist_setup(args.gpus)
     try:
-        if args.workload == "prefill":
+        if args.kernel == "allreduce":
+            if world < 2:
+                raise SystemExit("--kernel allreduce needs torchrun with at least two ranks")
+            run_allreduce(args, rank, world, local)
+        elif args.workload == "prefill":
             run_prefill(args, rank, world, local)
         elif world > 1 or args.workload == "decode70b":
             run_tp(args, rank, world, local)

@@ -101,6 +101,21 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *                 instead of synchronizing the stream (0).
  *   "step_kernel" single-sequence greedy decode steps run as ONE persistent kernel (1)
  *                 or kernel by kernel, five launches per layer (0, default: faster on a B200).
+ *   "gemm_tma"    the GEMM's activation tiles arrive by TMA (1, default) or through cp.async
+ *                 loader warps (0);
+ *   "gemm_pg"     weight-producer groups of the GEMM: 0 (default) = two groups taking alternate K
+ *                 steps for tiles of one 128-row activation sub-tile, one group otherwise; 1, 2 = forced;
+ *   "gemm_pair"   from 129 activation rows on, the GEMM runs on CTA pairs (tcgen05 cta_group::2,
+ *                 persistent, two accumulators in tensor memory) (1) or on single CTAs (0,
+ *                 default: faster on a B200);
+ *   "gemv_splitk" 2 to 16 activation rows whose fragments crowd the shared memory: K is cut into
+ *                 windows, one pass over the weights (2, default: windows sized for one CTA per
+ *                 SM; 1: for two CTAs per SM) or several passes (0);
+ *   "gemv_f8"     one activation row of a Q4_0 weight on the FP8 tensor-core form (1) or the
+ *                 f16 form (0, default: faster);
+ *   "q6k_resident" Q6_K tensors stay quantized in HBM (1, default) or become f16 at upload (0);
+ *   "attn_wide"   decode attention of one sequence with at most four KV heads over a long
+ *                 context runs on clusters of sixteen key splits (1) or eight (0, default: no slower).
  * Unknown names fail with TLC_ERR_INVALID_OPERATION. */
 TLC_API int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value);
 /* Failure-detection self-test.  Enqueues a kernel whose device-side wait can never be

@@ -57,6 +57,7 @@ struct AttnParams {
     float *part_o;   // [rows][nsplit][D]
     int *counters;   // [B][q_tiles][Hkv], zero between launches
     int push_offset; // cluster mode: byte offset of the merge area in dynamic shared memory
+    int push_splits; // cluster mode: splits the merge area of rank 0 is laid out for (8 or 16)
     int cluster;     // 1: the nsplit CTAs of a tile form a thread-block cluster and merge through
                      // distributed shared memory instead of global scratch
     int key_limit;   // keys the launch was sized for (<= Tmax): a sequence whose position says it
@@ -340,7 +341,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         // [nsplit][16] max, [nsplit][16] sum, [nsplit][16][D] O, behind the K/V tiles
         float *push = reinterpret_cast<float *>(smem_raw + p.push_offset);
         float *r0 = cl.map_shared_rank(push, 0);
-        float *pm = r0, *pl = r0 + 8 * 16, *po = r0 + 2 * 8 * 16;
+        const int PS = p.push_splits;
+        float *pm = r0, *pl = r0 + PS * 16, *po = r0 + 2 * PS * 16;
         asm volatile("barrier.cluster.wait.aligned;" ::: "memory");  // every CTA of the cluster has started
         if ((tid & 7) == 0) {
             pm[split * 16 + row] = M;
@@ -353,12 +355,14 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         if (cl.block_rank() == 0 && row_valid) {
-            const float *lm = push, *ll = push + 8 * 16, *lo = push + 2 * 8 * 16;
+            const float *lm = push, *ll = push + PS * 16, *lo = push + 2 * PS * 16;
             float Mg = -INFINITY;
+#pragma unroll 4
             for (int sp = 0; sp < p.nsplit; sp++) Mg = fmaxf(Mg, lm[sp * 16 + row]);
             float Lg = 0.f;
 #pragma unroll
             for (int j = 0; j < DPT; j++) acc[j] = 0.f;
+#pragma unroll 4
             for (int sp = 0; sp < p.nsplit; sp++) {
                 const float ms = lm[sp * 16 + row];
                 const float wgt = ms == -INFINITY ? 0.f : expf(ms - Mg);
@@ -388,7 +392,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
             p.part_ml[pi * 2 + 1] = L;
         }
 #pragma unroll
-        for (int j = 0; j < DPT; j++) p.part_o[pi * D + d0 + j] = acc[j];
+        for (int j = 0; j < DPT; j += 4)
+            *reinterpret_cast<float4 *>(p.part_o + pi * D + d0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
     }
     __threadfence();
     __syncthreads();
@@ -402,18 +407,27 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     if (!sm_last) return;
     __threadfence();
     if (row_valid) {
+        // loads of several splits in flight at once: a merge of 64 splits is a chain of L2 round trips otherwise
         float Mg = -INFINITY;
+#pragma unroll 8
         for (int sp = 0; sp < p.nsplit; sp++) Mg = fmaxf(Mg, __ldcg(&p.part_ml[(out_row * p.nsplit + sp) * 2]));
         float Lg = 0.f;
 #pragma unroll
         for (int j = 0; j < DPT; j++) acc[j] = 0.f;
+#pragma unroll 4
         for (int sp = 0; sp < p.nsplit; sp++) {
             const size_t pi = out_row * p.nsplit + sp;
-            const float ms = __ldcg(&p.part_ml[pi * 2]);
-            const float wgt = ms == -INFINITY ? 0.f : expf(ms - Mg);
-            Lg += __ldcg(&p.part_ml[pi * 2 + 1]) * wgt;
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(p.part_ml + pi * 2));
+            const float wgt = ml.x == -INFINITY ? 0.f : expf(ml.x - Mg);
+            Lg += ml.y * wgt;
 #pragma unroll
-            for (int j = 0; j < DPT; j++) acc[j] += __ldcg(&p.part_o[pi * D + d0 + j]) * wgt;
+            for (int j = 0; j < DPT; j += 4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(p.part_o + pi * D + d0 + j));
+                acc[j] += v.x * wgt;
+                acc[j + 1] += v.y * wgt;
+                acc[j + 2] += v.z * wgt;
+                acc[j + 3] += v.w * wgt;
+            }
         }
         const float inv = Lg > 0.f ? 1.0f / Lg : 0.f;
 #pragma unroll
@@ -604,7 +618,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_prefill_kernel(const A
 // cluster mode, the merge area of rank 0.  Every place that sets the kernel's limit uses this
 // value, so one launcher never lowers the limit another one needs.
 static constexpr size_t attention_smem_limit(int D) {
-    return (size_t)4 * kTileKeys * (D + 8) * sizeof(__half) + 128 + (size_t)8 * 16 * (D + 2) * sizeof(float);
+    return (size_t)4 * kTileKeys * (D + 8) * sizeof(__half) + 128 + (size_t)16 * 16 * (D + 2) * sizeof(float);
 }
 
 __global__ void kv_append_kernel(const __half *__restrict__ k, const __half *__restrict__ v,
@@ -621,6 +635,44 @@ __global__ void kv_append_kernel(const __half *__restrict__ k, const __half *__r
 }
 
 }  // namespace
+
+// How many clusters of sixteen attention CTAs (with the merge area for sixteen splits) the
+// device can hold at once; 0 when it cannot place one.  Allows the non-portable cluster size
+// on first use.
+static int attention_wide_clusters(tlc_ctx *ctx, int D) {
+    static int cached[2][64];
+    static bool known[2][64] = {};
+    const int di = D == 64 ? 0 : 1, dev = ctx->device & 63;
+    if (known[di][dev]) return cached[di][dev];
+    known[di][dev] = true;
+    cached[di][dev] = 0;
+    const void *fn = D == 64 ? (const void *)attention_kernel<64> : (const void *)attention_kernel<128>;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess ||
+        cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attention_smem_limit(D)) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(16, 1, 1);
+    cfg.blockDim = dim3(kAttnThreads);
+    cfg.dynamicSmemBytes = attention_smem_limit(D);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 16;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t e = D == 64 ? cudaOccupancyMaxActiveClusters(&n, attention_kernel<64>, &cfg)
+                            : cudaOccupancyMaxActiveClusters(&n, attention_kernel<128>, &cfg);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    cached[di][dev] = n;
+    return n;
+}
 
 // Host-side launcher shared by the ABI entry point and the decode runner.
 //   batch sequences, I queries each (I == 1 when positions_dev is given).
@@ -709,15 +761,21 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
     // (8 CTAs, up to 16 tiles each, walked with the double-buffered tile loop) and merge
     // through distributed shared memory; beyond that, up to 64 independent splits and the
     // global-memory merge.
+    // A portable cluster holds eight splits.  With few (sequence, KV head) tiles -- one KV head
+    // per rank of a tensor-parallel model, one sequence -- eight CTAs would walk a long context
+    // alone on an otherwise idle GPU: such launches use clusters of sixteen (option attn_wide).
     const bool cluster = I == 1 && nsplit > 1 && (T + kTileKeys - 1) / kTileKeys <= 128;
-    if (cluster && nsplit > 8) nsplit = 8;
+    const bool wide = cluster && ctx->attn_wide && nsplit >= 16 && (T + kTileKeys - 1) / kTileKeys >= 24 &&
+                      (long)batch * Hkv * 32 <= ctx->sm_count && attention_wide_clusters(ctx, D) > 0;
+    if (cluster && nsplit > (wide ? 16 : 8)) nsplit = wide ? 16 : 8;
+    p.push_splits = wide ? 16 : 8;
     p.nsplit = nsplit;
     p.cluster = cluster ? 1 : 0;
     const int tiles_total = (T + kTileKeys - 1) / kTileKeys;
     p.keys_per_split = ((tiles_total + nsplit - 1) / nsplit) * kTileKeys;
     if (nsplit > 1 && !cluster) {
         const size_t rows = (size_t)batch * I * n_heads;
-        const size_t ml = rows * nsplit * 2 * sizeof(float), po = rows * nsplit * D * sizeof(float);
+        const size_t ml = (rows * nsplit * 2 * sizeof(float) + 15) & ~(size_t)15, po = rows * nsplit * D * sizeof(float);
         // Ticket counters (one per tile, zero between launches: the merging
         // CTA resets its own) live in a small zero-initialised context buffer.
         TLC_REQUIRE((size_t)batch * p.q_tiles * Hkv <= ctx->n_tickets, TLC_ERR_INVALID_OPERATION,
@@ -733,7 +791,7 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
     size_t smem_bytes = smem > smem_o ? smem : smem_o;
     if (cluster) {  // the merge area of rank 0 (every CTA of the launch has the same layout)
         p.push_offset = (int)((smem_bytes + 127) & ~(size_t)127);
-        smem_bytes = (size_t)p.push_offset + (size_t)8 * 16 * (D + 2) * sizeof(float);
+        smem_bytes = (size_t)p.push_offset + (size_t)p.push_splits * 16 * (D + 2) * sizeof(float);
     }
     // All kernels of a decode step ask for the same (maximal) shared-memory
     // carve-out: switching the L1/shared split between consecutive launches
@@ -974,7 +1032,7 @@ extern "C" int32_t tlc_attention_decode_static(void *stream, const void *q_dev, 
     p.nsplit = nsplit;
     p.keys_per_split = ((tiles + nsplit - 1) / nsplit) * kTileKeys;
     const size_t rows = (size_t)batch * n_heads;
-    const size_t ml = rows * nsplit * 2 * sizeof(float), po = rows * nsplit * D * sizeof(float);
+    const size_t ml = (rows * nsplit * 2 * sizeof(float) + 15) & ~(size_t)15, po = rows * nsplit * D * sizeof(float);
     TLC_REQUIRE(nsplit == 1 || ml + po <= kStaticPartialBytes, TLC_ERR_BUFFER_EXHAUSTED,
                 "attention_decode_static: %d sequences x %d heads x %d key splits need %zu bytes of partials, the "
                 "built-in scratch holds %zu; use tlc_attention or a smaller batch",

@@ -41,7 +41,9 @@
 namespace tlc_gemm {
 
 constexpr int kBK = 64;  // K elements per stage (one 128-byte swizzle row)
-constexpr int kThreads = 416;
+// Threads of a CTA: 4 warps at the activation tile (one TMA issuer, or four cp.async loaders),
+// 4*nt*pg weight-producer warps, the MMA warp.
+__host__ __device__ constexpr int gemm_threads(int nt, int pg) { return 32 * (4 + 4 * nt * pg + 1); }
 
 struct GemmParams {
     const uint8_t *w;   // weight tiles [slab of 16 rows][k-tile] (tlc_tile.cuh)

@@ -125,11 +125,102 @@ __device__ __forceinline__ void produce_b(const GemmParams &p, uint8_t *btiles, 
     }
 }
 
+// B producer for the form with two producer groups (PG = 2): the warps of group g fill the K
+// steps kt = g, g + 2, ...  A thread still owns one weight row, but only every other ring stage,
+// so twice as many warps share the dequantization of a K step sequence: the per-step latency of
+// the producers, which bounds the GEMM when the tensor cores have little to do (one sub-tile of
+// activation rows), halves.  Per own step a thread fetches its row's quants (32 bytes of Q4_0 in
+// four 8-byte loads, 64 bytes of Q8_0) and scale word two own steps ahead.
+template <int QT, int STAGES, int STAGE_BYTES>
+__device__ __forceinline__ void produce_b_alt(const GemmParams &p, uint8_t *btiles, uint64_t *full, uint64_t *empty,
+                                              volatile int *abort_flag, const uint8_t *wbase, int wrow, int row, int KT,
+                                              int lane, int group) {
+    constexpr int TILE = QT == TLC_TYPE_Q4_0 ? 1152 : 1088;
+    constexpr int PF = 2;                             // own steps fetched ahead
+    constexpr int QW = QT == TLC_TYPE_Q4_0 ? 8 : 16;  // quant words of a row per K step
+    const bool row_ok = wrow < p.n;
+    const int r16 = wrow & 15;
+    const uint8_t *slab = wbase + (size_t)(row_ok ? wrow >> 4 : 0) * p.w_pitch;
+    const uint32_t qoff = (uint32_t)((r16 >> 3) * 512 + (r16 & 7) * 64);
+    const uint32_t soff = 1024u + (uint32_t)r16 * (QT == TLC_TYPE_Q4_0 ? 8u : 4u);
+    uint32_t piece[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) piece[j] = (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4));
+    uint32_t qn[PF][QW], sn[PF];
+    auto fetch = [&](int kt, uint32_t (&qw)[QW], uint32_t &sc) {
+        const int wt = QT == TLC_TYPE_Q4_0 ? kt >> 1 : kt;
+        const bool ok = row_ok && kt < KT && wt < p.k_tiles;
+        const uint8_t *tile = slab + (size_t)(ok ? wt : 0) * TILE;
+        if (QT == TLC_TYPE_Q4_0) {
+            const int half = kt & 1;  // which pair of the tile's four blocks
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint2 v = ok ? __ldg(reinterpret_cast<const uint2 *>(tile + qoff + 16 * i + 8 * half)) : make_uint2(0, 0);
+                qw[2 * i] = v.x;
+                qw[2 * i + 1] = v.y;
+            }
+            sc = ok ? __ldg(reinterpret_cast<const uint32_t *>(tile + soff + 4 * half)) : 0u;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint4 v = ok ? __ldg(reinterpret_cast<const uint4 *>(tile + qoff) + i) : make_uint4(0, 0, 0, 0);
+                qw[4 * i] = v.x;
+                qw[4 * i + 1] = v.y;
+                qw[4 * i + 2] = v.z;
+                qw[4 * i + 3] = v.w;
+            }
+            sc = ok ? __ldg(reinterpret_cast<const uint32_t *>(tile + soff)) : 0u;
+        }
+    };
+#pragma unroll
+    for (int u = 0; u < PF; u++) fetch(group + 2 * u, qn[u], sn[u]);
+#pragma unroll 1
+    for (int base = group; base < KT; base += 2 * PF) {
+#pragma unroll
+        for (int u = 0; u < PF; u++) {
+            const int kt = base + 2 * u;
+            if (kt >= KT) break;
+            uint32_t cw[QW];
+#pragma unroll
+            for (int i = 0; i < QW; i++) cw[i] = qn[u][i];
+            const uint32_t scw = sn[u];
+            fetch(kt + 2 * PF, qn[u], sn[u]);
+            const int s = kt % STAGES;
+            mbar_wait(&empty[s], ((kt / STAGES) & 1u) ^ 1u, abort_flag, p.status, 15, p.wait_ns);
+            uint8_t *bt = btiles + (size_t)s * STAGE_BYTES;
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const __half d = __ushort_as_half((unsigned short)(e == 0 ? scw & 0xFFFFu : scw >> 16));
+                if (QT == TLC_TYPE_Q4_0) {
+                    uint32_t qb[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) qb[i] = cw[2 * i + e];
+                    dequant_block<QT>(qb, d, bt, piece, e);
+                } else {
+                    uint32_t qb[8];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        qb[2 * i] = cw[4 * i + 2 * e];
+                        qb[2 * i + 1] = cw[4 * i + 2 * e + 1];
+                    }
+                    dequant_block<QT>(qb, d, bt, piece, e);
+                }
+            }
+            fence_async_proxy();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+        }
+    }
+}
+
 // SW: the SiLU.mul pair.  The weight tile holds 128 rows of the gate weight (tile rows
 // 0-127) and the same 128 rows of the up weight (tile rows 128-255); the epilogue reads
 // both accumulators and stores silu(gate) * up for the 128 output columns of the CTA.
-template <int QT, int MT, int NT, bool SW>
-__global__ void __launch_bounds__(kThreads, 1)
+// PG: producer groups.  1: the 4*NT producer warps fill every K step.  2: twice the warps, each
+// group every other step (produce_b_alt) -- for tiles of one activation sub-tile, where the
+// producers and not the MMAs set the pace.
+template <int QT, int MT, int NT, bool SW, int PG>
+__global__ void __launch_bounds__(gemm_threads(NT, PG), 1)
     gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap x_map) {
     static_assert(!SW || NT == 2, "the gate/up pair fills a 256-row weight tile");
     constexpr int BN = 128 * NT;
@@ -138,7 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr int kStages = stages_for(MT, NT);
     constexpr uint32_t TMEM_COLS = MT * BN;  // 128, 256 or 512: a power of two
     constexpr uint32_t IDESC = idesc_for(BN);
-    constexpr int MMA_WARP = 12;
+    constexpr int MMA_WARP = 4 + 4 * NT * PG;  // 12 with NT = 2, PG = 1 (eight producer warps) or NT = 1, PG = 2
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -175,11 +266,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t tmem_base = *tmem_slot;
     tlc_pdl_prologue();  // x (and residual) come from the previous kernel of the stream
 
-    if (warp >= 4 && warp < 4 + 4 * NT) {
-        const int trow = tid - 128;  // row of the weight tile
+    if (warp >= 4 && warp < 4 + 4 * NT * PG) {
+        const int trow = (tid - 128) % BN;  // row of the weight tile
         const uint8_t *wbase = SW && trow >= 128 ? p.w2 : p.w;
         const int wrow = SW ? n0 + (trow & 127) : n0 + trow;
-        produce_b<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, wbase, wrow, trow, KT, lane);
+        if (PG == 1)
+            produce_b<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, wbase, wrow, trow, KT, lane);
+        else
+            produce_b_alt<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, wbase, wrow, trow, KT,
+                                                    lane, (tid - 128) / BN);
     } else if (warp < 4 && p.a_tma) {
         // ------------------------------ A tile by TMA ------------------------------
         // One thread issues, per K step, MT boxes of 128 rows x 64 columns with the 128-byte
@@ -258,7 +353,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ------------------------------ epilogue ------------------------------
     // Warp w reads tensor-memory lanes 32*(w%4) .. +31 (= activation rows of a
-    // sub-tile); the three warps of a lane quarter take the 32-column pieces in turn.
+    // sub-tile); the warps of a lane quarter (three, or five with two producer groups of a
+    // 256-row weight tile) take the 32-column pieces in turn.
     if (warp < MMA_WARP) {
         mbar_wait(accum_bar, 0, abort_flag, p.status, 13, p.wait_ns);
         tc_fence_after();
@@ -266,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         constexpr int OUT_COLS = SW ? 128 : BN;  // output columns of the CTA
         constexpr int PIECES = MT * OUT_COLS / 32;
 #pragma unroll 1
-        for (int pc = warp >> 2; pc < PIECES; pc += 3) {
+        for (int pc = warp >> 2; pc < PIECES; pc += MMA_WARP / 4) {
             const int i = pc / (OUT_COLS / 32), c0 = (pc % (OUT_COLS / 32)) * 32;
             const int row = m0 + 128 * i + 32 * wq + lane;
             bool row_ok = row < p.m;
@@ -300,15 +396,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
-template <int QT, int MT, int NT, bool SW = false>
-int32_t launch_tile(tlc_ctx *ctx, const GemmParams &p) {
+template <int QT, int MT, int NT, bool SW, int PG>
+int32_t launch_tile_pg(tlc_ctx *ctx, const GemmParams &p) {
     const size_t smem = smem_bytes(MT, NT);
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT, SW, PG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem));
-        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT, SW>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                      cudaSharedmemCarveoutMaxShared));
+        TLC_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<QT, MT, NT, SW, PG>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 63] = true;
     }
     const int out_cols = SW ? 128 : 128 * NT;  // output columns per CTA
@@ -317,13 +413,23 @@ int32_t launch_tile(tlc_ctx *ctx, const GemmParams &p) {
     CUtensorMap x_map;
     memset(&x_map, 0, sizeof x_map);
     q.a_tma = ctx->gemm_tma && encode_x_map(&x_map, p) ? 1 : 0;
-    cudaError_t le = tlc_launch_pdl(ctx, gemm_tcgen05_kernel<QT, MT, NT, SW>, grid, dim3(kThreads), smem, q, x_map);
+    cudaError_t le = tlc_launch_pdl(ctx, gemm_tcgen05_kernel<QT, MT, NT, SW, PG>, grid, dim3(gemm_threads(NT, PG)), smem, q,
+                                    x_map);
     if (le != cudaSuccess) {
         cudaGetLastError();
         return tlc_fail(TLC_ERR_CUDA, "gemm launch failed: %s", cudaGetErrorString(le));
     }
     TLC_CHECK_LAUNCH(ctx);
     return TLC_OK;
+}
+
+// One activation sub-tile per CTA: the producers set the pace, two producer groups (option
+// "gemm_pg": 0 = this rule, 1 or 2 = forced).  Two sub-tiles: the MMAs do, one group.
+template <int QT, int MT, int NT, bool SW = false>
+int32_t launch_tile(tlc_ctx *ctx, const GemmParams &p) {
+    const bool two = ctx->gemm_pg == 2 || (ctx->gemm_pg == 0 && MT == 1);
+    if (MT == 1 && two) return launch_tile_pg<QT, 1, NT, SW, 2>(ctx, p);
+    return launch_tile_pg<QT, MT, NT, SW, 1>(ctx, p);
 }
 
 template <int QT>

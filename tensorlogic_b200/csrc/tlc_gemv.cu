@@ -421,8 +421,10 @@ static int gemv_max_m(tlc_ctx *ctx, int type, int k) {
 //  - A launch that runs two CTAs per SM without a split is left alone.
 //  - More than four rows that fit one launch at one CTA per SM stay unsplit (sixteen consumer
 //    warps; 8 rows of K = 8192: 44 us against 50 us split).
-//  - Otherwise the windows are sized for two CTAs per SM, or (option gemv_splitk = 2: first
-//    choice) for one CTA per SM with sixteen consumer warps; a window holds at least eight tiles.
+//  - Otherwise the windows are sized for one CTA per SM with sixteen consumer warps (option
+//    gemv_splitk = 2, the default: 16 rows of K = 8192 take 76 us, against 120 us with windows
+//    for two CTAs per SM and 87 us in two passes), else, or first with gemv_splitk = 1, for two
+//    CTAs per SM; a window holds at least eight tiles.
 static int gemv_choose_ksplit(tlc_ctx *ctx, int type, int64_t ktiles, int m, int n_sub, int max_m, int mode) {
     const int tb = tlc_tile::tile_blocks(type);
     const size_t stage = (size_t)kTilesPerStage * tlc_tile::tile_bytes(type);

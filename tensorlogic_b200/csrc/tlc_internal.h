@@ -56,13 +56,18 @@ struct tlc_ctx {
     // TLC_GEMM_MIN_M: activation rows from which quantized linears run as the
     // tensor-core GEMM (0: decide from the shape; a huge value keeps the GEMV).
     int gemm_min_m = 0;
+    // Decode attention with few (sequence, KV head) tiles and a long context: clusters of sixteen
+    // key splits (a non-portable cluster size) instead of eight.  Off: measured no faster (one
+    // rank's share of the 70B-shape decode at TP8, 2048 keys: 3.79 ms per step against 3.73 ms).
+    int attn_wide = 0;
     int l2_hint = 1;         // GEMV weight copies marked evict-first in the L2 (measured: +3 % on the decode step)
     bool host_graph = true;  // decode_host: ids up, the step, results down as ONE graph launch
     bool host_poll = true;   // ... and the host watches the pinned result words instead of a stream sync
     // How long a device-side wait (mbarrier, peer flag) may last before the kernel gives up,
     // sets the status word and drains; option "wait_limit_ms".
     uint64_t wait_ns = 2000000000ull;
-    bool gemm_pair = true;  // GEMM tiles of 256 x 256 on CTA pairs (tcgen05 cta_group::2) from 129 rows on
+    bool gemm_pair = false;  // GEMM tiles of 256 x 256 on CTA pairs (tcgen05 cta_group::2) from 129 rows on; measured slower
+    int gemm_pg = 0;  // producer groups of the GEMM: 0 = two for one-sub-tile CTAs, else one; 1 / 2 = forced
     bool gemm_tma = true;  // activation tiles of the GEMM by TMA (false: cp.async loader warps)
     int gemm_tile = 0;  // 0: pick the GEMM tile from the shape; 11, 12, 22: force 128x128, 128x256, 256x256
     // Option "gemv_f8" / TLC_GEMV_F8=1: one activation row against a Q4_0 weight takes the FP8-limb
@@ -71,7 +76,7 @@ struct tlc_ctx {
     bool gemv_f8 = false;
     // Option "gemv_splitk" / TLC_GEMV_SPLITK=0: 2..16 activation rows whose fragments crowd the
     // shared memory take further passes over the weights instead of one pass with K cut into windows.
-    int gemv_splitk = 1;  // 0: off; 1: windows sized for two CTAs per SM first; 2: for one CTA per SM first
+    int gemv_splitk = 2;  // 0: off; 1: windows sized for two CTAs per SM first; 2: for one CTA per SM first (measured faster)
     // Option "q6k_resident" / TLC_Q6K_RESIDENT=0: Q6_K tensors are expanded to f16 at upload (what
     // the reference's loader keeps) instead of staying quantized in HBM.
     bool q6k_resident = true;

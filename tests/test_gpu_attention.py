@@ -42,6 +42,29 @@ def test_decode_attention(dev, ref, H, Hkv, D, T):
     assert rel_l2(got2, want) < TIGHT
 
 
+@pytest.mark.parametrize("H,Hkv,D", [(8, 1, 128), (32, 4, 64), (16, 2, 128)])
+@pytest.mark.parametrize("T", [1536, 2048, 1990])
+def test_decode_attention_few_heads_long_context(dev, ref, H, Hkv, D, T):
+    """One sequence with one to four KV heads (a rank of a tensor-parallel model) over a long
+    context: a cluster of sixteen key splits (option attn_wide) and the portable cluster of
+    eight splits walking twice the tiles each (the default) give the same result."""
+    from tensorlogic_b200.api import KVCache
+    q, k, v = _qkv(T + 3 * H, 1, T, H, Hkv, D)
+    cache = KVCache(dev, 1, Hkv, D, max_seq=2048)
+    cache.append(0, dev.tensor(k), dev.tensor(v))
+    want = ref.attention(q, k, v, 1.0 / np.sqrt(D), q_pos0=T - 1)
+    outs = []
+    for wide in (1, 0):
+        dev.set_option("attn_wide", wide)
+        try:
+            outs.append(cache.attention(0, dev.tensor(q), H, q_pos0=T - 1).numpy())
+            outs.append(cache.attention(0, dev.tensor(q), H, positions=np.array([T - 1])).numpy())
+        finally:
+            dev.set_option("attn_wide", 0)
+    for got in outs:
+        assert rel_l2(got, want) < TIGHT
+
+
 @pytest.mark.parametrize("H,Hkv,D,T,cap", [(8, 1, 128, 4100, 8192), (32, 4, 64, 9000, 9216), (8, 1, 64, 2184, 2200)])
 def test_decode_attention_long_context(dev, ref, H, Hkv, D, T, cap):
     """Contexts past 2048 keys: cluster splits that walk several tiles (up to 8192 keys of capacity), and

@@ -103,24 +103,30 @@ def test_every_tile_shape(dev, ref, qtype, tile, n, k, m):
     raw = _weights(qtype, n, k, seed=17, name=f"t{n}x{k}")
     x = _x(m, k, seed=17, name=f"tx{m}x{k}")
     w = QTensor.from_blocks(dev, qtype, n, k, raw)
+    want = ref.linear_q(qtype, raw, n, k, x)
+    want_t = ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]
     dev.set_option("gemm_tile", tile)
     try:
-        with gemm_from(dev, 1):
-            y = linear(dev.tensor(x), w).numpy()
-            yt = linear(dev.tensor(np.eye(k, dtype=np.float16)[:m]), w).numpy()
+        # one producer group, and (tiles of one activation sub-tile) two groups taking alternate K steps
+        for pg in (1, 2):
+            dev.set_option("gemm_pg", pg)
+            with gemm_from(dev, 1):
+                y = linear(dev.tensor(x), w).numpy()
+                yt = linear(dev.tensor(np.eye(k, dtype=np.float16)[:m]), w).numpy()
+            assert rel_l2(y, want) < TIGHT, pg
+            assert np.array_equal(_bits(yt), _bits(want_t)), pg
     finally:
         dev.set_option("gemm_tile", 0)
-    assert rel_l2(y, ref.linear_q(qtype, raw, n, k, x)) < TIGHT
-    assert np.array_equal(_bits(yt), _bits(ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]))
+        dev.set_option("gemm_pg", 0)
 
 
 @pytest.mark.parametrize("qtype", [Q4, Q8])
 @pytest.mark.parametrize("n,k,m", [(300, 640, 300), (512, 1088, 130), (40, 4096, 257), (1000, 64, 129),
                                    (2100, 96, 2500), (256, 8192, 256)])
 def test_cta_pair_tiles(dev, ref, qtype, n, k, m):
-    """The CTA-pair kernel (two SMs per 256 x 256 tile, persistent): ragged shapes, a walk of
-    several tiles per cluster (2100 x 2500: 90 tiles), both accumulators, ring wrap-around; and
-    the same shapes with the pair form switched off give the single-CTA kernel's result."""
+    """The CTA-pair kernel (option gemm_pair: two SMs per 256 x 256 tile, persistent): ragged
+    shapes, a walk of several tiles per cluster (2100 x 2500: 90 tiles), both accumulators, ring
+    wrap-around; the same shapes on the default single-CTA kernel give the same result."""
     from tensorlogic_b200.api import QTensor, linear
     raw = _weights(qtype, n, k, seed=19, name=f"p{n}x{k}")
     x = _x(m, k, seed=19, name=f"px{m}x{k}")
@@ -128,13 +134,15 @@ def test_cta_pair_tiles(dev, ref, qtype, n, k, m):
     want = ref.linear_q(qtype, raw, n, k, x)
     eye = np.eye(k, dtype=np.float16)[:m] if m <= k else None
     with gemm_from(dev, 1):
-        y = linear(dev.tensor(x), w).numpy()
-        yt = linear(dev.tensor(eye), w).numpy() if eye is not None else None
-        dev.set_option("gemm_pair", 0)
+        y1 = linear(dev.tensor(x), w).numpy()
+        dev.set_option("gemm_pair", 1)
         try:
-            y1 = linear(dev.tensor(x), w).numpy()
+            l0 = dev.launch_count
+            y = linear(dev.tensor(x), w).numpy()
+            assert dev.launch_count - l0 == 1
+            yt = linear(dev.tensor(eye), w).numpy() if eye is not None else None
         finally:
-            dev.set_option("gemm_pair", 1)
+            dev.set_option("gemm_pair", 0)
     assert rel_l2(y, want) < TIGHT
     assert rel_l2(y1, want) < TIGHT
     assert rel_l2(y, y1) < 1e-4
@@ -193,8 +201,12 @@ def test_fused_contract_on_gemm(dev, ref, qtype):
 
 @pytest.mark.parametrize("qtype", [Q4, Q8])
 def test_fused_contract_on_cta_pairs(dev, ref, qtype):
-    """The same contract from 129 rows on, where the CTA-pair kernel runs."""
-    _fused_contract(dev, qtype, 300)
+    """The same contract on the CTA-pair kernel (option gemm_pair, from 129 rows on)."""
+    dev.set_option("gemm_pair", 1)
+    try:
+        _fused_contract(dev, qtype, 300)
+    finally:
+        dev.set_option("gemm_pair", 0)
 
 
 def _fused_contract(dev, qtype, m):

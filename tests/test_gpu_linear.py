@@ -387,13 +387,13 @@ def test_split_k_for_many_rows_of_a_wide_input(dev, ref, qtype, n, k):
     for m in (2, 8, 13, 16):
         x = synth.activations(23, f"skx{m}", (m, k))
         want = ref.linear_q(qtype, raw, n, k, x)
-        dev.set_option("gemv_splitk", 2)                      # windows sized for one CTA per SM first
+        dev.set_option("gemv_splitk", 1)                      # windows sized for two CTAs per SM first
         try:
             l0 = dev.launch_count
             y = linear(dev.tensor(x), w).numpy()
             launches2 = dev.launch_count - l0
         finally:
-            dev.set_option("gemv_splitk", 1)
+            dev.set_option("gemv_splitk", 2)
         assert rel_l2(y, want) < TIGHT, m
         l0 = dev.launch_count
         y = linear(dev.tensor(x), w).numpy()
@@ -405,7 +405,7 @@ def test_split_k_for_many_rows_of_a_wide_input(dev, ref, qtype, n, k):
             y_passes = linear(dev.tensor(x), w).numpy()
             passes = dev.launch_count - l0
         finally:
-            dev.set_option("gemv_splitk", 1)
+            dev.set_option("gemv_splitk", 2)
         assert rel_l2(y, y_passes) < 5e-4
         if passes > 1:
             assert launches == 2 and launches2 == 2, (m, launches, launches2, passes)  # one pass + the finish

@@ -42,11 +42,16 @@ def main() -> int:
 
     # residual + all-reduce before and after the peer-memory exchange exists (NCCL + add, then one kernel)
     rng = np.random.default_rng(100 + rank)
-    ok = True
+    failed = []                                               # names of the checks this rank failed
+
+    def check(name, cond):
+        if not bool(cond):
+            failed.append(name)
+
     for phase in ("nccl", "p2p", "p2p-too-large"):
         if phase == "p2p":
             comm.enable_p2p(4096, gather)
-            ok &= comm.p2p_ready
+            check("p2p_ready", comm.p2p_ready)
         for rep, n in enumerate((8, 40, 1024, 4096, 4096, 2048) if phase != "p2p-too-large" else (8192,)):
             part = rng.standard_normal(n).astype(np.float16)
             res = np.random.default_rng(7 * rep + n).standard_normal(n).astype(np.float16)  # same on every rank
@@ -59,19 +64,21 @@ def main() -> int:
             got_sum = comm.all_reduce_residual(dev.tensor(part)).numpy()
             if phase == "nccl" or phase == "p2p-too-large":   # the library's own f16 summation order
                 # f16 partial sums inside the library: a few f16 roundings of values up to ~world * 3
-                ok &= bool(np.allclose(got_sum.astype(np.float32), acc, rtol=1e-2, atol=8e-3 * world))
-                ok &= bool(np.allclose(got.astype(np.float32), acc + res.astype(np.float32), rtol=1e-2, atol=8e-3 * world))
+                check(f"{phase} sum n={n}", np.allclose(got_sum.astype(np.float32), acc, rtol=1e-2, atol=8e-3 * world))
+                check(f"{phase} sum+residual n={n}",
+                      np.allclose(got.astype(np.float32), acc + res.astype(np.float32), rtol=1e-2, atol=8e-3 * world))
             else:
-                ok &= bool(np.array_equal(got_sum.view(np.uint16), want_sum.view(np.uint16)))
-                ok &= bool(np.array_equal(got.view(np.uint16), (res + want_sum).view(np.uint16)))
+                check(f"{phase} sum n={n} rep={rep} (bit-exact)", np.array_equal(got_sum.view(np.uint16), want_sum.view(np.uint16)))
+                check(f"{phase} sum+residual n={n} rep={rep} (bit-exact)",
+                      np.array_equal(got.view(np.uint16), (res + want_sum).view(np.uint16)))
     dev.synchronize()
 
     # all-reduce / all-gather on their own
     t = dev.tensor(np.full((3, 5), rank + 1, np.float16))
     comm.all_reduce(t)
-    ok &= bool(np.all(t.numpy() == np.float16(world * (world + 1) / 2)))
+    check("all_reduce", np.all(t.numpy() == np.float16(world * (world + 1) / 2)))
     g = comm.all_gather(dev.tensor(np.full((4,), rank, np.float16))).numpy()
-    ok &= bool(np.array_equal(g, np.repeat(np.arange(world, dtype=np.float16), 4).reshape(world, 4)))
+    check("all_gather", np.array_equal(g, np.repeat(np.arange(world, dtype=np.float16), 4).reshape(world, 4)))
 
     arch = LlamaArch(n_layers=3, d_model=512, n_heads=8, n_kv_heads=8 if world > 4 else 4, head_dim=64,
                      ffn_dim=1024, vocab=2048)
@@ -91,7 +98,7 @@ def main() -> int:
         rel = lambda a, b: float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) /
                                  np.linalg.norm(b.astype(np.float64)))
         errs.append(rel(logits, want))
-        ok &= nxt == ref.argmax_last(logits[-1])
+        check("prefill token == argmax of own logits", nxt == ref.argmax_last(logits[-1]))
         tok = ref.argmax_last(want[-1])
     else:
         tok = 0
@@ -102,18 +109,20 @@ def main() -> int:
         if rank == 0:
             w = oracle.forward([box[0]])
             errs.append(rel(lg, w))
-            ok &= int(got[0]) == ref.argmax_last(lg[0])
+            check(f"decode step {step}: token == argmax of own logits", int(got[0]) == ref.argmax_last(lg[0]))
             box = [ref.argmax_last(w[0])]
     # every rank must hold the same full logits and the same sampled token
     all_lg = [None] * world
     dist.all_gather_object(all_lg, (lg.tobytes(), int(got[0])))
-    ok &= all(a == all_lg[0] for a in all_lg)
+    check("same logits and token on every rank", all(a == all_lg[0] for a in all_lg))
     flags = [None] * world
-    dist.all_gather_object(flags, bool(ok))
+    dist.all_gather_object(flags, list(failed))
+    ok = not any(flags)
     if rank == 0:
-        if not all(flags):
-            print(f"per-rank checks: {flags}", flush=True)
-        ok = all(flags) and max(errs) < 1e-2
+        for r, f in enumerate(flags):
+            if f:
+                print(f"rank {r} failed: {f}", flush=True)
+        ok = ok and max(errs) < 1e-2
         print(f"tp={world} rel-L2 of logits vs oracle: {['%.2e' % e for e in errs]}  {'PASS' if ok else 'FAIL'}",
               flush=True)
     flag = [bool(ok)]
