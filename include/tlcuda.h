@@ -104,7 +104,10 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *   "gemm_tma"    the GEMM's activation tiles arrive by TMA (1, default) or through cp.async
  *                 loader warps (0);
  *   "gemm_pg"     weight-producer groups of the GEMM: 0 (default) = two groups taking alternate K
- *                 steps for tiles of one 128-row activation sub-tile, one group otherwise; 1, 2 = forced;
+ *                 steps where the K steps of a tile are shared out ("gemm_splitk"), one group
+ *                 otherwise; 1 = one group and no sharing; 2 = two groups wherever possible;
+ *   "gemm_splitk" GEMMs of up to 128 activation rows whose weight gives fewer tiles than SMs share
+ *                 the K steps over several CTAs per tile, one finishing kernel adds (1, default); 0 = off;
  *   "gemm_pair"   from 129 activation rows on, the GEMM runs on CTA pairs (tcgen05 cta_group::2,
  *                 persistent, two accumulators in tensor memory) (1) or on single CTAs (0,
  *                 default: faster on a B200);

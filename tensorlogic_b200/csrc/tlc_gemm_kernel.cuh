@@ -64,6 +64,12 @@ struct GemmParams {
     int max_pos;  // > 0: rows addressed by position are dropped from this position on (status TLC_DEV_INDEX)
     float rope_base;
     int vec_ok;  // strides, N and pointers allow 16-byte stores
+    // Split K (up to 128 activation rows, few weight tiles): CTA z of gridDim.z = ksplit takes a
+    // share of the K steps and stores its f32 accumulators to partial[z][row][noff + n] (rows of
+    // ntot floats; the SiLU.mul pair: gate at n, up at N + n); gemv_splitk_finish_kernel adds
+    // the shares and applies the epilogue.
+    float *partial;
+    int ksplit, ntot, noff;
     int a_tma;   // the activation tile arrives by TMA (tensor map in the second kernel argument)
     tlc_dev_status *status;
     uint64_t wait_ns;  // how long a wait may last before the kernel gives up

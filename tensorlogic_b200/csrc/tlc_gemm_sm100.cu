@@ -134,7 +134,8 @@ __device__ __forceinline__ void produce_b(const GemmParams &p, uint8_t *btiles, 
 template <int QT, int STAGES, int STAGE_BYTES>
 __device__ __forceinline__ void produce_b_alt(const GemmParams &p, uint8_t *btiles, uint64_t *full, uint64_t *empty,
                                               volatile int *abort_flag, const uint8_t *wbase, int wrow, int row, int KT,
-                                              int lane, int group) {
+                                              int lane, int group, int kt0) {
+    // KT: K steps of this CTA, the first one being step kt0 of the weight (split K)
     constexpr int TILE = QT == TLC_TYPE_Q4_0 ? 1152 : 1088;
     constexpr int PF = 2;                             // own steps fetched ahead
     constexpr int QW = QT == TLC_TYPE_Q4_0 ? 8 : 16;  // quant words of a row per K step
@@ -147,9 +148,10 @@ __device__ __forceinline__ void produce_b_alt(const GemmParams &p, uint8_t *btil
 #pragma unroll
     for (int j = 0; j < 8; j++) piece[j] = (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4));
     uint32_t qn[PF][QW], sn[PF];
-    auto fetch = [&](int kt, uint32_t (&qw)[QW], uint32_t &sc) {
+    auto fetch = [&](int kl, uint32_t (&qw)[QW], uint32_t &sc) {
+        const int kt = kt0 + kl;
         const int wt = QT == TLC_TYPE_Q4_0 ? kt >> 1 : kt;
-        const bool ok = row_ok && kt < KT && wt < p.k_tiles;
+        const bool ok = row_ok && kl < KT && wt < p.k_tiles;
         const uint8_t *tile = slab + (size_t)(ok ? wt : 0) * TILE;
         if (QT == TLC_TYPE_Q4_0) {
             const int half = kt & 1;  // which pair of the tile's four blocks
@@ -216,6 +218,20 @@ __device__ __forceinline__ void produce_b_alt(const GemmParams &p, uint8_t *btil
 // SW: the SiLU.mul pair.  The weight tile holds 128 rows of the gate weight (tile rows
 // 0-127) and the same 128 rows of the up weight (tile rows 128-255); the epilogue reads
 // both accumulators and stores silu(gate) * up for the 128 output columns of the CTA.
+// 32 consecutive f32 accumulators of one activation row to the split-K partial sums.
+__device__ __forceinline__ void store_partial(float *dst, const uint32_t (&r)[32], bool ok, bool vec, int left) {
+    if (!ok) return;
+    if (vec) {
+#pragma unroll
+        for (int v = 0; v < 8; v++)
+            *reinterpret_cast<uint4 *>(dst + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            if (e < left) dst[e] = __uint_as_float(r[e]);
+    }
+}
+
 // PG: producer groups.  1: the 4*NT producer warps fill every K step.  2: twice the warps, each
 // group every other step (produce_b_alt) -- for tiles of one activation sub-tile, where the
 // producers and not the MMAs set the pace.
@@ -241,7 +257,15 @@ __global__ void __launch_bounds__(gemm_threads(NT, PG), 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * (SW ? 128 : BN), m0 = blockIdx.y * 128 * MT;
-    const int KT = (p.k + kBK - 1) / kBK;  // K is a multiple of 32: the last step may hold one block only
+    const int KT_all = (p.k + kBK - 1) / kBK;  // K is a multiple of 32: the last step may hold one block only
+    // split K (two-group form only): this CTA's share of the K steps, never empty
+    int kt0 = 0, KT = KT_all;
+    const bool split = PG == 2 && p.ksplit > 1;
+    if (split) {
+        const int per = (KT_all + p.ksplit - 1) / p.ksplit;
+        kt0 = (int)blockIdx.z * per;
+        KT = KT_all - kt0 < per ? KT_all - kt0 : per;
+    }
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
@@ -274,7 +298,7 @@ __global__ void __launch_bounds__(gemm_threads(NT, PG), 1)
             produce_b<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, wbase, wrow, trow, KT, lane);
         else
             produce_b_alt<QT, kStages, STAGE_BYTES>(p, tiles + A_BYTES, full, empty, abort_flag, wbase, wrow, trow, KT,
-                                                    lane, (tid - 128) / BN);
+                                                    lane, (tid - 128) / BN, kt0);
     } else if (warp < 4 && p.a_tma) {
         // ------------------------------ A tile by TMA ------------------------------
         // One thread issues, per K step, MT boxes of 128 rows x 64 columns with the 128-byte
@@ -290,7 +314,7 @@ __global__ void __launch_bounds__(gemm_threads(NT, PG), 1)
                 mbar_arrive_expect_tx(&full[s], A_BYTES);
 #pragma unroll
                 for (int i = 0; i < MT; i++)
-                    tma_load_2d(abase + i * (128 * 128), &x_map, j * kBK, m0 + 128 * i, bar);
+                    tma_load_2d(abase + i * (128 * 128), &x_map, (kt0 + j) * kBK, m0 + 128 * i, bar);
             }
         }
         __syncwarp();  // the other lanes of warp 0 sleep here instead of polling beside the issuer
@@ -305,8 +329,8 @@ __global__ void __launch_bounds__(gemm_threads(NT, PG), 1)
             for (int it = 0; it < 8 * MT; it++) {
                 const int row = it * 16 + (tid >> 3), c = tid & 7;
                 // rows past M and, in a last step of one block, columns past K are zero-filled
-                const bool ok = m0 + row < p.m && j * kBK + c * 8 < p.k;
-                const __half *src = p.x + (ok ? (size_t)(m0 + row) * p.k + (size_t)j * kBK + c * 8 : 0);
+                const bool ok = m0 + row < p.m && (kt0 + j) * kBK + c * 8 < p.k;
+                const __half *src = p.x + (ok ? (size_t)(m0 + row) * p.k + (size_t)(kt0 + j) * kBK + c * 8 : 0);
                 cp_async16(abase + row * 128 + ((c ^ (row & 7)) << 4), src, ok);
             }
         };
@@ -376,6 +400,18 @@ __global__ void __launch_bounds__(gemm_threads(NT, PG), 1)
             __half *ybase = p.y + (size_t)((long long)row * p.row_stride + (long long)pos * p.pos_stride);
             uint32_t r[32];
             tmem_ld32(tmem_base + ((uint32_t)(32 * wq) << 16) + (uint32_t)(BN * i + c0), r);
+            if (split) {
+                // this CTA's f32 share; the finishing kernel rounds and applies the epilogue
+                float *dst = p.partial + ((size_t)blockIdx.z * p.m + (row < p.m ? row : 0)) * p.ntot + p.noff + n0 + c0;
+                const bool ok = row < p.m && n0 + c0 < p.n;
+                const bool vec = ok && n0 + c0 + 32 <= p.n && ((p.ntot | p.noff | p.n) & 3) == 0;
+                store_partial(dst, r, ok, vec, p.n - (n0 + c0));
+                if (SW) {
+                    tmem_ld32(tmem_base + ((uint32_t)(32 * wq) << 16) + (uint32_t)(BN * i + 128 + c0), r);
+                    store_partial(dst + p.n, r, ok, vec, p.n - (n0 + c0));
+                }
+                continue;
+            }
             if (SW) {
                 // s = sigmoid(g) (f32, RNE); a = g*s; act = a*u: three f16 roundings as in
                 // debug/chat_demo_with_kvcache.tl:26-41 (the GEMV's SiLU.mul epilogue does the same)
@@ -408,8 +444,13 @@ int32_t launch_tile_pg(tlc_ctx *ctx, const GemmParams &p) {
         configured[ctx->device & 63] = true;
     }
     const int out_cols = SW ? 128 : 128 * NT;  // output columns per CTA
-    const dim3 grid((unsigned)((p.n + out_cols - 1) / out_cols), (unsigned)((p.m + 128 * MT - 1) / (128 * MT)));
     GemmParams q = p;
+    if (PG != 2 || q.ksplit < 2) {  // split K exists in the two-group form only
+        q.ksplit = 1;
+        q.partial = nullptr;
+    }
+    const dim3 grid((unsigned)((p.n + out_cols - 1) / out_cols), (unsigned)((p.m + 128 * MT - 1) / (128 * MT)),
+                    (unsigned)q.ksplit);
     CUtensorMap x_map;
     memset(&x_map, 0, sizeof x_map);
     q.a_tma = ctx->gemm_tma && encode_x_map(&x_map, p) ? 1 : 0;
@@ -423,12 +464,13 @@ int32_t launch_tile_pg(tlc_ctx *ctx, const GemmParams &p) {
     return TLC_OK;
 }
 
-// One activation sub-tile per CTA: the producers set the pace, two producer groups (option
-// "gemm_pg": 0 = this rule, 1 or 2 = forced).  Two sub-tiles: the MMAs do, one group.
+// Two producer groups (the form split K exists in) when the K steps of a tile are shared out, or
+// when option "gemm_pg" = 2 forces them; one group otherwise (1 = forced, and no split K).  On
+// unsplit launches two groups measured no faster (8192 -> 28672, 32 rows: 86 against 80 us).
 template <int QT, int MT, int NT, bool SW = false>
 int32_t launch_tile(tlc_ctx *ctx, const GemmParams &p) {
-    const bool two = ctx->gemm_pg == 2 || (ctx->gemm_pg == 0 && MT == 1);
-    if (MT == 1 && two) return launch_tile_pg<QT, 1, NT, SW, 2>(ctx, p);
+    const bool two = MT == 1 && (ctx->gemm_pg == 2 || (ctx->gemm_pg == 0 && p.ksplit > 1));
+    if (two) return launch_tile_pg<QT, 1, NT, SW, 2>(ctx, p);
     return launch_tile_pg<QT, MT, NT, SW, 1>(ctx, p);
 }
 
@@ -478,9 +520,36 @@ inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 }  // namespace
 
-size_t tlc_gemm_scratch_bytes(int m, int64_t k, int64_t n_swiglu) {
-    (void)n_swiglu;  // the SiLU.mul pair is fused into the GEMM epilogue and needs no scratch
-    return align256((size_t)m * k * 2);
+// Split K for the GEMM: with at most 128 activation rows a weight of few rows gives few CTAs (a
+// 2048-row projection: eight), each walking all of K at the producers' pace.  The K steps are
+// then shared out over gridDim.z CTAs per tile, enough to fill the SMs, at least eight steps
+// each; f32 shares go to scratch and gemv_splitk_finish_kernel finishes.  `tiles`: weight tiles
+// of 256 rows over all outputs of the call.  1: no split.
+static int gemm_choose_ksplit(const tlc_ctx *ctx, int m, int64_t k, int64_t tiles) {
+    if (!ctx->gemm_splitk || m > 128 || ctx->gemm_pg == 1 || ctx->gemm_tile == 22 || tiles < 1) return 1;
+    const int KT = (int)((k + kBK - 1) / kBK);
+    int64_t ks = ctx->sm_count / tiles;
+    if (ks > KT / 8) ks = KT / 8;
+    if (ks > 16) ks = 16;
+    if (ks < 2) return 1;
+    const int per = (KT + (int)ks - 1) / (int)ks;
+    return (KT + per - 1) / per;  // no empty share
+}
+static int64_t gemm_tiles(const tlc_gemv_args &a) {
+    if (a.epilogue == TLC_EPI_SWIGLU) return (a.outs[0].w->n_rows + 127) / 128;
+    int64_t t = 0;
+    for (int i = 0; i < a.n_out; i++) t += (a.outs[i].w->n_rows + 255) / 256;
+    return t;
+}
+
+// Context scratch the GEMM form of a linear over m rows of width k with n_total outputs (all
+// outputs of a fused call; the SiLU.mul pair counts twice) may need: the normalized rows and
+// the split-K partial sums.  Callers that capture graphs reserve it up front.
+size_t tlc_gemm_scratch_bytes(const tlc_ctx *ctx, int m, int64_t k, int64_t n_total) {
+    const int mp = m < 128 ? m : 128;
+    // the fewest tiles n_total outputs can have bound the split from above
+    const int ks = gemm_choose_ksplit(ctx, mp, k, (n_total + 255) / 256 > 0 ? (n_total + 255) / 256 : 1);
+    return align256((size_t)m * k * 2) + (ks > 1 ? align256((size_t)ks * mp * (size_t)n_total * sizeof(float)) : 0);
 }
 
 bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a) {
@@ -493,6 +562,8 @@ bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a) {
     // Below 17 rows one GEMV pass reads the weights once.  Up to 48 rows the
     // GEMV's few passes still win unless the weight has enough 128-row tiles
     // to occupy half of the SMs.
+    // With split K the few CTAs of a narrow weight share K, and the GEMM wins from 17 rows on.
+    if (gemm_choose_ksplit(ctx, a.m, w0->n_cols, gemm_tiles(a)) > 1) return a.m > 16;
     int64_t tiles = 0;
     for (int i = 0; i < a.n_out; i++) tiles = tiles < (a.outs[i].w->n_rows + 128 - 1) / 128 ? (a.outs[i].w->n_rows + 128 - 1) / 128 : tiles;
     return a.m > (tiles * 2 >= ctx->sm_count ? 16 : 48);
@@ -507,9 +578,15 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
     const int64_t k = w0->n_cols;
     const bool swiglu = a.epilogue == TLC_EPI_SWIGLU;
     const size_t norm_bytes = a.norm_w ? align256((size_t)a.m * k * 2) : 0;
-    if (norm_bytes > 0)
-        if (int32_t rc = tlc_scratch_reserve(ctx, norm_bytes)) return rc;
+    const int ksplit = gemm_choose_ksplit(ctx, a.m, k, gemm_tiles(a));
+    int64_t ntot = 0;
+    for (int i = 0; i < a.n_out; i++) ntot += a.outs[i].w->n_rows;
+    const size_t part_bytes = ksplit > 1 ? align256((size_t)ksplit * a.m * (size_t)ntot * sizeof(float)) : 0;
+    if (norm_bytes + part_bytes > 0)
+        if (int32_t rc = tlc_scratch_reserve(ctx, norm_bytes + part_bytes)) return rc;
     uint8_t *scratch = static_cast<uint8_t *>(ctx->scratch);
+    float *partial = ksplit > 1 ? reinterpret_cast<float *>(scratch + norm_bytes) : nullptr;
+    int noff = 0;
     const __half *x = static_cast<const __half *>(a.x);
     if (a.norm_w) {
         if (int32_t rc = tlc_rms_norm(ctx, a.x, a.norm_w, scratch, a.m, (int32_t)k, a.eps)) return rc;
@@ -549,7 +626,13 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
         p.rope_base = (float)a.rope_base;
         p.vec_ok = ((p.row_stride | p.pos_stride | (long long)p.n) & 7) == 0 && ((uintptr_t)p.y & 15) == 0 &&
                    ((uintptr_t)p.residual & 15) == 0;
+        p.partial = partial;
+        p.ksplit = ksplit;
+        p.ntot = (int)ntot;
+        p.noff = noff;
+        noff += p.n;
         if (int32_t rc = launch_one(ctx, p, w->type)) return rc;
     }
+    if (ksplit > 1) return tlc_gemv_splitk_finish(ctx, a, ksplit, partial);
     return TLC_OK;
 }

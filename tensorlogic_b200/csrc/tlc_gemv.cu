@@ -223,6 +223,7 @@ __global__ void __launch_bounds__(256) gemv_splitk_finish_kernel(const GemvParam
     const int noff = nn - n;
     auto sum = [&](int off) {
         float v = 0.f;
+#pragma unroll 4
         for (int w = 0; w < p.ksplit; w++) v += p.partial[((size_t)w * p.m + col) * p.ntot + off];
         return v;
     };
@@ -462,6 +463,43 @@ size_t tlc_gemv_scratch_bytes(tlc_ctx *ctx, int type, int64_t k, int m, int64_t 
             ks = c > ks ? c : ks;
         }
     return ks > 1 ? (size_t)ks * m * (size_t)n_total * sizeof(float) : 0;
+}
+
+int32_t tlc_gemv_splitk_finish(tlc_ctx *ctx, const tlc_gemv_args &a, int ksplit, float *partial) {
+    GemvParams p{};
+    p.n_out = a.n_out;
+    p.ntot = 0;
+    for (int i = 0; i < a.n_out; i++) {
+        const tlc_qtensor *w = a.outs[i].w;
+        p.t[i].n = (int)w->n_rows;
+        p.t[i].row_stride = a.outs[i].row_stride >= 0 ? a.outs[i].row_stride : (long long)w->n_rows;
+        p.t[i].pos_stride = a.outs[i].pos_stride;
+        p.t[i].y = static_cast<__half *>(a.outs[i].y);
+        p.t[i].rope_heads = a.outs[i].rope_heads;
+        p.t[i].head_dim = a.outs[i].rope_heads > 0 ? (int)(w->n_rows / a.outs[i].rope_heads) : 0;
+        p.ntot += p.t[i].n;
+    }
+    p.subs = a.epilogue == TLC_EPI_SWIGLU ? 2 : 1;
+    p.m = a.m;
+    p.epilogue = a.epilogue;
+    p.bias = static_cast<const __half *>(a.bias);
+    p.residual = static_cast<const __half *>(a.residual);
+    p.pos_offset = a.pos_offset;
+    p.rope_base = (float)a.rope_base;
+    p.positions = a.positions;
+    p.max_pos = a.max_pos;
+    p.status = ctx->dev_status;
+    p.ksplit = ksplit;
+    p.partial = partial;
+    const int nout = p.subs == 2 ? p.t[0].n : p.ntot;
+    const size_t total = (size_t)a.m * nout;
+    cudaError_t le = tlc_launch_pdl(ctx, gemv_splitk_finish_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, p);
+    if (le != cudaSuccess) {
+        cudaGetLastError();
+        return tlc_fail(TLC_ERR_CUDA, "split-K finish launch failed: %s", cudaGetErrorString(le));
+    }
+    TLC_CHECK_LAUNCH(ctx);
+    return TLC_OK;
 }
 
 int32_t tlc_launch_gemv(tlc_ctx *ctx, const tlc_gemv_args &a) {

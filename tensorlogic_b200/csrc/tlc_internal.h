@@ -67,7 +67,8 @@ struct tlc_ctx {
     // sets the status word and drains; option "wait_limit_ms".
     uint64_t wait_ns = 2000000000ull;
     bool gemm_pair = false;  // GEMM tiles of 256 x 256 on CTA pairs (tcgen05 cta_group::2) from 129 rows on; measured slower
-    int gemm_pg = 0;  // producer groups of the GEMM: 0 = two for one-sub-tile CTAs, else one; 1 / 2 = forced
+    bool gemm_splitk = true;  // GEMMs of up to 128 rows and few weight tiles share K over several CTAs per tile
+    int gemm_pg = 0;  // producer groups of the GEMM: 0 = two where K is shared out over CTAs, else one; 1 / 2 = forced
     bool gemm_tma = true;  // activation tiles of the GEMM by TMA (false: cp.async loader warps)
     int gemm_tile = 0;  // 0: pick the GEMM tile from the shape; 11, 12, 22: force 128x128, 128x256, 256x256
     // Option "gemv_f8" / TLC_GEMV_F8=1: one activation row against a Q4_0 weight takes the FP8-limb
@@ -232,7 +233,9 @@ bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a);
 int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a);
 // Scratch the GEMM path needs for m rows of width k with a fused RMSNorm and a
 // SiLU.mul pair of n_swiglu outputs (reserve it before capturing a graph).
-size_t tlc_gemm_scratch_bytes(int m, int64_t k, int64_t n_swiglu);
+size_t tlc_gemm_scratch_bytes(const tlc_ctx *ctx, int m, int64_t k, int64_t n_total);
+// Adds the ksplit f32 shares in partial[ksplit][m][sum of N] and applies the epilogue of `a` (tlc_gemv.cu).
+int32_t tlc_gemv_splitk_finish(tlc_ctx *ctx, const tlc_gemv_args &a, int ksplit, float *partial);
 // Scratch the fused GEMV may need for m rows (split-K partial sums; 0 when it does not split).
 size_t tlc_gemv_scratch_bytes(tlc_ctx *ctx, int type, int64_t k, int m, int64_t n_total);
 

@@ -490,7 +490,16 @@ extern "C" int32_t tlc_llama_create(tlc_ctx *ctx, tlc_model *model, const tlc_ll
     // reserve it now so that no allocation happens inside a graph capture.
     {
         const int64_t kmax = d > qd ? d : qd;
-        if (int32_t rc = tlc_scratch_reserve(ctx, tlc_gemm_scratch_bytes(L->max_rows, kmax, L->ffn_local))) return rc;
+        {
+            const int64_t shapes[][2] = {{d, qd + 2 * kvd}, {qd, d}, {d, 2 * (int64_t)L->ffn_local}, {L->ffn_local, d},
+                                         {d, L->vocab_local}};
+            size_t need = tlc_gemm_scratch_bytes(ctx, L->max_rows, kmax, 0);
+            for (auto &sh : shapes) {
+                const size_t b = tlc_gemm_scratch_bytes(ctx, L->max_rows, sh[0], sh[1]);
+                need = b > need ? b : need;
+            }
+            if (int32_t rc = tlc_scratch_reserve(ctx, need)) return rc;
+        }
         // ... and the split-K partial sums of the batched decode GEMVs
         const int qt0 = L->layers[0].wq->type;
         size_t need = 0;

@@ -150,6 +150,35 @@ def test_cta_pair_tiles(dev, ref, qtype, n, k, m):
         assert np.array_equal(_bits(yt), _bits(ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]))
 
 
+@pytest.mark.parametrize("qtype", [Q4, Q8])
+@pytest.mark.parametrize("n,k,m", [(512, 2048, 100), (200, 4096, 37), (2048, 8192, 128), (96, 1088, 64), (300, 1056, 17)])
+def test_gemm_split_k(dev, ref, qtype, n, k, m):
+    """Up to 128 rows against a weight of few tiles: the K steps are shared out over several CTAs
+    per tile (f32 shares in scratch, one finishing kernel).  Same answer as the oracle and as the
+    unsplit GEMM (option gemm_splitk = 0); ragged N, K with a last step of one block, uneven shares."""
+    from tensorlogic_b200.api import QTensor, linear
+    raw = _weights(qtype, n, k, seed=21, name=f"s{n}x{k}")
+    x = _x(m, k, seed=21, name=f"sx{m}x{k}")
+    w = QTensor.from_blocks(dev, qtype, n, k, raw)
+    want = ref.linear_q(qtype, raw, n, k, x)
+    with gemm_from(dev, 1):
+        l0 = dev.launch_count
+        y = linear(dev.tensor(x), w).numpy()
+        launches = dev.launch_count - l0
+        yt = linear(dev.tensor(np.eye(k, dtype=np.float16)[:m]), w).numpy()
+        dev.set_option("gemm_splitk", 0)
+        try:
+            l0 = dev.launch_count
+            y1 = linear(dev.tensor(x), w).numpy()
+            assert dev.launch_count - l0 == 1
+        finally:
+            dev.set_option("gemm_splitk", 1)
+    assert launches == 2, launches            # the GEMM with K shared out + the finishing kernel
+    assert rel_l2(y, want) < TIGHT and rel_l2(y1, want) < TIGHT
+    assert rel_l2(y, y1) < 1e-4
+    assert np.array_equal(_bits(yt), _bits(ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]))
+
+
 def test_automatic_tile_choice_large(dev, ref):
     """Shapes large enough that the launcher picks the wide tiles by itself."""
     from tensorlogic_b200.api import QTensor, linear
@@ -209,10 +238,16 @@ def test_fused_contract_on_cta_pairs(dev, ref, qtype):
         dev.set_option("gemm_pair", 0)
 
 
-def _fused_contract(dev, qtype, m):
+@pytest.mark.parametrize("qtype", [Q4, Q8])
+def test_fused_contract_on_split_k_gemm(dev, ref, qtype):
+    """The same contract with K = 2048 and 45 rows: every GEMM of it shares K over several CTAs."""
+    _fused_contract(dev, qtype, 45, d=2048)
+
+
+def _fused_contract(dev, qtype, m, d=256):
     from tensorlogic_b200 import synth
     from tensorlogic_b200.api import QTensor, linear, linear_residual, norm_linear_multi, swiglu_gate_up
-    d, heads, kvh, hd, ffn = 256, 4, 2, 64, 384
+    heads, kvh, hd, ffn = 4, 2, 64, 384
     wq = QTensor.from_blocks(dev, qtype, heads * hd, d, _weights(qtype, heads * hd, d, 16, "q"))
     wk = QTensor.from_blocks(dev, qtype, kvh * hd, d, _weights(qtype, kvh * hd, d, 16, "k"))
     wv = QTensor.from_blocks(dev, qtype, kvh * hd, d, _weights(qtype, kvh * hd, d, 16, "v"))
