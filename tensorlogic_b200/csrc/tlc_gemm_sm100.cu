@@ -522,18 +522,30 @@ inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 // Split K for the GEMM: with at most 128 activation rows a weight of few rows gives few CTAs (a
 // 2048-row projection: eight), each walking all of K at the producers' pace.  The K steps are
-// then shared out over gridDim.z CTAs per tile, enough to fill the SMs, at least eight steps
-// each; f32 shares go to scratch and gemv_splitk_finish_kernel finishes.  `tiles`: weight tiles
-// of 256 rows over all outputs of the call.  1: no split.
-static int gemm_choose_ksplit(const tlc_ctx *ctx, int m, int64_t k, int64_t tiles) {
+// then shared out over gridDim.z CTAs per tile, at most enough to fill the SMs, at least eight
+// steps each; f32 shares go to scratch and gemv_splitk_finish_kernel finishes.  `tiles`: weight
+// tiles of 256 rows over all outputs of the call, `n_total`: their output columns.  1: no split.
+static int gemm_choose_ksplit(const tlc_ctx *ctx, int m, int64_t k, int64_t tiles, int64_t n_total) {
     if (!ctx->gemm_splitk || m > 128 || ctx->gemm_pg == 1 || ctx->gemm_tile == 22 || tiles < 1) return 1;
     const int KT = (int)((k + kBK - 1) / kBK);
-    int64_t ks = ctx->sm_count / tiles;
-    if (ks > KT / 8) ks = KT / 8;
-    if (ks > 16) ks = 16;
-    if (ks < 2) return 1;
-    const int per = (KT + (int)ks - 1) / (int)ks;
-    return (KT + per - 1) / per;  // no empty share
+    int64_t ks_max = ctx->sm_count / tiles;
+    if (ks_max > KT / 8) ks_max = KT / 8;
+    if (ks_max > 16) ks_max = 16;
+    // Cost in microseconds: K steps of a CTA at 0.45 us, plus, when split, the finishing launch and
+    // the f32 shares written and read back (about 3 TB/s through the L2).  128 rows of a
+    // 2048 -> 8192 projection are faster unsplit (18 against 28 us), 32 rows split (18 against 30 us).
+    int best = 1;
+    double best_t = KT * 0.45;
+    for (int ks = 2; ks <= ks_max; ks++) {
+        const int per = (KT + ks - 1) / ks;
+        if ((KT + per - 1) / per != ks) continue;  // a share would be empty
+        const double t = per * 0.45 + 4.0 + (double)ks * m * (double)n_total * 8.0 / 3.0e6;
+        if (t < best_t) {
+            best_t = t;
+            best = ks;
+        }
+    }
+    return best;
 }
 static int64_t gemm_tiles(const tlc_gemv_args &a) {
     if (a.epilogue == TLC_EPI_SWIGLU) return (a.outs[0].w->n_rows + 127) / 128;
@@ -547,8 +559,17 @@ static int64_t gemm_tiles(const tlc_gemv_args &a) {
 // the split-K partial sums.  Callers that capture graphs reserve it up front.
 size_t tlc_gemm_scratch_bytes(const tlc_ctx *ctx, int m, int64_t k, int64_t n_total) {
     const int mp = m < 128 ? m : 128;
-    // the fewest tiles n_total outputs can have bound the split from above
-    const int ks = gemm_choose_ksplit(ctx, mp, k, (n_total + 255) / 256 > 0 ? (n_total + 255) / 256 : 1);
+    // the most shares any row count and any tiling of n_total outputs can get, whatever the options
+    // say when the launch comes
+    int ks = 1;
+    {
+        const int KT = (int)((k + kBK - 1) / kBK);
+        const int64_t tiles = (n_total + 255) / 256 > 0 ? (n_total + 255) / 256 : 1;
+        int64_t ks_max = ctx->sm_count / tiles;
+        if (ks_max > KT / 8) ks_max = KT / 8;
+        if (ks_max > 16) ks_max = 16;
+        if (ks_max > 1) ks = (int)ks_max;
+    }
     return align256((size_t)m * k * 2) + (ks > 1 ? align256((size_t)ks * mp * (size_t)n_total * sizeof(float)) : 0);
 }
 
@@ -563,7 +584,9 @@ bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a) {
     // GEMV's few passes still win unless the weight has enough 128-row tiles
     // to occupy half of the SMs.
     // With split K the few CTAs of a narrow weight share K, and the GEMM wins from 17 rows on.
-    if (gemm_choose_ksplit(ctx, a.m, w0->n_cols, gemm_tiles(a)) > 1) return a.m > 16;
+    int64_t n_total = 0;
+    for (int i = 0; i < a.n_out; i++) n_total += a.outs[i].w->n_rows;
+    if (gemm_choose_ksplit(ctx, a.m, w0->n_cols, gemm_tiles(a), n_total) > 1) return a.m > 16;
     int64_t tiles = 0;
     for (int i = 0; i < a.n_out; i++) tiles = tiles < (a.outs[i].w->n_rows + 128 - 1) / 128 ? (a.outs[i].w->n_rows + 128 - 1) / 128 : tiles;
     return a.m > (tiles * 2 >= ctx->sm_count ? 16 : 48);
@@ -578,9 +601,9 @@ int32_t tlc_launch_gemm(tlc_ctx *ctx, const tlc_gemv_args &a) {
     const int64_t k = w0->n_cols;
     const bool swiglu = a.epilogue == TLC_EPI_SWIGLU;
     const size_t norm_bytes = a.norm_w ? align256((size_t)a.m * k * 2) : 0;
-    const int ksplit = gemm_choose_ksplit(ctx, a.m, k, gemm_tiles(a));
     int64_t ntot = 0;
     for (int i = 0; i < a.n_out; i++) ntot += a.outs[i].w->n_rows;
+    const int ksplit = gemm_choose_ksplit(ctx, a.m, k, gemm_tiles(a), ntot);
     const size_t part_bytes = ksplit > 1 ? align256((size_t)ksplit * a.m * (size_t)ntot * sizeof(float)) : 0;
     if (norm_bytes + part_bytes > 0)
         if (int32_t rc = tlc_scratch_reserve(ctx, norm_bytes + part_bytes)) return rc;
