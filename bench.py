@@ -723,9 +723,13 @@ def run_allreduce(args, rank: int, world: int, local: int) -> None:
         return o
     comm.enable_p2p(max(n, 16 * 8192), gather)
     us_p2p = timed()
+    dev.set_option("comm_ll", 0)
+    us_fenced = timed()
+    dev.set_option("comm_ll", 1)
     if rank == 0:
         print(json.dumps({"kernel": "allreduce_residual", "n": n, "n_gpus": world, "calls": 100 * args.steps,
-                          "us_per_call_peer_memory_kernel": us_p2p, "us_per_call_nccl_plus_add": us_nccl,
+                          "us_per_call_peer_memory_flagged_words": us_p2p,
+                          "us_per_call_peer_memory_fences_and_flags": us_fenced, "us_per_call_nccl_plus_add": us_nccl,
                           "note": "back-to-back calls from the host, nothing else on the stream; max over ranks"}),
               flush=True)
     dev.synchronize()

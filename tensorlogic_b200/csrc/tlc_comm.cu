@@ -93,7 +93,11 @@ constexpr int kP2pChunks = 8;
 constexpr int kP2pMaxWorld = 8;
 constexpr size_t kP2pFlagsOffset = 0;     // uint32 [world][kP2pChunks], written by peers
 constexpr size_t kP2pSeqOffset = 1024;    // uint32 [kP2pChunks], local
+constexpr size_t kP2pLLSeqOffset = 2048;  // uint32 [kP2pLLMaxCtas], local: the flagged-word form's call counters
 constexpr size_t kP2pDataOffset = 4096;   // f16 [2][world][max_elems], written by peers
+// then, 256-byte aligned: {f16 x 2, flag} [2][world][ll_cap / 2], written by peers (flagged-word form)
+constexpr uint32_t kP2pLLMaxElems = 65536;  // longest vector the flagged-word form takes
+constexpr int kP2pLLMaxCtas = kP2pLLMaxElems / (4 * 256);
 
 struct P2pParams {
     uint8_t *peer[kP2pMaxWorld];  // exchange blocks, peer[rank] is the local one
@@ -102,6 +106,8 @@ struct P2pParams {
     __half *out;                  // [n]
     int rank, world;
     uint32_t n, max_elems;
+    size_t ll_off;    // byte offset of the flagged-word slots in an exchange block
+    uint32_t ll_cap;  // elements per flagged-word slot
     tlc_dev_status *status;
     uint64_t wait_ns;  // how long the wait for the peers may last
 };
@@ -192,6 +198,91 @@ __global__ void __launch_bounds__(256) allreduce_residual_kernel(const P2pParams
     if (tid == 0) *seq = s;
 }
 
+
+// ---------------------------------------------------------------------------
+// The same all-reduce + residual for short vectors (a decode step's [M, d] partial sums up to
+// 64 Ki values) without any fence or separate flag: every 4 bytes of data (two f16) travel in
+// one 8-byte store together with the call's sequence number, and the receiver polls the very
+// words it needs until they carry that number (the scheme of NCCL's LL protocol).  An 8-byte
+// aligned store arrives whole, so a word whose flag matches holds this call's data.  Latency
+// is one store across NVLink plus the poll, against two system-scope fences and a flag hop in
+// the kernel above.  A thread owns four values: it sends them as one 16-byte store (two
+// flagged words) to every peer, polls the peers' words for the same four values in its own
+// block, sums in rank order in f32, rounds once, adds the residual.  Two slots alternate by
+// the parity of the sequence number, as above.  Every poll is bounded.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void st_volatile_v4(void *p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(256) allreduce_ll_kernel(const P2pParams p) {
+    tlc_pdl_prologue();  // the partial sums come from the previous kernel of the stream
+    uint8_t *local = p.peer[p.rank];
+    uint32_t *seq = reinterpret_cast<uint32_t *>(local + kP2pLLSeqOffset) + blockIdx.x;
+    const uint32_t s = *seq + 1;  // the first call carries 1: a zero-initialised slot matches no call; later a slot holds s - 2
+    const uint32_t parity = s & 1u;
+    const uint32_t i = 4u * (blockIdx.x * blockDim.x + threadIdx.x);  // first of this thread's four values
+    if (i < p.n) {
+        const uint2 mine = *reinterpret_cast<const uint2 *>(p.partial + i);
+        // byte offset of values i .. i+3 in slot [parity][rank]: 4 bytes per value (2 of data, 2 of flag)
+        const size_t word = (size_t)i * 4;
+        const size_t slot_bytes = (size_t)p.ll_cap * 4;
+        const uint4 packet = make_uint4(mine.x, s, mine.y, s);
+        for (int r = 0; r < p.world; r++)
+            if (r != p.rank) st_volatile_v4(p.peer[r] + p.ll_off + ((size_t)parity * p.world + p.rank) * slot_bytes + word, packet);
+        uint2 got[kP2pMaxWorld];
+        bool ok = true;
+        for (int r = 0; r < p.world && ok; r++) {
+            if (r == p.rank) {
+                got[r] = mine;
+                continue;
+            }
+            const uint8_t *src = local + p.ll_off + ((size_t)parity * p.world + r) * slot_bytes + word;
+            uint4 v = ld_volatile_v4(src);
+            if (v.y != s || v.w != s) {
+                const uint64_t t0 = tlc_globaltimer_ns();
+                do {
+                    v = ld_volatile_v4(src);
+                } while ((v.y != s || v.w != s) && tlc_globaltimer_ns() - t0 < p.wait_ns);
+                if (v.y != s || v.w != s) {
+                    ok = false;
+                    if (atomicCAS(&p.status->code, 0, 3) == 0) p.status->where = 120 + r;
+                }
+            }
+            got[r] = make_uint2(v.x, v.z);
+        }
+        if (ok) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < p.world; r++) {  // rank order: every rank computes the same bits
+                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&got[r].x));
+                const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&got[r].y));
+                acc[0] += a.x;
+                acc[1] += a.y;
+                acc[2] += b.x;
+                acc[3] += b.y;
+            }
+            __align__(8) __half o[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) o[j] = __float2half_rn(acc[j]);
+            if (p.residual) {
+                const uint2 rv = *reinterpret_cast<const uint2 *>(p.residual + i);
+                const __half *rh = reinterpret_cast<const __half *>(&rv);
+#pragma unroll
+                for (int j = 0; j < 4; j++) o[j] = __hadd(rh[j], o[j]);
+            }
+            *reinterpret_cast<uint2 *>(p.out + i) = *reinterpret_cast<const uint2 *>(o);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *seq = s;
+}
+
 __global__ void add_f16_kernel(const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ y,
                                size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -208,6 +299,8 @@ struct tlc_comm {
     uint8_t *p2p_local = nullptr;
     uint8_t *p2p_peer[kP2pMaxWorld] = {};
     size_t p2p_max_elems = 0;
+    size_t p2p_ll_off = 0;  // flagged-word slots of the exchange block
+    uint32_t p2p_ll_cap = 0;
     bool p2p_ready = false;
 };
 
@@ -306,7 +399,9 @@ extern "C" int32_t tlc_comm_p2p_export(tlc_comm *comm, size_t max_elems, void *h
     TLC_REQUIRE(max_elems > 0 && max_elems % 8 == 0, TLC_ERR_INVALID_DIMENSION,
                 "comm_p2p_export: capacity %zu is not a positive multiple of 8", max_elems);
     static_assert(sizeof(cudaIpcMemHandle_t) == TLC_IPC_HANDLE_BYTES, "IPC handle size");
-    const size_t bytes = kP2pDataOffset + (size_t)2 * comm->world * max_elems * sizeof(__half);
+    const size_t ll_off = (kP2pDataOffset + (size_t)2 * comm->world * max_elems * sizeof(__half) + 255) & ~(size_t)255;
+    const uint32_t ll_cap = (uint32_t)(max_elems < kP2pLLMaxElems ? max_elems : kP2pLLMaxElems);
+    const size_t bytes = ll_off + (size_t)2 * comm->world * ll_cap * 4;
     void *blk = nullptr;
     cudaError_t e = cudaMalloc(&blk, bytes);
     if (e != cudaSuccess) {
@@ -325,6 +420,8 @@ extern "C" int32_t tlc_comm_p2p_export(tlc_comm *comm, size_t max_elems, void *h
     memcpy(handle_out, &h, sizeof(h));
     comm->p2p_local = static_cast<uint8_t *>(blk);
     comm->p2p_max_elems = max_elems;
+    comm->p2p_ll_off = ll_off;
+    comm->p2p_ll_cap = ll_cap;
     return TLC_OK;
 }
 
@@ -382,7 +479,12 @@ extern "C" int32_t tlc_allreduce_residual_f16(tlc_ctx *ctx, tlc_comm *comm, void
         p.max_elems = (uint32_t)comm->p2p_max_elems;
         p.status = ctx->dev_status;
         p.wait_ns = ctx->wait_ns;
-        cudaError_t le = tlc_launch_pdl(ctx, allreduce_residual_kernel, dim3(kP2pChunks), dim3(256), 0, p);
+        p.ll_off = comm->p2p_ll_off;
+        p.ll_cap = comm->p2p_ll_cap;
+        // short vectors: data and flag in one word, no fences (option "comm_ll")
+        const bool ll = ctx->comm_ll && count <= comm->p2p_ll_cap && ((uintptr_t)partial_dev | (uintptr_t)out_dev | (uintptr_t)residual_dev) % 8 == 0;
+        cudaError_t le = ll ? tlc_launch_pdl(ctx, allreduce_ll_kernel, dim3((unsigned)((count / 4 + 255) / 256)), dim3(256), 0, p)
+                            : tlc_launch_pdl(ctx, allreduce_residual_kernel, dim3(kP2pChunks), dim3(256), 0, p);
         if (le != cudaSuccess) {
             cudaGetLastError();
             return tlc_fail(TLC_ERR_CUDA, "all-reduce launch failed: %s", cudaGetErrorString(le));

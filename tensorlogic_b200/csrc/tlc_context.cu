@@ -78,6 +78,7 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (const char *e = getenv("TLC_PDL_SMALL")) ctx->pdl_small = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMM_MIN_M")) ctx->gemm_min_m = atoi(e);
     if (const char *e = getenv("TLC_GEMM_PAIR")) ctx->gemm_pair = atoi(e) != 0;
+    if (const char *e = getenv("TLC_COMM_LL")) ctx->comm_ll = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMM_SPLITK")) ctx->gemm_splitk = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMM_PG")) ctx->gemm_pg = atoi(e);
     if (const char *e = getenv("TLC_GEMM_TMA")) ctx->gemm_tma = atoi(e) != 0;
@@ -107,6 +108,8 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         ctx->gemm_tile = (int)value;
     } else if (n == "gemm_pair")
         ctx->gemm_pair = value != 0;
+    else if (n == "comm_ll")
+        ctx->comm_ll = value != 0;
     else if (n == "gemm_splitk")
         ctx->gemm_splitk = value != 0;
     else if (n == "gemm_pg") {

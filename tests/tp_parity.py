@@ -48,10 +48,13 @@ def main() -> int:
         if not bool(cond):
             failed.append(name)
 
-    for phase in ("nccl", "p2p", "p2p-too-large"):
+    # nccl: library all-reduce + add; p2p: flagged words over peer memory (no fences);
+    # p2p-fenced: the store + fence + flag form longer vectors use; p2p-too-large: back to NCCL
+    for phase in ("nccl", "p2p", "p2p-fenced", "p2p-too-large"):
         if phase == "p2p":
             comm.enable_p2p(4096, gather)
             check("p2p_ready", comm.p2p_ready)
+        dev.set_option("comm_ll", 0 if phase == "p2p-fenced" else 1)
         for rep, n in enumerate((8, 40, 1024, 4096, 4096, 2048) if phase != "p2p-too-large" else (8192,)):
             part = rng.standard_normal(n).astype(np.float16)
             res = np.random.default_rng(7 * rep + n).standard_normal(n).astype(np.float16)  # same on every rank
