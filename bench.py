@@ -564,7 +564,7 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
 
     # the one-GPU point of the scaling curve: the unsharded model on rank 0's GPU
     tp1 = None
-    if world > 1:
+    if world > 1 and not args.no_tp1:
         barrier()
         if rank == 0:
             del llm, model
@@ -835,6 +835,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=1, help="decode batch of the tensor-parallel (N > 1) workload")
     ap.add_argument("--as-shard", type=int, default=1,
                     help="with --workload decode70b on one GPU: run ONE rank's share of TP<N> (no collectives)")
+    ap.add_argument("--no-tp1", action="store_true",
+                    help="N > 1: do not time the unsharded model on rank 0 afterwards (no `tp1` / `speedup_vs_tp1`)")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="N > 1: keep the all-reduces on NCCL instead of the peer-memory kernel (for comparison)")
     args = ap.parse_args()
