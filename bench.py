@@ -54,16 +54,26 @@ def workload_name(n_gpus: int, batch: int = 1, big: bool = False) -> str:
     return "tinyllama-1.1b q4_0 decode, batch 1, 512-token prompt"
 
 
-def profiled_traffic(key: str):
+def profiled_traffic(key: str, algorithmic_bytes: float | None = None):
     """DRAM bytes per launch of a kernel from the ncu summaries under profiles/ (traffic.json):
-    (bytes or None, where it comes from).  Taken from a capture, never measured in the run."""
+    (bytes or None, where it comes from).  Taken from a capture, never measured in the run.  An
+    entry holds either the captured bytes per launch of exactly this workload, or -- for workloads
+    too large to capture -- the ratio of captured to algorithmic bytes of a smaller capture of the
+    same kernel, applied to this run's algorithmic bytes per launch."""
     path = os.path.join(ROOT, "profiles", "traffic.json")
     if not os.path.exists(path):
         return None, None
     entry = json.load(open(path)).get(key)
     if not entry:
         return None, None
-    return float(entry["dram_bytes_per_launch"]), f"from profiles/{entry['summary']} (one ncu capture), not measured in this run"
+    if "dram_bytes_per_launch" in entry:
+        return float(entry["dram_bytes_per_launch"]), \
+            f"from profiles/{entry['summary']} (one ncu capture), not measured in this run"
+    if "ratio_to_algorithmic" in entry and algorithmic_bytes:
+        return float(entry["ratio_to_algorithmic"]) * algorithmic_bytes, \
+            (f"algorithmic bytes x {entry['ratio_to_algorithmic']} (DRAM / algorithmic bytes of the capture in "
+             f"profiles/{entry['summary']}, a smaller case of the same kernel), not measured in this run")
+    return None, None
 
 
 def load_peaks() -> dict:
@@ -588,7 +598,8 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
     us = gemv_ms * 1e3 / (K * gemv_launches)
     achieved = wbytes / gemv_launches / (us * 1e-6) / 1e9
     step_bytes = llama_bytes_per_step(arch, world, batch, context + 2 * W + K // 2)
-    traffic, traffic_src = profiled_traffic(f"llama70b_tp{world}_gemv")
+    traffic, traffic_src = profiled_traffic(f"llama70b_tp{world if shard_of == 1 else shard_of}_gemv" if batch == 1 else "none",
+                                            wbytes / gemv_launches)
     line = {
         "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

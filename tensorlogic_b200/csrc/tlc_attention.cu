@@ -537,16 +537,25 @@ __global__ void __launch_bounds__(kAttnThreads) attention_prefill_kernel(const A
                 }
             }
             float mx[2] = {-INFINITY, -INFINITY};
+            // a tile wholly below the diagonal of this warp's rows and inside the context needs no mask
+            const bool unmasked = j0 + kTileKeys <= k_end && j0 + kTileKeys - 1 <= pos0 + qt * RQ + (16 * warp) / G;
+            const __half2 scale_h2 = __half2half2(scale_h);
 #pragma unroll
             for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int key = j0 + nt * 8 + 2 * t + (e & 1);
-                    const int rpos = e < 2 ? rpos_lo : rpos_hi;
-                    float v = __half2float(__hmul(__float2half_rn(s[nt][e]), scale_h));
-                    if (key >= k_end || key > rpos) v = -INFINITY;
-                    s[nt][e] = v;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                for (int e = 0; e < 4; e += 2) {
+                    // two roundings as the reference does: the score to f16, then its product with the scale
+                    const float2 v2 = __half22float2(__hmul2(__floats2half2_rn(s[nt][e], s[nt][e + 1]), scale_h2));
+                    float v0 = v2.x, v1 = v2.y;
+                    if (!unmasked) {
+                        const int key = j0 + nt * 8 + 2 * t;
+                        const int rpos = e < 2 ? rpos_lo : rpos_hi;
+                        if (key >= k_end || key > rpos) v0 = -INFINITY;
+                        if (key + 1 >= k_end || key + 1 > rpos) v1 = -INFINITY;
+                    }
+                    s[nt][e] = v0;
+                    s[nt][e + 1] = v1;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], fmaxf(v0, v1));
                 }
             float corr[2], msafe[2];
 #pragma unroll
