@@ -106,7 +106,7 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *   "gemm_pg"     weight-producer groups of the GEMM: 0 (default) = two groups taking alternate K
  *                 steps where the K steps of a tile are shared out ("gemm_splitk"), one group
  *                 otherwise; 1 = one group and no sharing; 2 = two groups wherever possible;
- *   "comm_ll"     peer-memory all-reduces of up to 65536 values send data and flag in one word and
+ *   "comm_ll"     peer-memory all-reduces of up to 262144 values send data and flag in one word and
  *                 poll the data (1, default) or use stores + fences + flags (0);
  *   "gemm_splitk" GEMMs of up to 128 activation rows whose weight gives fewer tiles than SMs share
  *                 the K steps over several CTAs per tile, one finishing kernel adds (1, default); 0 = off;

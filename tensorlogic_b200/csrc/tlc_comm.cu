@@ -96,7 +96,7 @@ constexpr size_t kP2pSeqOffset = 1024;    // uint32 [kP2pChunks], local
 constexpr size_t kP2pLLSeqOffset = 2048;  // uint32 [kP2pLLMaxCtas], local: the flagged-word form's call counters
 constexpr size_t kP2pDataOffset = 4096;   // f16 [2][world][max_elems], written by peers
 // then, 256-byte aligned: {f16 x 2, flag} [2][world][ll_cap / 2], written by peers (flagged-word form)
-constexpr uint32_t kP2pLLMaxElems = 65536;  // longest vector the flagged-word form takes
+constexpr uint32_t kP2pLLMaxElems = 262144;  // longest vector the flagged-word form takes (32 rows of 8192)
 constexpr int kP2pLLMaxCtas = kP2pLLMaxElems / (4 * 256);
 
 struct P2pParams {
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(256) allreduce_residual_kernel(const P2pParams
 
 // ---------------------------------------------------------------------------
 // The same all-reduce + residual for short vectors (a decode step's [M, d] partial sums up to
-// 64 Ki values) without any fence or separate flag: every 4 bytes of data (two f16) travel in
+// 256 Ki values) without any fence or separate flag: every 4 bytes of data (two f16) travel in
 // one 8-byte store together with the call's sequence number, and the receiver polls the very
 // words it needs until they carry that number (the scheme of NCCL's LL protocol).  An 8-byte
 // aligned store arrives whole, so a word whose flag matches holds this call's data.  Latency

@@ -580,13 +580,14 @@ bool tlc_gemm_eligible(const tlc_ctx *ctx, const tlc_gemv_args &a) {
     // zero padding (rows are padded to 16 bytes with zeros at upload) against zero-filled activations
     if (w0->n_cols % 32 != 0 || w0->n_cols < kBK) return false;
     if (ctx->gemm_min_m > 0) return a.m >= ctx->gemm_min_m;
-    // Below 17 rows one GEMV pass reads the weights once.  Up to 48 rows the
-    // GEMV's few passes still win unless the weight has enough 128-row tiles
-    // to occupy half of the SMs.
+    // Below 17 rows one GEMV pass reads the weights once.
+    if (a.m <= 16) return false;
     // With split K the few CTAs of a narrow weight share K, and the GEMM wins from 17 rows on.
     int64_t n_total = 0;
     for (int i = 0; i < a.n_out; i++) n_total += a.outs[i].w->n_rows;
-    if (gemm_choose_ksplit(ctx, a.m, w0->n_cols, gemm_tiles(a), n_total) > 1) return a.m > 16;
+    if (gemm_choose_ksplit(ctx, a.m, w0->n_cols, gemm_tiles(a), n_total) > 1) return true;
+    // Without it, up to 48 rows the GEMV's few passes still win unless the weight has enough
+    // 128-row tiles to occupy half of the SMs.
     int64_t tiles = 0;
     for (int i = 0; i < a.n_out; i++) tiles = tiles < (a.outs[i].w->n_rows + 128 - 1) / 128 ? (a.outs[i].w->n_rows + 128 - 1) / 128 : tiles;
     return a.m > (tiles * 2 >= ctx->sm_count ? 16 : 48);

@@ -67,7 +67,7 @@ struct tlc_ctx {
     // sets the status word and drains; option "wait_limit_ms".
     uint64_t wait_ns = 2000000000ull;
     bool gemm_pair = false;  // GEMM tiles of 256 x 256 on CTA pairs (tcgen05 cta_group::2) from 129 rows on; measured slower
-    bool comm_ll = true;  // peer-memory all-reduces of up to 64 Ki values use flagged words instead of fences + flags
+    bool comm_ll = true;  // peer-memory all-reduces of up to 256 Ki values use flagged words instead of fences + flags
     bool gemm_splitk = true;  // GEMMs of up to 128 rows and few weight tiles share K over several CTAs per tile
     int gemm_pg = 0;  // producer groups of the GEMM: 0 = two where K is shared out over CTAs, else one; 1 / 2 = forced
     bool gemm_tma = true;  // activation tiles of the GEMM by TMA (false: cp.async loader warps)
