@@ -109,7 +109,8 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *   "comm_ll"     peer-memory all-reduces of up to 262144 values send data and flag in one word and
  *                 poll the data (1, default) or use stores + fences + flags (0);
  *   "gemm_splitk" GEMMs of up to 128 activation rows whose weight gives fewer tiles than SMs share
- *                 the K steps over several CTAs per tile, one finishing kernel adds (1, default); 0 = off;
+ *                 the K steps over several CTAs per tile where a cost model says it pays, one finishing
+ *                 kernel adds (1, default); 2 = wherever possible; 0 = off;
  *   "gemm_pair"   from 129 activation rows on, the GEMM runs on CTA pairs (tcgen05 cta_group::2,
  *                 persistent, two accumulators in tensor memory) (1) or on single CTAs (0,
  *                 default: faster on a B200);

@@ -79,7 +79,7 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (const char *e = getenv("TLC_GEMM_MIN_M")) ctx->gemm_min_m = atoi(e);
     if (const char *e = getenv("TLC_GEMM_PAIR")) ctx->gemm_pair = atoi(e) != 0;
     if (const char *e = getenv("TLC_COMM_LL")) ctx->comm_ll = atoi(e) != 0;
-    if (const char *e = getenv("TLC_GEMM_SPLITK")) ctx->gemm_splitk = atoi(e) != 0;
+    if (const char *e = getenv("TLC_GEMM_SPLITK")) ctx->gemm_splitk = atoi(e);
     if (const char *e = getenv("TLC_GEMM_PG")) ctx->gemm_pg = atoi(e);
     if (const char *e = getenv("TLC_GEMM_TMA")) ctx->gemm_tma = atoi(e) != 0;
     if (const char *e = getenv("TLC_ATTN_WIDE")) ctx->attn_wide = atoi(e);
@@ -111,7 +111,7 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
     else if (n == "comm_ll")
         ctx->comm_ll = value != 0;
     else if (n == "gemm_splitk")
-        ctx->gemm_splitk = value != 0;
+        ctx->gemm_splitk = (int)value;
     else if (n == "gemm_pg") {
         TLC_REQUIRE(value >= 0 && value <= 2, TLC_ERR_INVALID_OPERATION, "set_option: gemm_pg must be 0, 1 or 2");
         ctx->gemm_pg = (int)value;

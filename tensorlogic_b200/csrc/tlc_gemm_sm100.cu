@@ -540,7 +540,7 @@ static int gemm_choose_ksplit(const tlc_ctx *ctx, int m, int64_t k, int64_t tile
         const int per = (KT + ks - 1) / ks;
         if ((KT + per - 1) / per != ks) continue;  // a share would be empty
         const double t = per * 0.45 + 4.0 + (double)ks * m * (double)n_total * 8.0 / 3.0e6;
-        if (t < best_t) {
+        if (t < best_t || ctx->gemm_splitk == 2) {  // 2: the most shares, whatever they cost (tests)
             best_t = t;
             best = ks;
         }

@@ -68,7 +68,7 @@ struct tlc_ctx {
     uint64_t wait_ns = 2000000000ull;
     bool gemm_pair = false;  // GEMM tiles of 256 x 256 on CTA pairs (tcgen05 cta_group::2) from 129 rows on; measured slower
     bool comm_ll = true;  // peer-memory all-reduces of up to 256 Ki values use flagged words instead of fences + flags
-    bool gemm_splitk = true;  // GEMMs of up to 128 rows and few weight tiles share K over several CTAs per tile
+    int gemm_splitk = 1;  // GEMMs of up to 128 rows and few weight tiles share K over several CTAs per tile: 0 off, 1 where a cost model says it pays, 2 wherever possible
     int gemm_pg = 0;  // producer groups of the GEMM: 0 = two where K is shared out over CTAs, else one; 1 / 2 = forced
     bool gemm_tma = true;  // activation tiles of the GEMM by TMA (false: cp.async loader warps)
     int gemm_tile = 0;  // 0: pick the GEMM tile from the shape; 11, 12, 22: force 128x128, 128x256, 256x256

@@ -162,18 +162,22 @@ def test_gemm_split_k(dev, ref, qtype, n, k, m):
     w = QTensor.from_blocks(dev, qtype, n, k, raw)
     want = ref.linear_q(qtype, raw, n, k, x)
     with gemm_from(dev, 1):
-        l0 = dev.launch_count
-        y = linear(dev.tensor(x), w).numpy()
-        launches = dev.launch_count - l0
-        yt = linear(dev.tensor(np.eye(k, dtype=np.float16)[:m]), w).numpy()
-        dev.set_option("gemm_splitk", 0)
         try:
+            dev.set_option("gemm_splitk", 2)  # share K wherever possible, also where the cost model would not
+            l0 = dev.launch_count
+            y = linear(dev.tensor(x), w).numpy()
+            launches = dev.launch_count - l0
+            yt = linear(dev.tensor(np.eye(k, dtype=np.float16)[:m]), w).numpy()
+            dev.set_option("gemm_splitk", 1)  # the default: by cost
+            y2 = linear(dev.tensor(x), w).numpy()
+            dev.set_option("gemm_splitk", 0)
             l0 = dev.launch_count
             y1 = linear(dev.tensor(x), w).numpy()
             assert dev.launch_count - l0 == 1
         finally:
             dev.set_option("gemm_splitk", 1)
     assert launches == 2, launches            # the GEMM with K shared out + the finishing kernel
+    assert rel_l2(y2, want) < TIGHT
     assert rel_l2(y, want) < TIGHT and rel_l2(y1, want) < TIGHT
     assert rel_l2(y, y1) < 1e-4
     assert np.array_equal(_bits(yt), _bits(ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]))
