@@ -126,7 +126,8 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
 TLC_API int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value);
 /* Failure-detection self-test.  Enqueues a kernel whose device-side wait can never be
  * satisfied -- kind 0: an mbarrier nothing arrives on (the wait of the GEMV / GEMM
- * pipelines); kind 1: the peer flags of the all-reduce with no peer present.  The wait
+ * pipelines); kind 1: the peer flags of the all-reduce with no peer present; kind 2: the
+ * flagged words of its short-vector form.  The wait
  * gives up after the "wait_limit_ms" option (default 2000), the kernel returns, and the
  * next tlc_synchronize reports TLC_ERR_TIMEOUT once; the context stays usable. */
 TLC_API int32_t tlc_selftest_wait_timeout(tlc_ctx *ctx, int32_t kind);

@@ -507,12 +507,15 @@ extern "C" int32_t tlc_allreduce_residual_f16(tlc_ctx *ctx, tlc_comm *comm, void
     return TLC_OK;
 }
 
-// Failure-detection self-test (no second GPU, no communicator needed): the
-// all-reduce kernel runs as "rank 0 of 2" over two exchange blocks on this GPU;
-// nothing ever plays rank 1, so the wait for its flags runs out after the
-// context's limit, the status word is set and the kernel returns.
-int32_t tlc_selftest_peer_wait(tlc_ctx *ctx) {
-    const size_t n = 1024, bytes = kP2pDataOffset + (size_t)2 * 2 * n * sizeof(__half);
+// Failure-detection self-test (no second GPU, no communicator needed): an
+// all-reduce kernel (the fenced form, or the flagged-word form) runs as "rank 0 of 2"
+// over two exchange blocks on this GPU; nothing ever plays rank 1, so the wait for its
+// flags (its flagged words) runs out after the context's limit, the status word is set
+// and the kernel returns.
+int32_t tlc_selftest_peer_wait(tlc_ctx *ctx, bool flagged_words) {
+    const size_t n = 1024;
+    const size_t ll_off = (kP2pDataOffset + (size_t)2 * 2 * n * sizeof(__half) + 255) & ~(size_t)255;
+    const size_t bytes = ll_off + (size_t)2 * 2 * n * 4;
     uint8_t *blk[2] = {nullptr, nullptr};
     __half *vec = nullptr;
     TLC_CUDA(cudaMalloc(&blk[0], bytes));
@@ -531,9 +534,14 @@ int32_t tlc_selftest_peer_wait(tlc_ctx *ctx) {
     p.world = 2;
     p.n = (uint32_t)n;
     p.max_elems = (uint32_t)n;
+    p.ll_off = ll_off;
+    p.ll_cap = (uint32_t)n;
     p.status = ctx->dev_status;
     p.wait_ns = ctx->wait_ns;
-    allreduce_residual_kernel<<<kP2pChunks, 256, 0, ctx->stream>>>(p);
+    if (flagged_words)
+        allreduce_ll_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, ctx->stream>>>(p);
+    else
+        allreduce_residual_kernel<<<kP2pChunks, 256, 0, ctx->stream>>>(p);
     ctx->launches++;
     cudaError_t e = cudaGetLastError();
     cudaStreamSynchronize(ctx->stream);

@@ -144,8 +144,8 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
 
 extern "C" int32_t tlc_selftest_wait_timeout(tlc_ctx *ctx, int32_t kind) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
-    TLC_REQUIRE(kind == 0 || kind == 1, TLC_ERR_INVALID_OPERATION, "selftest_wait_timeout: kind %d (0 or 1)", kind);
-    return kind == 0 ? tlc_selftest_mbarrier_wait(ctx) : tlc_selftest_peer_wait(ctx);
+    TLC_REQUIRE(kind >= 0 && kind <= 2, TLC_ERR_INVALID_OPERATION, "selftest_wait_timeout: kind %d (0, 1 or 2)", kind);
+    return kind == 0 ? tlc_selftest_mbarrier_wait(ctx) : tlc_selftest_peer_wait(ctx, kind == 2);
 }
 
 extern "C" int32_t tlc_destroy(tlc_ctx *ctx) {

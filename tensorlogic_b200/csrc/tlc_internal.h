@@ -146,7 +146,7 @@ static inline size_t tlc_block_bytes(int32_t type) {
 int32_t tlc_qtensor_to_f16(tlc_ctx *ctx, tlc_qtensor *qt, tlc_qtensor **out);
 // Failure-detection self-tests: launch a kernel whose bounded wait must run out.
 int32_t tlc_selftest_mbarrier_wait(tlc_ctx *ctx);
-int32_t tlc_selftest_peer_wait(tlc_ctx *ctx);
+int32_t tlc_selftest_peer_wait(tlc_ctx *ctx, bool flagged_words);
 // Makes the context's device current; every entry point calls it first.
 int32_t tlc_enter(tlc_ctx *ctx);
 // After a stream synchronize that followed a copy of the status word to host_status.

@@ -286,10 +286,10 @@ def test_pool_reuse_and_stats(dev):
     assert dev.pool_stats()["total_pooled"] == 0
 
 
-@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("kind", [0, 1, 2])
 def test_bounded_wait_reports_timeout_and_context_survives(dev, ref, kind):
     """Failure detection without a fault: a device-side wait that nothing satisfies (an mbarrier of the
-    GEMV pipeline; the peer flags of the all-reduce) runs out, the kernel returns, synchronize reports it
+    GEMV pipeline; the peer flags of the all-reduce; the flagged words of its short-vector form) runs out, the kernel returns, synchronize reports it
     once, and the next launch on the same context works."""
     from tensorlogic_b200 import _lib
     from tensorlogic_b200.api import QTensor, TensorError, check, linear
