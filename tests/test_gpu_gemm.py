@@ -183,6 +183,27 @@ def test_gemm_split_k(dev, ref, qtype, n, k, m):
     assert np.array_equal(_bits(yt), _bits(ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]))
 
 
+@pytest.mark.parametrize("qtype", [Q4, Q8])
+@pytest.mark.parametrize("n,k,m", [(300, 640, 300), (512, 2048, 100), (2100, 96, 2500), (64, 1376, 40)])
+def test_gemm_with_cp_async_activation_loaders(dev, ref, qtype, n, k, m):
+    """Option gemm_tma = 0: four warps copy the activation tile with cp.async instead of the TMA
+    boxes (the path taken when no tensor map can be made); one and two producer groups, split K."""
+    from tensorlogic_b200.api import QTensor, linear
+    raw = _weights(qtype, n, k, seed=22, name=f"c{n}x{k}")
+    x = _x(m, k, seed=22, name=f"cx{m}x{k}")
+    w = QTensor.from_blocks(dev, qtype, n, k, raw)
+    dev.set_option("gemm_tma", 0)
+    try:
+        with gemm_from(dev, 1):
+            y = linear(dev.tensor(x), w).numpy()
+            yt = linear(dev.tensor(np.eye(k, dtype=np.float16)[:m]), w).numpy() if m <= k else None
+    finally:
+        dev.set_option("gemm_tma", 1)
+    assert rel_l2(y, ref.linear_q(qtype, raw, n, k, x)) < TIGHT
+    if yt is not None:
+        assert np.array_equal(_bits(yt), _bits(ref.dequant(qtype, raw, n * k).reshape(n, k).T[:m]))
+
+
 def test_automatic_tile_choice_large(dev, ref):
     """Shapes large enough that the launcher picks the wide tiles by itself."""
     from tensorlogic_b200.api import QTensor, linear
