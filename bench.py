@@ -610,7 +610,8 @@ def run_tp(args, rank: int, world: int, local: int) -> None:
                    "parallelism": f"tp{world}" if shard_of == 1 else f"one shard of tp{shard_of}", "batch": batch,
                    "collectives_per_step": 2 * arch.n_layers + 1 if world > 1 else 0,
                    "allreduce_bytes": batch * d * 2 if world > 1 else 0,
-                   "allreduce": ("one-shot peer-memory kernel fused with the residual add" if comm.p2p_ready
+                   "allreduce": ("one-shot peer-memory kernel fused with the residual add (data and sequence number in one "
+                                 "8-byte store over NVLink, no fences)" if comm.p2p_ready
                                  else "nccl all-reduce + add kernel") if comm else "none (one GPU)",
                    "step_hbm_bytes_per_gpu": step_bytes,
                    "step_hbm_gbs_per_gpu": step_bytes / (ms / K * 1e-3) / 1e9,
