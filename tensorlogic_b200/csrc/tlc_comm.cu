@@ -89,10 +89,11 @@ namespace {
 // sequence number lives in device memory (one per chunk), so a CUDA graph that
 // replays the same launch keeps counting.
 // ---------------------------------------------------------------------------
-constexpr int kP2pChunks = 8;
+constexpr int kP2pChunks = 8;      // CTAs of a short all-reduce (each on its own slice and flags)
+constexpr int kP2pMaxChunks = 32;  // CTAs of a long one (from 64 Ki values on); the flag rows are this wide
 constexpr int kP2pMaxWorld = 8;
-constexpr size_t kP2pFlagsOffset = 0;     // uint32 [world][kP2pChunks], written by peers
-constexpr size_t kP2pSeqOffset = 1024;    // uint32 [kP2pChunks], local
+constexpr size_t kP2pFlagsOffset = 0;     // uint32 [world][kP2pMaxChunks], written by peers
+constexpr size_t kP2pSeqOffset = 1024;    // uint32 [kP2pMaxChunks], local
 constexpr size_t kP2pLLSeqOffset = 2048;  // uint32 [kP2pLLMaxCtas], local: the flagged-word form's call counters
 constexpr size_t kP2pDataOffset = 4096;   // f16 [2][world][max_elems], written by peers
 // then, 256-byte aligned: {f16 x 2, flag} [2][world][ll_cap / 2], written by peers (flagged-word form)
@@ -124,8 +125,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 __global__ void __launch_bounds__(256) allreduce_residual_kernel(const P2pParams p) {
     __shared__ int timed_out;
     tlc_pdl_prologue();  // the partial sums come from the previous kernel of the stream
-    const int tid = threadIdx.x, chunk = blockIdx.x;
-    const uint32_t per = ((p.n + kP2pChunks * 8 - 1) / (kP2pChunks * 8)) * 8;  // elements per chunk, multiple of 8
+    const int tid = threadIdx.x, chunk = blockIdx.x, chunks = (int)gridDim.x;  // 8 or 32 CTAs, by the vector's length
+    const uint32_t per = ((p.n + chunks * 8 - 1) / (chunks * 8)) * 8;  // elements per chunk, multiple of 8
     const uint32_t lo = min(p.n, chunk * per), hi = min(p.n, lo + per);
     uint8_t *local = p.peer[p.rank];
     uint32_t *seq = reinterpret_cast<uint32_t *>(local + kP2pSeqOffset) + chunk;
@@ -144,11 +145,11 @@ __global__ void __launch_bounds__(256) allreduce_residual_kernel(const P2pParams
     __threadfence_system();
     __syncthreads();
     if (tid < p.world && tid != p.rank)
-        st_release_sys(reinterpret_cast<uint32_t *>(p.peer[tid] + kP2pFlagsOffset) + p.rank * kP2pChunks + chunk, s);
+        st_release_sys(reinterpret_cast<uint32_t *>(p.peer[tid] + kP2pFlagsOffset) + p.rank * kP2pMaxChunks + chunk, s);
 
     // 2. wait for every peer's slice
     if (tid < p.world && tid != p.rank) {
-        const uint32_t *flag = reinterpret_cast<const uint32_t *>(local + kP2pFlagsOffset) + tid * kP2pChunks + chunk;
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(local + kP2pFlagsOffset) + tid * kP2pMaxChunks + chunk;
         bool ok = false;
         const uint64_t t0 = tlc_globaltimer_ns();
         do {
@@ -195,7 +196,10 @@ __global__ void __launch_bounds__(256) allreduce_residual_kernel(const P2pParams
             *reinterpret_cast<uint4 *>(p.out + i) = *reinterpret_cast<const uint4 *>(o);
         }
     }
-    if (tid == 0) *seq = s;
+    // Every one of the kP2pMaxChunks counters follows every call, whatever its CTA count: the
+    // parity of the slots is then the same for all slices of all calls, also when short and long
+    // vectors alternate on one communicator.
+    if (tid < kP2pMaxChunks / chunks) seq[tid * chunks] = s;
 }
 
 
@@ -484,7 +488,8 @@ extern "C" int32_t tlc_allreduce_residual_f16(tlc_ctx *ctx, tlc_comm *comm, void
         // short vectors: data and flag in one word, no fences (option "comm_ll")
         const bool ll = ctx->comm_ll && count <= comm->p2p_ll_cap && ((uintptr_t)partial_dev | (uintptr_t)out_dev | (uintptr_t)residual_dev) % 8 == 0;
         cudaError_t le = ll ? tlc_launch_pdl(ctx, allreduce_ll_kernel, dim3((unsigned)((count / 4 + 255) / 256)), dim3(256), 0, p)
-                            : tlc_launch_pdl(ctx, allreduce_residual_kernel, dim3(kP2pChunks), dim3(256), 0, p);
+                            : tlc_launch_pdl(ctx, allreduce_residual_kernel, dim3(count >= 65536 ? kP2pMaxChunks : kP2pChunks),
+                                             dim3(256), 0, p);
         if (le != cudaSuccess) {
             cudaGetLastError();
             return tlc_fail(TLC_ERR_CUDA, "all-reduce launch failed: %s", cudaGetErrorString(le));

@@ -55,7 +55,7 @@ def main() -> int:
             comm.enable_p2p(65536, gather)
             check("p2p_ready", comm.p2p_ready)
         dev.set_option("comm_ll", 0 if phase == "p2p-fenced" else 1)
-        for rep, n in enumerate((8, 40, 1024, 4096, 4096, 2048, 65536) if phase != "p2p-too-large" else (131072,)):
+        for rep, n in enumerate((8, 40, 1024, 4096, 4096, 2048, 65536, 2048, 65536, 8) if phase != "p2p-too-large" else (131072,)):
             part = rng.standard_normal(n).astype(np.float16)
             res = np.random.default_rng(7 * rep + n).standard_normal(n).astype(np.float16)  # same on every rank
             parts = gather(part.tobytes())
