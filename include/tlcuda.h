@@ -106,6 +106,7 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *   "gemm_pg"     weight-producer groups of the GEMM: 0 (default) = two groups taking alternate K
  *                 steps where the K steps of a tile are shared out ("gemm_splitk"), one group
  *                 otherwise; 1 = one group and no sharing; 2 = two groups wherever possible;
+ *   "perf"        per-op timing on (1) / off (0, default): see tlc_perf_report;
  *   "comm_ll"     peer-memory all-reduces of up to 262144 values send data and flag in one word and
  *                 poll the data (1, default) or use stores + fences + flags (0);
  *   "gemm_splitk" GEMMs of up to 128 activation rows whose weight gives fewer tiles than SMs share
@@ -145,6 +146,15 @@ TLC_API void *tlc_stream(tlc_ctx *ctx);
 /* Number of kernels this context has launched since creation (TL_PERF-style
  * accounting, src/device/kernel_executor.rs:33-41). */
 TLC_API uint64_t tlc_launch_count(tlc_ctx *ctx);
+/* Per-op timing, the counterpart of the reference's TL_PERF environment switch
+ * (src/interpreter/builtin_math.rs:190-197, builtin_nn.rs:119, ops/elementwise.rs:274-299): with
+ * the option "perf" set (tlc_set_option, TLC_PERF=1, or TL_PERF in the environment) every op entry
+ * point times its launches with CUDA events, waits for them, prints "[PERF] op(shape): x.xxxms" to
+ * stderr and adds to per-op totals.  tlc_perf_report writes those totals as text, one line per op:
+ * "name calls total_ms"; needed_out (optional) receives the report's length; reset != 0 clears
+ * the totals.  A measuring mode: every timed op synchronizes; nothing is timed inside a stream
+ * capture. */
+TLC_API int32_t tlc_perf_report(tlc_ctx *ctx, char *buf, size_t buflen, int32_t reset, size_t *needed_out);
 
 /* ---- allocator --------------------------------------------------------- */
 

@@ -67,6 +67,7 @@ PROTOTYPES = {
     "tlc_synchronize": (i32, [vp]),
     "tlc_stream": (vp, [vp]),
     "tlc_launch_count": (u64, [vp]),
+    "tlc_perf_report": (i32, [vp, C.c_char_p, sz, i32, P(sz)]),
     "tlc_alloc": (i32, [vp, sz, P(vp)]),
     "tlc_free": (i32, [vp]),
     "tlc_buf_ptr": (vp, [vp]),

@@ -74,6 +74,18 @@ class Device:
     def launch_count(self) -> int:
         return int(self.lib.tlc_launch_count(self.handle))
 
+    def perf_report(self, reset: bool = False) -> dict[str, tuple[int, float]]:
+        """Per-op totals of the "perf" option (the reference's TL_PERF): {op: (calls, total ms)}."""
+        need = C.c_size_t()
+        check(self.lib.tlc_perf_report(self.handle, None, 0, 0, C.byref(need)))
+        buf = C.create_string_buffer(need.value + 1)
+        check(self.lib.tlc_perf_report(self.handle, buf, len(buf), 1 if reset else 0, None))
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, calls, ms = line.rsplit(" ", 2)
+            out[name] = (int(calls), float(ms))
+        return out
+
     def mem_info(self) -> tuple[int, int]:
         f, t = C.c_size_t(), C.c_size_t()
         check(self.lib.tlc_mem_info(self.handle, C.byref(f), C.byref(t)))

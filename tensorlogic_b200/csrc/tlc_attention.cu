@@ -927,6 +927,7 @@ extern "C" int32_t tlc_attention(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer
                                  void *out_dev, int32_t batch, int32_t n_queries, int32_t n_heads,
                                  int32_t q_pos0, const int32_t *positions_dev, int32_t max_keys, float scale) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
+    tlc_perf_scope perf(ctx, "attention(batch=%d, queries=%d, heads=%d)", batch, n_queries, n_heads);
     return tlc_launch_attention(ctx, cache, layer, q_dev, out_dev, batch, n_queries, n_heads, q_pos0,
                                 positions_dev, max_keys, scale);
 }

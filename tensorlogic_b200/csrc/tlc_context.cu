@@ -78,6 +78,8 @@ extern "C" int32_t tlc_init(int32_t ordinal, tlc_ctx **out) {
     if (const char *e = getenv("TLC_PDL_SMALL")) ctx->pdl_small = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMM_MIN_M")) ctx->gemm_min_m = atoi(e);
     if (const char *e = getenv("TLC_GEMM_PAIR")) ctx->gemm_pair = atoi(e) != 0;
+    if (const char *e = getenv("TLC_PERF")) ctx->perf = atoi(e) != 0;
+    else if (getenv("TL_PERF")) ctx->perf = true;  // the reference's own switch
     if (const char *e = getenv("TLC_COMM_LL")) ctx->comm_ll = atoi(e) != 0;
     if (const char *e = getenv("TLC_GEMM_SPLITK")) ctx->gemm_splitk = atoi(e);
     if (const char *e = getenv("TLC_GEMM_PG")) ctx->gemm_pg = atoi(e);
@@ -108,6 +110,8 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         ctx->gemm_tile = (int)value;
     } else if (n == "gemm_pair")
         ctx->gemm_pair = value != 0;
+    else if (n == "perf")
+        ctx->perf = value != 0;
     else if (n == "comm_ll")
         ctx->comm_ll = value != 0;
     else if (n == "gemm_splitk")
@@ -139,6 +143,69 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         ctx->q6k_resident = value != 0;
     else
         return tlc_fail(TLC_ERR_INVALID_OPERATION, "set_option: unknown option '%s'", name);
+    return TLC_OK;
+}
+
+tlc_perf_scope::tlc_perf_scope(tlc_ctx *c, const char *fmt, ...) : ctx(c) {
+    name[0] = 0;
+    if (!c || !c->perf) return;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(c->stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        cudaGetLastError();
+        return;
+    }
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(name, sizeof name, fmt, ap);
+    va_end(ap);
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess ||
+        cudaEventRecord(e0, c->stream) != cudaSuccess) {
+        cudaGetLastError();
+        if (e0) cudaEventDestroy(e0);
+        if (e1) cudaEventDestroy(e1);
+        e0 = e1 = nullptr;
+        return;
+    }
+    on = true;
+}
+
+tlc_perf_scope::~tlc_perf_scope() {
+    if (!on) return;
+    float ms = 0.f;
+    if (cudaEventRecord(e1, ctx->stream) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) {
+        fprintf(stderr, "[PERF] %s: %.3fms\n", name, ms);
+        // totals by op name without its shape: "linear(q4_0, ...)" counts under "linear"
+        std::string key(name);
+        const size_t paren = key.find('(');
+        if (paren != std::string::npos) key.resize(paren);
+        tlc_ctx::perf_total &t = ctx->perf_totals[key];
+        t.calls++;
+        t.ms += ms;
+    } else {
+        cudaGetLastError();
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+}
+
+// Per-op totals of the "perf" option as text, one line per op: "name calls total_ms".  Returns the
+// number of bytes the whole report needs (excluding the terminating zero); `reset` clears the totals.
+extern "C" int32_t tlc_perf_report(tlc_ctx *ctx, char *buf, size_t buflen, int32_t reset, size_t *needed_out) {
+    if (int32_t rc = tlc_enter(ctx)) return rc;
+    std::string out;
+    char line[160];
+    for (const auto &kv : ctx->perf_totals) {
+        snprintf(line, sizeof line, "%s %llu %.3f\n", kv.first.c_str(), (unsigned long long)kv.second.calls, kv.second.ms);
+        out += line;
+    }
+    if (needed_out) *needed_out = out.size();
+    if (buf && buflen > 0) {
+        const size_t n = out.size() < buflen - 1 ? out.size() : buflen - 1;
+        memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    if (reset) ctx->perf_totals.clear();
     return TLC_OK;
 }
 

@@ -38,6 +38,13 @@ struct tlc_ctx {
     int sm_count = 0;
     tlc_pool pool;
     uint64_t launches = 0;
+    // Option "perf" / TLC_PERF=1 (or the reference's TL_PERF in the environment): every op entry
+    // point times its launches with CUDA events, prints "[PERF] op: x.xxxms" to stderr as the
+    // reference's builtins do (src/interpreter/builtin_math.rs:190-197) and adds to these totals
+    // (tlc_perf_report).  Each timed op waits for its own launches: a measuring mode, not a fast one.
+    bool perf = false;
+    struct perf_total { uint64_t calls = 0; double ms = 0.0; };
+    std::map<std::string, perf_total> perf_totals;
     tlc_dev_status *dev_status = nullptr;   // device memory
     tlc_dev_status *host_status = nullptr;  // pinned mirror
     // Reusable scratch for kernels that need global workspace (grows on demand).
@@ -173,6 +180,19 @@ inline cudaError_t tlc_launch_pdl(tlc_ctx *ctx, void (*kernel)(KArgs...), dim3 g
     cfg.numAttrs = ctx->use_pdl && ctx->pdl_small ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// Times the launches an op entry point makes between its construction and destruction when the
+// context's "perf" option is on (never inside a stream capture).
+struct tlc_perf_scope {
+    tlc_ctx *ctx;
+    char name[96];
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    bool on = false;
+    tlc_perf_scope(tlc_ctx *c, const char *fmt, ...);
+    ~tlc_perf_scope();
+    tlc_perf_scope(const tlc_perf_scope &) = delete;
+    tlc_perf_scope &operator=(const tlc_perf_scope &) = delete;
+};
 
 #ifdef __CUDACC__
 __device__ __forceinline__ uint64_t tlc_globaltimer_ns() {

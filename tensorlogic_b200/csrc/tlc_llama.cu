@@ -714,6 +714,7 @@ extern "C" int32_t tlc_llama_prefill(tlc_llama *L, const int32_t *ids_host, int3
                                      void *logits_host, int32_t all_rows, int32_t *next_id_host) {
     TLC_REQUIRE(L && ids_host, TLC_ERR_INVALID_OPERATION, "llama_prefill: null pointer");
     if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    tlc_perf_scope perf(L->ctx, "llama_prefill(tokens=%d)", n);
     TLC_REQUIRE(n >= 1 && n <= L->max_rows, TLC_ERR_SHAPE_MISMATCH, "prefill of %d tokens (buffers hold %d)", n,
                 L->max_rows);
     TLC_REQUIRE(pos0 >= 0 && pos0 + n <= L->cfg.max_seq, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d",
@@ -840,6 +841,7 @@ extern "C" int32_t tlc_llama_decode_host(tlc_llama *L, int32_t batch, const int3
                                          int32_t *next_ids_host, void *logits_host) {
     TLC_REQUIRE(L && next_ids_host, TLC_ERR_INVALID_OPERATION, "llama_decode_host: null pointer");
     if (int32_t rc = tlc_enter(L->ctx)) return rc;
+    tlc_perf_scope perf(L->ctx, "llama_decode(batch=%d)", batch);
     TLC_REQUIRE(batch >= 1 && batch <= L->cfg.max_batch, TLC_ERR_SHAPE_MISMATCH, "batch %d (max %d)", batch,
                 L->cfg.max_batch);
     if (ids_host) {

@@ -255,6 +255,7 @@ inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threa
 extern "C" int32_t tlc_rms_norm(tlc_ctx *ctx, const void *x_dev, const void *w_dev, void *y_dev, int32_t rows,
                                 int32_t d, float eps) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
+    tlc_perf_scope perf(ctx, "rms_norm(rows=%d, d=%d)", rows, d);
     TLC_REQUIRE(x_dev && w_dev && y_dev, TLC_ERR_INVALID_OPERATION, "rms_norm: null pointer");
     TLC_REQUIRE(rows >= 0 && d > 0, TLC_ERR_INVALID_DIMENSION, "rms_norm: bad shape [%d, %d]", rows, d);
     if (rows == 0) return TLC_OK;
@@ -268,6 +269,7 @@ extern "C" int32_t tlc_rms_norm(tlc_ctx *ctx, const void *x_dev, const void *w_d
 extern "C" int32_t tlc_rope(tlc_ctx *ctx, const void *x_dev, void *y_dev, int32_t seq, int32_t heads,
                             int32_t d, int32_t pos_offset, uint32_t base, const int32_t *positions_dev) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
+    tlc_perf_scope perf(ctx, "rope(seq=%d, heads=%d, d=%d)", seq, heads, d);
     TLC_REQUIRE(x_dev && y_dev, TLC_ERR_INVALID_OPERATION, "rope: null pointer");
     // Tensor::rope rejects an odd head_dim (src/ops/rope.rs:90-96).
     TLC_REQUIRE(d > 0 && d % 2 == 0, TLC_ERR_INVALID_OPERATION, "RoPE requires even head_dim, got %d", d);
@@ -295,6 +297,7 @@ extern "C" int32_t tlc_rope_table(tlc_ctx *ctx, const void *x_dev, const void *c
                                   void *y_dev, int32_t seq, int32_t heads, int32_t d, int32_t table_rows,
                                   int32_t pitch) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
+    tlc_perf_scope perf(ctx, "rope_table(seq=%d, heads=%d, d=%d)", seq, heads, d);
     TLC_REQUIRE(x_dev && cos_dev && sin_dev && y_dev, TLC_ERR_INVALID_OPERATION, "rope: null pointer");
     TLC_REQUIRE(d > 0 && d % 2 == 0, TLC_ERR_INVALID_OPERATION, "RoPE requires even head_dim, got %d", d);
     TLC_REQUIRE(seq >= 0 && heads > 0, TLC_ERR_INVALID_DIMENSION, "rope: bad shape [%d, %d, %d]", seq, heads, d);
@@ -316,6 +319,7 @@ extern "C" int32_t tlc_rope_table(tlc_ctx *ctx, const void *x_dev, const void *c
 extern "C" int32_t tlc_matmul(tlc_ctx *ctx, const void *a_dev, const void *b_dev, void *y_dev, int32_t m, int32_t k,
                               int32_t k2, int32_t n) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
+    tlc_perf_scope perf(ctx, "matmul(m=%d, k=%d, n=%d)", m, k, n);
     TLC_REQUIRE(a_dev && b_dev && y_dev, TLC_ERR_INVALID_OPERATION, "matmul: null pointer");
     TLC_REQUIRE(m >= 0 && k >= 0 && k2 >= 0 && n >= 0, TLC_ERR_INVALID_DIMENSION, "matmul: bad shape");
     TLC_REQUIRE(k == k2, TLC_ERR_INVALID_OPERATION, "matmul shape mismatch: [%d, %d] @ [%d, %d]", m, k, k2, n);
@@ -332,6 +336,7 @@ extern "C" int32_t tlc_matmul(tlc_ctx *ctx, const void *a_dev, const void *b_dev
         if (int32_t rc = tlc_enter(ctx)) return rc;                                                      \
         TLC_REQUIRE(x_dev && y_dev, TLC_ERR_INVALID_OPERATION, #name ": null pointer");                  \
         if (n == 0) return TLC_OK;                                                                       \
+        tlc_perf_scope perf(ctx, "%s(n=%zu)", #name + 4, n);                                             \
         kernel<<<blocks_for(n, 256), 256, 0, ctx->stream>>>(static_cast<const __half *>(x_dev),          \
                                                             static_cast<__half *>(y_dev), n);            \
         TLC_CHECK_LAUNCH(ctx);                                                                           \
@@ -342,6 +347,7 @@ extern "C" int32_t tlc_matmul(tlc_ctx *ctx, const void *a_dev, const void *b_dev
         if (int32_t rc = tlc_enter(ctx)) return rc;                                                      \
         TLC_REQUIRE(a_dev && b_dev && y_dev, TLC_ERR_INVALID_OPERATION, #name ": null pointer");         \
         if (n == 0) return TLC_OK;                                                                       \
+        tlc_perf_scope perf(ctx, "%s(n=%zu)", #name + 4, n);                                             \
         kernel<<<blocks_for(n, 256), 256, 0, ctx->stream>>>(static_cast<const __half *>(a_dev),          \
                                                             static_cast<const __half *>(b_dev),          \
                                                             static_cast<__half *>(y_dev), n);            \
@@ -354,6 +360,7 @@ TLC_ELEMENTWISE_2(tlc_mul, mul_kernel)
 TLC_ELEMENTWISE_2(tlc_add, add_kernel)
 extern "C" int32_t tlc_swiglu(tlc_ctx *ctx, const void *a_dev, const void *b_dev, void *y_dev, size_t n) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
+    tlc_perf_scope perf(ctx, "swiglu(n=%zu)", n);
     TLC_REQUIRE(a_dev && b_dev && y_dev, TLC_ERR_INVALID_OPERATION, "tlc_swiglu: null pointer");
     if (n == 0) return TLC_OK;
     if (n % 8 == 0 && (((uintptr_t)a_dev | (uintptr_t)b_dev | (uintptr_t)y_dev) & 15) == 0)
@@ -368,6 +375,7 @@ extern "C" int32_t tlc_swiglu(tlc_ctx *ctx, const void *a_dev, const void *b_dev
 
 extern "C" int32_t tlc_softmax(tlc_ctx *ctx, const void *x_dev, void *y_dev, int32_t rows, int32_t last_dim) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
+    tlc_perf_scope perf(ctx, "softmax(rows=%d, d=%d)", rows, last_dim);
     TLC_REQUIRE(x_dev && y_dev, TLC_ERR_INVALID_OPERATION, "softmax: null pointer");
     TLC_REQUIRE(rows >= 0 && last_dim > 0, TLC_ERR_INVALID_DIMENSION, "softmax: bad shape [%d, %d]", rows, last_dim);
     if (rows == 0) return TLC_OK;
@@ -380,6 +388,7 @@ extern "C" int32_t tlc_softmax(tlc_ctx *ctx, const void *x_dev, void *y_dev, int
 extern "C" int32_t tlc_embedding(tlc_ctx *ctx, const void *table_dev, int32_t vocab, int32_t d,
                                  const int32_t *ids_host, int32_t m, void *y_dev) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
+    tlc_perf_scope perf(ctx, "embedding(d=%d)", d);
     TLC_REQUIRE(table_dev && ids_host && y_dev, TLC_ERR_INVALID_OPERATION, "embedding: null pointer");
     TLC_REQUIRE(vocab > 0 && d > 0 && m >= 0, TLC_ERR_INVALID_DIMENSION, "embedding: bad shape");
     // Host-side bounds check as in src/interpreter/builtin_nn.rs:681-688.
@@ -426,10 +435,15 @@ static int32_t check_linear(tlc_ctx *ctx, tlc_qtensor *w, const void *x, int32_t
     return TLC_OK;
 }
 
+static const char *type_name(const tlc_qtensor *w) {
+    return !w ? "?" : w->type == TLC_TYPE_Q4_0 ? "q4_0" : w->type == TLC_TYPE_Q8_0 ? "q8_0" : w->type == TLC_TYPE_Q6_K ? "q6_k" : "f16";
+}
+
 extern "C" int32_t tlc_linear(tlc_ctx *ctx, tlc_qtensor *w, const void *x_dev, int32_t m, int64_t x_cols,
                               void *y_dev, const void *bias_dev) {
     if (int32_t rc = tlc_enter(ctx)) return rc;
     if (int32_t rc = check_linear(ctx, w, x_dev, m, x_cols, y_dev)) return rc;
+    tlc_perf_scope perf(ctx, "linear(%s, m=%d, n=%lld, k=%lld)", type_name(w), m, (long long)w->n_rows, (long long)w->n_cols);
     tlc_gemv_args a;
     a.n_out = 1;
     a.outs[0] = {w, y_dev, 0};
@@ -478,6 +492,8 @@ extern "C" int32_t tlc_norm_linear_multi(tlc_ctx *ctx, int32_t n_weights, tlc_qt
     a.pos_offset = pos_offset;
     a.rope_base = rope_base;
     a.positions = positions_dev;
+    tlc_perf_scope perf(ctx, "norm_linear_multi(%s, %d weights, m=%d, k=%lld)", type_name(w[0]), n_weights, m,
+                        (long long)w[0]->n_cols);
     return tlc_launch_gemv(ctx, a);
 }
 
@@ -495,6 +511,8 @@ extern "C" int32_t tlc_swiglu_gate_up(tlc_ctx *ctx, tlc_qtensor *w_gate, tlc_qte
     a.norm_w = norm_w_dev;
     a.eps = eps;
     a.epilogue = TLC_EPI_SWIGLU;
+    tlc_perf_scope perf(ctx, "swiglu_gate_up(%s, m=%d, n=%lld, k=%lld)", type_name(w_gate), m, (long long)w_gate->n_rows,
+                        (long long)w_gate->n_cols);
     return tlc_launch_gemv(ctx, a);
 }
 
@@ -510,5 +528,7 @@ extern "C" int32_t tlc_linear_residual(tlc_ctx *ctx, tlc_qtensor *w, const void 
     a.m = m;
     a.epilogue = TLC_EPI_RESIDUAL;
     a.residual = residual_dev;
+    tlc_perf_scope perf(ctx, "linear_residual(%s, m=%d, n=%lld, k=%lld)", type_name(w), m, (long long)w->n_rows,
+                        (long long)w->n_cols);
     return tlc_launch_gemv(ctx, a);
 }

@@ -243,3 +243,34 @@ def test_matmul_builtin(dev, ref):
     with pytest.raises(TensorError) as e:
         matmul(dev.tensor(np.zeros((2, 3), np.float16)), dev.tensor(np.zeros((4, 2), np.float16)))
     assert e.value.code == _lib.ERR_INVALID_OPERATION and "matmul shape mismatch: [2, 3] @ [4, 2]" in str(e.value)
+
+
+def test_perf_switch_times_every_op(dev, ref, capfd):
+    """Option "perf" (the reference's TL_PERF): each op prints "[PERF] op(shape): x.xxxms" on stderr
+    and tlc_perf_report returns per-op call counts and device milliseconds; off again, nothing is
+    printed or counted, and results are unchanged."""
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.api import QTensor, linear, rms_norm
+    n, k = 256, 512
+    raw = synth.blocks(2, 5, synth.tensor_id("perf"), n, k)
+    w = QTensor.from_blocks(dev, 2, n, k, raw)
+    x = synth.activations(5, "perfx", (3, k))
+    nw = synth.norm_weight(5, "perfn", k)
+    want = ref.linear_q(2, raw, n, k, x)
+    dev.perf_report(reset=True)
+    dev.set_option("perf", 1)
+    try:
+        y = linear(dev.tensor(x), w).numpy()
+        linear(dev.tensor(x), w)
+        rms_norm(dev.tensor(x), dev.tensor(nw), 1e-5)
+    finally:
+        dev.set_option("perf", 0)
+    err = capfd.readouterr().err
+    assert err.count("[PERF] linear(q4_0, m=3, n=256, k=512): ") == 2 and "[PERF] rms_norm(rows=3, d=512): " in err
+    rep = dev.perf_report(reset=True)
+    assert rep["linear"][0] == 2 and rep["rms_norm"][0] == 1
+    assert all(0.0 < ms < 1000.0 for _, ms in rep.values())
+    assert np.max(np.abs(y.astype(np.float32) - want.astype(np.float32))) < 2e-3 * max(float(np.max(np.abs(want))), 1.0)
+    linear(dev.tensor(x), w)
+    dev.synchronize()
+    assert "[PERF]" not in capfd.readouterr().err and dev.perf_report() == {}
