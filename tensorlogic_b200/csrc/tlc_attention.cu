@@ -60,6 +60,8 @@ struct AttnParams {
     int push_splits; // cluster mode: splits the merge area of rank 0 is laid out for (8 or 16)
     int cluster;     // 1: the nsplit CTAs of a tile form a thread-block cluster and merge through
                      // distributed shared memory instead of global scratch
+    int pos_settled; // 1: the launcher vouches that positions[] was final before this kernel could start
+                     // (see tlc_launch_attention); the kernel then reads it once, before the wait
     int key_limit;   // keys the launch was sized for (<= Tmax): a sequence whose position says it
                      // holds more is cut there and the status word (when given) says so
     tlc_dev_status *status;  // device word or null
@@ -146,35 +148,42 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         }
         cp_async_commit();
     };
-    bool early = false;
-    if (p.positions && p.I == 1) {
-        const int hint = min(*reinterpret_cast<const volatile int *>(p.positions + b), p.key_limit - 1);
-        early = k_begin + kTileKeys <= hint && k_begin + kTileKeys <= p.keys_per_split * (split + 1);
-        if (early) {
-            k_end = k_begin + kTileKeys;
-            load_tile(0, 0);
-        }
-    }
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    int pos0 = p.positions ? *reinterpret_cast<const volatile int *>(p.positions + b) : p.q_pos0;  // position of query 0
-    if (pos0 < 0) pos0 = 0;
-    if (pos0 + p.I > p.key_limit) {  // more keys than the launch (or the cache) holds: cut, and say so
-        pos0 = p.key_limit - p.I;
-        if (p.status && tid == 0 && atomicCAS(&p.status->code, 0, TLC_DEV_INDEX) == 0) p.status->where = 200 + b;
-    }
-    const int T = pos0 + p.I;  // keys in the cache (incl. the new ones)
     // Rows of the tile: r -> (query qt*RQ + r/G, head hk*G + r%G).
     const int qi_lo = qt * RQ + g / G, qi_hi = qt * RQ + (g + 8) / G;
     const int head_lo = hk * G + g % G, head_hi = hk * G + (g + 8) % G;
     const bool valid_lo = qi_lo < p.I, valid_hi = qi_hi < p.I;
-    const int rpos_lo = pos0 + qi_lo, rpos_hi = pos0 + qi_hi;  // last visible key of the row
-
-    // Keys this CTA covers: its split, cut at the last key any row of the tile may see.
     const int last_q = min(p.I, (qt + 1) * RQ) - 1;
-    const int visible_end = min(T, pos0 + last_q + 1);
-    k_end = min(visible_end, k_begin + p.keys_per_split);
-    const int ntiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
+    // Everything that depends on the position of query 0.
+    int pos0 = 0, rpos_lo = 0, rpos_hi = 0, ntiles = 0;
+    auto derive = [&](int pos_raw, bool final_value) {
+        pos0 = pos_raw < 0 ? 0 : pos_raw;
+        if (pos0 + p.I > p.key_limit) {  // more keys than the launch (or the cache) holds: cut, and say so
+            pos0 = p.key_limit - p.I;
+            if (final_value && p.status && tid == 0 && atomicCAS(&p.status->code, 0, TLC_DEV_INDEX) == 0)
+                p.status->where = 200 + b;
+        }
+        const int T = pos0 + p.I;  // keys in the cache (incl. the new ones)
+        rpos_lo = pos0 + qi_lo;    // last visible key of the row
+        rpos_hi = pos0 + qi_hi;
+        // Keys this CTA covers: its split, cut at the last key any row of the tile may see.
+        const int visible_end = min(T, pos0 + last_q + 1);
+        k_end = min(visible_end, k_begin + p.keys_per_split);
+        ntiles = k_end > k_begin ? (k_end - k_begin + kTileKeys - 1) / kTileKeys : 0;
+    };
+    // A launch argument is final; a device word is final before the wait only if the launcher vouches
+    // for it (tlc_launch_attention).  Then all of the above is worked out while the previous kernel
+    // still runs; otherwise the word is a lower bound, good for the early tile only, and is read
+    // again after the wait (an L2 round trip on the critical path of the layer).
+    const bool settled = !p.positions || p.pos_settled;
+    const int pos_seen = p.positions ? *reinterpret_cast<const volatile int *>(p.positions + b) : p.q_pos0;
+    derive(pos_seen, settled);
+    const bool early = p.I == 1 && ntiles > 0 && k_begin + kTileKeys <= pos0;
+    if (early) {
+        if (!settled) k_end = k_begin + kTileKeys;  // the tile is whole whatever the final position is
+        load_tile(0, 0);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!settled) derive(*reinterpret_cast<const volatile int *>(p.positions + b), true);
 
     // Q fragments (A operand), straight from global memory.
     uint32_t qa[KSTEPS][4];
@@ -687,9 +696,15 @@ static int attention_wide_clusters(tlc_ctx *ctx, int D) {
 //   batch sequences, I queries each (I == 1 when positions_dev is given).
 //   nsplit_hint <= 0: choose from the key count; with positions_dev the key
 //   count is only known on the device, so max_keys bounds it.
+//   positions_settled: the caller vouches that positions_dev[] is final before this kernel can
+//   be scheduled, not merely before its dependency wait returns.  True for the decode runner when
+//   every kernel between the one that writes the positions (the sampling kernel of the previous
+//   step) and this one lets its successor start only after its own dependency wait (GEMV
+//   pdl_mode 2, the default) or when programmatic dependent launch is off; false for the
+//   builtin, whose caller may have written the positions with the kernel right before.
 int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const void *q_dev, void *out_dev,
                              int batch, int I, int n_heads, int q_pos0, const int *positions_dev, int max_keys,
-                             float scale) {
+                             float scale, bool positions_settled) {
     TLC_REQUIRE(cache && q_dev && out_dev, TLC_ERR_INVALID_OPERATION, "attention: null pointer");
     TLC_REQUIRE(layer >= 0 && layer < cache->n_layers, TLC_ERR_INDEX, "Index out of bounds: index %d, size %d",
                 layer, cache->n_layers);
@@ -721,6 +736,7 @@ int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const 
     p.q_pos0 = q_pos0;
     p.positions = positions_dev;
     p.scale = scale;
+    p.pos_settled = positions_settled ? 1 : 0;
     p.key_limit = T;  // <= max_seq (checked above); a position beyond it is cut on the device
     p.status = ctx->dev_status;
     if (I > 1) {
@@ -929,7 +945,7 @@ extern "C" int32_t tlc_attention(tlc_ctx *ctx, tlc_kvcache *cache, int32_t layer
     if (int32_t rc = tlc_enter(ctx)) return rc;
     tlc_perf_scope perf(ctx, "attention(batch=%d, queries=%d, heads=%d)", batch, n_queries, n_heads);
     return tlc_launch_attention(ctx, cache, layer, q_dev, out_dev, batch, n_queries, n_heads, q_pos0,
-                                positions_dev, max_keys, scale);
+                                positions_dev, max_keys, scale, false);
 }
 
 // ---------------------------------------------------------------------------

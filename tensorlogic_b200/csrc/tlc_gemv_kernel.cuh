@@ -76,14 +76,16 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     // Split K (p.ksplit > 1): CTA b works on K window b % ksplit -- tiles [kt0, kt0 + p.ktiles) of
     // every slab it owns, p.nblk blocks of the activation rows starting at block kb0 -- and shares
     // the slabs with the other CTAs of the same window.
-    const int ks = p.ksplit > 1 ? (int)blockIdx.x % p.ksplit : 0;
-    const int cta_i = p.ksplit > 1 ? (int)blockIdx.x / p.ksplit : (int)blockIdx.x;
-    const int cta_n = p.ksplit > 1 ? (int)gridDim.x / p.ksplit : (int)gridDim.x;
-    const int kt0 = ks * p.ktiles_win;
+    // (One activation row never splits: its instantiation folds all of this away.)
+    const bool split = !M1 && p.ksplit > 1;
+    const int ks = split ? (int)blockIdx.x % p.ksplit : 0;
+    const int cta_i = split ? (int)blockIdx.x / p.ksplit : (int)blockIdx.x;
+    const int cta_n = split ? (int)gridDim.x / p.ksplit : (int)gridDim.x;
+    const int kt0 = split ? ks * p.ktiles_win : 0;
     const int kb0 = kt0 * T::TB;
-    const int my_ktiles = p.ksplit > 1 ? max(0, min(p.ktiles_win, p.ktiles_full - kt0)) : p.ktiles;
-    const int my_nchunks = p.ksplit > 1 ? (my_ktiles + kTilesPerStage - 1) / kTilesPerStage : p.nchunks;
-    const int my_nblk = p.ksplit > 1 ? max(0, min(p.ktiles_win * T::TB, p.k / 32 - kb0)) : p.nblk;
+    const int my_ktiles = split ? max(0, min(p.ktiles_win, p.ktiles_full - kt0)) : p.ktiles;
+    const int my_nchunks = split ? (my_ktiles + kTilesPerStage - 1) / kTilesPerStage : p.nchunks;
+    const int my_nblk = split ? max(0, min(p.ktiles_win * T::TB, p.k / 32 - kb0)) : p.nblk;
 
     if (tid == 0) {
         for (int s = 0; s < S; s++) {
@@ -641,7 +643,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                 if (F8) return v * *f8_scale;  // undo the row's scale and the 2^-9 of the e4m3 nibbles
                 return v * 16777216.0f;  // undo the 2^-24 of the integer fragments
             };
-            if (p.ksplit > 1) {
+            if (split) {
                 // Split K: this window's f32 share of the dot product; gemv_splitk_finish_kernel adds
                 // the windows and applies the epilogue.  Outputs of the fused weights lie side by side.
                 const int noff = ti == 0 ? 0 : ti == 1 ? p.t[0].n : p.t[0].n + p.t[1].n;

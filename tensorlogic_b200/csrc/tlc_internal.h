@@ -263,4 +263,4 @@ size_t tlc_gemv_scratch_bytes(tlc_ctx *ctx, int type, int64_t k, int m, int64_t 
 struct tlc_kvcache;
 int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const void *q_dev, void *out_dev,
                              int batch, int n_queries, int n_heads, int q_pos0, const int *positions_dev,
-                             int max_keys, float scale);
+                             int max_keys, float scale, bool positions_settled);

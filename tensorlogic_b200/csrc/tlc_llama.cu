@@ -591,8 +591,12 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
             if (int32_t rc = tlc_launch_gemv(ctx, a)) return rc;
         }
         if (parts & 2)
+            // positions[] is written by the previous step's sampling kernel (or by set_state / prefill);
+            // the embedding gather and the q/k/v kernel lie between it and this launch, and the q/k/v GEMV
+            // lets this kernel start only after its own dependency wait unless pdl_mode says otherwise
             if (int32_t rc = tlc_launch_attention(ctx, L->cache, l, L->q, L->attn, decode ? m : 1, decode ? 1 : m,
-                                                  L->heads_local, pos0, positions, c.max_seq, scale))
+                                                  L->heads_local, pos0, positions, c.max_seq, scale,
+                                                  !ctx->use_pdl || ctx->pdl_mode == 2))
                 return rc;
         if (parts & 1) {
             tlc_gemv_args a;
