@@ -64,7 +64,8 @@ struct GemvParams {
     int pos_offset;
     float rope_base;
     const int *positions;
-    int max_pos;   // > 0: outputs addressed by position are dropped from this position on (status TLC_DEV_INDEX)
+    int max_pos;   // > 0: positions of outputs addressed by position are brought into [0, max_pos) (the one-pass
+                   // kernel; the attention kernel reports them) or dropped with status TLC_DEV_INDEX (split-K finish)
     int nstages;
     int contig;    // 1: each CTA takes a contiguous range of units, 0: units blockIdx.x, + gridDim.x, ...
     int l2_hint;   // 1: weight copies carry the evict-first L2 hint

@@ -659,15 +659,16 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
             const int hdim = ti == 0 ? p.t[0].head_dim : ti == 1 ? p.t[1].head_dim : p.t[2].head_dim;
             __half h = __float2half_rn(total(a0, row));
             const size_t oidx = (size_t)col * wn + n;  // dense [m, N] index (residual, act)
-            const int pos = p.positions ? p.positions[col] : p.pos_offset + col;
+            int pos = p.positions ? p.positions[col] : p.pos_offset + col;
+            // Second line of defence behind the host-side bound of the positions: a position outside
+            // the cache is brought back to its last row, so the store stays inside the allocation; the
+            // attention kernel of the same layer meets the same position, cuts it and raises the status
+            // word (TLC_ERR_INDEX).  A clamp, not a test: a branch with a status update in this loop
+            // cost the TinyLlama decode step 1.5 %.
+            if (p.max_pos > 0) pos = min(max(pos, 0), p.max_pos - 1);
             // Where this output goes: dense rows by default; a KV-cache destination
             // addresses rows by (sequence, position) instead.
             const size_t yidx = (size_t)((long long)col * rstride + (long long)pos * pstride) + n;
-            if (pstride != 0 && p.max_pos > 0 && (pos < 0 || pos >= p.max_pos)) {
-                // a cache row that does not exist: nothing is written, the host hears about it
-                if (atomicCAS(&p.status->code, 0, TLC_DEV_INDEX) == 0) p.status->where = 300;
-                continue;
-            }
             if (rheads > 0) {
                 // Interleaved RoPE on the f16-rounded projection
                 // (rope_f16, shaders/unified.metal:2355-2417).

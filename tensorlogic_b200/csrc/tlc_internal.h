@@ -241,8 +241,10 @@ struct tlc_gemv_args {
     int32_t pos_offset = 0;
     uint32_t rope_base = 10000;
     const int32_t *positions = nullptr;  // device int32 [m] or null
-    // Outputs addressed by position (pos_stride != 0, a KV cache): positions >= max_pos are
-    // not stored and the device status word reports TLC_DEV_INDEX.  0: no limit.
+    // Outputs addressed by position (pos_stride != 0, a KV cache): a position outside [0, max_pos)
+    // never reaches memory outside the cache -- the one-pass GEMV stores at the last row instead (the
+    // attention kernel that follows reports the position), the split-K finish and the GEMM drop the
+    // row and raise TLC_DEV_INDEX themselves.  0: no limit.
     int32_t max_pos = 0;
 };
 
