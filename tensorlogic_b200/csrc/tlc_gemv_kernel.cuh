@@ -622,8 +622,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
         }
         consumer_bar<CT>();
         // Outputs of the batch: (unit, row, activation row) items over the consumer threads.
-        const int per_unit = kRows * p.m;
-        for (int item = ctid; item < (nsets / p.subs) * per_unit; item += CT) {
+        const int per_unit = M1 ? kRows : kRows * p.m;  // one activation row: a constant, shifts instead of divisions below
+        for (int item = ctid; item < (nsets >> (p.subs - 1)) * per_unit; item += CT) {  // subs is 1 or 2
             const int ui = item / per_unit, rc = item % per_unit;
             const int col = rc >> 4, row = rc & 15;
             const int a0 = ui * p.subs;
