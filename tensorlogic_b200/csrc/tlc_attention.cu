@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     const int g = lane >> 2, t = lane & 3;
     const int b = blockIdx.z, hk = blockIdx.y;
     const int qt = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
-    const int G = p.G, RQ = 16 / G;
+    // the group size is a power of two (1 .. 16, checked by the launcher): shifts, not divisions
+    const int G = p.G, gsh = 31 - __clz(p.G), RQ = 16 >> gsh;
 
     // A decode step's query, its newest cache row AND its position come from earlier kernels
     // of the stream.  Before griddepcontrol.wait the position word may still hold the previous
@@ -149,8 +150,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         cp_async_commit();
     };
     // Rows of the tile: r -> (query qt*RQ + r/G, head hk*G + r%G).
-    const int qi_lo = qt * RQ + g / G, qi_hi = qt * RQ + (g + 8) / G;
-    const int head_lo = hk * G + g % G, head_hi = hk * G + (g + 8) % G;
+    const int qi_lo = qt * RQ + (g >> gsh), qi_hi = qt * RQ + ((g + 8) >> gsh);
+    const int head_lo = hk * G + (g & (G - 1)), head_hi = hk * G + ((g + 8) & (G - 1));
     const bool valid_lo = qi_lo < p.I, valid_hi = qi_hi < p.I;
     const int last_q = min(p.I, (qt + 1) * RQ) - 1;
     // Everything that depends on the position of query 0.
@@ -315,7 +316,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     // thread -> (row, D/8 consecutive dims)
     constexpr int DPT = D / 8;
     const int row = tid >> 3, d0 = (tid & 7) * DPT;
-    const int qi = qt * RQ + row / G, head = hk * G + row % G;
+    const int qi = qt * RQ + (row >> gsh), head = hk * G + (row & (G - 1));
     const bool row_valid = qi < p.I;
     float M = -INFINITY;
 #pragma unroll

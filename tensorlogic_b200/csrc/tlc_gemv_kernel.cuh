@@ -101,6 +101,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     // warps only read weights, everything else waits for this grid to finish.
     if (p.pdl_mode == 1) pdl_launch_dependents();
 
+    // Units of this CTA (see the main loop below).  Worked out here, before anything waits for the
+    // previous kernel: the divisions are then off the critical path of the decode step.
+    const int u_lo = p.contig ? (int)((long long)cta_i * p.total_units / cta_n) : 0;
+    const int u_hi = p.contig ? (int)((long long)(cta_i + 1) * p.total_units / cta_n) : 0;
+    const int n_mine = p.contig ? u_hi - u_lo : ((int)p.total_units - cta_i + cta_n - 1) / cta_n;
+
     if (warp == CW) {
         // ------------------------------ producer ------------------------------
         // Weights are never written by a kernel, so the ring starts filling
@@ -108,9 +114,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
         int rs = 0;
         uint32_t rpar = 1;
         const uint64_t policy = l2_evict_first_policy();
-        const int pu_lo = (int)((long long)cta_i * p.total_units / cta_n);
-        const int pu_hi = (int)((long long)(cta_i + 1) * p.total_units / cta_n);
-        const int pcount = p.contig ? pu_hi - pu_lo : ((int)p.total_units - cta_i + cta_n - 1) / cta_n;
+        const int pu_lo = u_lo, pcount = n_mine;
         for (int ui = 0; ui < pcount; ui++) {
             const int unit = p.contig ? pu_lo + ui : cta_i + ui * cta_n;
             for (int sub = 0; sub < p.subs; sub++) {
@@ -158,7 +162,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     if (do_norm) {
         const int items = p.nblk_pad * p.m * 4;
         for (int idx = ctid; idx < items; idx += CT) {
-            const int t = idx & 3, b = (idx >> 2) / p.m;
+            const int t = idx & 3, b = M1 ? idx >> 2 : (idx >> 2) / p.m;
             if (b >= my_nblk) continue;
             const __half *wr = p.norm_w + (kb0 + b) * 32;
             if (idx == ctid) {
@@ -270,8 +274,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
             const bool live = idx < items;
             const int t = idx & 3;
             const int bm = idx >> 2;
-            const int b = live ? bm / p.m : 0;
-            const int m = live ? bm % p.m : 0;
+            const int b = !live ? 0 : M1 ? bm : bm / p.m;
+            const int m = !live || M1 ? 0 : bm % p.m;
             float v[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) v[j] = 0.f;
@@ -407,10 +411,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     // rows (9 % faster on a 132 MB weight).  They are processed in batches of AS
     // accumulator sets (one set = one 16-row slab; a gate/up unit takes two) with
     // ONE cross-warp reduction per batch.
-    const int u_lo = (int)((long long)cta_i * p.total_units / cta_n);
-    const int u_hi = (int)((long long)(cta_i + 1) * p.total_units / cta_n);
-    const int n_mine = p.contig ? u_hi - u_lo : ((int)p.total_units - cta_i + cta_n - 1) / cta_n;
-    const int ub = AS / p.subs;  // units per batch
+    const int ub = AS >> (p.subs - 1);  // units per batch (subs is 1 or 2)
     int rs = 0;           // ring position and its parity, carried from stage to stage
     uint32_t rpar = 0;
     int batch_count = 0;
