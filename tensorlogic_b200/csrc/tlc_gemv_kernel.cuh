@@ -178,6 +178,10 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
             }
         }
     }
+    // (nothing of the previous kernel is needed to clear the accumulator start values)
+    for (int i = ctid; i < (M1 ? p.nblk_pad * 2 : p.nblk_pad * NT * 4); i += CT)
+        cinit[i] = make_float2(0.f, 0.f);
+    if (ctid == 0) *xzero = make_uint4(0, 0, 0, 0);
     pdl_wait();  // the activations (and residual) come from the previous kernel
 
     // (a) sum of squares per activation row: every thread takes 8-element chunks.
@@ -239,9 +243,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
             if (lane == 0) sq_part[m * CW + warp] = sq;
         }
     }
-    for (int i = ctid; i < (M1 ? p.nblk_pad * 2 : p.nblk_pad * NT * 4); i += CT)
-        cinit[i] = make_float2(0.f, 0.f);
-    if (ctid == 0) *xzero = make_uint4(0, 0, 0, 0);
     consumer_bar<CT>();
 
     // (b) activations into fragment order + accumulator start values.  Item =
@@ -412,6 +413,32 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
     // accumulator sets (one set = one 16-row slab; a gate/up unit takes two) with
     // ONE cross-warp reduction per batch.
     const int ub = AS >> (p.subs - 1);  // units per batch (subs is 1 or 2)
+    // The first output of this thread (item `ctid` of the first batch) adds a residual value and / or
+    // is addressed by a position that earlier kernels wrote: both are fetched now, so that their
+    // latency runs beside the dot products instead of after the reduction at the very end of the
+    // kernel (the tail of every kernel is on the critical path of a decode step).
+    __half res_first = __ushort_as_half((unsigned short)0);
+    int pos_first = 0;
+    bool have_first = false;
+    if (!split) {
+        const int pu = M1 ? kRows : kRows * p.m;
+        const int ui = M1 ? ctid >> 4 : ctid / pu, rc = M1 ? ctid & 15 : ctid % pu;
+        const int col = rc >> 4, row = rc & 15;
+        if (ui < min(ub, n_mine)) {
+            int ti = 0, sl = p.contig ? u_lo + ui : cta_i + ui * cta_n;
+            if (p.subs == 1) {
+                if (sl >= p.slabs[0]) { sl -= p.slabs[0]; ti = 1; }
+                if (ti == 1 && sl >= p.slabs[1]) { sl -= p.slabs[1]; ti = 2; }
+            }
+            const int n = sl * kRows + row;
+            const int wn = ti == 0 ? p.t[0].n : ti == 1 ? p.t[1].n : p.t[2].n;
+            if (n < wn) {
+                have_first = true;
+                pos_first = p.positions ? p.positions[col] : p.pos_offset + col;
+                if (p.epilogue == TLC_EPI_RESIDUAL) res_first = p.residual[(size_t)col * wn + n];
+            }
+        }
+    }
     int rs = 0;           // ring position and its parity, carried from stage to stage
     uint32_t rpar = 0;
     int batch_count = 0;
@@ -660,7 +687,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
             const int hdim = ti == 0 ? p.t[0].head_dim : ti == 1 ? p.t[1].head_dim : p.t[2].head_dim;
             __half h = __float2half_rn(total(a0, row));
             const size_t oidx = (size_t)col * wn + n;  // dense [m, N] index (residual, act)
-            int pos = p.positions ? p.positions[col] : p.pos_offset + col;
+            const bool first = have_first && i0 == 0 && item == ctid;
+            int pos = first ? pos_first : p.positions ? p.positions[col] : p.pos_offset + col;
             // Second line of defence behind the host-side bound of the positions: a position outside
             // the cache is brought back to its last row, so the store stays inside the allocation; the
             // attention kernel of the same layer meets the same position, cuts it and raises the status
@@ -686,7 +714,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
                                           : __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
                 yout[yidx] = __float2half_rn(r);
             } else if (p.epilogue == TLC_EPI_RESIDUAL) {
-                yout[yidx] = __hadd(h, p.residual[oidx]);
+                yout[yidx] = __hadd(h, first ? res_first : p.residual[oidx]);
             } else if (p.epilogue == TLC_EPI_SWIGLU) {
                 // h = gate; s = sigmoid(g) (f32, RNE); a = g*s; act = a*u: three
                 // f16 roundings as in debug/chat_demo_with_kvcache.tl:26-41.
