@@ -701,7 +701,7 @@ static int attention_wide_clusters(tlc_ctx *ctx, int D) {
 //   be scheduled, not merely before its dependency wait returns.  True for the decode runner when
 //   every kernel between the one that writes the positions (the sampling kernel of the previous
 //   step) and this one lets its successor start only after its own dependency wait (GEMV
-//   pdl_mode 2, the default) or when programmatic dependent launch is off; false for the
+//   pdl_mode 2, the default, or 3) or when programmatic dependent launch is off; false for the
 //   builtin, whose caller may have written the positions with the kernel right before.
 int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const void *q_dev, void *out_dev,
                              int batch, int I, int n_heads, int q_pos0, const int *positions_dev, int max_keys,

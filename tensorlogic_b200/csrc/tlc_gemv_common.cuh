@@ -69,7 +69,7 @@ struct GemvParams {
     int nstages;
     int contig;    // 1: each CTA takes a contiguous range of units, 0: units blockIdx.x, + gridDim.x, ...
     int l2_hint;   // 1: weight copies carry the evict-first L2 hint
-    int pdl_mode;  // 1: let the next kernel be scheduled at once, 2: only when this CTA's last slab is done
+    int pdl_mode;  // 1: let the next kernel be scheduled at once, 2: only when this CTA's last slab is done, 3: after this CTA's own dependency wait
     tlc_dev_status *status;
     uint64_t wait_ns;  // how long a wait may last before the kernel gives up
     // Split K (ksplit > 1): the K range is cut into ksplit windows of ktiles_win tiles (nblk_pad is

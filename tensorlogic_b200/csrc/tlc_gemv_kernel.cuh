@@ -183,6 +183,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, CW == 8 ? 2 : 1) gemv_mma_kerne
         cinit[i] = make_float2(0.f, 0.f);
     if (ctid == 0) *xzero = make_uint4(0, 0, 0, 0);
     pdl_wait();  // the activations (and residual) come from the previous kernel
+    // Mode 3: the successor may be scheduled while this CTA does its own work, but not before the
+    // predecessor is done (its CTAs then never wait behind two grids).
+    if (p.pdl_mode == 3) pdl_launch_dependents();
 
     // (a) sum of squares per activation row: every thread takes 8-element chunks.
     if (F8) {

@@ -58,7 +58,7 @@ struct tlc_ctx {
     // griddepcontrol.wait before they touch a predecessor's output); the
     // environment variable TLC_NO_PDL=1 turns it off.
     bool use_pdl = true;
-    int pdl_mode = 2;      // TLC_PDL_MODE: when the GEMV lets its successor be scheduled (1 at once, 2 after its last slab; measured: 2 is 1-2 % faster than no PDL, 1 is 10 % slower)
+    int pdl_mode = 4;      // TLC_PDL_MODE: when the GEMV lets its successor be scheduled (1 at once, 2 after its last slab, 3 after its own dependency wait, 4 = 3 for long kernels and 2 for short ones; measured on TinyLlama decode: 2 is 9 % faster than no PDL, 1 is 10 % slower than 2)
     bool pdl_small = true; // TLC_PDL_SMALL=0: keep PDL off for the non-GEMV kernels
     // TLC_GEMM_MIN_M: activation rows from which quantized linears run as the
     // tensor-core GEMM (0: decide from the shape; a huge value keeps the GEMV).

@@ -596,7 +596,7 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
             // lets this kernel start only after its own dependency wait unless pdl_mode says otherwise
             if (int32_t rc = tlc_launch_attention(ctx, L->cache, l, L->q, L->attn, decode ? m : 1, decode ? 1 : m,
                                                   L->heads_local, pos0, positions, c.max_seq, scale,
-                                                  !ctx->use_pdl || ctx->pdl_mode == 2))
+                                                  !ctx->use_pdl || ctx->pdl_mode >= 2))
                 return rc;
         if (parts & 1) {
             tlc_gemv_args a;
