@@ -95,7 +95,7 @@ TLC_API int32_t tlc_destroy(tlc_ctx *ctx);
  *   "pdl"         programmatic dependent launch on (1) / off (0);
  *   "pdl_mode"    when a GEMV lets the next kernel of the stream be scheduled: 1 = at once,
  *                 2 = after its last slab, 3 = after its own dependency wait, 4 (default) = 3 for
- *                 kernels that stream 32 MB of weights or more and 2 for shorter ones;
+ *                 kernels that stream 40 MB of weights or more and 2 for shorter ones;
  *   "l2_hint"     the GEMV's weight copies carry the evict-first L2 hint (1, default) or none (0);
  *   "host_graph"  tlc_llama_decode_host runs as one graph launch with copy nodes (1, default)
  *                 or as copy + graph + copy (0);

@@ -367,12 +367,12 @@ int32_t launch_mma(tlc_ctx *ctx, GemvParams &p) {
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages > per_cta) stages = per_cta < 2 ? 2 : (int)per_cta;
     p.nstages = stages;
-    // Mode 4 decides per launch.  A kernel whose CTAs stream six or more ring stages (32 MB over the
-    // grid, about 5 us of HBM time) lets its successor in right after its own dependency wait: the
+    // Mode 4 decides per launch.  A kernel whose CTAs stream eight or more ring stages (40 MB over the
+    // grid, about 6 us of HBM time) lets its successor in right after its own dependency wait: the
     // successor is then resident with its ring filled when this grid ends (Llama-70B decode: 10.07 ->
-    // 9.74 ms per token).  Shorter kernels keep the late trigger (TinyLlama decode is 0.5 % slower
-    // with the early one).
-    p.pdl_mode = ctx->pdl_mode == 4 ? (per_cta >= 6 ? 3 : 2) : ctx->pdl_mode;
+    // 9.74 ms per token).  Shorter kernels keep the late trigger (TinyLlama decode: 2.2 % slower with
+    // the early one from three stages on, 0.5 % slower with it everywhere).
+    p.pdl_mode = ctx->pdl_mode == 4 ? (per_cta >= 8 ? 3 : 2) : ctx->pdl_mode;
     p.l2_hint = ctx->l2_hint;
     p.contig = units_per_cta <= 4 ? 1 : 0;
     const size_t smem = smem_fixed + (size_t)stages * STAGE_BYTES;
