@@ -123,9 +123,10 @@ extern "C" int32_t tlc_set_option(tlc_ctx *ctx, const char *name, int64_t value)
         ctx->gemm_tma = value != 0;
     else if (n == "pdl")
         ctx->use_pdl = value != 0;
-    else if (n == "pdl_mode")
+    else if (n == "pdl_mode") {
+        TLC_REQUIRE(value >= 0 && value <= 4, TLC_ERR_INVALID_OPERATION, "set_option: pdl_mode must be 0..4");
         ctx->pdl_mode = (int)value;
-    else if (n == "attn_wide")
+    } else if (n == "attn_wide")
         ctx->attn_wide = (int)value;
     else if (n == "l2_hint")
         ctx->l2_hint = value != 0;

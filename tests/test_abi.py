@@ -168,3 +168,17 @@ def test_rust_shim_matches_header():
                     assert name in declared, (f, name)
                 for const in set(re.findall(r"ffi::(TLC_\w+)", text)):
                     assert re.search(r"pub const %s:" % const, ffi), (f, const)
+
+
+def test_every_option_is_documented_in_the_header():
+    """tlc_set_option's names (the parser in tlc_context.cu) and the list in the header's comment
+    are the same set."""
+    import re
+    src = open(os.path.join(ROOT, "tensorlogic_b200", "csrc", "tlc_context.cu")).read()
+    body = src[src.index("tlc_set_option("):]
+    body = body[:body.index("unknown option")]
+    parsed = set(re.findall(r'n == "(\w+)"', body))
+    header = open(os.path.join(ROOT, "include", "tlcuda.h")).read()
+    comment = header[header.index("Runtime switches the reference reads"):header.index("tlc_set_option(")]
+    documented = set(re.findall(r'^ \*   "(\w+)"', comment, flags=re.M))
+    assert parsed and parsed == documented, (sorted(parsed - documented), sorted(documented - parsed))
