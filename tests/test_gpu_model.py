@@ -138,6 +138,40 @@ def test_graph_replay_matches_eager_and_free_running_decode(dev):
     assert llm.launches_per_step == 5 * arch.n_layers + 3
 
 
+def test_decode_is_the_same_for_every_dependent_launch_setting(dev):
+    """When a kernel lets its successor be scheduled changes the timing only: tokens, logits and
+    positions are bit-identical with dependent launch off and with each of its trigger points
+    (the decode attention reads its position before or after its dependency wait accordingly)."""
+    from tensorlogic_b200 import synth
+    from tensorlogic_b200.model import Llama, model_from_host, synthetic_host_weights
+    arch = _small_arch()
+    model = model_from_host(dev, synthetic_host_weights(arch, seed=9))
+    ids = synth.token_ids(9, "prompt", 70, arch.vocab)  # more than one key tile: the early K/V fetch runs
+    outs = []
+    try:
+        for pdl, mode in ((1, 4), (0, 4), (1, 0), (1, 1), (1, 2), (1, 3)):
+            dev.set_option("pdl", pdl)
+            dev.set_option("pdl_mode", mode)
+            llm = Llama(dev, model, arch, max_seq=160, max_prefill=70)
+            first, _ = llm.prefill(ids)
+            toks = [first]
+            for _ in range(6):
+                nxt, lg = llm.decode(None, batch=1, return_logits=True)
+                toks.append(int(nxt[0]))
+            llm.decode_enqueue(1, 4)
+            nxt, pos = llm.read_state(1)
+            outs.append((toks, lg.copy(), int(nxt[0]), int(pos[0])))
+    finally:
+        dev.set_option("pdl", 1)
+        dev.set_option("pdl_mode", 4)
+    for o in outs[1:]:
+        assert o[0] == outs[0][0] and o[2:] == outs[0][2:]
+        assert np.array_equal(o[1].view(np.uint16), outs[0][1].view(np.uint16))
+    assert outs[0][3] == 70 + 6 + 4
+    with pytest.raises(Exception):
+        dev.set_option("pdl_mode", 5)
+
+
 def test_step_kernel_against_the_kernel_by_kernel_path(dev, ref):
     """Option step_kernel=1 runs single-sequence greedy decode as one persistent kernel per step;
     the default is the five-launches-per-layer path.  Same tokens, logits within the forward tolerance of
