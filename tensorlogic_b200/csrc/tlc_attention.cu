@@ -700,10 +700,14 @@ static int attention_wide_clusters(tlc_ctx *ctx, int D) {
 //   nsplit_hint <= 0: choose from the key count; with positions_dev the key
 //   count is only known on the device, so max_keys bounds it.
 //   positions_settled: the caller vouches that positions_dev[] is final before this kernel can
-//   be scheduled, not merely before its dependency wait returns.  True for the decode runner when
-//   every kernel between the one that writes the positions (the sampling kernel of the previous
-//   step) and this one lets its successor start only after its own dependency wait (GEMV
-//   pdl_mode 2, the default, or 3) or when programmatic dependent launch is off; false for the
+//   be scheduled, not merely before its dependency wait returns.  A kernel can be scheduled once
+//   every CTA of its predecessor has let dependents in, so this holds when some kernel between
+//   the writer of the positions and this one does that only after its own dependency wait, or is
+//   launched the plain way: that kernel's wait returns when its predecessor is complete, and a
+//   grid is complete only when its threads have passed their own waits, back to the writer.  In
+//   the decode runner the writer is the previous step's sampling kernel and the kernel in between
+//   is the q/k/v GEMV (pdl_mode 2, 3 or 4) or, from 17 rows on, the plain-launched RMSNorm in
+//   front of the q/k/v GEMM; with pdl_mode 0 or 1 the runner passes false, and so does the
 //   builtin, whose caller may have written the positions with the kernel right before.
 int32_t tlc_launch_attention(tlc_ctx *ctx, tlc_kvcache *cache, int layer, const void *q_dev, void *out_dev,
                              int batch, int I, int n_heads, int q_pos0, const int *positions_dev, int max_keys,

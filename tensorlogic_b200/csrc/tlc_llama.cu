@@ -592,8 +592,10 @@ static int32_t forward(tlc_llama *L, int m, bool decode, int pos0, bool all_logi
         }
         if (parts & 2)
             // positions[] is written by the previous step's sampling kernel (or by set_state / prefill);
-            // the embedding gather and the q/k/v kernel lie between it and this launch, and the q/k/v GEMV
-            // lets this kernel start only after its own dependency wait unless pdl_mode says otherwise
+            // the embedding gather and the q/k/v kernels lie between it and this launch.  The q/k/v GEMV
+            // lets its successor in only after its own dependency wait (pdl_mode 2 and up), and the
+            // q/k/v GEMM of 17 rows and more comes behind a plain-launched RMSNorm: either way the
+            // positions are final before this kernel can be scheduled
             if (int32_t rc = tlc_launch_attention(ctx, L->cache, l, L->q, L->attn, decode ? m : 1, decode ? 1 : m,
                                                   L->heads_local, pos0, positions, c.max_seq, scale,
                                                   !ctx->use_pdl || ctx->pdl_mode >= 2))
